@@ -1,0 +1,515 @@
+// Python bindings (pybind11): the `bagua_core` API surface plus the hooks the
+// `bagua_core_b200` Python layer and the tests use.
+//
+// Reference surface: bagua-core-py/src/lib.rs:21-193 (BaguaSingleCommunicatorPy),
+// 203-298 (BaguaTensorPy), 308-349 (BaguaCommBackendPy), 359-485 (BaguaBucketPy),
+// 506-514 (module).  Method names, argument order, defaults and the `op: u8` encoding
+// are kept.  Blocking calls release the GIL; every BaguaError surfaces as RuntimeError.
+// Tensor metadata comes from `at::Tensor`'s public API instead of private struct
+// layouts (bagua-core-internal/src/torch_ffi.rs).
+#include <cuda_runtime.h>
+#include <pybind11/functional.h>
+#include <pybind11/numpy.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "comm/arena.h"
+#include "comm/communicator.h"
+#include "kernels/fused.h"
+#include "kernels/kernels.h"
+#include "ops/comm_op.h"
+#include "pool/resource_pool.h"
+#include "runtime/backend.h"
+#include "telemetry/telemetry.h"
+#include "tensor/tensor.h"
+
+namespace py = pybind11;
+using namespace bagua;
+
+namespace {
+
+DType dtype_from_torch(at::ScalarType st) {
+  switch (st) {
+    case at::kFloat: return DType::F32;
+    case at::kHalf: return DType::F16;
+    case at::kLong: return DType::I64;
+    case at::kByte: return DType::U8;
+    case at::kBFloat16: return DType::BF16;
+    default: throw BaguaError(ErrorKind::Tensor, std::string("unsupported tensor dtype ") + c10::toString(st));
+  }
+}
+
+// A framework tensor: every query goes to the live at::Tensor, so storage swaps made by
+// the Python layer (flattening into bucket storage) are seen without re-registration.
+class TorchRawTensor : public RawTensor {
+ public:
+  explicit TorchRawTensor(at::Tensor t) : t_(std::move(t)), dtype_(dtype_from_torch(t_.scalar_type())) {
+    BAGUA_CHECK(t_.is_contiguous(), Tensor, "bagua tensors must be contiguous");
+    BAGUA_CHECK(t_.is_cuda() || t_.is_cpu(), Tensor, "bagua tensors must live on a CUDA device or on the host");
+  }
+  ~TorchRawTensor() override {
+    // at::Tensor may hold the last reference to Python-owned memory.
+    py::gil_scoped_acquire g;
+    t_.reset();
+  }
+  void* data_ptr() const override { return t_.data_ptr(); }
+  int64_t num_elements() const override { return t_.numel(); }
+  int64_t num_elements_allocated() const override { return t_.numel(); }
+  int device_id() const override { return t_.is_cuda() ? (int)t_.device().index() : -1; }
+  DType dtype() const override { return dtype_; }
+  const at::Tensor& tensor() const { return t_; }
+
+ private:
+  at::Tensor t_;
+  DType dtype_;
+};
+
+struct PyTensor {
+  TensorPtr inner;
+};
+struct PyBucket {
+  BucketPtr inner;
+  std::vector<py::object> py_tensors;  // keeps the Python wrappers alive for tensors()
+};
+struct PyComm {
+  SingleCommPtr inner;
+};
+struct PyBackend {
+  std::unique_ptr<CommBackend> inner;
+};
+
+SingleCommPtr opt_comm(const py::object& o) { return o.is_none() ? nullptr : o.cast<PyComm&>().inner; }
+
+kernels::Ctx ctx_of(const at::Tensor& t, uint64_t stream) {
+  return kernels::Ctx{t.is_cuda() ? (int)t.device().index() : -1, (cudaStream_t)stream};
+}
+
+void check_pair(const at::Tensor& a, const at::Tensor& b) {
+  BAGUA_CHECK(a.scalar_type() == b.scalar_type() && a.numel() == b.numel() && a.device() == b.device() &&
+                  a.is_contiguous() && b.is_contiguous(),
+              Tensor, "tensors must be contiguous and agree in dtype, size and device");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "bagua-core for B200: scheduler, buckets, communicators and fused sm_100a communication kernels";
+
+  py::register_exception_translator([](std::exception_ptr p) {
+    try {
+      if (p) std::rethrow_exception(p);
+    } catch (const BaguaError& e) {
+      PyErr_SetString(PyExc_RuntimeError, e.what());
+    }
+  });
+
+  // -------------------------------------------------------------------------------
+  py::class_<PyComm>(m, "BaguaSingleCommunicatorPy", py::dynamic_attr())
+      .def(py::init([](int rank, int nranks, int device_id, uint64_t stream_ptr, const std::string& uid) {
+             py::gil_scoped_release rel;
+             return PyComm{std::make_shared<SingleCommunicator>(rank, nranks, device_id, stream_ptr, uid)};
+           }),
+           py::arg("rank"), py::arg("nranks"), py::arg("device_id"), py::arg("stream_ptr"),
+           py::arg("nccl_unique_id_str"))
+      .def("nranks", [](PyComm& c) { return c.inner->nranks(); })
+      .def("rank", [](PyComm& c) { return c.inner->rank(); })
+      .def("device_id", [](PyComm& c) { return c.inner->device_id(); })
+      .def("abort", [](PyComm& c) { c.inner->abort(); }, py::call_guard<py::gil_scoped_release>())
+      .def("check_abort", [](PyComm& c) { return c.inner->check_abort(); })
+      .def("allreduce",
+           [](PyComm& c, PyTensor& s, PyTensor& r, int op) {
+             c.inner->allreduce(*s.inner->raw(), *r.inner->raw(), reduction_op_from_u8(op));
+           },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::arg("op"), py::call_guard<py::gil_scoped_release>())
+      .def("allreduce_inplace",
+           [](PyComm& c, PyTensor& t, int op) { c.inner->allreduce_inplace(*t.inner->raw(), reduction_op_from_u8(op)); },
+           py::arg("tensor"), py::arg("op"), py::call_guard<py::gil_scoped_release>())
+      .def("broadcast", [](PyComm& c, PyTensor& t, int root) { c.inner->broadcast(*t.inner->raw(), root); },
+           py::arg("tensor"), py::arg("root_rank"), py::call_guard<py::gil_scoped_release>())
+      .def("reduce",
+           [](PyComm& c, PyTensor& s, PyTensor& r, int dst, int op) {
+             c.inner->reduce(*s.inner->raw(), *r.inner->raw(), dst, reduction_op_from_u8(op));
+           },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::arg("dst"), py::arg("op"),
+           py::call_guard<py::gil_scoped_release>())
+      .def("reduce_inplace",
+           [](PyComm& c, PyTensor& t, int dst, int op) {
+             c.inner->reduce_inplace(*t.inner->raw(), dst, reduction_op_from_u8(op));
+           },
+           py::arg("tensor"), py::arg("dst"), py::arg("op"), py::call_guard<py::gil_scoped_release>())
+      .def("send", [](PyComm& c, PyTensor& t, int peer) { c.inner->send(*t.inner->raw(), peer); }, py::arg("tensor"),
+           py::arg("peer_rank"), py::call_guard<py::gil_scoped_release>())
+      .def("recv", [](PyComm& c, PyTensor& t, int peer) { c.inner->recv(*t.inner->raw(), peer); }, py::arg("tensor"),
+           py::arg("peer_rank"), py::call_guard<py::gil_scoped_release>())
+      .def("alltoall", [](PyComm& c, PyTensor& s, PyTensor& r) { c.inner->alltoall(*s.inner->raw(), *r.inner->raw()); },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::call_guard<py::gil_scoped_release>())
+      .def("alltoall_inplace", [](PyComm& c, PyTensor& t) { c.inner->alltoall_inplace(*t.inner->raw()); },
+           py::arg("tensor"), py::call_guard<py::gil_scoped_release>())
+      .def("alltoall_v",
+           [](PyComm& c, PyTensor& s, std::vector<int64_t> sc, std::vector<int64_t> sd, PyTensor& r,
+              std::vector<int64_t> rc, std::vector<int64_t> rd) {
+             c.inner->alltoall_v(*s.inner->raw(), sc, sd, *r.inner->raw(), rc, rd);
+           },
+           py::arg("send_tensor"), py::arg("send_counts"), py::arg("send_displs"), py::arg("recv_tensor"),
+           py::arg("recv_counts"), py::arg("recv_displs"), py::call_guard<py::gil_scoped_release>())
+      .def("allgather",
+           [](PyComm& c, PyTensor& s, PyTensor& r) { c.inner->allgather(*s.inner->raw(), *r.inner->raw()); },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::call_guard<py::gil_scoped_release>())
+      .def("allgather_inplace", [](PyComm& c, PyTensor& t) { c.inner->allgather_inplace(*t.inner->raw()); },
+           py::arg("tensor"), py::call_guard<py::gil_scoped_release>())
+      .def("gather",
+           [](PyComm& c, PyTensor& s, PyTensor& r, int dst) { c.inner->gather(*s.inner->raw(), *r.inner->raw(), dst); },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::arg("dst"), py::call_guard<py::gil_scoped_release>())
+      .def("gather_inplace",
+           [](PyComm& c, PyTensor& t, int64_t count, int dst) { c.inner->gather_inplace(*t.inner->raw(), count, dst); },
+           py::arg("tensor"), py::arg("count"), py::arg("dst"), py::call_guard<py::gil_scoped_release>())
+      .def("scatter",
+           [](PyComm& c, PyTensor& s, PyTensor& r, int src) { c.inner->scatter(*s.inner->raw(), *r.inner->raw(), src); },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::arg("src"), py::call_guard<py::gil_scoped_release>())
+      .def("scatter_inplace",
+           [](PyComm& c, PyTensor& t, int64_t count, int src) {
+             c.inner->scatter_inplace(*t.inner->raw(), count, src);
+           },
+           py::arg("tensor"), py::arg("count"), py::arg("src"), py::call_guard<py::gil_scoped_release>())
+      .def("reduce_scatter",
+           [](PyComm& c, PyTensor& s, PyTensor& r, int op) {
+             c.inner->reduce_scatter(*s.inner->raw(), *r.inner->raw(), reduction_op_from_u8(op));
+           },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::arg("op"), py::call_guard<py::gil_scoped_release>())
+      .def("reduce_scatter_inplace",
+           [](PyComm& c, PyTensor& t, int op) {
+             c.inner->reduce_scatter_inplace(*t.inner->raw(), reduction_op_from_u8(op));
+           },
+           py::arg("tensor"), py::arg("op"), py::call_guard<py::gil_scoped_release>())
+      .def("barrier", [](PyComm& c) { c.inner->barrier(); }, py::call_guard<py::gil_scoped_release>())
+      .def_static("generate_nccl_unique_id_str", []() { return nccl_generate_unique_id_b64(); })
+      // ---- additions for the B200 engine ----
+      .def("transport", [](PyComm& c) { return std::string(c.inner->transport_kind()); })
+      .def("set_fused", [](PyComm& c, bool on) { c.inner->set_fused(on); },
+           "Enable/disable the fused peer-memory kernels for ops on this communicator.")
+      .def("fused_available", [](PyComm& c) { return c.inner->arena() != nullptr; },
+           py::call_guard<py::gil_scoped_release>(),
+           "Collective: sets up the peer arena if needed and reports whether fused kernels can be used.")
+      .def("set_device_wait_ms",
+           [](PyComm& c, double ms) {
+             if (auto* a = c.inner->arena()) a->set_deadline_ms(ms);
+           },
+           py::call_guard<py::gil_scoped_release>())
+      .def("check_device_status", [](PyComm& c) { c.inner->check_device_status(); })
+      .def("fused_launches", [](PyComm& c) {
+        auto* a = c.inner->arena();
+        return a ? a->fused_launches() : (uint64_t)0;
+      })
+      .def("fused_allreduce",
+           [](PyComm& c, PyTensor& s, PyTensor& r, bool average) {
+             auto* a = c.inner->arena();
+             BAGUA_CHECK(a != nullptr, Communicator, "fused kernels are not available on this communicator");
+             auto sr = s.inner->raw();
+             auto rr = r.inner->raw();
+             BAGUA_CHECK(sr->dtype() == rr->dtype() && sr->num_elements_allocated() == rr->num_elements_allocated(),
+                         Tensor, "send and recv must agree in dtype and size");
+             return fused::allreduce(*a, sr->data_ptr(), rr->data_ptr(), sr->num_elements_allocated(), sr->dtype(),
+                                     average ? 1.0f / (float)c.inner->nranks() : 1.0f, (cudaStream_t)c.inner->stream());
+           },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::arg("average"),
+           py::call_guard<py::gil_scoped_release>(),
+           "Launch the fused all-reduce kernel directly (returns False if the layout is not eligible).");
+
+  // -------------------------------------------------------------------------------
+  py::class_<PyTensor>(m, "BaguaTensorPy", py::dynamic_attr())
+      .def(py::init([](const at::Tensor& t, const std::string& name) {
+             return PyTensor{std::make_shared<BaguaTensor>(name, std::make_shared<TorchRawTensor>(t))};
+           }),
+           py::arg("torch_tensor"), py::arg("name"))
+      .def("compress",
+           [](PyTensor& t, const std::string& method, int n_chunks, int target_chunk) {
+             return PyTensor{t.inner->compress(method, n_chunks, target_chunk)};
+           },
+           py::arg("method"), py::arg("n_chunks"), py::arg("target_chunk"), py::call_guard<py::gil_scoped_release>())
+      .def("decompress_from",
+           [](PyTensor& t, const std::string& method, int n_chunks, PyTensor& c) {
+             t.inner->decompress_from(method, n_chunks, *c.inner);
+           },
+           py::arg("method"), py::arg("n_chunks"), py::arg("compressed_buffer"),
+           py::call_guard<py::gil_scoped_release>())
+      .def("to_numpy_f32",
+           [](PyTensor& t) {
+             BAGUA_CHECK(t.inner->dtype() == DType::F32, Tensor, "to_numpy_f32 needs an F32 tensor");
+             py::array_t<float> a((py::ssize_t)t.inner->num_elements());
+             t.inner->copy_to_host(a.mutable_data());
+             return a;
+           })
+      .def("to_numpy_u8",
+           [](PyTensor& t) {
+             BAGUA_CHECK(t.inner->dtype() == DType::U8, Tensor, "to_numpy_u8 needs a U8 tensor");
+             py::array_t<uint8_t> a((py::ssize_t)t.inner->num_elements());
+             t.inner->copy_to_host(a.mutable_data());
+             return a;
+           })
+      .def("data_ptr", [](PyTensor& t) { return t.inner->data_ptr(); })
+      .def("device_id", [](PyTensor& t) { return t.inner->device_id(); })
+      .def("num_elements", [](PyTensor& t) { return t.inner->num_elements(); })
+      .def("num_elements_allocated", [](PyTensor& t) { return t.inner->num_elements_allocated(); })
+      .def("dtype", [](PyTensor& t) { return std::string(dtype_name(t.inner->dtype())); })
+      .def("name", [](PyTensor& t) { return t.inner->name(); })
+      .def("ready_for_comm", [](PyTensor& t) { return t.inner->ready_for_comm(); })
+      .def("torch_tensor", [](PyTensor& t) -> py::object {
+        auto raw = t.inner->raw();
+        if (auto* tr = dynamic_cast<TorchRawTensor*>(raw.get())) return py::cast(tr->tensor());
+        return py::none();
+      });
+
+  // -------------------------------------------------------------------------------
+  py::class_<PyBucket>(m, "BaguaBucketPy", py::dynamic_attr())
+      .def(py::init([](const std::string& name, py::list tensors) {
+             PyBucket b;
+             std::vector<TensorPtr> ts;
+             for (auto h : tensors) {
+               ts.push_back(h.cast<PyTensor&>().inner);
+               b.py_tensors.push_back(py::reinterpret_borrow<py::object>(h));
+             }
+             b.inner = std::make_shared<BaguaBucket>(name, std::move(ts));
+             return b;
+           }),
+           py::arg("name"), py::arg("tensors"))
+      .def("tensors", [](PyBucket& b) { return b.py_tensors; })
+      .def("name", [](PyBucket& b) { return b.inner->name(); })
+      .def("append_python_op",
+           [](PyBucket& b, py::object op) {
+             if (!PyCallable_Check(op.ptr())) throw py::type_error("python op should be a callable");
+             // the callable is released under the GIL, whichever thread drops the op
+             auto holder = std::shared_ptr<py::object>(new py::object(std::move(op)), [](py::object* o) {
+               py::gil_scoped_acquire g;
+               delete o;
+             });
+             b.inner->append_op(make_callback_op(
+                 [holder](const std::string& bucket_name) {
+                   py::gil_scoped_acquire g;
+                   try {
+                     (*holder)(bucket_name);
+                   } catch (py::error_already_set& e) {
+                     std::string what = e.what();
+                     e.restore();
+                     PyErr_Clear();
+                     throw std::runtime_error(what);
+                   }
+                 },
+                 "python callable"));
+           },
+           py::arg("op"))
+      .def("append_centralized_synchronous_op",
+           [](PyBucket& b, py::object inter, py::object intra, bool hierarchical, bool average, bool scattergather,
+              py::object compression) {
+             auto comm = Communicator::create(opt_comm(inter), opt_comm(intra), hierarchical);
+             if (compression.is_none())
+               b.inner->append_op(make_centralized_full_precision_op(comm, average, scattergather));
+             else
+               b.inner->append_op(make_centralized_low_precision_op(comm, average, compression.cast<std::string>()));
+           },
+           py::arg("communicator_internode") = py::none(), py::arg("communicator_intranode") = py::none(),
+           py::arg("hierarchical") = false, py::arg("average") = true, py::arg("scattergather") = false,
+           py::arg("compression") = py::none())
+      .def("append_decentralized_synchronous_op",
+           [](PyBucket& b, py::object inter, py::object intra, bool hierarchical, const std::string& mode,
+              PyTensor& peer_weight) {
+             auto comm = Communicator::create(opt_comm(inter), opt_comm(intra), hierarchical);
+             b.inner->append_op(
+                 make_decentralized_full_precision_op(comm, parse_peer_selection_mode(mode), peer_weight.inner));
+           },
+           py::arg("communicator_internode") = py::none(), py::arg("communicator_intranode") = py::none(),
+           py::arg("hierarchical") = false, py::arg("peer_selection_mode"), py::arg("peer_weight"))
+      .def("append_low_precision_decentralized_synchronous_op",
+           [](PyBucket& b, py::object inter, py::object intra, bool hierarchical, const std::string& mode,
+              const std::string& compression, PyTensor& w, PyTensor& l, PyTensor& r) {
+             auto comm = Communicator::create(opt_comm(inter), opt_comm(intra), hierarchical);
+             b.inner->append_op(make_decentralized_low_precision_op(comm, parse_peer_selection_mode(mode), compression,
+                                                                    w.inner, l.inner, r.inner));
+           },
+           py::arg("communicator_internode") = py::none(), py::arg("communicator_intranode") = py::none(),
+           py::arg("hierarchical") = false, py::arg("peer_selection_mode"), py::arg("compression"), py::arg("weight"),
+           py::arg("left_peer_weight"), py::arg("right_peer_weight"))
+      .def("append_decentralized_asynchronous_op",
+           [](PyBucket& b, py::object inter, py::object intra, const std::string& mode, uint64_t torch_stream) {
+             auto comm = Communicator::create(opt_comm(inter), opt_comm(intra), false);
+             b.inner->append_op(make_decentralized_async_op(comm, parse_peer_selection_mode(mode), torch_stream));
+           },
+           py::arg("communicator_internode") = py::none(), py::arg("communicator_intranode") = py::none(),
+           py::arg("peer_selection_mode"), py::arg("torch_stream"))
+      .def("print_ops", [](PyBucket& b) { py::print(b.inner->describe_ops()); })
+      .def("describe_ops", [](PyBucket& b) { return b.inner->describe_ops(); })
+      .def("clear_ops", [](PyBucket& b) { b.inner->clear_ops(); })
+      .def("ready_for_comm", [](PyBucket& b) { return b.inner->ready_for_comm(); })
+      .def("reset_comm_ready", [](PyBucket& b) { b.inner->reset_comm_ready(); })
+      .def("ops_state",
+           [](PyBucket& b) {
+             std::vector<std::vector<std::pair<std::string, int64_t>>> out;
+             for (auto& o : b.inner->ops_snapshot()) out.push_back(o->state());
+             return out;
+           },
+           "Checkpointable state of every op of the bucket (e.g. the gossip step counter).")
+      .def("load_ops_state", [](PyBucket& b, std::vector<std::vector<std::pair<std::string, int64_t>>> st) {
+        auto ops = b.inner->ops_snapshot();
+        BAGUA_CHECK(st.size() == ops.size(), Bucket, "state does not match the bucket's ops");
+        for (size_t i = 0; i < ops.size(); ++i) ops[i]->load_state(st[i]);
+      });
+
+  // -------------------------------------------------------------------------------
+  py::class_<PyBackend>(m, "BaguaCommBackendPy", py::dynamic_attr())
+      .def(py::init([](size_t cap, int device_id) {
+             return PyBackend{std::make_unique<CommBackend>(cap, device_id)};
+           }),
+           py::arg("schedule_channel_cap"), py::arg("device_id"))
+      .def("register_ordered_buckets",
+           [](PyBackend& be, py::list buckets) {
+             std::vector<BucketPtr> bs;
+             for (auto h : buckets) bs.push_back(h.cast<PyBucket&>().inner);
+             py::gil_scoped_release rel;
+             be.inner->register_ordered_buckets(bs);
+           },
+           py::arg("buckets"))
+      .def("mark_communication_ready",
+           [](PyBackend& be, PyTensor& t, uint64_t ev) { be.inner->mark_communication_ready(t.inner, ev); },
+           py::arg("tensor"), py::arg("ready_cuda_event_ptr"), py::call_guard<py::gil_scoped_release>())
+      .def("wait_pending_comm_ops", [](PyBackend& be) { return be.inner->wait_pending_comm_ops(); },
+           py::call_guard<py::gil_scoped_release>())
+      .def("set_watchdog_timeout", [](PyBackend& be, double s) { be.inner->set_watchdog_timeout(s); })
+      .def("watchdog_timeout", [](PyBackend& be) { return be.inner->watchdog_timeout(); })
+      .def("close", [](PyBackend& be) {
+        py::gil_scoped_release rel;
+        be.inner.reset();
+      });
+
+  // -------------------------------------------------------------------------------
+  m.def("show_version", []() {
+    std::fprintf(stderr, "project_name: bagua-core-b200\nis_debug: false\nversion: %s\n", "0.1.0");
+    std::fprintf(stderr, "build: %s %s, nvcc target sm_100a\n", __DATE__, __TIME__);
+    int rt = 0;
+    cudaRuntimeGetVersion(&rt);
+    std::fprintf(stderr, "cuda runtime: %d\nNCCL version: %d\n", rt, nccl_version());
+  });
+  m.def("nccl_version", &nccl_version);
+
+  // engine configuration / statistics
+  m.def("set_sync_per_bucket", [](bool on) { EngineConfig::global().sync_per_bucket = on; },
+        "Reference-faithful mode: synchronise the communication stream after every bucket.");
+  m.def("get_sync_per_bucket", []() { return EngineConfig::global().sync_per_bucket; });
+  m.def("set_log_level", [](const std::string& s) { set_log_level(parse_log_level(s.c_str())); });
+  m.def("stats", []() {
+    auto& s = EngineStats::global();
+    py::dict d;
+    d["buckets_scheduled"] = s.buckets_scheduled.load();
+    d["ops_executed"] = s.ops_executed.load();
+    d["fused_launches"] = s.fused_launches.load();
+    d["library_fallbacks"] = s.library_fallbacks.load();
+    d["staged_copies"] = s.staged_copies.load();
+    d["bytes_communicated"] = s.bytes_communicated.load();
+    return d;
+  });
+  m.def("reset_stats", []() {
+    auto& s = EngineStats::global();
+    s.buckets_scheduled = 0;
+    s.ops_executed = 0;
+    s.fused_launches = 0;
+    s.library_fallbacks = 0;
+    s.staged_copies = 0;
+    s.bytes_communicated = 0;
+  });
+  m.def("pool_stats", [](int device) {
+    PoolStats s = MemoryPool::for_device(device).stats();
+    py::dict d;
+    d["device_allocs"] = s.device_allocs;
+    d["pulls"] = s.pulls;
+    d["bytes_reserved"] = s.bytes_reserved;
+    d["bytes_in_use"] = s.bytes_in_use;
+    return d;
+  });
+  m.def("pool_size_class", [](size_t bytes) { return MemoryPool::size_class(bytes); });
+  m.def("pool_release_cached", [](int device) { MemoryPool::for_device(device).release_cached(); });
+  m.def("shift_one_peer", &shift_one_peer, py::arg("rank"), py::arg("nranks"), py::arg("step"));
+  m.def("compressed_buffer_size", [](int n_chunks, int64_t chunk_size, const std::string& dt) {
+    DType d = dt == "F16" ? DType::F16 : dt == "BF16" ? DType::BF16 : DType::F32;
+    return kernels::compressed_buffer_size(n_chunks, chunk_size, d);
+  });
+
+  // telemetry
+  m.def("telemetry_init", [](const std::string& addr) { Telemetry::instance().init(addr); });
+  m.def("telemetry_enabled", []() { return Telemetry::instance().enabled(); });
+  m.def("telemetry_flush", [](int timeout_ms) { return Telemetry::instance().flush(timeout_ms); },
+        py::arg("timeout_ms") = 2000, py::call_guard<py::gil_scoped_release>());
+  m.def("telemetry_shutdown", []() { Telemetry::instance().shutdown(); }, py::call_guard<py::gil_scoped_release>());
+  m.def("telemetry_stats", []() {
+    py::dict d;
+    d["exported"] = Telemetry::instance().exported();
+    d["failed_batches"] = Telemetry::instance().failed_batches();
+    return d;
+  });
+
+  // raw kernels on torch tensors (tests, optimisers).  `stream` is a cudaStream_t value.
+  m.def("k_divide_inplace", [](at::Tensor x, float d, uint64_t stream) {
+    kernels::divide_inplace(x.data_ptr(), dtype_from_torch(x.scalar_type()), x.numel(), d, ctx_of(x, stream));
+  });
+  m.def("k_add_inplace", [](at::Tensor x, at::Tensor y, uint64_t stream) {
+    check_pair(x, y);
+    kernels::add_inplace(x.data_ptr(), y.data_ptr(), dtype_from_torch(x.scalar_type()), x.numel(), ctx_of(x, stream));
+  });
+  m.def("k_subtract_inplace", [](at::Tensor x, at::Tensor y, uint64_t stream) {
+    check_pair(x, y);
+    kernels::subtract_inplace(x.data_ptr(), y.data_ptr(), dtype_from_torch(x.scalar_type()), x.numel(),
+                              ctx_of(x, stream));
+  });
+  m.def("k_addmul_inplace", [](at::Tensor x, at::Tensor y, float f, uint64_t stream) {
+    check_pair(x, y);
+    kernels::addmul_inplace(x.data_ptr(), y.data_ptr(), f, dtype_from_torch(x.scalar_type()), x.numel(),
+                            ctx_of(x, stream));
+  });
+  m.def("k_average_inplace", [](at::Tensor x, at::Tensor y, uint64_t stream) {
+    check_pair(x, y);
+    kernels::average_inplace(x.data_ptr(), y.data_ptr(), dtype_from_torch(x.scalar_type()), x.numel(),
+                             ctx_of(x, stream));
+  });
+  m.def("k_async_model_average", [](at::Tensor t, at::Tensor reduced, at::Tensor copy, float nranks, uint64_t stream) {
+    check_pair(t, reduced);
+    check_pair(t, copy);
+    BAGUA_CHECK(t.scalar_type() == at::kFloat, Tensor, "async_model_average supports float32 only");
+    kernels::async_model_average((float*)t.data_ptr(), (const float*)reduced.data_ptr(), (const float*)copy.data_ptr(),
+                                 nranks, t.numel(), ctx_of(t, stream));
+  });
+  m.def("k_reduce_chunk_inplace", [](at::Tensor x, int n_chunks, int target, bool average, uint64_t stream) {
+    BAGUA_CHECK(x.is_contiguous() && n_chunks > 0 && x.numel() % n_chunks == 0, Tensor,
+                "tensor must be contiguous and divisible into chunks");
+    kernels::reduce_chunk_inplace(x.data_ptr(), dtype_from_torch(x.scalar_type()), x.numel() / n_chunks, n_chunks,
+                                  target, average, ctx_of(x, stream));
+  });
+  m.def(
+      "k_sgd_momentum_flat",
+      [](at::Tensor p, at::Tensor g, at::Tensor buf, float lr, float momentum, float dampening, float wd, bool nesterov,
+         bool first_step, uint64_t stream) {
+        check_pair(p, g);
+        check_pair(p, buf);
+        BAGUA_CHECK(p.scalar_type() == at::kFloat, Tensor, "fused SGD works on float32 flat buffers");
+        kernels::sgd_momentum_flat((float*)p.data_ptr(), (const float*)g.data_ptr(), (float*)buf.data_ptr(), p.numel(),
+                                   lr, momentum, dampening, wd, nesterov, first_step, ctx_of(p, stream));
+      },
+      py::arg("param"), py::arg("grad"), py::arg("momentum_buffer"), py::arg("lr"), py::arg("momentum"),
+      py::arg("dampening"), py::arg("weight_decay"), py::arg("nesterov"), py::arg("first_step"), py::arg("stream"));
+
+  m.def(
+      "debug_wait_timeout",
+      [](int device, double wait_ms) {
+        DeviceStatus s;
+        {
+          py::gil_scoped_release rel;
+          s = fused::debug_wait_timeout(device, wait_ms);
+        }
+        py::dict d;
+        d["code"] = s.code;
+        d["phase"] = s.phase;
+        d["peer"] = s.peer;
+        d["block"] = s.block;
+        d["epoch"] = s.epoch;
+        d["seen"] = s.seen;
+        return d;
+      },
+      py::arg("device"), py::arg("wait_ms"),
+      "Runs a kernel whose only wait can never be satisfied and returns the status record it left.");
+}

@@ -1,0 +1,145 @@
+#include "arena.h"
+
+#include <cuda_runtime.h>
+
+namespace bagua {
+
+namespace {
+struct HandlePair {
+  cudaIpcMemHandle_t staging;
+  cudaIpcMemHandle_t signals;
+  uint64_t staging_bytes;
+  uint64_t has_signals;  // signals handle is only exchanged once
+};
+static_assert(sizeof(HandlePair) == 144, "unexpected IPC handle size");
+}  // namespace
+
+PeerArena::PeerArena(Transport& transport, int rank, int nranks, int device, cudaStream_t stream)
+    : transport_(transport), rank_(rank), nranks_(nranks), device_(device), stream_(stream) {
+  BAGUA_CHECK(nranks <= kArenaMaxRanks, Communicator,
+              "the peer arena supports at most " << kArenaMaxRanks << " ranks, got " << nranks);
+  deadline_ns_ = (uint64_t)(env_double("BAGUA_B200_DEVICE_WAIT_MS", 120000.0) * 1e6);
+  max_blocks_ = (int)std::min<long>(std::max<long>(env_long("BAGUA_B200_COMM_CTAS", 32), 1), kArenaMaxBlocks);
+  BAGUA_CUDA_CHECK(cudaSetDevice(device));
+  // every peer must be reachable with peer access
+  int ndev = 0;
+  BAGUA_CUDA_CHECK(cudaGetDeviceCount(&ndev));
+  BAGUA_CUDA_CHECK(cudaMalloc(&local_signals_, kSigWords * sizeof(uint32_t)));
+  BAGUA_CUDA_CHECK(cudaMemset(local_signals_, 0, kSigWords * sizeof(uint32_t)));
+  BAGUA_CUDA_CHECK(cudaHostAlloc((void**)&status_host_, sizeof(DeviceStatus), cudaHostAllocMapped));
+  std::memset(status_host_, 0, sizeof(DeviceStatus));
+  BAGUA_CUDA_CHECK(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
+  BAGUA_CUDA_CHECK(cudaDeviceSynchronize());
+  allocate_and_exchange((size_t)env_long("BAGUA_B200_STAGING_MB", 64) << 20);
+}
+
+PeerArena::~PeerArena() {
+  // Best effort; at interpreter shutdown the runtime may already be gone.
+  for (int p = 0; p < nranks_; ++p) {
+    if (p == rank_) continue;
+    if (peer_staging_[p]) cudaIpcCloseMemHandle(peer_staging_[p]);
+    if (peer_signals_[p]) cudaIpcCloseMemHandle(peer_signals_[p]);
+  }
+  for (void* p : retired_peer_) cudaIpcCloseMemHandle(p);
+  if (local_staging_) cudaFree(local_staging_);
+  for (void* p : retired_) cudaFree(p);
+  if (local_signals_) cudaFree(local_signals_);
+  if (status_host_) cudaFreeHost(status_host_);
+  cudaGetLastError();
+}
+
+void PeerArena::allocate_and_exchange(size_t bytes) {
+  bytes = align_up(bytes, (size_t)2 << 20);
+  const bool first = (local_staging_ == nullptr);
+  // Everything queued on the stream so far may still use the old staging.
+  BAGUA_CUDA_CHECK(cudaStreamSynchronize(stream_));
+  void* fresh = nullptr;
+  BAGUA_CUDA_CHECK(cudaMalloc(&fresh, bytes));
+
+  HandlePair mine;
+  std::memset(&mine, 0, sizeof(mine));
+  BAGUA_CUDA_CHECK(cudaIpcGetMemHandle(&mine.staging, fresh));
+  mine.staging_bytes = bytes;
+  if (first) {
+    BAGUA_CUDA_CHECK(cudaIpcGetMemHandle(&mine.signals, local_signals_));
+    mine.has_signals = 1;
+  }
+  // all-gather the handles through the library transport (device buffers)
+  void* dev = nullptr;
+  BAGUA_CUDA_CHECK(cudaMalloc(&dev, sizeof(HandlePair) * (size_t)nranks_));
+  BAGUA_CUDA_CHECK(cudaMemcpyAsync((char*)dev + sizeof(HandlePair) * (size_t)rank_, &mine, sizeof(mine),
+                                   cudaMemcpyHostToDevice, stream_));
+  transport_.allgather((char*)dev + sizeof(HandlePair) * (size_t)rank_, dev, (int64_t)sizeof(HandlePair), DType::U8);
+  std::vector<HandlePair> all((size_t)nranks_);
+  BAGUA_CUDA_CHECK(cudaMemcpyAsync(all.data(), dev, sizeof(HandlePair) * (size_t)nranks_, cudaMemcpyDeviceToHost,
+                                   stream_));
+  BAGUA_CUDA_CHECK(cudaStreamSynchronize(stream_));
+  BAGUA_CUDA_CHECK(cudaFree(dev));
+
+  for (int p = 0; p < nranks_; ++p) {
+    BAGUA_CHECK(all[p].staging_bytes == bytes, Communicator,
+                "ranks disagree on the staging size (" << all[p].staging_bytes << " vs " << bytes
+                                                       << "); fused ops must be issued identically on every rank");
+    if (p == rank_) continue;
+    if (peer_staging_[p]) retired_peer_.push_back(peer_staging_[p]);
+    void* mapped = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&mapped, all[p].staging, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      throw BaguaError(ErrorKind::Communicator, std::string("cannot map the staging buffer of rank ") +
+                                                    std::to_string(p) + ": " + cudaGetErrorString(e));
+    }
+    peer_staging_[p] = mapped;
+    if (first) {
+      e = cudaIpcOpenMemHandle(&mapped, all[p].signals, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        throw BaguaError(ErrorKind::Communicator, std::string("cannot map the signal pad of rank ") +
+                                                      std::to_string(p) + ": " + cudaGetErrorString(e));
+      }
+      peer_signals_[p] = mapped;
+    }
+  }
+  if (local_staging_) retired_.push_back(local_staging_);
+  local_staging_ = fresh;
+  peer_staging_[rank_] = fresh;
+  peer_signals_[rank_] = local_signals_;
+  staging_bytes_ = bytes;
+  // Nobody may write into the new staging before every rank has mapped it.
+  transport_.barrier();
+  BAGUA_LOG(Info, "peer arena rank " << rank_ << "/" << nranks_ << ": staging " << (bytes >> 20) << " MiB mapped");
+}
+
+void PeerArena::ensure_staging(size_t bytes) {
+  if (bytes <= staging_bytes_) return;
+  size_t want = staging_bytes_ ? staging_bytes_ : ((size_t)64 << 20);
+  while (want < bytes) want <<= 1;
+  allocate_and_exchange(want);
+}
+
+ArenaView PeerArena::next_view(int grid, int grid_barriers) {
+  ArenaView v;
+  std::memset(&v, 0, sizeof(v));
+  for (int p = 0; p < nranks_; ++p) {
+    v.staging[p] = (uint8_t*)peer_staging_[p];
+    v.signals[p] = (uint32_t*)peer_signals_[p];
+  }
+  v.status = status_dev_;
+  v.staging_bytes = staging_bytes_;
+  v.rank = rank_;
+  v.nranks = nranks_;
+  v.epoch = ++epoch_;
+  v.deadline_ns = deadline_ns_;
+  v.grid_bar_base = grid_bar_;
+  grid_bar_ += (uint64_t)grid * (uint64_t)grid_barriers;
+  return v;
+}
+
+DeviceStatus PeerArena::read_status() const {
+  DeviceStatus s;
+  std::memcpy(&s, (const void*)status_host_, sizeof(s));
+  return s;
+}
+void PeerArena::clear_status() { std::memset(status_host_, 0, sizeof(DeviceStatus)); }
+
+}  // namespace bagua

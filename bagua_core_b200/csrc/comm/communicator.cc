@@ -1,0 +1,267 @@
+#include "communicator.h"
+
+#include <cuda_runtime.h>
+
+#include "arena.h"
+
+namespace bagua {
+
+namespace {
+void same_kind(const RawTensor& a, const RawTensor& b, const char* what) {
+  BAGUA_CHECK(a.dtype() == b.dtype(), Communicator, what << ": send and recv dtypes differ");
+  BAGUA_CHECK(a.device_id() == b.device_id(), Communicator, what << ": send and recv devices differ");
+}
+}  // namespace
+
+SingleCommunicator::SingleCommunicator(int rank, int nranks, int device_id, uint64_t stream,
+                                       const std::string& unique_id)
+    : rank_(rank), nranks_(nranks), device_id_(device_id), stream_(stream) {
+  BAGUA_CHECK(nranks >= 1 && rank >= 0 && rank < nranks, Communicator, "invalid rank " << rank << " / " << nranks);
+  if (is_c10d_unique_id(unique_id)) {
+    BAGUA_CHECK(device_id < 0, Communicator, "the c10d transport works on host memory: pass device_id = -1");
+    transport_ = make_c10d_transport(rank, nranks, unique_id.substr(5));
+  } else {
+    BAGUA_CHECK(device_id >= 0, Communicator, "an NCCL communicator needs a CUDA device id");
+    transport_ = make_nccl_transport(rank, nranks, device_id, stream, unique_id);
+  }
+  fused_enabled_ = env_long("BAGUA_B200_FUSED", 1) != 0;
+}
+
+SingleCommunicator::~SingleCommunicator() {
+  arena_.reset();
+  transport_.reset();
+}
+
+void SingleCommunicator::abort() {
+  aborted_.store(true, std::memory_order_release);
+  transport_->abort();
+}
+
+void SingleCommunicator::check_live() const {
+  if (check_abort()) throw BaguaError(ErrorKind::Communicator, "communicator was aborted");
+}
+
+PeerArena* SingleCommunicator::arena() {
+  if (device_id_ < 0 || nranks_ < 2 || nranks_ > kArenaMaxRanks || !fused_enabled_) return nullptr;
+  std::lock_guard<std::mutex> g(arena_mu_);
+  if (!arena_tried_) {
+    arena_tried_ = true;
+    try {
+      arena_ = std::make_unique<PeerArena>(*transport_, rank_, nranks_, device_id_, (cudaStream_t)stream_);
+    } catch (const std::exception& e) {
+      // Mapping peers failed (no P2P between the devices, IPC disabled ...).  Every
+      // rank sees the same topology, so every rank lands here and the library path
+      // is used consistently.
+      BAGUA_LOG(Warn, "peer arena unavailable, using library collectives: " << e.what());
+      arena_.reset();
+    }
+  }
+  return arena_.get();
+}
+
+void SingleCommunicator::check_device_status() {
+  std::lock_guard<std::mutex> g(arena_mu_);
+  if (!arena_) return;
+  DeviceStatus s = arena_->read_status();
+  if (s.code == 0) return;
+  aborted_.store(true, std::memory_order_release);
+  std::ostringstream o;
+  static const char* what[] = {"", "wait for a peer to finish its previous op", "wait for a peer's data signal",
+                               "grid barrier"};
+  o << "a device-side " << (s.code < 4 ? what[s.code] : "wait") << " ran out after " << arena_->deadline_ms()
+    << " ms (rank " << rank_ << ", peer " << s.peer << ", phase " << s.phase << ", block " << s.block << ", epoch "
+    << s.epoch << ", last value seen " << s.seen << "); the communicator is now aborted";
+  throw BaguaError(ErrorKind::Communicator, o.str());
+}
+
+// ---- collectives ------------------------------------------------------------------
+void SingleCommunicator::allreduce(const RawTensor& send, RawTensor& recv, ReductionOp op) {
+  check_live();
+  same_kind(send, recv, "allreduce");
+  BAGUA_CHECK(send.num_elements_allocated() == recv.num_elements_allocated(), Communicator,
+              "allreduce: send and recv sizes differ");
+  transport_->allreduce(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype(), op);
+}
+void SingleCommunicator::allreduce_inplace(RawTensor& t, ReductionOp op) {
+  check_live();
+  transport_->allreduce(t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), op);
+}
+void SingleCommunicator::broadcast(RawTensor& t, int root) {
+  check_live();
+  transport_->broadcast(t.data_ptr(), t.num_elements_allocated(), t.dtype(), root);
+}
+void SingleCommunicator::reduce(const RawTensor& send, RawTensor& recv, int dst, ReductionOp op) {
+  check_live();
+  same_kind(send, recv, "reduce");
+  BAGUA_CHECK(send.num_elements_allocated() == recv.num_elements_allocated(), Communicator,
+              "reduce: send and recv sizes differ");
+  transport_->reduce(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype(), dst, op);
+}
+void SingleCommunicator::reduce_inplace(RawTensor& t, int dst, ReductionOp op) {
+  check_live();
+  transport_->reduce(t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), dst, op);
+}
+void SingleCommunicator::send(const RawTensor& t, int peer) {
+  check_live();
+  transport_->send(t.data_ptr(), t.num_elements_allocated(), t.dtype(), peer);
+}
+void SingleCommunicator::recv(RawTensor& t, int peer) {
+  check_live();
+  transport_->recv(t.data_ptr(), t.num_elements_allocated(), t.dtype(), peer);
+}
+void SingleCommunicator::alltoall(const RawTensor& send, RawTensor& recv) {
+  check_live();
+  same_kind(send, recv, "alltoall");
+  BAGUA_CHECK(send.num_elements_allocated() == recv.num_elements_allocated(), Communicator,
+              "alltoall: send and recv sizes differ");
+  BAGUA_CHECK(send.num_elements_allocated() % nranks_ == 0, Communicator,
+              "alltoall: tensor size must be divisible by the number of ranks");
+  transport_->alltoall(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated() / nranks_, send.dtype());
+}
+void SingleCommunicator::alltoall_inplace(RawTensor& t) {
+  check_live();
+  BAGUA_CHECK(t.num_elements_allocated() % nranks_ == 0, Communicator,
+              "alltoall: tensor size must be divisible by the number of ranks");
+  // Exchange out of a copy: slot p is both what goes to p and where p's data lands.
+  auto tmp = PoolRawTensor::allocate(t.device_id(), t.dtype(), t.num_elements_allocated(), stream_);
+  kernels::copy_bytes(tmp->data_ptr(), t.data_ptr(), t.bytes_allocated(), t.ctx(stream_));
+  transport_->alltoall(tmp->data_ptr(), t.data_ptr(), t.num_elements_allocated() / nranks_, t.dtype());
+}
+void SingleCommunicator::alltoall_v(const RawTensor& send, const std::vector<int64_t>& sc,
+                                    const std::vector<int64_t>& sd, RawTensor& recv, const std::vector<int64_t>& rc,
+                                    const std::vector<int64_t>& rd) {
+  check_live();
+  same_kind(send, recv, "alltoall_v");
+  BAGUA_CHECK((int)sc.size() == nranks_ && (int)sd.size() == nranks_ && (int)rc.size() == nranks_ &&
+                  (int)rd.size() == nranks_,
+              Communicator, "alltoall_v: counts and displacements must have one entry per rank");
+  for (int p = 0; p < nranks_; ++p) {
+    BAGUA_CHECK(sc[p] >= 0 && sd[p] >= 0 && sd[p] + sc[p] <= send.num_elements_allocated(), Communicator,
+                "alltoall_v: send range of rank " << p << " is outside the tensor");
+    BAGUA_CHECK(rc[p] >= 0 && rd[p] >= 0 && rd[p] + rc[p] <= recv.num_elements_allocated(), Communicator,
+                "alltoall_v: recv range of rank " << p << " is outside the tensor");
+  }
+  transport_->alltoall_v(send.data_ptr(), sc, sd, recv.data_ptr(), rc, rd, send.dtype());
+}
+void SingleCommunicator::allgather(const RawTensor& send, RawTensor& recv) {
+  check_live();
+  same_kind(send, recv, "allgather");
+  BAGUA_CHECK(send.num_elements_allocated() * nranks_ == recv.num_elements_allocated(), Communicator,
+              "allgather: recv must hold nranks * send elements");
+  transport_->allgather(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype());
+}
+void SingleCommunicator::allgather_inplace(RawTensor& t) {
+  check_live();
+  BAGUA_CHECK(t.num_elements_allocated() % nranks_ == 0, Communicator,
+              "allgather: tensor size must be divisible by the number of ranks");
+  const int64_t count = t.num_elements_allocated() / nranks_;
+  const size_t es = dtype_bytes(t.dtype());
+  transport_->allgather((char*)t.data_ptr() + (size_t)rank_ * count * es, t.data_ptr(), count, t.dtype());
+}
+void SingleCommunicator::gather(const RawTensor& send, RawTensor& recv, int dst) {
+  check_live();
+  same_kind(send, recv, "gather");
+  if (rank_ == dst)
+    BAGUA_CHECK(send.num_elements_allocated() * nranks_ == recv.num_elements_allocated(), Communicator,
+                "gather: recv on the root must hold nranks * send elements");
+  transport_->gather(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype(), dst);
+}
+void SingleCommunicator::gather_inplace(RawTensor& t, int64_t count, int dst) {
+  check_live();
+  if (rank_ == dst)
+    BAGUA_CHECK(t.num_elements_allocated() == count * nranks_, Communicator,
+                "gather_inplace: the root tensor must hold count * nranks elements");
+  else
+    BAGUA_CHECK(t.num_elements_allocated() >= count, Communicator, "gather_inplace: tensor smaller than count");
+  const size_t es = dtype_bytes(t.dtype());
+  const void* src = rank_ == dst ? (char*)t.data_ptr() + (size_t)rank_ * count * es : t.data_ptr();
+  transport_->gather(src, t.data_ptr(), count, t.dtype(), dst);
+}
+void SingleCommunicator::scatter(const RawTensor& send, RawTensor& recv, int src) {
+  check_live();
+  same_kind(send, recv, "scatter");
+  if (rank_ == src)
+    BAGUA_CHECK(recv.num_elements_allocated() * nranks_ == send.num_elements_allocated(), Communicator,
+                "scatter: send on the root must hold nranks * recv elements");
+  transport_->scatter(send.data_ptr(), recv.data_ptr(), recv.num_elements_allocated(), recv.dtype(), src);
+}
+void SingleCommunicator::scatter_inplace(RawTensor& t, int64_t count, int src) {
+  check_live();
+  if (rank_ == src)
+    BAGUA_CHECK(t.num_elements_allocated() == count * nranks_, Communicator,
+                "scatter_inplace: the root tensor must hold count * nranks elements");
+  else
+    BAGUA_CHECK(t.num_elements_allocated() >= count, Communicator, "scatter_inplace: tensor smaller than count");
+  const size_t es = dtype_bytes(t.dtype());
+  void* dst = rank_ == src ? (char*)t.data_ptr() + (size_t)rank_ * count * es : t.data_ptr();
+  transport_->scatter(t.data_ptr(), dst, count, t.dtype(), src);
+}
+void SingleCommunicator::reduce_scatter(const RawTensor& send, RawTensor& recv, ReductionOp op) {
+  check_live();
+  same_kind(send, recv, "reduce_scatter");
+  BAGUA_CHECK(recv.num_elements_allocated() * nranks_ == send.num_elements_allocated(), Communicator,
+              "reduce_scatter: send must hold nranks * recv elements");
+  transport_->reduce_scatter(send.data_ptr(), recv.data_ptr(), recv.num_elements_allocated(), send.dtype(), op);
+}
+void SingleCommunicator::reduce_scatter_inplace(RawTensor& t, ReductionOp op) {
+  check_live();
+  BAGUA_CHECK(t.num_elements_allocated() % nranks_ == 0, Communicator,
+              "reduce_scatter: tensor size must be divisible by the number of ranks");
+  const int64_t count = t.num_elements_allocated() / nranks_;
+  const size_t es = dtype_bytes(t.dtype());
+  transport_->reduce_scatter(t.data_ptr(), (char*)t.data_ptr() + (size_t)rank_ * count * es, count, t.dtype(), op);
+}
+void SingleCommunicator::barrier() {
+  check_live();
+  transport_->barrier();
+}
+
+// ---- two-level ----------------------------------------------------------------------
+std::shared_ptr<Communicator> Communicator::create(SingleCommPtr internode, SingleCommPtr intranode,
+                                                   bool hierarchical) {
+  auto c = std::make_shared<Communicator>();
+  if (!hierarchical) {
+    BAGUA_CHECK(internode != nullptr, Communicator, "inter node communicator must be given in non-hierarchical mode");
+    c->kind_ = Kind::Single;
+    c->internode_ = std::move(internode);
+    return c;
+  }
+  BAGUA_CHECK(intranode != nullptr, Communicator, "intra node communicator must be given in hierarchical mode");
+  if (intranode->rank() == 0) {
+    BAGUA_CHECK(internode != nullptr, Communicator,
+                "inter node communicator must be given on the leader GPU in hierarchical mode");
+    BAGUA_CHECK(intranode->stream() == internode->stream(), Communicator,
+                "intra node communicator should use the same stream as the inter node communicator");
+    BAGUA_CHECK(intranode->device_id() == internode->device_id(), Communicator,
+                "intra node and inter node communicators must be on the same device");
+    c->kind_ = Kind::HierarchicalLeader;
+    c->internode_ = std::move(internode);
+    c->intranode_ = std::move(intranode);
+  } else {
+    c->kind_ = Kind::HierarchicalWorker;
+    c->intranode_ = std::move(intranode);
+  }
+  return c;
+}
+
+uint64_t Communicator::stream() const {
+  return kind_ == Kind::HierarchicalWorker ? intranode_->stream() : internode_->stream();
+}
+
+void Communicator::execute_communication(RawTensor& t, bool intranode_average, bool pre, bool post,
+                                         const std::function<void(SingleCommunicator&, RawTensor&)>& hook) {
+  switch (kind_) {
+    case Kind::Single: hook(*internode_, t); return;
+    case Kind::HierarchicalLeader:
+      if (pre) intranode_->reduce_inplace(t, 0, intranode_average ? ReductionOp::AVG : ReductionOp::SUM);
+      hook(*internode_, t);
+      if (post) intranode_->broadcast(t, 0);
+      return;
+    case Kind::HierarchicalWorker:
+      if (pre) intranode_->reduce_inplace(t, 0, intranode_average ? ReductionOp::AVG : ReductionOp::SUM);
+      if (post) intranode_->broadcast(t, 0);
+      return;
+  }
+}
+
+}  // namespace bagua

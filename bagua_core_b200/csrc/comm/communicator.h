@@ -1,0 +1,122 @@
+// Communicators: the collective API the ops and the Python layer call.
+//
+// `SingleCommunicator` = one group of ranks bound to one stream (reference
+// `BaguaSingleCommunicator`, bagua-core-internal/src/communicators/mod.rs:19-241).  It
+// owns a library transport (NCCL on GPUs, c10d/gloo on host memory) and, on GPUs of one
+// NVLink domain, a `PeerArena`: IPC-mapped staging memory and signal words of every
+// rank, which the fused sm_100a kernels use to move data with plain peer stores.
+//
+// `Communicator` adds the two-level form (reference `BaguaCommunicator`,
+// communicators/mod.rs:243-428): leader = intranode rank 0 runs
+// reduce(intranode) → hook(internode) → broadcast(intranode); workers only take part in
+// the reduce and the broadcast.
+#pragma once
+
+#include <functional>
+
+#include "../tensor/tensor.h"
+#include "transport.h"
+
+namespace bagua {
+
+class PeerArena;
+
+class SingleCommunicator {
+ public:
+  // unique_id: base64 NCCL id, or "c10d:<group name>" for the host transport
+  // (device_id < 0).
+  SingleCommunicator(int rank, int nranks, int device_id, uint64_t stream, const std::string& unique_id);
+  ~SingleCommunicator();
+
+  int rank() const { return rank_; }
+  int nranks() const { return nranks_; }
+  int device_id() const { return device_id_; }
+  uint64_t stream() const { return stream_; }
+  const char* transport_kind() const { return transport_->kind(); }
+
+  void abort();
+  bool check_abort() const { return aborted_.load(std::memory_order_acquire); }
+
+  // Collectives; counts come from num_elements_allocated(), like the reference.
+  void allreduce(const RawTensor& send, RawTensor& recv, ReductionOp op);
+  void allreduce_inplace(RawTensor& t, ReductionOp op);
+  void broadcast(RawTensor& t, int root);
+  void reduce(const RawTensor& send, RawTensor& recv, int dst, ReductionOp op);
+  void reduce_inplace(RawTensor& t, int dst, ReductionOp op);
+  void send(const RawTensor& t, int peer);
+  void recv(RawTensor& t, int peer);
+  void alltoall(const RawTensor& send, RawTensor& recv);
+  void alltoall_inplace(RawTensor& t);
+  void alltoall_v(const RawTensor& send, const std::vector<int64_t>& send_counts,
+                  const std::vector<int64_t>& send_displs, RawTensor& recv, const std::vector<int64_t>& recv_counts,
+                  const std::vector<int64_t>& recv_displs);
+  void allgather(const RawTensor& send, RawTensor& recv);
+  void allgather_inplace(RawTensor& t);
+  void gather(const RawTensor& send, RawTensor& recv, int dst);
+  void gather_inplace(RawTensor& t, int64_t count, int dst);
+  void scatter(const RawTensor& send, RawTensor& recv, int src);
+  void scatter_inplace(RawTensor& t, int64_t count, int src);
+  void reduce_scatter(const RawTensor& send, RawTensor& recv, ReductionOp op);
+  void reduce_scatter_inplace(RawTensor& t, ReductionOp op);
+  void barrier();
+  void group_start() { transport_->group_start(); }
+  void group_end() { transport_->group_end(); }
+
+  // Fused path.  Null when the communicator is on the host, has one rank, was disabled
+  // (BAGUA_B200_FUSED=0 or set_fused(false)) or peer mapping failed.
+  PeerArena* arena();
+  void set_fused(bool on) { fused_enabled_ = on; }
+  bool fused_enabled() const { return fused_enabled_; }
+  // Throws CommunicatorError if a fused kernel reported a device-side wait that ran out.
+  void check_device_status();
+
+  Transport& transport() { return *transport_; }
+
+ private:
+  void check_live() const;
+  int rank_, nranks_, device_id_;
+  uint64_t stream_;
+  std::unique_ptr<Transport> transport_;
+  std::atomic<bool> aborted_{false};
+  bool fused_enabled_ = true;
+  bool arena_tried_ = false;
+  std::unique_ptr<PeerArena> arena_;
+  std::mutex arena_mu_;
+};
+
+using SingleCommPtr = std::shared_ptr<SingleCommunicator>;
+
+// RAII ncclGroupStart/End (reference NCCLGroupGuard, communicators/mod.rs:430-453).
+class GroupGuard {
+ public:
+  explicit GroupGuard(SingleCommunicator& c) : c_(c) { c_.group_start(); }
+  ~GroupGuard() noexcept(false) { c_.group_end(); }
+
+ private:
+  SingleCommunicator& c_;
+};
+
+class Communicator {
+ public:
+  enum class Kind { Single, HierarchicalLeader, HierarchicalWorker };
+  // hierarchical=false: `internode` is used alone.  hierarchical=true: `intranode` is
+  // required; the rank whose intranode rank is 0 is the leader and needs `internode`.
+  static std::shared_ptr<Communicator> create(SingleCommPtr internode, SingleCommPtr intranode, bool hierarchical);
+
+  Kind kind() const { return kind_; }
+  uint64_t stream() const;
+  SingleCommPtr internode() const { return internode_; }
+  SingleCommPtr intranode() const { return intranode_; }
+  // The communicator whose rank/nranks the hook sees.
+  SingleCommPtr hook_comm() const { return kind_ == Kind::Single ? internode_ : internode_; }
+
+  // reference: BaguaCommunicator::execute_communication (communicators/mod.rs:390-427)
+  void execute_communication(RawTensor& t, bool intranode_average, bool hierarchical_pre, bool hierarchical_post,
+                             const std::function<void(SingleCommunicator&, RawTensor&)>& hook);
+
+ private:
+  Kind kind_ = Kind::Single;
+  SingleCommPtr internode_, intranode_;
+};
+
+}  // namespace bagua

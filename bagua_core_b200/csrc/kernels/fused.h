@@ -1,0 +1,45 @@
+// Host entry points of the fused communication kernels (sm_100a, peer stores over
+// NVLink/NVSwitch through a PeerArena).  Each returns false — without launching
+// anything — when the buffer layout is not eligible (alignment, size, dtype); the
+// caller then takes the unfused library path.  All ranks of the communicator must make
+// the same sequence of calls with the same sizes.
+//
+// What each call replaces in the reference (bagua-core-internal/src/comm_ops/):
+//   allreduce      ncclAllReduce (+AVG), or alltoall → chunk reduce → allgather
+//                  (centralized_full_precision_synchronous.rs:16-55)
+//   bytegrad       min/max ×2N, compress, alltoall, decompress, chunk reduce, min/max,
+//                  compress, allgather, decompress
+//                  (centralized_low_precision_synchronous.rs:16-73)
+//   pair_average   grouped send/recv with one peer + average kernel
+//                  (decentralized_full_precision_synchronous.rs:62-92)
+//   lp_ring        3 addmul, min/max, compress, 4 grouped send/recv, 3 decompress,
+//                  3 add, copy (decentralized_low_precision_synchronous.rs:23-154)
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include "../comm/arena.h"
+#include "../common.h"
+
+namespace bagua {
+namespace fused {
+
+// out = scale * sum_r in_r.  `in` and `out` may be the same buffer.
+bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream);
+
+// In-place ByteGrad on `bucket` (n elements, n % (16*nranks) == 0).
+bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream);
+
+// out = (in + peer's in) / 2; `peer` pairs must be mutual.
+bool pair_average(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, int peer, cudaStream_t stream);
+
+// Low-precision ring gossip step on weights x with replicas w (own), l / r (neighbours').
+bool lp_ring(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, DType dt, cudaStream_t stream);
+
+// Test hook: launches a one-CTA kernel that waits `wait_ms` for a signal nobody sends
+// and returns the status record the host read back (code != 0 expected).  Uses only
+// rank-local memory; needs no peers.
+DeviceStatus debug_wait_timeout(int device, double wait_ms);
+
+}  // namespace fused
+}  // namespace bagua

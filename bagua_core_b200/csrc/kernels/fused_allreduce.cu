@@ -1,0 +1,342 @@
+// Fused all-reduce (+scale) and pair-average over peer memory, sm_100a.
+//
+// One launch per bucket, no library collective.  Work is cut in 16-byte vectors; block b
+// of every rank owns the same vector range, so blocks pair up across GPUs through
+// per-block signal words and never need a grid-wide barrier.
+//
+//   one-shot  (small buffers): every rank stores its slice into slot[rank] of every
+//             peer's staging, signals, waits for the N-1 signals addressed to it, and sums
+//             the N contributions in rank order (bit-identical on all ranks).
+//             Wire per GPU: (N-1)·S out.  One signalling hop.
+//   two-shot  (large buffers): reduce-scatter by push (chunk q of my data → slot[me] of
+//             q's staging), owner sums chunk `me` in rank order, scales, and stores the
+//             result both locally and into every peer's all-gather area; peers copy it
+//             out of their own staging.  Wire per GPU: 2(N-1)/N·S out.  Two hops.
+//
+// Accumulation is fp32 for every dtype, rounded once.  Remote traffic is stores only;
+// every load is from local HBM/L2.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "fused.h"
+#include "peer_sync.cuh"
+
+namespace bagua {
+namespace fused {
+
+namespace {
+
+constexpr int kThreads = 512;
+
+template <typename T>
+struct VecOps;
+template <>
+struct VecOps<float> {
+  static constexpr int N = 4;
+  __device__ static void acc(float (&a)[N], const uint4& r) {
+    a[0] += __uint_as_float(r.x);
+    a[1] += __uint_as_float(r.y);
+    a[2] += __uint_as_float(r.z);
+    a[3] += __uint_as_float(r.w);
+  }
+  __device__ static uint4 pack(const float (&a)[N], float s) {
+    return make_uint4(__float_as_uint(a[0] * s), __float_as_uint(a[1] * s), __float_as_uint(a[2] * s),
+                      __float_as_uint(a[3] * s));
+  }
+};
+template <>
+struct VecOps<__half> {
+  static constexpr int N = 8;
+  __device__ static void acc(float (&a)[N], const uint4& r) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __half22float2(h[k]);
+      a[2 * k] += f.x;
+      a[2 * k + 1] += f.y;
+    }
+  }
+  __device__ static uint4 pack(const float (&a)[N], float s) {
+    uint4 r;
+    __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2half2_rn(a[2 * k] * s, a[2 * k + 1] * s);
+    return r;
+  }
+};
+template <>
+struct VecOps<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void acc(float (&a)[N], const uint4& r) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __bfloat1622float2(h[k]);
+      a[2 * k] += f.x;
+      a[2 * k + 1] += f.y;
+    }
+  }
+  __device__ static uint4 pack(const float (&a)[N], float s) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(a[2 * k] * s, a[2 * k + 1] * s);
+    return r;
+  }
+};
+
+__device__ __forceinline__ uint32_t all_peers_mask(const ArenaView& v) {
+  return ((1u << v.nranks) - 1u) & ~(1u << v.rank);
+}
+
+// Streaming copy of vectors [lo, hi) from src to dst (same indexing), 4 in flight per thread.
+__device__ __forceinline__ void copy_vecs(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t lo,
+                                          int64_t hi) {
+  int64_t i = lo + threadIdx.x;
+  for (; i + 3 * kThreads < hi; i += 4 * kThreads) {
+    uint4 a = src[i], b = src[i + kThreads], c = src[i + 2 * kThreads], d = src[i + 3 * kThreads];
+    dst[i] = a;
+    dst[i + kThreads] = b;
+    dst[i + 2 * kThreads] = c;
+    dst[i + 3 * kThreads] = d;
+  }
+  for (; i < hi; i += kThreads) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------------
+// one-shot
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    allreduce_oneshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec,
+                             int64_t slot_vecs, float scale) {
+  using O = VecOps<T>;
+  const int me = v.rank, N = v.nranks;
+  const int64_t lo = nvec * blockIdx.x / gridDim.x, hi = nvec * (blockIdx.x + 1) / gridDim.x;
+  bool ok = psync::cta_wait_prev_done(v);
+  if (ok) {
+    for (int i = 1; i < N; ++i) {
+      const int q = (me + i) % N;
+      uint4* dst = reinterpret_cast<uint4*>(v.staging[q]) + (int64_t)me * slot_vecs;
+      copy_vecs(dst, in, lo, hi);
+    }
+    psync::cta_signal_phase(v, 0, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, 0, all_peers_mask(v));
+  }
+  if (ok) {
+    const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) {
+      float a[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+      for (int r = 0; r < N; ++r) {
+        const uint4 x = (r == me) ? in[i] : mine[(int64_t)r * slot_vecs + i];
+        O::acc(a, x);
+      }
+      out[i] = O::pack(a, scale);
+    }
+  }
+  psync::cta_finish_op(v);
+}
+
+// ---------------------------------------------------------------------------------
+// two-shot
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    allreduce_twoshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec,
+                             int64_t max_chunk_vecs, float scale) {
+  using O = VecOps<T>;
+  const int me = v.rank, N = v.nranks;
+  const int G = gridDim.x, b = blockIdx.x;
+  auto chunk_lo = [&](int c) { return nvec * c / N; };
+  // block slice inside chunk c
+  auto slice = [&](int c, int64_t& lo, int64_t& hi) {
+    const int64_t c0 = chunk_lo(c), len = chunk_lo(c + 1) - c0;
+    lo = c0 + len * b / G;
+    hi = c0 + len * (b + 1) / G;
+  };
+  const int64_t ag_base = (int64_t)N * max_chunk_vecs;  // all-gather area follows the N reduce-scatter slots
+
+  bool ok = psync::cta_wait_prev_done(v);
+  if (ok) {
+    // step A: push my slice of chunk q into slot[me] of q
+    for (int i = 1; i < N; ++i) {
+      const int q = (me + i) % N;
+      int64_t lo, hi;
+      slice(q, lo, hi);
+      uint4* dst = reinterpret_cast<uint4*>(v.staging[q]) + (int64_t)me * max_chunk_vecs - chunk_lo(q);
+      copy_vecs(dst, in, lo, hi);
+      psync::cta_signal_phase(v, 0, 1u << q);
+    }
+    ok = psync::cta_wait_phase(v, 0, all_peers_mask(v));
+  }
+  if (ok) {
+    // step B: reduce my chunk in rank order, scale, store locally and to every peer
+    int64_t lo, hi;
+    slice(me, lo, hi);
+    const int64_t c0 = chunk_lo(me);
+    const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) {
+      float a[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+      for (int r = 0; r < N; ++r) {
+        const uint4 x = (r == me) ? in[i] : mine[(int64_t)r * max_chunk_vecs + (i - c0)];
+        O::acc(a, x);
+      }
+      const uint4 res = O::pack(a, scale);
+      out[i] = res;
+      for (int k = 1; k < N; ++k) {
+        const int q = (me + k) % N;
+        reinterpret_cast<uint4*>(v.staging[q])[ag_base + i] = res;
+      }
+    }
+    psync::cta_signal_phase(v, 1, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, 1, all_peers_mask(v));
+  }
+  if (ok) {
+    // step C: collect the other chunks from my own all-gather area
+    const uint4* ag = reinterpret_cast<const uint4*>(v.staging[me]) + ag_base;
+    for (int k = 1; k < N; ++k) {
+      const int q = (me + k) % N;
+      int64_t lo, hi;
+      slice(q, lo, hi);
+      copy_vecs(out, ag, lo, hi);
+    }
+  }
+  psync::cta_finish_op(v);
+}
+
+// ---------------------------------------------------------------------------------
+// pair average: out = (in + peer's in) / 2
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    pair_average_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec, int peer) {
+  using O = VecOps<T>;
+  const int64_t lo = nvec * blockIdx.x / gridDim.x, hi = nvec * (blockIdx.x + 1) / gridDim.x;
+  bool ok = psync::cta_wait_prev_done(v);
+  if (ok) {
+    copy_vecs(reinterpret_cast<uint4*>(v.staging[peer]), in, lo, hi);
+    psync::cta_signal_phase(v, 0, 1u << peer);
+    ok = psync::cta_wait_phase(v, 0, 1u << peer);
+  }
+  if (ok) {
+    const uint4* got = reinterpret_cast<const uint4*>(v.staging[v.rank]);
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) {
+      float a[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+      O::acc(a, in[i]);
+      O::acc(a, got[i]);
+      out[i] = O::pack(a, 0.5f);
+    }
+  }
+  psync::cta_finish_op(v);
+}
+
+__global__ void wait_probe_kernel(ArenaView v) {
+  // waits for a phase signal from "rank 1" that nobody will ever send
+  psync::cta_wait_phase(v, 0, 1u << 1);
+}
+
+int pick_grid(const PeerArena& arena, size_t bytes) {
+  // one CTA per 64 KiB, at least 1, at most the arena's CTA budget
+  int64_t g = (int64_t)((bytes + (64 << 10) - 1) / (64 << 10));
+  g = std::max<int64_t>(1, std::min<int64_t>(g, arena.max_blocks()));
+  return (int)g;
+}
+
+template <typename T>
+bool allreduce_t(PeerArena& arena, const void* in, void* out, int64_t n, float scale, cudaStream_t stream) {
+  const size_t bytes = (size_t)n * sizeof(T);
+  if (bytes == 0) return true;
+  if (bytes % 16 != 0 || (uintptr_t)in % 16 != 0 || (uintptr_t)out % 16 != 0) return false;
+  const int64_t nvec = (int64_t)(bytes / 16);
+  const int N = arena.nranks();
+  static const size_t oneshot_max = (size_t)env_long("BAGUA_B200_ONESHOT_BYTES", 256 << 10);
+  const int grid = pick_grid(arena, bytes);
+  if (bytes <= oneshot_max) {
+    arena.ensure_staging((size_t)N * bytes);
+    ArenaView v = arena.next_view(grid, 0);
+    allreduce_oneshot_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, nvec, nvec, scale);
+  } else {
+    const int64_t max_chunk = (nvec + N - 1) / N;
+    arena.ensure_staging(((size_t)N * (size_t)max_chunk + (size_t)nvec) * 16);
+    ArenaView v = arena.next_view(grid, 0);
+    allreduce_twoshot_kernel<T>
+        <<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, nvec, max_chunk, scale);
+  }
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+template <typename T>
+bool pair_average_t(PeerArena& arena, const void* in, void* out, int64_t n, int peer, cudaStream_t stream) {
+  const size_t bytes = (size_t)n * sizeof(T);
+  if (bytes == 0) return true;
+  if (bytes % 16 != 0 || (uintptr_t)in % 16 != 0 || (uintptr_t)out % 16 != 0) return false;
+  arena.ensure_staging(bytes);
+  const int grid = pick_grid(arena, bytes);
+  ArenaView v = arena.next_view(grid, 0);
+  pair_average_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, (int64_t)(bytes / 16), peer);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+}  // namespace
+
+bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream) {
+  switch (dt) {
+    case DType::F32: return allreduce_t<float>(arena, in, out, n, scale, stream);
+    case DType::F16: return allreduce_t<__half>(arena, in, out, n, scale, stream);
+    case DType::BF16: return allreduce_t<__nv_bfloat16>(arena, in, out, n, scale, stream);
+    default: return false;
+  }
+}
+
+bool pair_average(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, int peer, cudaStream_t stream) {
+  if (peer < 0 || peer >= arena.nranks() || peer == arena.rank()) return false;
+  switch (dt) {
+    case DType::F32: return pair_average_t<float>(arena, in, out, n, peer, stream);
+    case DType::F16: return pair_average_t<__half>(arena, in, out, n, peer, stream);
+    case DType::BF16: return pair_average_t<__nv_bfloat16>(arena, in, out, n, peer, stream);
+    default: return false;
+  }
+}
+
+DeviceStatus debug_wait_timeout(int device, double wait_ms) {
+  BAGUA_CUDA_CHECK(cudaSetDevice(device));
+  uint32_t* pad = nullptr;
+  DeviceStatus* host = nullptr;
+  DeviceStatus* dev = nullptr;
+  BAGUA_CUDA_CHECK(cudaMalloc((void**)&pad, kSigWords * sizeof(uint32_t)));
+  BAGUA_CUDA_CHECK(cudaMemset(pad, 0, kSigWords * sizeof(uint32_t)));
+  BAGUA_CUDA_CHECK(cudaHostAlloc((void**)&host, sizeof(DeviceStatus), cudaHostAllocMapped));
+  std::memset(host, 0, sizeof(DeviceStatus));
+  BAGUA_CUDA_CHECK(cudaHostGetDevicePointer((void**)&dev, host, 0));
+  ArenaView v;
+  std::memset(&v, 0, sizeof(v));
+  v.signals[0] = pad;
+  v.signals[1] = pad;  // never written
+  v.status = dev;
+  v.rank = 0;
+  v.nranks = 2;
+  v.epoch = 1;
+  v.deadline_ns = (uint64_t)(wait_ms * 1e6);
+  wait_probe_kernel<<<1, 32>>>(v);
+  cudaError_t e = cudaDeviceSynchronize();
+  DeviceStatus s;
+  std::memcpy(&s, host, sizeof(s));
+  cudaFree(pad);
+  cudaFreeHost(host);
+  BAGUA_CUDA_CHECK(e);
+  return s;
+}
+
+}  // namespace fused
+}  // namespace bagua

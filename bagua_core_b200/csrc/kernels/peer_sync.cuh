@@ -1,0 +1,179 @@
+// Device-side signalling between GPUs for the fused communication kernels.
+//
+// Memory model: a producer CTA writes payload with ordinary stores to a peer pointer,
+// executes bar.sync, then one thread issues fence.sys + st.release.sys on the peer's
+// signal word.  The consumer thread polls the word with ld.acquire.sys, then bar.sync
+// releases the rest of its CTA, which may now read the payload.  Signal values are op
+// epochs that only grow (compared with wrap-around arithmetic).
+//
+// Every wait is bounded twice: by %globaltimer against the view's deadline and by an
+// iteration cap.  When a wait runs out the thread records what it was waiting for in
+// the host-mapped status record, raises the rank-local poison word so that all other
+// waits on this GPU return at once, and gives up; no trap, no assert.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../comm/arena.h"
+
+namespace bagua {
+namespace psync {
+
+constexpr int kSigPoison = kSigCounter + 1;  // rank-local: non-zero once any wait ran out
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t ld_acquire_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint32_t* phase_word(uint32_t* pad, int phase, int src, int block) {
+  return pad + kSigPhase + (phase * kArenaMaxRanks + src) * kArenaMaxBlocks + block;
+}
+
+__device__ __noinline__ void record_timeout(const ArenaView& v, uint32_t code, uint32_t phase, uint32_t peer,
+                                            uint32_t seen) {
+  DeviceStatus* s = v.status;
+  if (s) {
+    volatile uint32_t* w = reinterpret_cast<volatile uint32_t*>(s);
+    w[1] = phase;
+    w[2] = peer;
+    w[3] = blockIdx.x;
+    w[4] = v.epoch;
+    w[5] = seen;
+    __threadfence_system();
+    w[0] = code;
+  }
+  volatile uint32_t* poison = v.signals[v.rank] + kSigPoison;
+  *poison = 1u;
+  __threadfence();
+}
+
+// One thread waits until *flag has reached `want`.  Returns false when it gave up.
+__device__ __forceinline__ bool wait_word(const ArenaView& v, const uint32_t* flag, uint32_t want, uint32_t code,
+                                          uint32_t phase, uint32_t peer) {
+  uint32_t seen = ld_acquire_sys(flag);
+  if ((int32_t)(seen - want) >= 0) return true;
+  const uint32_t* poison = v.signals[v.rank] + kSigPoison;
+  const uint64_t start = globaltimer_ns();
+  const uint64_t max_spins = v.deadline_ns / 64 + (1ull << 20);
+  for (uint64_t spins = 1;; ++spins) {
+    seen = ld_acquire_sys(flag);
+    if ((int32_t)(seen - want) >= 0) return true;
+    if ((spins & 31) == 0) {
+      if (ld_relaxed_gpu(poison) != 0) return false;
+      if (globaltimer_ns() - start > v.deadline_ns || spins > max_spins) {
+        record_timeout(v, code, phase, peer, seen);
+        return false;
+      }
+      if (spins > 4096) __nanosleep(200);
+    }
+  }
+}
+
+// CTA-wide: wait until every peer's previous fused op has finished (its `done` word
+// reached epoch-1).  All threads must call.  Returns false if any wait gave up.
+__device__ __forceinline__ bool cta_wait_prev_done(const ArenaView& v) {
+  bool ok = true;
+  const int t = threadIdx.x;
+  if (t < v.nranks && t != v.rank) ok = wait_word(v, v.signals[v.rank] + kSigDone + t, v.epoch - 1, 1, 0, t);
+  return __syncthreads_and(ok) != 0;
+}
+
+// CTA-wide: publish "this block finished writing phase `phase` data" to every peer in
+// `peer_mask` (bit q).  All threads must call; payload stores must precede the call.
+__device__ __forceinline__ void cta_signal_phase(const ArenaView& v, int phase, uint32_t peer_mask) {
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t < v.nranks && ((peer_mask >> t) & 1u)) {
+    __threadfence_system();
+    st_release_sys(phase_word(v.signals[t], phase, v.rank, blockIdx.x), v.epoch);
+  }
+}
+
+// CTA-wide: wait for block `blockIdx.x` of every peer in `peer_mask` to have published
+// phase `phase`.  Returns false if any wait gave up.
+__device__ __forceinline__ bool cta_wait_phase(const ArenaView& v, int phase, uint32_t peer_mask) {
+  bool ok = true;
+  const int t = threadIdx.x;
+  if (t < v.nranks && ((peer_mask >> t) & 1u))
+    ok = wait_word(v, phase_word(v.signals[v.rank], phase, t, blockIdx.x), v.epoch, 2, phase, t);
+  return __syncthreads_and(ok) != 0;
+}
+
+// CTA-wide, at the very end of a fused op: the last CTA of the grid tells every peer
+// that this rank is done with the op (so they may overwrite its staging next op).
+__device__ __forceinline__ void cta_finish_op(const ArenaView& v) {
+  __syncthreads();
+  __shared__ int s_last;
+  uint32_t* pad = v.signals[v.rank];
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(pad + kSigCounter, 1u);
+    s_last = (prev == gridDim.x - 1);
+    if (s_last) pad[kSigCounter] = 0u;  // ready for the next launch (stream-ordered)
+  }
+  __syncthreads();
+  if (s_last) {
+    const int t = threadIdx.x;
+    if (t < v.nranks && t != v.rank) {
+      __threadfence_system();
+      st_release_sys(v.signals[t] + kSigDone + v.rank, v.epoch);
+    }
+  }
+}
+
+// Grid-wide barrier on a rank-local 64-bit counter that only grows; `index` is the
+// barrier's ordinal inside this launch (0, 1, ...).  Needs all CTAs co-resident
+// (cooperative launch).  Returns false if the wait gave up.
+__device__ __forceinline__ bool grid_barrier(const ArenaView& v, int index) {
+  __syncthreads();
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    unsigned long long* ctr = reinterpret_cast<unsigned long long*>(v.signals[v.rank] + kSigGridBar);
+    const unsigned long long target = v.grid_bar_base + (unsigned long long)(index + 1) * gridDim.x;
+    __threadfence();
+    atomicAdd(ctr, 1ull);
+    bool ok = true;
+    const uint32_t* poison = v.signals[v.rank] + kSigPoison;
+    const uint64_t start = globaltimer_ns();
+    const uint64_t max_spins = v.deadline_ns / 64 + (1ull << 20);
+    for (uint64_t spins = 1; ld_acquire_gpu_u64(ctr) < target; ++spins) {
+      if ((spins & 31) == 0) {
+        if (ld_relaxed_gpu(poison) != 0) {
+          ok = false;
+          break;
+        }
+        if (globaltimer_ns() - start > v.deadline_ns || spins > max_spins) {
+          record_timeout(v, 3, (uint32_t)index, 0, 0);
+          ok = false;
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+}  // namespace psync
+}  // namespace bagua
