@@ -44,7 +44,7 @@ DType dtype_from_torch(at::ScalarType st) {
 class TorchRawTensor : public RawTensor {
  public:
   explicit TorchRawTensor(at::Tensor t) : t_(std::move(t)), dtype_(dtype_from_torch(t_.scalar_type())) {
-    BAGUA_CHECK(t_.is_contiguous(), Tensor, "bagua tensors must be contiguous");
+    BAGUA_CHECK(t_.is_non_overlapping_and_dense(), Tensor, "bagua tensors must be dense (no gaps, no overlap)");
     BAGUA_CHECK(t_.is_cuda() || t_.is_cpu(), Tensor, "bagua tensors must live on a CUDA device or on the host");
   }
   ~TorchRawTensor() override {

@@ -73,6 +73,7 @@ class CentralizedFullPrecisionSynchronous : public CommOp {
   void execute_background_communication(const BucketPtr& bucket) override {
     OpFrame f(bucket, *comm_, false, false);
     comm_->execute_communication(*f.ct.raw, average_, true, true, [&](SingleCommunicator& c, RawTensor& t) {
+      if (c.nranks() == 1) return;  // sum or mean over one rank: nothing to do
       if (PeerArena* a = fused_arena(c, t)) {
         const float scale = average_ ? 1.0f / (float)c.nranks() : 1.0f;
         if (fused::allreduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,

@@ -1,0 +1,23 @@
+"""Data-parallel training layer: process groups, flat buckets, `with_bagua` and the algorithms."""
+from .algorithms import (  # noqa: F401
+    Algorithm,
+    AsyncModelAverageAlgorithm,
+    ByteGradAlgorithm,
+    DecentralizedAlgorithm,
+    GradientAllReduceAlgorithm,
+    LowPrecisionDecentralizedAlgorithm,
+    QAdamAlgorithm,
+    QAdamOptimizer,
+)
+from .bucket import BaguaBucket, BaguaTensor, split_into_buckets  # noqa: F401
+from .communication import (  # noqa: F401
+    BaguaProcessGroup,
+    destroy_process_group,
+    get_local_rank,
+    get_process_group,
+    get_rank,
+    get_world_size,
+    init_process_group,
+)
+from .distributed import BaguaModule, with_bagua  # noqa: F401
+from .optim import FlatSGD  # noqa: F401

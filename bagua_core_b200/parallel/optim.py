@@ -1,0 +1,98 @@
+"""Optimizers that work on flat bucket memory with one fused kernel per bucket.
+
+The reference contains no optimizer (it is only the communication engine); the benchmarks
+named for it train with SGD momentum 0.9, so the engine ships the obvious companion: since
+gradients already live in flat buckets, parameters and momentum are laid out the same way
+and `step()` is ONE sm_100a kernel per bucket (read p, g, m; write p, m: 20 bytes per
+parameter, the HBM minimum) instead of torch's multi-tensor loops.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .._native import C as _C
+
+
+class FlatSGD(torch.optim.Optimizer):
+    """torch.optim.SGD semantics (momentum, dampening, weight decay, Nesterov).
+
+    Before `with_bagua` attaches it (or for parameters outside any bucket) it updates
+    parameter by parameter with the same kernel."""
+
+    def __init__(self, params, lr: float = 1e-3, momentum: float = 0.0, dampening: float = 0.0,
+                 weight_decay: float = 0.0, nesterov: bool = False):
+        if nesterov and (momentum <= 0 or dampening != 0):
+            raise ValueError("Nesterov momentum requires a momentum and zero dampening")
+        defaults = dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay, nesterov=nesterov)
+        super().__init__(params, defaults)
+        self._flat: List[dict] = []
+        self._attached_ids = set()
+        self._steps = 0
+        self.kernel_launches = 0
+
+    # called by BaguaModule after it has built gradient buckets
+    def bagua_attach(self, bm):
+        self._flat.clear()
+        self._attached_ids.clear()
+        for b in bm.bagua_buckets:
+            if b.flattened is None or any(t.kind != "grad" for t in b.tensors):
+                continue
+            if b.flattened.dtype != torch.float32:
+                continue
+            flat_p = torch.zeros_like(b.flattened)
+            off = 0
+            with torch.no_grad():
+                for t in b.tensors:
+                    p = t.owner
+                    n = p.numel()
+                    shape, stride = tuple(p.shape), tuple(p.stride())
+                    if tuple(t.tensor.stride()) != stride:
+                        raise RuntimeError("parameter and gradient layouts differ; cannot share a flat layout")
+                    flat_p[off:off + n].as_strided(shape, stride).copy_(p)
+                    p.set_(flat_p.untyped_storage(), off, shape, stride)
+                    self._attached_ids.add(id(p))
+                    off += n
+            self._flat.append({"p": flat_p, "g": b.flattened, "m": torch.zeros_like(flat_p), "first": True})
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        g0 = self.param_groups[0]
+        stream = torch.cuda.current_stream().cuda_stream if (self._flat and self._flat[0]["p"].is_cuda) else 0
+        for f in self._flat:
+            _C.k_sgd_momentum_flat(f["p"], f["g"], f["m"], g0["lr"], g0["momentum"], g0["dampening"],
+                                   g0["weight_decay"], g0["nesterov"], f["first"], stream)
+            f["first"] = False
+            self.kernel_launches += 1
+        for group in self.param_groups:
+            for p in group["params"]:
+                if id(p) in self._attached_ids or p.grad is None:
+                    continue
+                st = self.state[p]
+                first = "momentum_buffer" not in st
+                if first:
+                    st["momentum_buffer"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                if p.dtype != torch.float32 or not p.is_non_overlapping_and_dense():
+                    raise RuntimeError("FlatSGD updates dense float32 parameters")
+                s = torch.cuda.current_stream().cuda_stream if p.is_cuda else 0
+                # dense tensors with equal strides can be updated as flat memory
+                pv = torch.as_strided(p, (p.numel(),), (1,))
+                gv = torch.as_strided(p.grad, (p.numel(),), (1,))
+                mv = torch.as_strided(st["momentum_buffer"], (p.numel(),), (1,))
+                _C.k_sgd_momentum_flat(pv, gv, mv, group["lr"], group["momentum"], group["dampening"],
+                                       group["weight_decay"], group["nesterov"], first, s)
+                self.kernel_launches += 1
+        self._steps += 1
+        return loss
+
+    def zero_grad(self, set_to_none: bool = False):
+        """Zero the flat gradient buffers with one memset per bucket; gradients stay views
+        of the bucket (never set to None, which would detach them from the bucket)."""
+        for f in self._flat:
+            f["g"].zero_()
+        for group in self.param_groups:
+            for p in group["params"]:
+                if id(p) not in self._attached_ids and p.grad is not None:
+                    p.grad.zero_()

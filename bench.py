@@ -1,0 +1,288 @@
+#!/usr/bin/env python
+"""Headline benchmark: training throughput (samples/s) of the named model/config through
+the engine's public API (`with_bagua`), on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+
+Default config: VGG-16 (138 M parameters), bf16 autocast with fp32 gradients, batch 32 per
+GPU of 3x224x224 N(0,1) images, uniform labels over 1000 classes, gradient_allreduce with
+10 MB buckets in reverse registration order, SGD momentum 0.9.  Other configs:
+`--model bert_large --algorithm bytegrad`, `--model resnet50 --algorithm decentralized`.
+
+`--impl` selects the arm: `ours` (fused sm_100a kernels), `baseline_nccl` (same engine,
+library collectives replaying the reference's call sequence with a stream sync per
+bucket), `ddp` (torch DistributedDataParallel), `reference` (the unmodified reference
+package, which cannot be installed offline: prints an `unavailable` line).
+
+Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events, barrier + synchronize
+on both sides, max over ranks) with inputs resident on the device; `e2e.value` is the same
+loop fed from pinned host memory every step and reading the loss back every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline_nccl", "ddp"])
+    ap.add_argument("--model", default="vgg16", choices=["vgg16", "bert_large", "resnet50", "mlp"])
+    ap.add_argument("--algorithm", default=None,
+                    choices=[None, "gradient_allreduce", "bytegrad", "decentralized", "decentralized_shift_one",
+                             "low_precision_decentralized", "qadam", "async"])
+    ap.add_argument("--batch", type=int, default=None, help="per-GPU batch size")
+    ap.add_argument("--bucket-mb", type=float, default=None)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+CONFIGS = {
+    # model: (default algorithm, per-GPU batch, bucket MB, seq_len)
+    "vgg16": ("gradient_allreduce", 32, 10, None),
+    "bert_large": ("bytegrad", 8, 25, 384),
+    "resnet50": ("decentralized_shift_one", 128, 10, None),
+    "mlp": ("gradient_allreduce", 64, 1, None),
+}
+
+
+def reference_arm(args):
+    why = ("reference cannot be installed offline: pip metadata step fails with ModuleNotFoundError "
+           "setuptools_rust; no cargo/rustc/mpicxx on the image, Aluminum submodule empty, installer downloads NCCL")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def build_model(name, device):
+    import torch
+
+    from bagua_core_b200 import models
+
+    if name == "vgg16":
+        m = models.VGG16().to(device).to(memory_format=torch.channels_last)
+    elif name == "resnet50":
+        m = models.ResNet50().to(device).to(memory_format=torch.channels_last)
+    elif name == "bert_large":
+        m = models.BertForQuestionAnswering(models.BertConfig.large()).to(device)
+    else:
+        m = models.MLP(1024, 4096, 1000, depth=4).to(device)
+    return m
+
+
+def make_batch(name, batch, seq, device, pinned=False):
+    """Synthetic data of the benchmark's shape.  pinned=True → host tensors in pinned memory."""
+    import torch
+
+    g = torch.Generator().manual_seed(1 + int(os.environ.get("RANK", "0")))
+    if name in ("vgg16", "resnet50"):
+        x = torch.randn(batch, 3, 224, 224, generator=g)
+        y = torch.randint(0, 1000, (batch,), generator=g)
+    elif name == "bert_large":
+        x = torch.randint(0, 30522, (batch, seq), generator=g)
+        y = torch.randint(0, seq, (batch, 2), generator=g)
+    else:
+        x = torch.randn(batch, 1024, generator=g)
+        y = torch.randint(0, 1000, (batch,), generator=g)
+    if pinned:
+        return x.pin_memory(), y.pin_memory()
+    x = x.to(device)
+    if x.dim() == 4:
+        x = x.contiguous(memory_format=torch.channels_last)
+    return x, y.to(device)
+
+
+def loss_fn(name, model, x, y):
+    import torch
+    import torch.nn.functional as F
+
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        if name == "bert_large":
+            return model(x, y[:, 0], y[:, 1])
+        out = model(x)
+    return F.cross_entropy(out.float(), y)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    import bagua_core_b200 as bb
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.utils import ClockSampler
+
+    algo_name, batch, bucket_mb, seq = CONFIGS[args.model]
+    algo_name = args.algorithm or algo_name
+    batch = args.batch or batch
+    bucket_mb = args.bucket_mb or bucket_mb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    torch.backends.cudnn.benchmark = True
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
+    torch.manual_seed(0)
+
+    if args.impl == "baseline_nccl":
+        os.environ["BAGUA_B200_FUSED"] = "0"
+        bb._C.set_sync_per_bucket(True)
+
+    model = build_model(args.model, device)
+    n_params = sum(p.numel() for p in model.parameters())
+    lr = 0.01 if args.model != "bert_large" else 1e-4
+    my_kernels = lambda: 0  # noqa: E731
+
+    if args.impl == "ddp":
+        if not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29500")
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+        opt = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9)
+        fwd = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
+                                                        bucket_cap_mb=bucket_mb, gradient_as_bucket_view=True)
+        zero = lambda: opt.zero_grad(set_to_none=False)  # noqa: E731
+    else:
+        pg = P.init_process_group(device)
+        if algo_name == "qadam":
+            opt = P.QAdamOptimizer(model.parameters(), lr=1e-4, warmup_steps=2)
+            algo = P.QAdamAlgorithm(opt)
+        else:
+            opt = P.FlatSGD(model.parameters(), lr=lr, momentum=0.9)
+            algo = {
+                "gradient_allreduce": lambda: P.GradientAllReduceAlgorithm(),
+                "bytegrad": lambda: P.ByteGradAlgorithm(),
+                "decentralized": lambda: P.DecentralizedAlgorithm(peer_selection_mode="all"),
+                "decentralized_shift_one": lambda: P.DecentralizedAlgorithm(
+                    peer_selection_mode="shift_one" if world % 2 == 0 else "all"),
+                "low_precision_decentralized": lambda: P.LowPrecisionDecentralizedAlgorithm(),
+                "async": lambda: P.AsyncModelAverageAlgorithm(sync_interval_ms=50),
+            }[algo_name]()
+        fwd = P.with_bagua(model, [opt], algo, bucket_bytes=int(bucket_mb * 1024 * 1024))
+        zero = lambda: opt.zero_grad(set_to_none=False)  # noqa: E731
+
+        def my_kernels():
+            s = bb._C.stats()
+            return int(s["fused_launches"]) + int(getattr(opt, "kernel_launches", 0))
+
+    def step(x, y):
+        zero()
+        loss = loss_fn(args.model, fwd, x, y)
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed loop, inputs resident on the device -----------------------------
+    x, y = make_batch(args.model, batch, seq, device)
+    for _ in range(max(args.warmup, 3)):
+        step(x, y)
+    barrier()
+    k0 = my_kernels()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step(x, y)
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    launches = my_kernels() - k0
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = world * batch * args.steps / (ms / 1e3)
+
+    # ---- end to end: pinned host inputs in, loss out, every step -----------------------
+    e2e = None
+    if not args.no_e2e:
+        hx, hy = make_batch(args.model, batch, seq, device, pinned=True)
+        h2d = hx.numel() * hx.element_size() + hy.numel() * hy.element_size()
+
+        def e2e_step():
+            dx = hx.to(device, non_blocking=True)
+            if dx.dim() == 4:
+                dx = dx.contiguous(memory_format=torch.channels_last)
+            dy = hy.to(device, non_blocking=True)
+            return float(step(dx, dy).item())  # 4-byte device→host read of the loss
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0.record()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            last = e2e_step()
+        e1.record()
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        ems = max(e0.elapsed_time(e1), wall_ms)  # the host read makes both agree; keep the slower
+        t = torch.tensor([ems], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ems = float(t.item())
+        e2e = {"value": world * batch * args.steps / (ems / 1e3), "unit": "samples/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4, "ms_per_step": ems / args.steps,
+               "last_loss": last}
+
+    if rank == 0:
+        line = {
+            "metric": f"{args.model} training throughput ({algo_name})",
+            "value": value,
+            "unit": "samples/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic (N(0,1) inputs, uniform labels), random-init weights",
+            "impl": args.impl,
+            "config": {
+                "model": args.model, "params": n_params, "global_batch": world * batch, "seq_len": seq,
+                "parallelism": f"dp{world}", "algorithm": algo_name, "bucket_mb": bucket_mb,
+                "optimizer": "sgd momentum 0.9" if algo_name != "qadam" else "qadam",
+                "precision": "bf16 autocast, fp32 master weights and gradients",
+                "l2": "working set per step (fp32 weights+grads+momentum and activations) exceeds the 126 MB L2",
+            },
+            "clocks": clocks.summary(),
+            "e2e": e2e,
+            "gpu_launches": launches,
+        }
+        print(json.dumps(line))
+    if args.impl != "ddp":
+        P.destroy_process_group()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,162 @@
+"""Single-GPU numerics of the sm_100a tensor kernels against plain PyTorch fp32 references
+(and against the engine's own host implementation, which defines the MinMaxUInt8 grid)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 31, 32, 33, 1023, 4096, (1 << 20) + 1, 3 << 20]
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def _tol(dt):
+    return {torch.float32: 1e-6, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dt]
+
+
+def _rand(n, dt, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(n, generator=g).to(dt).cuda()
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("dt", DTYPES)
+def test_elementwise(n, dt):
+    import bagua_core_b200.ops as ops
+
+    x, y = _rand(n, dt, 1), _rand(n, dt, 2)
+    xf, yf = x.float(), y.float()
+    cases = [
+        (lambda a: ops.add_inplace(a, y), xf + yf),
+        (lambda a: ops.subtract_inplace(a, y), xf - yf),
+        (lambda a: ops.addmul_inplace(a, y, -5.0 / 3.0), xf + yf * (-5.0 / 3.0)),
+        (lambda a: ops.average_inplace(a, y), (xf + yf) / 2),
+        (lambda a: ops.divide_inplace(a, 7.0), xf / 7.0),
+    ]
+    for fn, ref in cases:
+        a = x.clone()
+        fn(a)
+        torch.cuda.synchronize()
+        assert torch.allclose(a.float(), ref, rtol=_tol(dt), atol=_tol(dt)), (n, dt)
+
+
+@pytest.mark.parametrize("offset", [0, 1, 3])
+def test_elementwise_unaligned_views(offset):
+    import bagua_core_b200.ops as ops
+
+    base = _rand(5000 + offset, torch.float32, 3)
+    x = base[offset:]
+    y = _rand(5000, torch.float32, 4)
+    ref = x.clone() + y
+    ops.add_inplace(x, y)
+    torch.cuda.synchronize()
+    assert torch.allclose(x, ref, atol=1e-6)
+
+
+@pytest.mark.parametrize("n_chunks,chunk", [(2, 48), (8, 4096), (3, 1000), (8, (1 << 18))])
+@pytest.mark.parametrize("dt", DTYPES)
+def test_reduce_chunk(n_chunks, chunk, dt):
+    import bagua_core_b200.ops as ops
+
+    x = _rand(n_chunks * chunk, dt, 5)
+    for avg in (True, False):
+        a = x.clone()
+        ops.reduce_chunk_inplace(a, n_chunks, n_chunks - 1, average=avg)
+        torch.cuda.synchronize()
+        ref = x.float().view(n_chunks, chunk).sum(0)
+        if avg:
+            ref = ref / n_chunks
+        got = a.view(n_chunks, chunk)[n_chunks - 1].float()
+        assert torch.allclose(got, ref, rtol=_tol(dt) * 4, atol=_tol(dt) * 4)
+        # other chunks untouched
+        assert torch.equal(a.view(n_chunks, chunk)[: n_chunks - 1], x.view(n_chunks, chunk)[: n_chunks - 1])
+
+
+def test_async_model_average():
+    import bagua_core_b200.ops as ops
+
+    for n in (5, 4096, (1 << 20) + 3):
+        t, r, c = _rand(n, torch.float32, 6), _rand(n, torch.float32, 7), _rand(n, torch.float32, 8)
+        ref = t + (r / 4.0 - c)
+        ops.async_model_average(t, r, c, 4)
+        torch.cuda.synchronize()
+        assert torch.allclose(t, ref, atol=1e-5)
+
+
+@pytest.mark.parametrize("n_chunks,chunk", [(1, 16), (1, 1000), (2, 48), (8, 4096), (4, 1 << 19), (3, 37)])
+@pytest.mark.parametrize("dt", DTYPES)
+def test_minmax_uint8_matches_host_and_bound(n_chunks, chunk, dt):
+    import bagua_core as bc
+
+    x = _rand(n_chunks * chunk, dt, 9)
+    gpu_c = bc.BaguaTensorPy(x, "x").compress("MinMaxUInt8", n_chunks, -1)
+    cpu_c = bc.BaguaTensorPy(x.cpu(), "x").compress("MinMaxUInt8", n_chunks, -1)
+    g, c = gpu_c.to_numpy_u8(), cpu_c.to_numpy_u8()
+    total = g.shape[0]
+    off = total // n_chunks
+    for i in range(n_chunks):
+        # headers (min/max in the tensor dtype) and payloads agree with the host oracle
+        esz = x.element_size()
+        assert (g[i * off:i * off + 2 * esz] == c[i * off:i * off + 2 * esz]).all()
+        pg, pc = g[i * off + 32:i * off + 32 + chunk], c[i * off + 32:i * off + 32 + chunk]
+        # rounding of x*scale at exact .5 ties may differ by one level between FMA and non-FMA paths
+        assert (abs(pg.astype(int) - pc.astype(int)) <= 1).all()
+        assert (pg != pc).mean() < 0.01
+    out = torch.empty_like(x)
+    bc.BaguaTensorPy(out, "o").decompress_from("MinMaxUInt8", n_chunks, gpu_c)
+    torch.cuda.synchronize()
+    xf, of = x.float().view(n_chunks, chunk), out.float().view(n_chunks, chunk)
+    rng = (xf.max(1).values - xf.min(1).values)
+    err = (xf - of).abs().max(1).values
+    slack = {torch.float32: 0.0, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dt] * xf.abs().max()
+    assert (err <= rng / 255 * 0.51 + slack + 1e-6).all(), (err, rng / 255)
+
+
+def test_minmax_uint8_target_chunk_only():
+    import bagua_core as bc
+
+    n_chunks, chunk = 4, 4096
+    x = _rand(n_chunks * chunk, torch.float32, 10)
+    full = bc.BaguaTensorPy(x, "x").compress("MinMaxUInt8", n_chunks, -1).to_numpy_u8()
+    one = bc.BaguaTensorPy(x, "x").compress("MinMaxUInt8", n_chunks, 2).to_numpy_u8()
+    off = full.shape[0] // n_chunks
+    assert (full[2 * off:3 * off] == one[2 * off:3 * off]).all()
+
+
+def test_sgd_flat_matches_torch():
+    import bagua_core_b200.ops as ops
+
+    n = (1 << 20) + 5
+    p, g = _rand(n, torch.float32, 11), _rand(n, torch.float32, 12)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.SGD([ref_p], lr=0.1, momentum=0.9, weight_decay=1e-4, nesterov=True)
+    buf = torch.zeros_like(p)
+    for step in range(3):
+        ref_p.grad = g.clone()
+        opt.step()
+        ops.sgd_momentum_flat(p, g, buf, 0.1, 0.9, 0.0, 1e-4, True, first_step=(step == 0))
+    torch.cuda.synchronize()
+    assert torch.allclose(p, ref_p.detach(), atol=1e-5, rtol=1e-5)
+
+
+def test_device_wait_runs_out_and_reports():
+    """A wait that nothing will ever satisfy ends by itself with a status record; the
+    context stays usable."""
+    import bagua_core_b200 as bb
+
+    st = bb._C.debug_wait_timeout(0, 50.0)
+    assert st["code"] == 2 and st["peer"] == 1 and st["epoch"] == 1
+    x = torch.ones(16, device="cuda")
+    assert float((x * 2).sum()) == 32.0
+
+
+def test_pool_reuses_blocks():
+    import bagua_core as bc
+    import bagua_core_b200 as bb
+
+    x = _rand(1 << 16, torch.float32, 13)
+    bc.BaguaTensorPy(x, "x").compress("MinMaxUInt8", 1, -1)
+    a = bb._C.pool_stats(0)["device_allocs"]
+    for _ in range(5):
+        bc.BaguaTensorPy(x, "x").compress("MinMaxUInt8", 1, -1)
+    torch.cuda.synchronize()
+    assert bb._C.pool_stats(0)["device_allocs"] == a
