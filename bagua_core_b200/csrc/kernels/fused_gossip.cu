@@ -1,0 +1,184 @@
+// Fused low-precision ring gossip step (one cooperative sm_100a kernel per bucket).
+//
+// x: local weights after the optimizer step; w / l / r: this rank's replicas of its own,
+// its left and its right neighbour's weights.  The step computes
+//     d   = x + l/3 + r/3 - 5w/3
+//     c   = MinMaxUInt8(d)                       (one chunk, min/max over the whole bucket)
+//     send c to both neighbours, receive theirs  (direct peer stores into their staging)
+//     l  += Q⁻¹(c_left);  r += Q⁻¹(c_right);  x = w = w + Q⁻¹(c)
+// which is what the reference does with 3 addmul kernels, 2 CUB reductions, a compress
+// kernel, 4 grouped NCCL send/recv, 3 decompress kernels, 3 add kernels and a memcpy
+// (bagua-core-internal/src/comm_ops/decentralized_low_precision_synchronous.rs:23-154).
+// Intermediate values are rounded through the tensor dtype where the reference stores them.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cfloat>
+
+#include "fused.h"
+#include "minmax_device.cuh"
+#include "peer_sync.cuh"
+
+namespace bagua {
+namespace fused {
+
+namespace {
+
+using namespace kernels;
+constexpr int kThreads = 512;
+constexpr int kHdr = 32;
+
+template <typename T>
+__device__ __forceinline__ float rt(float x) {
+  return mmdev::to_f(mmdev::from_f<T>(x));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    lp_ring_kernel(const __grid_constant__ ArenaView v, T* __restrict__ x, T* __restrict__ w, T* __restrict__ l,
+                   T* __restrict__ r, int64_t n, size_t slot_bytes, size_t scratch_off) {
+  const int me = v.rank, N = v.nranks, G = gridDim.x, b = blockIdx.x;
+  const int left = (me + N - 1) % N, right = (me + 1) % N;
+  const uint32_t nb_mask = (1u << left) | (1u << right);
+  const int64_t groups = n / 16;
+  const int64_t lo = groups * b / G * 16, hi = groups * (b + 1) / G * 16;
+  uint8_t* stage = v.staging[me];
+  uint8_t* from_left = stage;                   // written by my left neighbour
+  uint8_t* from_right = stage + slot_bytes;     // written by my right neighbour
+  uint8_t* own = stage + 2 * slot_bytes;        // my own compressed difference
+  float2* part = reinterpret_cast<float2*>(stage + scratch_off);
+  const float third = 1.0f / 3.0f, m53 = -5.0f / 3.0f;
+
+  bool ok = psync::cta_wait_prev_done(v);
+
+  // ---- P1: d = x + l/3 + r/3 - 5w/3 (stored in x), partial min/max ----
+  float mn = FLT_MAX, mx = -FLT_MAX;
+  if (ok) {
+    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+      float fx[16], fl[16], fr[16], fw[16];
+      mmdev::load16(x + i, fx);
+      mmdev::load16(l + i, fl);
+      mmdev::load16(r + i, fr);
+      mmdev::load16(w + i, fw);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        float d = rt<T>(fmaf(fl[k], third, fx[k]));
+        d = rt<T>(fmaf(fr[k], third, d));
+        d = rt<T>(fmaf(fw[k], m53, d));
+        fx[k] = d;
+        mn = fminf(mn, d);
+        mx = fmaxf(mx, d);
+      }
+      mmdev::store16(x + i, fx);
+    }
+  }
+  mmdev::block_minmax<kThreads>(mn, mx);
+  if (threadIdx.x == 0) part[b] = make_float2(mn, mx);
+  ok = psync::grid_barrier(v, 0) && ok;
+
+  // ---- P2: quantise d, store to both neighbours and to my own slot ----
+  mmdev::Grid g_own;
+  if (ok) {
+    mn = FLT_MAX;
+    mx = -FLT_MAX;
+    for (int i = threadIdx.x; i < G; i += kThreads) {
+      const float2 p = part[i];
+      mn = fminf(mn, p.x);
+      mx = fmaxf(mx, p.y);
+    }
+    mmdev::block_minmax<kThreads>(mn, mx);
+    if (mn > mx) mn = mx = 0.f;
+    g_own = mmdev::make_grid(rt<T>(mn), rt<T>(mx));
+    uint8_t* to_left = v.staging[left] + slot_bytes;  // I am my left neighbour's right neighbour
+    uint8_t* to_right = v.staging[right];             // ... and my right neighbour's left neighbour
+    if (threadIdx.x == 0) {
+      mmdev::store_header<T>(to_left, mn, mx);
+      mmdev::store_header<T>(to_right, mn, mx);
+      mmdev::store_header<T>(own, mn, mx);
+    }
+    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+      float f[16];
+      mmdev::load16(x + i, f);
+      const uint4 packed = mmdev::pack_q16(f, g_own);
+      *reinterpret_cast<uint4*>(to_left + kHdr + i) = packed;
+      *reinterpret_cast<uint4*>(to_right + kHdr + i) = packed;
+      *reinterpret_cast<uint4*>(own + kHdr + i) = packed;
+    }
+    psync::cta_signal_phase(v, 0, nb_mask);
+    ok = psync::cta_wait_phase(v, 0, nb_mask);
+  }
+
+  // ---- P3: apply the three differences ----
+  if (ok) {
+    float a, c;
+    mmdev::load_header<T>(from_left, a, c);
+    const mmdev::Grid g_l = mmdev::make_grid(a, c);
+    mmdev::load_header<T>(from_right, a, c);
+    const mmdev::Grid g_r = mmdev::make_grid(a, c);
+    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+      float d[16], cur[16];
+      mmdev::load_dq16(from_left + kHdr + i, d, g_l);
+      mmdev::load16(l + i, cur);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) cur[k] = cur[k] + rt<T>(d[k]);
+      mmdev::store16(l + i, cur);
+      mmdev::load_dq16(from_right + kHdr + i, d, g_r);
+      mmdev::load16(r + i, cur);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) cur[k] = cur[k] + rt<T>(d[k]);
+      mmdev::store16(r + i, cur);
+      mmdev::load_dq16(own + kHdr + i, d, g_own);
+      mmdev::load16(w + i, cur);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) cur[k] = rt<T>(rt<T>(d[k]) + cur[k]);
+      mmdev::store16(x + i, cur);
+      mmdev::store16(w + i, cur);
+    }
+  }
+  psync::cta_finish_op(v);
+}
+
+template <typename T>
+bool lp_ring_t(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return true;
+  if (n % 16 != 0 || ((uintptr_t)x | (uintptr_t)w | (uintptr_t)l | (uintptr_t)r) % 16 != 0) return false;
+  const size_t slot = (size_t)n + kHdr;
+  int64_t g = (n + (32 << 10) - 1) / (32 << 10);
+  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, std::min(2 * arena.max_blocks(), kArenaMaxBlocks)));
+  static int coop_limit = 0;
+  if (coop_limit == 0) {
+    int per_sm = 0, sms = 0, dev = 0;
+    BAGUA_CUDA_CHECK(cudaGetDevice(&dev));
+    BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lp_ring_kernel<float>, kThreads, 0));
+    coop_limit = std::max(1, per_sm * sms);
+  }
+  grid = std::min(grid, coop_limit);
+  const size_t scratch_off = align_up(3 * slot, 256);
+  arena.ensure_staging(scratch_off + (size_t)grid * sizeof(float2));
+  ArenaView v = arena.next_view(grid, 1);
+  T *px = (T*)x, *pw = (T*)w, *pl = (T*)l, *pr = (T*)r;
+  int64_t n_arg = n;
+  size_t slot_arg = slot, scratch_arg = scratch_off;
+  void* args[] = {&v, &px, &pw, &pl, &pr, &n_arg, &slot_arg, &scratch_arg};
+  BAGUA_CUDA_CHECK(
+      cudaLaunchCooperativeKernel((const void*)lp_ring_kernel<T>, dim3(grid), dim3(kThreads), args, 0, stream));
+  arena.count_launch();
+  return true;
+}
+
+}  // namespace
+
+bool lp_ring(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, DType dt, cudaStream_t stream) {
+  if (arena.nranks() < 2) return false;
+  switch (dt) {
+    case DType::F32: return lp_ring_t<float>(arena, x, w, l, r, n, stream);
+    case DType::F16: return lp_ring_t<__half>(arena, x, w, l, r, n, stream);
+    case DType::BF16: return lp_ring_t<__nv_bfloat16>(arena, x, w, l, r, n, stream);
+    default: return false;
+  }
+}
+
+}  // namespace fused
+}  // namespace bagua

@@ -48,6 +48,36 @@ __device__ __forceinline__ uint8_t quantise(float x, const Grid& g) {
 }
 __device__ __forceinline__ float dequantise(uint8_t q, const Grid& g) { return ((float)q + g.lower) / g.scale; }
 
+// ---- chunk headers: {min, max} in the tensor dtype at the start of a compressed chunk.
+// A chunk may start at any byte offset when chunk sizes are not multiples of 32 (the
+// layout divides the buffer evenly), so unaligned headers go through byte copies.
+template <typename T>
+__device__ __forceinline__ void store_header(uint8_t* base, float mn, float mx) {
+  T h[2] = {from_f<T>(mn), from_f<T>(mx)};
+  if ((reinterpret_cast<uintptr_t>(base) % sizeof(T)) == 0) {
+    reinterpret_cast<T*>(base)[0] = h[0];
+    reinterpret_cast<T*>(base)[1] = h[1];
+  } else {
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(h);
+#pragma unroll
+    for (int i = 0; i < (int)(2 * sizeof(T)); ++i) base[i] = src[i];
+  }
+}
+template <typename T>
+__device__ __forceinline__ void load_header(const uint8_t* base, float& mn, float& mx) {
+  T h[2];
+  if ((reinterpret_cast<uintptr_t>(base) % sizeof(T)) == 0) {
+    h[0] = reinterpret_cast<const T*>(base)[0];
+    h[1] = reinterpret_cast<const T*>(base)[1];
+  } else {
+    uint8_t* dst = reinterpret_cast<uint8_t*>(h);
+#pragma unroll
+    for (int i = 0; i < (int)(2 * sizeof(T)); ++i) dst[i] = base[i];
+  }
+  mn = to_f(h[0]);
+  mx = to_f(h[1]);
+}
+
 // ---- 16-element groups (p must be 16-byte aligned) --------------------------------
 __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
   const float4* q = reinterpret_cast<const float4*>(p);

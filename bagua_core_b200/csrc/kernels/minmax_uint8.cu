@@ -103,10 +103,7 @@ __global__ void __launch_bounds__(kThreads)
   // round through the storage dtype so both sides build the same grid
   const float mn_r = mmdev::to_f(mmdev::from_f<T>(mn));
   const float mx_r = mmdev::to_f(mmdev::from_f<T>(mx));
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    reinterpret_cast<T*>(base)[0] = mmdev::from_f<T>(mn);
-    reinterpret_cast<T*>(base)[1] = mmdev::from_f<T>(mx);
-  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) mmdev::store_header<T>(base, mn, mx);
   const mmdev::Grid g = mmdev::make_grid(mn_r, mx_r);
   int64_t lo, hi;
   block_slice(chunk, blockIdx.x, gridDim.x, lo, hi);
@@ -129,8 +126,8 @@ __global__ void __launch_bounds__(kThreads)
                       bool vec) {
   const int c = blockIdx.y;
   const uint8_t* base = in + (size_t)c * chunk_offset;
-  const float mn = mmdev::to_f(reinterpret_cast<const T*>(base)[0]);
-  const float mx = mmdev::to_f(reinterpret_cast<const T*>(base)[1]);
+  float mn, mx;
+  mmdev::load_header<T>(base, mn, mx);
   const mmdev::Grid g = mmdev::make_grid(mn, mx);
   int64_t lo, hi;
   block_slice(chunk, blockIdx.x, gridDim.x, lo, hi);

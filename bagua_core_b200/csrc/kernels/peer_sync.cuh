@@ -49,7 +49,7 @@ __device__ __forceinline__ uint32_t* phase_word(uint32_t* pad, int phase, int sr
   return pad + kSigPhase + (phase * kArenaMaxRanks + src) * kArenaMaxBlocks + block;
 }
 
-__device__ __noinline__ void record_timeout(const ArenaView& v, uint32_t code, uint32_t phase, uint32_t peer,
+static __device__ __noinline__ void record_timeout(const ArenaView& v, uint32_t code, uint32_t phase, uint32_t peer,
                                             uint32_t seen) {
   DeviceStatus* s = v.status;
   if (s) {

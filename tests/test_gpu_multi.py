@@ -1,0 +1,294 @@
+"""Multi-GPU tests (one process per GPU, NCCL bootstrap): the fused peer-memory kernels
+against the library path that replays the reference's call sequence, and against plain
+fp32 PyTorch math."""
+import os
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _world():
+    return min(torch.cuda.device_count(), int(os.environ.get("BAGUA_TEST_WORLD", "8")))
+
+
+def _mk_comm(rank, world, stream):
+    import torch.distributed as dist
+
+    import bagua_core as bc
+
+    uid = [bc.BaguaSingleCommunicatorPy.generate_nccl_unique_id_str() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    return bc.BaguaSingleCommunicatorPy(rank, world, rank, stream.cuda_stream, uid[0])
+
+
+def _gather_all(t):
+    import torch.distributed as dist
+
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t)
+    return out
+
+
+def _fused_allreduce(rank, world):
+    import bagua_core as bc
+
+    dev = torch.device("cuda", rank)
+    stream = torch.cuda.Stream()
+    comm = _mk_comm(rank, world, stream)
+    assert comm.fused_available(), "peer arena must come up on an NVLink box"
+    comm.set_device_wait_ms(20000.0)
+    report = []
+    sizes = [16, 4096, 65536 + 16, 1 << 20, (3 << 20) + 4096, 1 << 24]
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        for n in sizes:
+            n = n // (8 if dt != torch.float32 else 4) * (8 if dt != torch.float32 else 4)
+            g = torch.Generator().manual_seed(100 * rank + n % 97)
+            x = torch.randn(n, generator=g).to(dt).to(dev)
+            allx = _gather_all(x)
+            ref_sum = torch.stack([a.float() for a in allx]).sum(0)
+            # out of place, average
+            out = torch.zeros_like(x)
+            torch.cuda.synchronize()
+            assert comm.fused_allreduce(bc.BaguaTensorPy(x, "s"), bc.BaguaTensorPy(out, "r"), True)
+            stream.synchronize()
+            comm.check_device_status()
+            tol = {torch.float32: 1e-6, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dt]
+            ref = ref_sum / world
+            assert torch.allclose(out.float(), ref, rtol=tol, atol=tol * max(1.0, ref.abs().max().item())), (dt, n)
+            # every rank holds the same bits
+            outs = _gather_all(out)
+            assert all(torch.equal(outs[0], o) for o in outs)
+            # in place, sum
+            y = x.clone()
+            torch.cuda.synchronize()
+            bt = bc.BaguaTensorPy(y, "y")
+            assert comm.fused_allreduce(bt, bt, False)
+            stream.synchronize()
+            assert torch.allclose(y.float(), ref_sum, rtol=tol, atol=tol * max(1.0, ref_sum.abs().max().item()))
+            report.append((str(dt), n))
+    # back-to-back ops of different sizes without host sync in between (staging reuse protocol)
+    xs = [torch.full((s,), float(rank + 1), device=dev) for s in (1 << 12, 1 << 22, 1 << 14, 1 << 21, 64)]
+    torch.cuda.synchronize()
+    for _ in range(5):
+        for x in xs:
+            bt = bc.BaguaTensorPy(x, "x")
+            assert comm.fused_allreduce(bt, bt, True)
+    stream.synchronize()
+    comm.check_device_status()
+    expect = sum(range(1, world + 1)) / world
+    for x in xs:
+        assert torch.allclose(x, torch.full_like(x, expect)), x[:4]
+    return len(report), comm.fused_launches()
+
+
+def test_fused_allreduce_matches_fp32_sum():
+    world = _world()
+    res = run_ranks(_fused_allreduce, world, backend="nccl", timeout=600)
+    assert all(r[0] == 18 for r in res)
+    assert all(r[1] > 0 for r in res)
+
+
+def _bucket_ops(rank, world):
+    """Each op: fused path vs library path on identical inputs."""
+    import bagua_core as bc
+    import bagua_core_b200 as bb
+
+    dev = torch.device("cuda", rank)
+    stream = torch.cuda.Stream()
+    comm = _mk_comm(rank, world, stream)
+    assert comm.fused_available()
+    comm.set_device_wait_ms(20000.0)
+    backend = bc.BaguaCommBackendPy(10, rank)
+    results = {}
+
+    def run(bucket, tensors):
+        backend.register_ordered_buckets([bucket])
+        events = []
+        for t in tensors:
+            ev = torch.cuda.Event()
+            ev.record()
+            events.append(ev)
+            backend.mark_communication_ready(t, ev.cuda_event)
+        backend.wait_pending_comm_ops()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        comm.check_device_status()
+
+    n = 16 * world * 4099  # odd multiple: exercises uneven block slices
+    for dt in (torch.float32, torch.float16):
+        g = torch.Generator().manual_seed(7 + rank)
+        base = torch.randn(n, generator=g).to(dt).to(dev)
+        allb = _gather_all(base)
+        mean = torch.stack([a.float() for a in allb]).mean(0)
+        tol = 1e-6 if dt == torch.float32 else 2e-3
+
+        # O1
+        outs = {}
+        for fused in (True, False):
+            comm.set_fused(fused)
+            x = base.clone()
+            bt = bc.BaguaTensorPy(x, "g")
+            b = bc.BaguaBucketPy("o1", [bt])
+            b.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True, scattergather=not fused)
+            run(b, [bt])
+            outs[fused] = x
+            assert torch.allclose(x.float(), mean, rtol=tol, atol=tol * 4), ("o1", dt, fused)
+        # O2 ByteGrad
+        for fused in (True, False):
+            comm.set_fused(fused)
+            x = base.clone()
+            bt = bc.BaguaTensorPy(x, "g")
+            b = bc.BaguaBucketPy("o2", [bt])
+            b.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True, scattergather=True,
+                                                compression="MinMaxUInt8")
+            run(b, [bt])
+            outs[("bg", fused)] = x
+            chunk = n // world
+            for c in range(world):
+                sl = slice(c * chunk, (c + 1) * chunk)
+                rng = max((a[sl].float().max() - a[sl].float().min()).item() for a in allb)
+                err = (x[sl].float() - mean[sl]).abs().max().item()
+                assert err <= 2 * rng / 255 + tol * 8, ("o2", dt, fused, c, err, rng)
+            same = _gather_all(x)
+            assert all(torch.equal(same[0], s) for s in same), "ranks disagree after ByteGrad"
+        # fused and library ByteGrad quantise the same grid: results agree up to rounding ties
+        d = (outs[("bg", True)].float() - outs[("bg", False)].float()).abs()
+        rng_all = (mean.max() - mean.min()).item()
+        assert d.max().item() <= 2.1 * rng_all / 255 and (d > 1e-3 * rng_all).float().mean().item() < 0.02
+
+        # O3 shift_one, 3 steps
+        if world % 2 == 0:
+            for fused in (True, False):
+                comm.set_fused(fused)
+                x = base.clone()
+                peer = torch.zeros_like(x)
+                bt = bc.BaguaTensorPy(x, "w")
+                b = bc.BaguaBucketPy("o3", [bt])
+                b.append_decentralized_synchronous_op(comm, None, hierarchical=False,
+                                                      peer_selection_mode="shift_one",
+                                                      peer_weight=bc.BaguaTensorPy(peer, "p"))
+                cur = [a.float() for a in allb]
+                for step in range(3):
+                    run(b, [bt])
+                    p = bb._C.shift_one_peer(rank, world, step)
+                    exp = (cur[rank] + cur[p]) / 2
+                    assert torch.allclose(peer.float(), exp, rtol=tol, atol=tol * 4), ("o3", dt, fused, step)
+                    cur = [(cur[r] + cur[bb._C.shift_one_peer(r, world, step)]) / 2 for r in range(world)]
+                    if dt != torch.float32:
+                        cur = [c.to(dt).float() for c in cur]
+                    x.copy_(peer)
+        # O3 all
+        comm.set_fused(True)
+        x = base.clone()
+        peer = torch.zeros_like(x)
+        bt = bc.BaguaTensorPy(x, "w")
+        b = bc.BaguaBucketPy("o3a", [bt])
+        b.append_decentralized_synchronous_op(comm, None, hierarchical=False, peer_selection_mode="all",
+                                              peer_weight=bc.BaguaTensorPy(peer, "p"))
+        run(b, [bt])
+        assert torch.allclose(peer.float(), mean, rtol=tol, atol=tol * 4)
+        assert torch.equal(x, base)
+
+        # O4 low-precision ring: fused vs library, two steps
+        lp = {}
+        for fused in (True, False):
+            comm.set_fused(fused)
+            x = base.clone()
+            w = allb[rank].clone()
+            left = allb[(rank - 1) % world].clone()
+            right = allb[(rank + 1) % world].clone()
+            bt = bc.BaguaTensorPy(x, "x")
+            b = bc.BaguaBucketPy("o4", [bt])
+            b.append_low_precision_decentralized_synchronous_op(
+                comm, None, hierarchical=False, peer_selection_mode="ring", compression="MinMaxUInt8",
+                weight=bc.BaguaTensorPy(w, "w"), left_peer_weight=bc.BaguaTensorPy(left, "l"),
+                right_peer_weight=bc.BaguaTensorPy(right, "r"))
+            for step in range(2):
+                x.add_(0.01)
+                run(b, [bt])
+            assert torch.equal(x, w)
+            ws = _gather_all(w)
+            atol = 1e-5 if dt == torch.float32 else 2e-2
+            assert torch.allclose(left.float(), ws[(rank - 1) % world].float(), atol=atol)
+            assert torch.allclose(right.float(), ws[(rank + 1) % world].float(), atol=atol)
+            lp[fused] = x.clone()
+        dd = (lp[True].float() - lp[False].float()).abs().max().item()
+        assert dd <= 0.05, dd
+
+    # O5 async (fp32 only)
+    comm.set_fused(True)
+    x = torch.full((1 << 16,), float(rank), device=dev)
+    bt = bc.BaguaTensorPy(x, "x")
+    b = bc.BaguaBucketPy("o5", [bt])
+    b.append_decentralized_asynchronous_op(comm, None, peer_selection_mode="all",
+                                           torch_stream=torch.cuda.current_stream().cuda_stream)
+    run(b, [bt])
+    assert torch.allclose(x, torch.full_like(x, (world - 1) / 2))
+    stats = bb._C.stats()
+    backend.close()
+    return stats["fused_launches"], stats["library_fallbacks"]
+
+
+def test_bucket_ops_fused_vs_library():
+    world = _world()
+    res = run_ranks(_bucket_ops, world, backend="nccl", timeout=900)
+    for fused, fallbacks in res:
+        assert fused >= 10
+        assert fallbacks == 0
+
+
+def _train(rank, world, algo_name):
+    import bagua_core_b200 as bb
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import MLP
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(3)
+    model = MLP(64, 256, 10, depth=3).to(dev)
+    pg = P.init_process_group(dev)
+    opt = P.FlatSGD(model.parameters(), lr=0.05, momentum=0.9)
+    algo = {"allreduce": P.GradientAllReduceAlgorithm, "bytegrad": P.ByteGradAlgorithm}[algo_name]()
+    bm = P.with_bagua(model, [opt], algo, bucket_bytes=64 * 1024)
+    g = torch.Generator().manual_seed(11)
+    xs = torch.randn(6, world * 16, 64, generator=g)
+    ys = torch.randn(6, world * 16, 10, generator=g)
+    for s in range(6):
+        x = xs[s, rank * 16:(rank + 1) * 16].to(dev)
+        y = ys[s, rank * 16:(rank + 1) * 16].to(dev)
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(bm(x), y).backward()
+        opt.step()
+    torch.cuda.synchronize()
+    pg.global_comm.check_device_status()
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu()
+    fused = bb._C.stats()["fused_launches"]
+    P.destroy_process_group()
+    return flat, fused
+
+
+@pytest.mark.parametrize("algo", ["allreduce", "bytegrad"])
+def test_with_bagua_training_multi_gpu(algo):
+    from bagua_core_b200.models import MLP
+
+    world = _world()
+    res = run_ranks(_train, world, backend="nccl", args=(algo,), timeout=600)
+    torch.manual_seed(3)
+    model = MLP(64, 256, 10, depth=3)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05, momentum=0.9)
+    g = torch.Generator().manual_seed(11)
+    xs = torch.randn(6, world * 16, 64, generator=g)
+    ys = torch.randn(6, world * 16, 10, generator=g)
+    for s in range(6):
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(model(xs[s]), ys[s]).backward()
+        opt.step()
+    ref = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    for flat, fused in res:
+        assert fused > 0, "training must run on the fused kernels"
+        assert torch.equal(flat, res[0][0])
+        tol = 2e-4 if algo == "allreduce" else 5e-2
+        assert (flat - ref).abs().max().item() < tol

@@ -30,9 +30,11 @@ def test_scheduler_with_cuda_events_single_rank():
                                              compression="MinMaxUInt8")
     backend.register_ordered_buckets([bucket])
     orig = flat.clone()
+    events = []  # the engine borrows the handles: keep the events alive until the wait returns
     for t in ts:
         ev = torch.cuda.Event()
         ev.record()
+        events.append(ev)
         backend.mark_communication_ready(t, ev.cuda_event)
     assert backend.wait_pending_comm_ops() == 1
     torch.cuda.current_stream().wait_stream(stream)
