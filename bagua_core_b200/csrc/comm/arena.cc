@@ -19,7 +19,8 @@ PeerArena::PeerArena(Transport& transport, int rank, int nranks, int device, cud
   BAGUA_CHECK(nranks <= kArenaMaxRanks, Communicator,
               "the peer arena supports at most " << kArenaMaxRanks << " ranks, got " << nranks);
   deadline_ns_ = (uint64_t)(env_double("BAGUA_B200_DEVICE_WAIT_MS", 120000.0) * 1e6);
-  max_blocks_ = (int)std::min<long>(std::max<long>(env_long("BAGUA_B200_COMM_CTAS", 32), 1), kArenaMaxBlocks);
+  max_blocks_ = (int)std::min<long>(std::max<long>(env_long("BAGUA_B200_COMM_CTAS", 64), 1), kArenaMaxBlocks);
+  max_coop_blocks_ = (int)std::min<long>(std::max<long>(env_long("BAGUA_B200_COOP_CTAS", 148), 1), kArenaMaxBlocks);
   BAGUA_CUDA_CHECK(cudaSetDevice(device));
   // every peer must be reachable with peer access
   int ndev = 0;

@@ -32,7 +32,7 @@
 namespace bagua {
 
 constexpr int kArenaMaxRanks = 8;
-constexpr int kArenaMaxBlocks = 128;
+constexpr int kArenaMaxBlocks = 160;
 constexpr int kArenaPhases = 2;
 
 // Word offsets inside a rank's signal pad.
@@ -80,8 +80,11 @@ class PeerArena {
   // `grid_barriers` = in-kernel grid barriers it executes.
   ArenaView next_view(int grid, int grid_barriers);
 
-  // Max CTAs per fused kernel (BAGUA_B200_COMM_CTAS, default 32, at most kArenaMaxBlocks).
+  // Max CTAs per fused kernel (BAGUA_B200_COMM_CTAS, default 64, at most kArenaMaxBlocks).
   int max_blocks() const { return max_blocks_; }
+  // Max CTAs of the cooperative kernels (ByteGrad, low-precision ring), which do several
+  // HBM passes and quantiser math per element (BAGUA_B200_COOP_CTAS, default 148 = one per SM).
+  int max_coop_blocks() const { return max_coop_blocks_; }
   void set_deadline_ms(double ms) { deadline_ns_ = (uint64_t)(ms * 1e6); }
   double deadline_ms() const { return (double)deadline_ns_ / 1e6; }
 
@@ -111,6 +114,7 @@ class PeerArena {
   uint64_t grid_bar_ = 0;
   uint64_t deadline_ns_;
   int max_blocks_;
+  int max_coop_blocks_;
   uint64_t launches_ = 0;
 };
 

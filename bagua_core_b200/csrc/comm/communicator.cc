@@ -68,7 +68,7 @@ void SingleCommunicator::check_device_status() {
   std::ostringstream o;
   static const char* what[] = {"", "wait for a peer to finish its previous op", "wait for a peer's data signal",
                                "grid barrier"};
-  o << "a device-side " << (s.code < 4 ? what[s.code] : "wait") << " ran out after " << arena_->deadline_ms()
+  o << "a device-side " << (s.code < 4 ? what[s.code] : "wait") << " ran out after " << fmt_double(arena_->deadline_ms())
     << " ms (rank " << rank_ << ", peer " << s.peer << ", phase " << s.phase << ", block " << s.block << ", epoch "
     << s.epoch << ", last value seen " << s.seen << "); the communicator is now aborted";
   throw BaguaError(ErrorKind::Communicator, o.str());

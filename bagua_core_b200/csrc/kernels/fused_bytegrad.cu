@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(kThreads)
   float2* part2 = part1 + (size_t)N * G;                               // [G]
   const size_t ag_off = (size_t)N * slot_bytes;
   __shared__ mmdev::Grid s_grid[kArenaMaxRanks];
+  __shared__ float s_lut[kArenaMaxRanks * 256];  // dequantiser tables, one per source chunk
 
   bool ok = psync::cta_wait_prev_done(v);
 
@@ -132,6 +133,8 @@ __global__ void __launch_bounds__(kThreads)
   if (ok) {
     if (threadIdx.x < N) s_grid[threadIdx.x] = read_grid<T>(my_stage + (size_t)threadIdx.x * slot_bytes);
     __syncthreads();
+    for (int r = 0; r < N; ++r) mmdev::build_dequant_lut<T>(s_lut + r * 256, s_grid[r]);
+    __syncthreads();
     T* out = x + (int64_t)me * chunk;
     for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
       float acc[16];
@@ -139,9 +142,9 @@ __global__ void __launch_bounds__(kThreads)
       for (int k = 0; k < 16; ++k) acc[k] = 0.f;
       for (int r = 0; r < N; ++r) {
         float f[16];
-        mmdev::load_dq16(my_stage + (size_t)r * slot_bytes + kHdr + i, f, s_grid[r]);
+        mmdev::lut_dq16(my_stage + (size_t)r * slot_bytes + kHdr + i, f, s_lut + r * 256);
 #pragma unroll
-        for (int k = 0; k < 16; ++k) acc[k] += round_through<T>(f[k]);
+        for (int k = 0; k < 16; ++k) acc[k] += f[k];
       }
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
@@ -180,13 +183,14 @@ __global__ void __launch_bounds__(kThreads)
   if (ok) {
     if (threadIdx.x < N) s_grid[threadIdx.x] = read_grid<T>(my_stage + ag_off + (size_t)threadIdx.x * slot_bytes);
     __syncthreads();
+    for (int c = 0; c < N; ++c) mmdev::build_dequant_lut<T>(s_lut + c * 256, s_grid[c]);
+    __syncthreads();
     for (int c = 0; c < N; ++c) {
       const uint8_t* q = my_stage + ag_off + (size_t)c * slot_bytes + kHdr;
       T* out = x + (int64_t)c * chunk;
-      const mmdev::Grid g = s_grid[c];
       for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
         float f[16];
-        mmdev::load_dq16(q + i, f, g);
+        mmdev::lut_dq16(q + i, f, s_lut + c * 256);
         mmdev::store16(out + i, f);
       }
     }
@@ -205,7 +209,7 @@ bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStr
   // one CTA per 32 Ki elements of the bucket, within the arena's budget (compute heavier
   // than a plain copy, so it gets twice the CTA budget of the all-reduce)
   int64_t g = (n + (32 << 10) - 1) / (32 << 10);
-  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, std::min(2 * arena.max_blocks(), kArenaMaxBlocks)));
+  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, arena.max_coop_blocks()));
   static int coop_limit = 0;
   if (coop_limit == 0) {
     int per_sm = 0, sms = 0, dev = 0;

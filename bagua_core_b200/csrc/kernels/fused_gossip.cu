@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(kThreads)
   uint8_t* own = stage + 2 * slot_bytes;        // my own compressed difference
   float2* part = reinterpret_cast<float2*>(stage + scratch_off);
   const float third = 1.0f / 3.0f, m53 = -5.0f / 3.0f;
+  __shared__ float s_lut[3 * 256];  // dequantiser tables: left, right, own
 
   bool ok = psync::cta_wait_prev_done(v);
 
@@ -116,22 +117,26 @@ __global__ void __launch_bounds__(kThreads)
     const mmdev::Grid g_l = mmdev::make_grid(a, c);
     mmdev::load_header<T>(from_right, a, c);
     const mmdev::Grid g_r = mmdev::make_grid(a, c);
+    mmdev::build_dequant_lut<T>(s_lut, g_l);
+    mmdev::build_dequant_lut<T>(s_lut + 256, g_r);
+    mmdev::build_dequant_lut<T>(s_lut + 512, g_own);
+    __syncthreads();
     for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
       float d[16], cur[16];
-      mmdev::load_dq16(from_left + kHdr + i, d, g_l);
+      mmdev::lut_dq16(from_left + kHdr + i, d, s_lut);
       mmdev::load16(l + i, cur);
 #pragma unroll
-      for (int k = 0; k < 16; ++k) cur[k] = cur[k] + rt<T>(d[k]);
+      for (int k = 0; k < 16; ++k) cur[k] = cur[k] + d[k];
       mmdev::store16(l + i, cur);
-      mmdev::load_dq16(from_right + kHdr + i, d, g_r);
+      mmdev::lut_dq16(from_right + kHdr + i, d, s_lut + 256);
       mmdev::load16(r + i, cur);
 #pragma unroll
-      for (int k = 0; k < 16; ++k) cur[k] = cur[k] + rt<T>(d[k]);
+      for (int k = 0; k < 16; ++k) cur[k] = cur[k] + d[k];
       mmdev::store16(r + i, cur);
-      mmdev::load_dq16(own + kHdr + i, d, g_own);
+      mmdev::lut_dq16(own + kHdr + i, d, s_lut + 512);
       mmdev::load16(w + i, cur);
 #pragma unroll
-      for (int k = 0; k < 16; ++k) cur[k] = rt<T>(rt<T>(d[k]) + cur[k]);
+      for (int k = 0; k < 16; ++k) cur[k] = rt<T>(d[k] + cur[k]);
       mmdev::store16(x + i, cur);
       mmdev::store16(w + i, cur);
     }
@@ -145,7 +150,7 @@ bool lp_ring_t(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, 
   if (n % 16 != 0 || ((uintptr_t)x | (uintptr_t)w | (uintptr_t)l | (uintptr_t)r) % 16 != 0) return false;
   const size_t slot = (size_t)n + kHdr;
   int64_t g = (n + (32 << 10) - 1) / (32 << 10);
-  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, std::min(2 * arena.max_blocks(), kArenaMaxBlocks)));
+  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, arena.max_coop_blocks()));
   static int coop_limit = 0;
   if (coop_limit == 0) {
     int per_sm = 0, sms = 0, dev = 0;

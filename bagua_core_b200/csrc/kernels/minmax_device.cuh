@@ -170,6 +170,23 @@ __device__ __forceinline__ void load_dq16(const uint8_t* q, float (&v)[16], cons
   unpack_dq16(*reinterpret_cast<const uint4*>(q), v, g);
 }
 
+// A chunk's dequantiser only has 256 possible outputs: tabulate them once per block (with
+// the exact IEEE division, and the rounding through the tensor dtype that a store would
+// apply) and turn every element into one shared-memory lookup.  Caller syncs the block.
+template <typename T>
+__device__ __forceinline__ void build_dequant_lut(float* lut, const Grid& g) {
+  for (int q = threadIdx.x; q < 256; q += blockDim.x) lut[q] = to_f(from_f<T>(dequantise((uint8_t)q, g)));
+}
+__device__ __forceinline__ void lut_dq16(const uint8_t* q, float (&v)[16], const float* lut) {
+  const uint4 a = *reinterpret_cast<const uint4*>(q);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[4 * j + k] = lut[(w[j] >> (8 * k)) & 0xffu];
+  }
+}
+
 // Block-wide min/max; the result is valid in every thread.
 template <int kThreads>
 __device__ __forceinline__ void block_minmax(float& mn, float& mx) {

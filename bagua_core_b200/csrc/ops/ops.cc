@@ -357,7 +357,7 @@ class DecentralizedFullPrecisionAsynchronous : public CommOp {
     tensor_ops::async_model_average(t, *reduced, *temp, (float)c.nranks(), comm_stream);
     if (gpu) BAGUA_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)comm_stream));
     f.finish();
-    BAGUA_LOG(Debug, "async model average update cost: " << (now_us_steady() - t0) / 1000.0 << " ms");
+    BAGUA_LOG(Debug, "async model average update cost: " << fmt_double((now_us_steady() - t0) / 1000.0) << " ms");
   }
   std::string describe() const override { return "DecentralizedFullPrecisionAsynchronous{peer_selection_mode=all}"; }
 

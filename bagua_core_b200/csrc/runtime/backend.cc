@@ -73,12 +73,12 @@ void CommBackend::monitor_loop() {
         break;
       }
       if ((*msg)->done.wait_for(std::chrono::milliseconds((int64_t)(limit * 1000)))) break;
-      std::ostringstream o;
-      o << "bucket `" << (*msg)->bucket << "` comm op has not finished for " << limit << " s";
-      BAGUA_LOG(Error, o.str());
+      const std::string what =
+          "bucket `" + (*msg)->bucket + "` comm op has not finished for " + fmt_double(limit) + " s";
+      BAGUA_LOG(Error, what);
       {
         std::lock_guard<std::mutex> g(err_mu_);
-        if (watchdog_error_.empty()) watchdog_error_ = o.str();
+        if (watchdog_error_.empty()) watchdog_error_ = what;
       }
       // keep waiting: the op may still complete; the error is reported to the next waiter
       (*msg)->done.wait();

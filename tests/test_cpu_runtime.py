@@ -1,0 +1,314 @@
+"""Single-process CPU tests of the runtime: scheduler semantics, validation, pools,
+telemetry export and the C API.  No GPU, no process group."""
+import ctypes
+import http.server
+import json
+import threading
+import time
+
+import numpy as np
+import pytest
+import torch
+
+import bagua_core as bc
+import bagua_core_b200 as bb
+
+
+def _tensor(n=8, name="t", dtype=torch.float32):
+    t = torch.zeros(n, dtype=dtype)
+    return t, bc.BaguaTensorPy(t, name)
+
+
+def _recording_bucket(name, tensors, log, delay=0.0):
+    b = bc.BaguaBucketPy(name, tensors)
+
+    def op(bucket_name):
+        if delay:
+            time.sleep(delay)
+        log.append(bucket_name)
+
+    b.append_python_op(op)
+    return b
+
+
+# ---- scheduler -----------------------------------------------------------------------
+def test_mark_ready_before_registration_is_an_error():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    _, t = _tensor()
+    with pytest.raises(RuntimeError, match="ordered buckets not yet set"):
+        backend.mark_communication_ready(t, 0)
+    backend.close()
+
+
+def test_buckets_run_in_registered_order_whatever_the_ready_order():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    log = []
+    ts = [_tensor(name=f"t{i}")[1] for i in range(6)]
+    b0 = _recording_bucket("b0", ts[0:2], log)
+    b1 = _recording_bucket("b1", ts[2:4], log)
+    b2 = _recording_bucket("b2", ts[4:6], log)
+    backend.register_ordered_buckets([b0, b1, b2])
+    # make the LAST bucket ready first: nothing may be scheduled until the front one is ready
+    for i in (5, 4, 3, 2):
+        backend.mark_communication_ready(ts[i], 0)
+    assert backend.wait_pending_comm_ops() == 0 and log == []
+    backend.mark_communication_ready(ts[0], 0)
+    assert backend.wait_pending_comm_ops() == 0
+    backend.mark_communication_ready(ts[1], 0)  # front completes → all three cascade
+    assert backend.wait_pending_comm_ops() == 3
+    assert log == ["b0", "b1", "b2"]
+    # readiness was reset and the queue rotated: a second round works the same way
+    for t in ts:
+        backend.mark_communication_ready(t, 0)
+    assert backend.wait_pending_comm_ops() == 3
+    assert log == ["b0", "b1", "b2"] * 2
+    backend.close()
+
+
+def test_padding_tensors_are_always_ready_and_all_padding_bucket_is_rejected():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    log = []
+    _, real = _tensor(name="w")
+    _, pad = _tensor(name="bagua_padding_tensor_bucket_0")
+    assert pad.ready_for_comm() and not real.ready_for_comm()
+    b = _recording_bucket("b", [real, pad], log)
+    backend.register_ordered_buckets([b])
+    backend.mark_communication_ready(real, 0)
+    assert backend.wait_pending_comm_ops() == 1 and log == ["b"]
+    _, pad2 = _tensor(name="bagua_padding_tensor_bucket_1")
+    only_pad = bc.BaguaBucketPy("p", [pad2])
+    with pytest.raises(RuntimeError, match="only padding"):
+        backend.register_ordered_buckets([only_pad])
+    backend.close()
+
+
+def test_duplicate_tensor_detection_by_name_and_pointer():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    t = torch.zeros(8)
+    a, b2 = bc.BaguaTensorPy(t, "a"), bc.BaguaTensorPy(t, "b")  # same memory
+    with pytest.raises(RuntimeError, match="duplicated tensor"):
+        backend.register_ordered_buckets([bc.BaguaBucketPy("x", [a]), bc.BaguaBucketPy("y", [b2])])
+    c, d = _tensor(name="same")[1], _tensor(name="same")[1]  # same name
+    with pytest.raises(RuntimeError, match="duplicated tensor"):
+        backend.register_ordered_buckets([bc.BaguaBucketPy("x", [c, d])])
+    backend.close()
+
+
+def test_bounded_channel_applies_back_pressure():
+    backend = bc.BaguaCommBackendPy(1, -1)  # capacity 1
+    log = []
+    _, t = _tensor()
+    b = _recording_bucket("slow", [t], log, delay=0.15)
+    backend.register_ordered_buckets([b])
+    t0 = time.perf_counter()
+    for _ in range(4):  # 1 executing + 1 queued fit; the rest must wait for the worker
+        backend.mark_communication_ready(t, 0)
+    blocked = time.perf_counter() - t0
+    assert blocked > 0.2, blocked
+    assert backend.wait_pending_comm_ops() == 4 and len(log) == 4
+    backend.close()
+
+
+def test_ops_are_snapshotted_at_schedule_time_and_can_be_swapped():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    log = []
+    _, t = _tensor()
+    b = _recording_bucket("b", [t], log)
+    backend.register_ordered_buckets([b])
+    backend.mark_communication_ready(t, 0)
+    backend.wait_pending_comm_ops()
+    b.clear_ops()  # the registered bucket shares state with the Python object
+    b.append_python_op(lambda name: log.append("second:" + name))
+    backend.mark_communication_ready(t, 0)
+    backend.wait_pending_comm_ops()
+    assert log == ["b", "second:b"]
+    assert "PythonFFIOp" in b.describe_ops()
+    backend.close()
+
+
+def test_python_op_errors_are_logged_not_raised():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    _, t = _tensor()
+    b = bc.BaguaBucketPy("b", [t])
+    b.append_python_op(lambda name: 1 / 0)
+    backend.register_ordered_buckets([b])
+    backend.mark_communication_ready(t, 0)
+    assert backend.wait_pending_comm_ops() == 1
+    backend.close()
+
+
+def test_reregistration_drains_pending_ops():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    log = []
+    _, t = _tensor()
+    b = _recording_bucket("old", [t], log, delay=0.1)
+    backend.register_ordered_buckets([b])
+    backend.mark_communication_ready(t, 0)
+    _, t2 = _tensor(name="t2")
+    backend.register_ordered_buckets([_recording_bucket("new", [t2], log)])  # waits for "old"
+    assert log == ["old"]
+    backend.mark_communication_ready(t2, 0)
+    backend.wait_pending_comm_ops()
+    assert log == ["old", "new"]
+    backend.close()
+
+
+def test_watchdog_reports_an_op_that_does_not_finish():
+    backend = bc.BaguaCommBackendPy(10, -1)
+    backend.set_watchdog_timeout(0.2)
+    release = threading.Event()
+    _, t = _tensor()
+    b = bc.BaguaBucketPy("stuck", [t])
+    b.append_python_op(lambda name: release.wait(5))
+    backend.register_ordered_buckets([b])
+    backend.mark_communication_ready(t, 0)
+    with pytest.raises(RuntimeError, match="watchdog.*stuck.*has not finished"):
+        backend.wait_pending_comm_ops()
+    release.set()
+    time.sleep(0.1)
+    backend.close()
+
+
+# ---- validation ------------------------------------------------------------------------
+def test_bucket_validation():
+    with pytest.raises(RuntimeError, match="at least one tensor"):
+        bc.BaguaBucketPy("e", [])
+    a = _tensor(dtype=torch.float32, name="a")[1]
+    h = _tensor(dtype=torch.float16, name="h")[1]
+    with pytest.raises(RuntimeError, match="same dtype"):
+        bc.BaguaBucketPy("m", [a, h])
+
+
+def test_tensor_dtypes_and_accessors():
+    for dt, name in [(torch.float32, "F32"), (torch.float16, "F16"), (torch.int64, "I64"), (torch.uint8, "U8"),
+                     (torch.bfloat16, "BF16")]:
+        t = torch.zeros(6, dtype=dt)
+        b = bc.BaguaTensorPy(t, "x")
+        assert b.dtype() == name and b.num_elements() == 6 and b.num_elements_allocated() == 6
+        assert b.device_id() == -1 and b.data_ptr() == t.data_ptr()
+    with pytest.raises(RuntimeError, match="unsupported tensor dtype"):
+        bc.BaguaTensorPy(torch.zeros(4, dtype=torch.float64), "d")
+    t = torch.arange(5, dtype=torch.float32)
+    assert np.array_equal(bc.BaguaTensorPy(t, "n").to_numpy_f32(), t.numpy())
+    u = torch.arange(5, dtype=torch.uint8)
+    assert np.array_equal(bc.BaguaTensorPy(u, "u").to_numpy_u8(), u.numpy())
+
+
+def test_op_string_arguments_are_validated():
+    _, t = _tensor()
+    b = bc.BaguaBucketPy("b", [t])
+    with pytest.raises(RuntimeError, match="inter node communicator must be given"):
+        b.append_centralized_synchronous_op(None, None, hierarchical=False)
+    with pytest.raises(RuntimeError, match="intra node communicator must be given"):
+        b.append_centralized_synchronous_op(None, None, hierarchical=True)
+
+
+def test_contiguous_bucket_is_aliased_and_scattered_bucket_is_staged():
+    bb._C.reset_stats()
+    backend = bc.BaguaCommBackendPy(10, -1)
+    flat = torch.zeros(16)
+    a, b2 = bc.BaguaTensorPy(flat[:8], "a"), bc.BaguaTensorPy(flat[8:], "b")
+    # no communicator available without a process group: contiguity is observable through stats only
+    # via ops that take the communication tensor, covered in the gloo tests; here check registration
+    bucket = bc.BaguaBucketPy("c", [a, b2])
+    backend.register_ordered_buckets([bucket])
+    backend.close()
+
+
+# ---- helpers exposed for the Python layer ------------------------------------------------
+@pytest.mark.parametrize("n", [2, 4, 6, 8, 16])
+def test_shift_one_pairing_is_mutual_and_covers_the_other_half(n):
+    seen = {r: set() for r in range(n)}
+    for step in range(n):
+        for r in range(n):
+            p = bb._C.shift_one_peer(r, n, step)
+            assert 0 <= p < n and p != r
+            assert (r < n // 2) != (p < n // 2)
+            assert bb._C.shift_one_peer(p, n, step) == r
+            seen[r].add(p)
+    for r in range(n):
+        assert len(seen[r]) == n // 2  # every rank meets the whole other half
+
+
+def test_pool_size_classes_and_reuse():
+    assert bb._C.pool_size_class(1) == 2048
+    assert bb._C.pool_size_class(2048) == 2048
+    assert bb._C.pool_size_class(2049) == 4096
+    assert bb._C.pool_size_class(5 << 20) == 8 << 20
+    x = torch.randn(4096)
+    t = bc.BaguaTensorPy(x, "x")
+    c = t.compress("MinMaxUInt8", 4, -1)
+    a0 = bb._C.pool_stats(-1)["device_allocs"]
+    del c
+    for _ in range(5):
+        c = t.compress("MinMaxUInt8", 4, -1)
+        del c
+    s = bb._C.pool_stats(-1)
+    assert s["device_allocs"] == a0 and s["bytes_in_use"] == 0
+
+
+# ---- telemetry ---------------------------------------------------------------------------
+def test_telemetry_posts_reference_schema():
+    received = []
+
+    class H(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = self.rfile.read(int(self.headers["Content-Length"]))
+            received.append((self.path, json.loads(body)))
+            self.send_response(200)
+            self.send_header("Content-Length", "0")
+            self.end_headers()
+
+        def log_message(self, *a):
+            pass
+
+    srv = http.server.HTTPServer(("127.0.0.1", 0), H)
+    th = threading.Thread(target=srv.serve_forever, daemon=True)
+    th.start()
+    try:
+        bb._C.telemetry_init(f"127.0.0.1:{srv.server_address[1]}")
+        assert bb._C.telemetry_enabled()
+        backend = bc.BaguaCommBackendPy(10, -1)
+        log = []
+        _, t = _tensor(name="layer1.weight")
+        backend.register_ordered_buckets([_recording_bucket("bkt", [t], log)])
+        backend.mark_communication_ready(t, 0)
+        backend.wait_pending_comm_ops()
+        backend.close()
+        bb._C.telemetry_flush(3000)
+        deadline = time.time() + 3
+        while time.time() < deadline and not any(
+                s["action"] == "tensor_ready" for _, b in received for s in b["spans"]):
+            time.sleep(0.05)
+    finally:
+        bb._C.telemetry_shutdown()
+        srv.shutdown()
+    spans = [s for path, b in received for s in b["spans"]]
+    assert all(path == "/api/v1/report_tensor_execution_order" for path, _ in received)
+    ready = [s for s in spans if s["action"] == "tensor_ready"]
+    assert ready and ready[0]["tensor_name"] == "layer1.weight"
+    assert set(ready[0]) == {"trace_id", "action", "tensor_name", "start_time", "end_time"}
+    assert ready[0]["end_time"] >= ready[0]["start_time"] > 1_600_000_000_000
+    assert {"bucket_scheduled", "bucket_executed"} <= {s["action"] for s in spans}
+
+
+# ---- C API ---------------------------------------------------------------------------------
+def test_c_api_symbols_and_null_handling():
+    lib = ctypes.CDLL(bb.SO_PATH)
+    lib.bagua_single_communicator_c_create.restype = ctypes.c_void_p
+    lib.bagua_single_communicator_c_create.argtypes = [ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t,
+                                                       ctypes.c_uint64, ctypes.c_char_p]
+    lib.bagua_core_c_last_error.restype = ctypes.c_char_p
+    null = ctypes.c_void_p(None)
+    n = ctypes.c_size_t(123)
+    assert lib.bagua_single_communicator_c_nranks(ctypes.byref(null), ctypes.byref(n)) == -1
+    lib.bagua_single_communicator_c_destroy(ctypes.byref(null))  # no-op
+    h = lib.bagua_single_communicator_c_create(0, 1, 0, 0, b"c10d:no_such_group")
+    assert h is None and b"process group" in lib.bagua_core_c_last_error()
+    assert lib.bagua_single_communicator_c_create(0, 1, 0, 0, None) is None
+
+
+def test_show_version_runs(capfd):
+    bc.show_version()
+    err = capfd.readouterr().err
+    assert "NCCL version" in err and "bagua-core-b200" in err
