@@ -196,6 +196,36 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            },
            py::call_guard<py::gil_scoped_release>())
       .def("check_device_status", [](PyComm& c) { c.inner->check_device_status(); })
+      .def(
+          "alloc_symmetric",
+          [](PyComm& c, int64_t numel, at::ScalarType dtype) -> py::object {
+            PeerArena* a = nullptr;
+            void* ptr = nullptr;
+            const size_t bytes = (size_t)numel * c10::elementSize(dtype);
+            {
+              py::gil_scoped_release rel;
+              a = c.inner->arena();
+              if (a) ptr = a->sym_alloc(bytes);
+            }
+            if (!a) return py::none();
+            // the memory belongs to the communicator's arena: keep the communicator alive
+            // for as long as any tensor views it
+            SingleCommPtr keep = c.inner;
+            at::Tensor t = at::from_blob(
+                ptr, {numel}, [keep](void*) {},
+                at::TensorOptions().dtype(dtype).device(at::kCUDA, c.inner->device_id()));
+            return py::cast(t);
+          },
+          py::arg("numel"), py::arg("dtype"),
+          "Collective: a 1-D CUDA tensor in memory that every rank of this communicator maps (all ranks must "
+          "call with the same sizes in the same order).  Buckets placed here are all-reduced in place without "
+          "staging copies.  Returns None when the peer arena is not available.")
+      .def("is_symmetric",
+           [](PyComm& c, const at::Tensor& t) {
+             PeerArena* a = c.inner->arena();
+             void* peers[kArenaMaxRanks];
+             return a && t.is_cuda() && a->sym_translate(t.data_ptr(), t.nbytes(), peers);
+           })
       .def("fused_launches", [](PyComm& c) {
         auto* a = c.inner->arena();
         return a ? a->fused_launches() : (uint64_t)0;

@@ -42,6 +42,14 @@ PeerArena::~PeerArena() {
     if (peer_signals_[p]) cudaIpcCloseMemHandle(peer_signals_[p]);
   }
   for (void* p : retired_peer_) cudaIpcCloseMemHandle(p);
+  for (Slab& s : slabs_)
+    for (int p = 0; p < nranks_; ++p) {
+      if (!s.base[p]) continue;
+      if (p == rank_)
+        cudaFree(s.base[p]);
+      else
+        cudaIpcCloseMemHandle(s.base[p]);
+    }
   if (local_staging_) cudaFree(local_staging_);
   for (void* p : retired_) cudaFree(p);
   if (local_signals_) cudaFree(local_signals_);
@@ -109,6 +117,84 @@ void PeerArena::allocate_and_exchange(size_t bytes) {
   // Nobody may write into the new staging before every rank has mapped it.
   transport_.barrier();
   BAGUA_LOG(Info, "peer arena rank " << rank_ << "/" << nranks_ << ": staging " << (bytes >> 20) << " MiB mapped");
+}
+
+void PeerArena::exchange_block(size_t bytes, void** local, void* peers[kArenaMaxRanks]) {
+  BAGUA_CUDA_CHECK(cudaSetDevice(device_));
+  void* fresh = nullptr;
+  BAGUA_CUDA_CHECK(cudaMalloc(&fresh, bytes));
+  BAGUA_CUDA_CHECK(cudaMemset(fresh, 0, bytes));
+  struct Msg {
+    cudaIpcMemHandle_t handle;
+    uint64_t bytes;
+  } mine;
+  std::memset(&mine, 0, sizeof(mine));
+  BAGUA_CUDA_CHECK(cudaIpcGetMemHandle(&mine.handle, fresh));
+  mine.bytes = bytes;
+  void* dev = nullptr;
+  BAGUA_CUDA_CHECK(cudaMalloc(&dev, sizeof(Msg) * (size_t)nranks_));
+  BAGUA_CUDA_CHECK(cudaMemcpyAsync((char*)dev + sizeof(Msg) * (size_t)rank_, &mine, sizeof(mine),
+                                   cudaMemcpyHostToDevice, stream_));
+  transport_.allgather((char*)dev + sizeof(Msg) * (size_t)rank_, dev, (int64_t)sizeof(Msg), DType::U8);
+  std::vector<Msg> all((size_t)nranks_);
+  BAGUA_CUDA_CHECK(cudaMemcpyAsync(all.data(), dev, sizeof(Msg) * (size_t)nranks_, cudaMemcpyDeviceToHost, stream_));
+  BAGUA_CUDA_CHECK(cudaStreamSynchronize(stream_));
+  BAGUA_CUDA_CHECK(cudaFree(dev));
+  for (int p = 0; p < nranks_; ++p) {
+    BAGUA_CHECK(all[p].bytes == bytes, Communicator,
+                "ranks disagree on a symmetric allocation (" << all[p].bytes << " vs " << bytes
+                                                             << " bytes); allocate identically on every rank");
+    if (p == rank_) {
+      peers[p] = fresh;
+      continue;
+    }
+    void* mapped = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&mapped, all[p].handle, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      throw BaguaError(ErrorKind::Communicator, std::string("cannot map symmetric memory of rank ") +
+                                                    std::to_string(p) + ": " + cudaGetErrorString(e));
+    }
+    peers[p] = mapped;
+  }
+  *local = fresh;
+  transport_.barrier();
+}
+
+void* PeerArena::sym_alloc(size_t bytes) {
+  std::lock_guard<std::mutex> g(sym_mu_);
+  bytes = align_up(bytes == 0 ? 1 : bytes, 256);
+  if (slabs_.empty() || slabs_.back().used + bytes > slabs_.back().bytes) {
+    static const size_t slab_min = (size_t)env_long("BAGUA_B200_SYM_SLAB_MB", 256) << 20;
+    const size_t slab_bytes = align_up(std::max(bytes, slab_min), (size_t)2 << 20);
+    Slab s;
+    std::memset(&s, 0, sizeof(s));
+    void* local = nullptr;
+    void* peers[kArenaMaxRanks] = {};
+    exchange_block(slab_bytes, &local, peers);
+    for (int p = 0; p < nranks_; ++p) s.base[p] = (char*)peers[p];
+    s.bytes = slab_bytes;
+    s.used = 0;
+    slabs_.push_back(s);
+  }
+  Slab& s = slabs_.back();
+  void* out = s.base[rank_] + s.used;
+  s.used += bytes;
+  sym_used_ += bytes;
+  return out;
+}
+
+bool PeerArena::sym_translate(const void* p, size_t bytes, void* peers[kArenaMaxRanks]) const {
+  std::lock_guard<std::mutex> g(sym_mu_);
+  const char* c = (const char*)p;
+  for (const Slab& s : slabs_) {
+    const char* b = s.base[rank_];
+    if (c >= b && c + bytes <= b + s.used) {
+      for (int q = 0; q < nranks_; ++q) peers[q] = s.base[q] + (c - b);
+      return true;
+    }
+  }
+  return false;
 }
 
 void PeerArena::ensure_staging(size_t bytes) {

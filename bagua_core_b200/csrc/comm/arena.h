@@ -95,8 +95,30 @@ class PeerArena {
   uint64_t fused_launches() const { return launches_; }
   void count_launch() { ++launches_; }
 
+  // ---- symmetric heap ---------------------------------------------------------------
+  // Memory that every rank allocates identically (same call sequence, same sizes) and
+  // that every peer maps: kernels given a pointer into it can address the same offset
+  // on any rank directly, so buckets placed here are reduced in place with no staging
+  // copy at all.  Collective when a new slab is needed; memory lives as long as the arena.
+  void* sym_alloc(size_t bytes);
+  // If [p, p+bytes) lies inside the heap, fills peers[q] with rank q's address of the
+  // same offset (peers[rank] == p) and returns true.
+  bool sym_translate(const void* p, size_t bytes, void* peers[kArenaMaxRanks]) const;
+  size_t sym_bytes_in_use() const { return sym_used_; }
+
  private:
   void allocate_and_exchange(size_t bytes);
+  // Collective: cudaMalloc `bytes` on every rank and map every peer's block.
+  void exchange_block(size_t bytes, void** local, void* peers[kArenaMaxRanks]);
+
+  struct Slab {
+    char* base[kArenaMaxRanks];  // this rank's mapping of every rank's slab
+    size_t bytes;
+    size_t used;
+  };
+  std::vector<Slab> slabs_;
+  size_t sym_used_ = 0;
+  mutable std::mutex sym_mu_;
 
   Transport& transport_;
   int rank_, nranks_, device_;

@@ -168,8 +168,10 @@ __global__ void __launch_bounds__(kThreads)
       slice(q, lo, hi);
       uint4* dst = reinterpret_cast<uint4*>(v.staging[q]) + (int64_t)me * max_chunk_vecs - chunk_lo(q);
       copy_vecs(dst, in, lo, hi);
-      psync::cta_signal_phase(v, 0, 1u << q);
     }
+    // one fence for all peers: a system-scope fence waits for every outstanding remote
+    // store, so fencing per peer would serialise N-1 NVLink round trips
+    psync::cta_signal_phase(v, 0, all_peers_mask(v));
     ok = psync::cta_wait_phase(v, 0, all_peers_mask(v));
   }
   if (ok) {
@@ -205,6 +207,71 @@ __global__ void __launch_bounds__(kThreads)
       slice(q, lo, hi);
       copy_vecs(out, ag, lo, hi);
     }
+  }
+  psync::cta_finish_op(v);
+}
+
+// ---------------------------------------------------------------------------------
+// two-shot on symmetric buffers: no staging at all
+// ---------------------------------------------------------------------------------
+// `in` and `out` live in the symmetric heap, so every rank can address every rank's copy.
+// Rank r owns chunk r: it loads chunk r of all N inputs (N-1 of them over NVLink), sums in
+// rank order, scales, and stores the result into chunk r of all N outputs.  Two signalling
+// rounds: "my input is ready" before the loads, "my stores are done" after them.  Wire
+// per GPU: (N-1)/N·S in, (N-1)/N·S out; HBM traffic is the bucket itself, once.
+struct SymPtrs {
+  const uint4* in[kArenaMaxRanks];
+  uint4* out[kArenaMaxRanks];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    allreduce_sym_kernel(const __grid_constant__ ArenaView v, const __grid_constant__ SymPtrs p, int64_t nvec,
+                         float scale) {
+  using O = VecOps<T>;
+  const int me = v.rank, N = v.nranks;
+  const int G = gridDim.x, b = blockIdx.x;
+  const int64_t c0 = nvec * me / N, len = nvec * (me + 1) / N - c0;
+  const int64_t lo = c0 + len * b / G, hi = c0 + len * (b + 1) / G;
+
+  // round 0: every peer's block b has started, i.e. that peer's input is final
+  psync::cta_signal_phase(v, 0, all_peers_mask(v));
+  bool ok = psync::cta_wait_phase(v, 0, all_peers_mask(v));
+  if (ok) {
+    constexpr int U = 2;  // vectors per thread per iteration: 2·N loads in flight
+    int64_t i = lo + threadIdx.x;
+    for (; i + (U - 1) * kThreads < hi; i += U * kThreads) {
+      uint4 x[U][kArenaMaxRanks];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int r = 0; r < kArenaMaxRanks; ++r)
+          if (r < N) x[u][r] = p.in[r][i + u * kThreads];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float a[O::N];
+#pragma unroll
+        for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kArenaMaxRanks; ++r)
+          if (r < N) O::acc(a, x[u][r]);
+        const uint4 res = O::pack(a, scale);
+#pragma unroll
+        for (int r = 0; r < kArenaMaxRanks; ++r)
+          if (r < N) p.out[r][i + u * kThreads] = res;
+      }
+    }
+    for (; i < hi; i += kThreads) {
+      float a[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+      for (int r = 0; r < N; ++r) O::acc(a, p.in[r][i]);
+      const uint4 res = O::pack(a, scale);
+      for (int r = 0; r < N; ++r) p.out[r][i] = res;
+    }
+    // round 1: my stores into everyone's output are complete / theirs into mine
+    psync::cta_signal_phase(v, 1, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, 1, all_peers_mask(v));
   }
   psync::cta_finish_op(v);
 }
@@ -256,12 +323,28 @@ bool allreduce_t(PeerArena& arena, const void* in, void* out, int64_t n, float s
   if (bytes % 16 != 0 || (uintptr_t)in % 16 != 0 || (uintptr_t)out % 16 != 0) return false;
   const int64_t nvec = (int64_t)(bytes / 16);
   const int N = arena.nranks();
-  static const size_t oneshot_max = (size_t)env_long("BAGUA_B200_ONESHOT_BYTES", 256 << 10);
+  // One-shot sends (N-1)·S per GPU in one hop, two-shot 2(N-1)/N·S in two hops: with two
+  // ranks the wire bytes are equal, so one-shot always wins; otherwise it wins while the
+  // extra bytes cost less than the extra hop (about 16 MB of wire traffic per GPU).
+  static const long oneshot_env = env_long("BAGUA_B200_ONESHOT_BYTES", -1);
+  const size_t oneshot_max = oneshot_env >= 0 ? (size_t)oneshot_env
+                             : N == 2         ? ((size_t)512 << 20)
+                                              : ((size_t)16 << 20) / (size_t)(N - 1);
   const int grid = pick_grid(arena, bytes);
   if (bytes <= oneshot_max) {
     arena.ensure_staging((size_t)N * bytes);
     ArenaView v = arena.next_view(grid, 0);
     allreduce_oneshot_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, nvec, nvec, scale);
+  } else if (void *pin[kArenaMaxRanks], *pout[kArenaMaxRanks];
+             arena.sym_translate(in, bytes, pin) && arena.sym_translate(out, bytes, pout)) {
+    SymPtrs p;
+    std::memset(&p, 0, sizeof(p));
+    for (int r = 0; r < N; ++r) {
+      p.in[r] = (const uint4*)pin[r];
+      p.out[r] = (uint4*)pout[r];
+    }
+    ArenaView v = arena.next_view(grid, 0);
+    allreduce_sym_kernel<T><<<grid, kThreads, 0, stream>>>(v, p, nvec, scale);
   } else {
     const int64_t max_chunk = (nvec + N - 1) / N;
     arena.ensure_staging(((size_t)N * (size_t)max_chunk + (size_t)nvec) * 16);

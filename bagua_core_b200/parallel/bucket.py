@@ -31,12 +31,15 @@ class BaguaTensor:
 
 
 class BaguaBucket:
-    def __init__(self, tensors: Sequence[BaguaTensor], name: str, flatten: bool = True, alignment: int = 1):
+    def __init__(self, tensors: Sequence[BaguaTensor], name: str, flatten: bool = True, alignment: int = 1,
+                 allocator=None):
         self.name = name
         self.tensors: List[BaguaTensor] = list(tensors)
         self.flattened: Optional[torch.Tensor] = None
         self.padding: Optional[BaguaTensor] = None
         self._alignment = max(1, alignment)
+        # allocator(numel, dtype, device) -> zero-filled 1-D tensor or None (e.g. symmetric memory)
+        self._allocator = allocator
         if flatten:
             self._flatten()
         backend_tensors = [t.backend_tensor for t in self.tensors]
@@ -49,7 +52,9 @@ class BaguaBucket:
         first = self.tensors[0].tensor
         total = sum(t.tensor.numel() for t in self.tensors)
         padded = (total + self._alignment - 1) // self._alignment * self._alignment
-        flat = torch.zeros(padded, dtype=first.dtype, device=first.device)
+        flat = self._allocator(padded, first.dtype, first.device) if self._allocator is not None else None
+        if flat is None:
+            flat = torch.zeros(padded, dtype=first.dtype, device=first.device)
         off = 0
         with torch.no_grad():
             for t in self.tensors:

@@ -68,7 +68,8 @@ class BaguaModule(nn.Module):
         groups = algo.tensors_to_buckets(self, tensors)
         align = ALIGN_ELEMS_PER_RANK * max(1, self.pg.world_size)
         self.bagua_buckets = [
-            BaguaBucket(g, f"bucket_{i}", flatten=algo.flatten_buckets, alignment=align) for i, g in enumerate(groups)
+            BaguaBucket(g, f"bucket_{i}", flatten=algo.flatten_buckets, alignment=align, allocator=self._alloc_flat)
+            for i, g in enumerate(groups)
         ]
         for b in self.bagua_buckets:
             algo.init_operations(self, b)
@@ -88,6 +89,20 @@ class BaguaModule(nn.Module):
         self._post_step = algo.init_post_optimizer_step_hook(self)
         self._wrap_optimizer_steps()
         self._arm()
+
+    def _alloc_flat(self, numel, dtype, device):
+        """Bucket storage: symmetric memory of the global communicator when there are peers
+        (the engine then all-reduces the bucket in place over NVLink with no staging copy);
+        None → the bucket falls back to an ordinary zero tensor.  Collective: every rank
+        builds the same buckets in the same order."""
+        import os
+
+        if (not self.pg.is_cuda or self.pg.world_size < 2 or os.environ.get("BAGUA_B200_SYMMETRIC", "1") == "0"
+                or os.environ.get("BAGUA_B200_FUSED", "1") == "0"):
+            return None
+        if dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            return None
+        return self.pg.global_comm.alloc_symmetric(int(numel), dtype)
 
     def _arm(self):
         self._remaining = {b.name: len(b.tensors) for b in self.bagua_buckets}

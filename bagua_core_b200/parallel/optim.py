@@ -15,6 +15,19 @@ import torch
 from .._native import C as _C
 
 
+def _is_dense(t: torch.Tensor) -> bool:
+    """True if the tensor's elements occupy one gap-free, non-overlapping block of memory."""
+    if t.numel() <= 1:
+        return True
+    dims = sorted((st, sz) for st, sz in zip(t.stride(), t.shape) if sz > 1)
+    expect = 1
+    for st, sz in dims:
+        if st != expect:
+            return False
+        expect *= sz
+    return True
+
+
 class FlatSGD(torch.optim.Optimizer):
     """torch.optim.SGD semantics (momentum, dampening, weight decay, Nesterov).
 
@@ -37,6 +50,19 @@ class FlatSGD(torch.optim.Optimizer):
         self._flat.clear()
         self._attached_ids.clear()
         for b in bm.bagua_buckets:
+            if b.flattened is not None and b.flattened.dtype == torch.float32 and all(
+                    t.kind == "weight" for t in b.tensors):
+                # weights are the bucket: give the gradients the same flat layout
+                flat_g = torch.zeros_like(b.flattened)
+                off = 0
+                for t in b.tensors:
+                    p = t.owner
+                    n = p.numel()
+                    p.grad = flat_g[off:off + n].as_strided(tuple(p.shape), tuple(p.stride()))
+                    self._attached_ids.add(id(p))
+                    off += n
+                self._flat.append({"p": b.flattened, "g": flat_g, "m": torch.zeros_like(flat_g), "first": True})
+                continue
             if b.flattened is None or any(t.kind != "grad" for t in b.tensors):
                 continue
             if b.flattened.dtype != torch.float32:
@@ -74,8 +100,21 @@ class FlatSGD(torch.optim.Optimizer):
                 first = "momentum_buffer" not in st
                 if first:
                     st["momentum_buffer"] = torch.zeros_like(p, memory_format=torch.preserve_format)
-                if p.dtype != torch.float32 or not p.is_non_overlapping_and_dense():
-                    raise RuntimeError("FlatSGD updates dense float32 parameters")
+                buf = st["momentum_buffer"]
+                same_layout = (p.dtype == torch.float32 and _is_dense(p) and p.grad.dtype == torch.float32
+                               and p.grad.stride() == p.stride() and buf.stride() == p.stride())
+                if not same_layout:
+                    # layouts differ (e.g. autograd produced a contiguous gradient for a
+                    # channels_last weight): element-wise torch math is layout-agnostic
+                    d = p.grad.add(p, alpha=group["weight_decay"]) if group["weight_decay"] else p.grad
+                    if group["momentum"]:
+                        if first:
+                            buf.copy_(d)
+                        else:
+                            buf.mul_(group["momentum"]).add_(d, alpha=1 - group["dampening"])
+                        d = d.add(buf, alpha=group["momentum"]) if group["nesterov"] else buf
+                    p.add_(d, alpha=-group["lr"])
+                    continue
                 s = torch.cuda.current_stream().cuda_stream if p.is_cuda else 0
                 # dense tensors with equal strides can be updated as flat memory
                 pv = torch.as_strided(p, (p.numel(),), (1,))

@@ -117,10 +117,18 @@ def main():
                     continue
                 if op == "shift_one" and world % 2:
                     continue
-                x = torch.randn(n, generator=g).to(dev)
+                if path == "fused_sym":
+                    # bucket in symmetric memory: in-place two-shot without staging
+                    if op != "gradient_allreduce":
+                        continue
+                    comm.set_fused(True)
+                    x = comm.alloc_symmetric(n, torch.float32)
+                    x.copy_(torch.randn(n, generator=g))
+                else:
+                    x = torch.randn(n, generator=g).to(dev)
                 bt = bc.BaguaTensorPy(x, "x")
                 bucket = bc.BaguaBucketPy(f"{op}_{S}", [bt])
-                comm.set_fused(path == "fused")
+                comm.set_fused(path != "library")
                 bb._C.set_sync_per_bucket(path == "library")
                 keep = []
                 if op == "gradient_allreduce":

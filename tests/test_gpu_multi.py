@@ -34,6 +34,8 @@ def _gather_all(t):
 
 
 def _fused_allreduce(rank, world):
+    # small one-shot limit so that the two-shot kernels are exercised at every world size
+    os.environ["BAGUA_B200_ONESHOT_BYTES"] = "262144"
     import bagua_core as bc
 
     dev = torch.device("cuda", rank)
@@ -70,6 +72,25 @@ def _fused_allreduce(rank, world):
             stream.synchronize()
             assert torch.allclose(y.float(), ref_sum, rtol=tol, atol=tol * max(1.0, ref_sum.abs().max().item()))
             report.append((str(dt), n))
+    # symmetric memory: in-place two-shot with direct peer loads/stores, no staging
+    for dt in (torch.float32, torch.bfloat16):
+        n = (24 << 20) + 4096
+        sym = comm.alloc_symmetric(n, dt)
+        assert sym is not None and comm.is_symmetric(sym)
+        g = torch.Generator().manual_seed(500 + rank)
+        sym.copy_(torch.randn(n, generator=g).to(dt))
+        allx = _gather_all(sym.clone())
+        ref = torch.stack([a.float() for a in allx]).mean(0)
+        torch.cuda.synchronize()
+        bt = bc.BaguaTensorPy(sym, "sym")
+        for rep in range(2):  # second pass averages identical values: result must not change
+            assert comm.fused_allreduce(bt, bt, True)
+            stream.synchronize()
+            comm.check_device_status()
+            tol = 1e-6 if dt == torch.float32 else 1.6e-2
+            assert torch.allclose(sym.float(), ref, rtol=tol, atol=tol * max(1.0, ref.abs().max().item())), (dt, rep)
+            outs = _gather_all(sym.clone())
+            assert all(torch.equal(outs[0], o) for o in outs)
     # back-to-back ops of different sizes without host sync in between (staging reuse protocol)
     xs = [torch.full((s,), float(rank + 1), device=dev) for s in (1 << 12, 1 << 22, 1 << 14, 1 << 21, 64)]
     torch.cuda.synchronize()
