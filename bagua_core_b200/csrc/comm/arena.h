@@ -20,8 +20,9 @@
 // returns.  The host turns a non-zero status into a CommunicatorError and marks the
 // communicator aborted; the CUDA context stays usable.
 //
-// No load with cluster multicast is used anywhere; remote data is only ever written by
-// its producer into the consumer's staging and then read locally.
+// The kernels use ordinary global loads and stores only (no TMA, no cluster features).
+// Through staging, remote data is written by its producer into the consumer's memory and
+// then read locally; buckets in the symmetric heap are also loaded directly from peers.
 #pragma once
 
 #include <cuda_runtime_api.h>

@@ -123,8 +123,9 @@ __global__ void __launch_bounds__(kThreads)
         mmdev::load16(p + i, f);
         mmdev::store_q16(q + i, f, g);
       }
-      psync::cta_signal_phase(v, 0, c == me ? 0u : (1u << c));
     }
+    // one system-scope fence for all peers instead of N-1 serialised NVLink round trips
+    psync::cta_signal_phase(v, 0, peers_mask(v));
     ok = psync::cta_wait_phase(v, 0, peers_mask(v));
   }
 
@@ -215,7 +216,7 @@ bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStr
     int per_sm = 0, sms = 0, dev = 0;
     BAGUA_CUDA_CHECK(cudaGetDevice(&dev));
     BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, bytegrad_kernel<float>, kThreads, 0));
+    BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, bytegrad_kernel<T>, kThreads, 0));
     coop_limit = std::max(1, per_sm * sms);
   }
   grid = std::min(grid, coop_limit);

@@ -156,7 +156,7 @@ bool lp_ring_t(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, 
     int per_sm = 0, sms = 0, dev = 0;
     BAGUA_CUDA_CHECK(cudaGetDevice(&dev));
     BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lp_ring_kernel<float>, kThreads, 0));
+    BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lp_ring_kernel<T>, kThreads, 0));
     coop_limit = std::max(1, per_sm * sms);
   }
   grid = std::min(grid, coop_limit);

@@ -170,6 +170,86 @@ __device__ __forceinline__ void load_dq16(const uint8_t* q, float (&v)[16], cons
   unpack_dq16(*reinterpret_cast<const uint4*>(q), v, g);
 }
 
+// ---- coalesced 16-byte vectors -------------------------------------------------------
+// The fused kernels walk a slice as 16-byte vectors of T (VE = 4 floats or 8 halves) with
+// consecutive lanes on consecutive vectors, so every load/store instruction of a warp
+// covers one contiguous 512-byte span; the VE quantised bytes of a vector are stored as
+// one 4- or 8-byte word at the same element offset.
+template <typename T>
+struct Vec16 {
+  static constexpr int VE = 16 / (int)sizeof(T);
+};
+__device__ __forceinline__ void load_vec(const float* base, int64_t vec, float (&f)[4]) {
+  const float4 a = reinterpret_cast<const float4*>(base)[vec];
+  f[0] = a.x;
+  f[1] = a.y;
+  f[2] = a.z;
+  f[3] = a.w;
+}
+__device__ __forceinline__ void load_vec(const __half* base, int64_t vec, float (&f)[8]) {
+  const uint4 a = reinterpret_cast<const uint4*>(base)[vec];
+  const __half2* h = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 v = __half22float2(h[k]);
+    f[2 * k] = v.x;
+    f[2 * k + 1] = v.y;
+  }
+}
+__device__ __forceinline__ void load_vec(const __nv_bfloat16* base, int64_t vec, float (&f)[8]) {
+  const uint4 a = reinterpret_cast<const uint4*>(base)[vec];
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 v = __bfloat1622float2(h[k]);
+    f[2 * k] = v.x;
+    f[2 * k + 1] = v.y;
+  }
+}
+__device__ __forceinline__ void store_vec(float* base, int64_t vec, const float (&f)[4]) {
+  reinterpret_cast<float4*>(base)[vec] = make_float4(f[0], f[1], f[2], f[3]);
+}
+__device__ __forceinline__ void store_vec(__half* base, int64_t vec, const float (&f)[8]) {
+  uint4 a;
+  __half2* h = reinterpret_cast<__half2*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2half2_rn(f[2 * k], f[2 * k + 1]);
+  reinterpret_cast<uint4*>(base)[vec] = a;
+}
+__device__ __forceinline__ void store_vec(__nv_bfloat16* base, int64_t vec, const float (&f)[8]) {
+  uint4 a;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+  reinterpret_cast<uint4*>(base)[vec] = a;
+}
+// quantised bytes of vector `vec` (payload pointer q must be 8-byte aligned)
+__device__ __forceinline__ uint32_t pack_q4(const float* f, const Grid& g) {
+  return (uint32_t)quantise(f[0], g) | ((uint32_t)quantise(f[1], g) << 8) | ((uint32_t)quantise(f[2], g) << 16) |
+         ((uint32_t)quantise(f[3], g) << 24);
+}
+__device__ __forceinline__ uint32_t pack_qvec(const float (&f)[4], const Grid& g) { return pack_q4(f, g); }
+__device__ __forceinline__ uint2 pack_qvec(const float (&f)[8], const Grid& g) {
+  return make_uint2(pack_q4(f, g), pack_q4(f + 4, g));
+}
+__device__ __forceinline__ void store_qword(uint8_t* q, int64_t vec, uint32_t w) {
+  reinterpret_cast<uint32_t*>(q)[vec] = w;
+}
+__device__ __forceinline__ void store_qword(uint8_t* q, int64_t vec, uint2 w) { reinterpret_cast<uint2*>(q)[vec] = w; }
+__device__ __forceinline__ void lut_dqvec(const uint8_t* q, int64_t vec, float (&f)[4], const float* lut) {
+  const uint32_t w = reinterpret_cast<const uint32_t*>(q)[vec];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) f[k] = lut[(w >> (8 * k)) & 0xffu];
+}
+__device__ __forceinline__ void lut_dqvec(const uint8_t* q, int64_t vec, float (&f)[8], const float* lut) {
+  const uint2 w = reinterpret_cast<const uint2*>(q)[vec];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    f[k] = lut[(w.x >> (8 * k)) & 0xffu];
+    f[4 + k] = lut[(w.y >> (8 * k)) & 0xffu];
+  }
+}
+
 // A chunk's dequantiser only has 256 possible outputs: tabulate them once per block (with
 // the exact IEEE division, and the rounding through the tensor dtype that a store would
 // apply) and turn every element into one shared-memory lookup.  Caller syncs the block.

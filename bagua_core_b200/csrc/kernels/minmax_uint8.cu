@@ -58,13 +58,16 @@ __global__ void __launch_bounds__(kThreads)
   const T* p = in + (int64_t)c * chunk;
   float mn = FLT_MAX, mx = -FLT_MAX;
   if (vec) {
-    // full 16-element groups, then a scalar tail when `real` cuts a group
-    int64_t full_hi = lo + ((hi > lo ? hi - lo : 0) / 16) * 16;
-    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < full_hi; i += (int64_t)kThreads * 16) {
-      float v[16];
-      mmdev::load16(p + i, v);
+    // whole 16-byte vectors (consecutive lanes on consecutive vectors), then a scalar tail
+    // when `real` cuts a vector
+    constexpr int VE = mmdev::Vec16<T>::VE;
+    const int64_t full_hi = lo + ((hi > lo ? hi - lo : 0) / VE) * VE;
+#pragma unroll 4
+    for (int64_t i = lo / VE + threadIdx.x; i < full_hi / VE; i += kThreads) {
+      float v[VE];
+      mmdev::load_vec(p, i, v);
 #pragma unroll
-      for (int k = 0; k < 16; ++k) {
+      for (int k = 0; k < VE; ++k) {
         mn = fminf(mn, v[k]);
         mx = fmaxf(mx, v[k]);
       }
@@ -110,10 +113,17 @@ __global__ void __launch_bounds__(kThreads)
   const T* p = in + (int64_t)c * chunk;
   uint8_t* q = base + kCompressHeaderBytes;
   if (vec) {
-    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
-      float v[16];
-      mmdev::load16(p + i, v);
-      mmdev::store_q16(q + i, v, g);
+    constexpr int VE = mmdev::Vec16<T>::VE;
+    constexpr int U = 4;
+    const int64_t vhi = hi / VE;
+    for (int64_t i0 = lo / VE + threadIdx.x; i0 < vhi; i0 += (int64_t)U * kThreads) {
+      float v[U][VE];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * kThreads < vhi) mmdev::load_vec(p, i0 + u * kThreads, v[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * kThreads < vhi) mmdev::store_qword(q, i0 + u * kThreads, mmdev::pack_qvec(v[u], g));
     }
   } else {
     for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) q[i] = mmdev::quantise(mmdev::to_f(p[i]), g);
@@ -134,10 +144,15 @@ __global__ void __launch_bounds__(kThreads)
   const uint8_t* q = base + kCompressHeaderBytes;
   T* o = out + (int64_t)c * chunk;
   if (vec) {
-    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
-      float v[16];
-      mmdev::load_dq16(q + i, v, g);
-      mmdev::store16(o + i, v);
+    constexpr int VE = mmdev::Vec16<T>::VE;
+    __shared__ float s_lut[256];
+    mmdev::build_dequant_lut<T>(s_lut, g);
+    __syncthreads();
+#pragma unroll 4
+    for (int64_t i = lo / VE + threadIdx.x; i < hi / VE; i += kThreads) {
+      float v[VE];
+      mmdev::lut_dqvec(q, i, v, s_lut);
+      mmdev::store_vec(o, i, v);
     }
   } else {
     for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) o[i] = mmdev::from_f<T>(mmdev::dequantise(q[i], g));
