@@ -6,6 +6,7 @@ import shutil
 import statistics
 import subprocess
 import threading
+import time
 from typing import Dict, List
 
 _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -14,12 +15,17 @@ _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,
 
 
 class ClockSampler:
-    def __init__(self, gpu_index: int = 0, period_ms: int = 200):
+    """Context manager around `nvidia-smi -lms`.  Call `mark()` right before the timed region
+    starts (it first waits for the sampler's first line, so short regions still get samples);
+    `summary()` then reports only samples taken after the mark."""
+
+    def __init__(self, gpu_index: int = 0, period_ms: int = 50):
         self.gpu_index = gpu_index
         self.period_ms = period_ms
         self._proc = None
         self._lines: List[str] = []
         self._thread = None
+        self._mark = 0
 
     def __enter__(self):
         if shutil.which("nvidia-smi") is None:
@@ -38,8 +44,18 @@ class ClockSampler:
         for line in self._proc.stdout:
             self._lines.append(line.strip())
 
+    def mark(self, wait_s: float = 3.0):
+        """Wait (bounded) until the sampler has produced its first line, then start counting."""
+        if self._proc is None:
+            return
+        deadline = time.time() + wait_s
+        while not self._lines and time.time() < deadline:
+            time.sleep(0.01)
+        self._mark = len(self._lines)
+
     def __exit__(self, *exc):
         if self._proc is not None:
+            time.sleep(self.period_ms / 1000.0 * 1.5)  # let the last sample of the region arrive
             self._proc.terminate()  # the exact child this object started
             try:
                 self._proc.wait(timeout=5)
@@ -48,9 +64,10 @@ class ClockSampler:
         return False
 
     def summary(self) -> Dict:
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self._lines:
+        lines = self._lines[self._mark:] or self._lines[-3:]
+        for line in lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -59,10 +76,14 @@ class ClockSampler:
                 mx.append(float(f[2]))
             except ValueError:
                 continue
+            try:
+                power.append(float(f[3]))
+            except ValueError:
+                pass
             for name, val in zip(names, f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "power_w_max": max(power) if power else None}

@@ -204,6 +204,7 @@ def main():
     k0 = my_kernels()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
+        clocks.mark()
         barrier()
         e0.record()
         for _ in range(args.steps):
