@@ -107,8 +107,6 @@ class Communicator {
   uint64_t stream() const;
   SingleCommPtr internode() const { return internode_; }
   SingleCommPtr intranode() const { return intranode_; }
-  // The communicator whose rank/nranks the hook sees.
-  SingleCommPtr hook_comm() const { return kind_ == Kind::Single ? internode_ : internode_; }
 
   // reference: BaguaCommunicator::execute_communication (communicators/mod.rs:390-427)
   void execute_communication(RawTensor& t, bool intranode_average, bool hierarchical_pre, bool hierarchical_post,

@@ -15,7 +15,6 @@ are marked ready.  They correspond to the six ops of the reference
 from __future__ import annotations
 
 import threading
-import time
 from typing import List
 
 import torch

@@ -1,0 +1,110 @@
+"""Trainer-layer features on CPU ranks: asynchronous model averaging, checkpointable op
+state, `no_sync`, gradients replaced by `zero_grad(set_to_none=True)`."""
+import time
+
+import torch
+
+from mp_util import run_ranks
+
+
+def _async(rank, world):
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import MLP
+
+    torch.manual_seed(100 + rank)  # different init per rank; with_bagua broadcasts rank 0's
+    model = MLP(8, 16, 4, depth=2)
+    pg = P.init_process_group(torch.device("cpu"))
+    opt = torch.optim.SGD(model.parameters(), lr=0.0)  # lr 0: only averaging moves the weights
+    algo = P.AsyncModelAverageAlgorithm(sync_interval_ms=20)
+    bm = P.with_bagua(model, [opt], algo)
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(float(rank))  # make replicas differ after the broadcast
+    x, y = torch.randn(4, 8), torch.randn(4, 4)
+    for _ in range(3):
+        opt.zero_grad(set_to_none=False)
+        torch.nn.functional.mse_loss(bm(x), y).backward()
+        opt.step()
+    deadline = time.time() + 20
+    while algo.rounds < 3 and time.time() < deadline:
+        time.sleep(0.05)
+    algo.abort(bm)
+    rounds = algo.rounds
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    P.destroy_process_group()
+    return flat, rounds
+
+
+def test_async_model_average_converges_replicas():
+    res = run_ranks(_async, 2)
+    (a, ra), (b, rb) = res
+    assert ra >= 3 and rb >= 3
+    # after a few averaging rounds both replicas sit at the mean of the perturbed weights
+    assert torch.allclose(a, b, atol=1e-5)
+
+
+def _state_and_nosync(rank, world):
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import MLP
+
+    torch.manual_seed(5)
+    model = MLP(8, 16, 4, depth=2)
+    pg = P.init_process_group(torch.device("cpu"))
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    bm = P.with_bagua(model, [opt], P.DecentralizedAlgorithm(peer_selection_mode="shift_one"))
+    x, y = torch.randn(4, 8) + rank, torch.randn(4, 4)
+    for _ in range(3):
+        opt.zero_grad(set_to_none=False)
+        torch.nn.functional.mse_loss(bm(x), y).backward()
+        opt.step()
+    state = bm.bagua_state_dict()
+    # restoring the state rewinds the gossip step counter
+    bm.load_bagua_state_dict({"step": 1, "ops": [[[("step", 1)]] for _ in bm.bagua_buckets], "algorithm": {}})
+    after = bm.bagua_state_dict()
+    P.destroy_process_group()
+    return state["step"], state["ops"], after["step"], after["ops"]
+
+
+def test_op_state_can_be_saved_and_restored():
+    res = run_ranks(_state_and_nosync, 2)
+    for step, ops, step2, ops2 in res:
+        assert step == 3
+        assert all(op == [[("step", 3)]] for op in ops)
+        assert step2 == 1 and all(op == [[("step", 1)]] for op in ops2)
+
+
+def _no_sync_and_set_to_none(rank, world):
+    import bagua_core_b200 as bb
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import MLP
+
+    torch.manual_seed(9)
+    model = MLP(8, 16, 4, depth=2)
+    pg = P.init_process_group(torch.device("cpu"))
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    bm = P.with_bagua(model, [opt], P.GradientAllReduceAlgorithm(), bucket_bytes=256)
+    g = torch.Generator().manual_seed(rank)
+    x, y = torch.randn(4, 8, generator=g), torch.randn(4, 4, generator=g)
+    bb._C.reset_stats()
+    with bm.no_sync():
+        opt.zero_grad(set_to_none=False)
+        torch.nn.functional.mse_loss(bm(x), y).backward()
+    local = torch.cat([p.grad.reshape(-1).clone() for p in model.parameters()])
+    scheduled_in_no_sync = bb._C.stats()["buckets_scheduled"]
+    # a user optimizer that drops the gradients: the hook must move the fresh ones into the bucket
+    opt.zero_grad(set_to_none=True)
+    torch.nn.functional.mse_loss(bm(x), y).backward()
+    synced = torch.cat([p.grad.reshape(-1).clone() for p in model.parameters()])
+    views_ok = all(p.grad.data_ptr() >= b.flattened.data_ptr() for b in bm.bagua_buckets for t in b.tensors
+                   for p in [t.owner])
+    P.destroy_process_group()
+    return local, synced, scheduled_in_no_sync, views_ok
+
+
+def test_no_sync_and_regrown_gradients():
+    res = run_ranks(_no_sync_and_set_to_none, 2)
+    mean_local = (res[0][0] + res[1][0]) / 2
+    for local, synced, scheduled, views_ok in res:
+        assert scheduled == 0  # nothing communicated under no_sync
+        assert torch.allclose(synced, mean_local, atol=1e-6)  # same data → all-reduced mean of the local grads
+        assert views_ok

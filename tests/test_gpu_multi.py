@@ -124,7 +124,6 @@ def _bucket_ops(rank, world):
     assert comm.fused_available()
     comm.set_device_wait_ms(20000.0)
     backend = bc.BaguaCommBackendPy(10, rank)
-    results = {}
 
     def run(bucket, tensors):
         backend.register_ordered_buckets([bucket])
