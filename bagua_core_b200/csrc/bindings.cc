@@ -20,6 +20,7 @@
 #include "ops/comm_op.h"
 #include "pool/resource_pool.h"
 #include "runtime/backend.h"
+#include "runtime/protocol_model.h"
 #include "telemetry/telemetry.h"
 #include "tensor/tensor.h"
 
@@ -523,6 +524,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       py::arg("param"), py::arg("grad"), py::arg("momentum_buffer"), py::arg("lr"), py::arg("momentum"),
       py::arg("dampening"), py::arg("weight_decay"), py::arg("nesterov"), py::arg("first_step"), py::arg("stream"));
 
+  m.def(
+      "protocol_model_check",
+      [](int nranks, int blocks, int n_ops, uint32_t seed, bool use_done_chain, int slow_rank) {
+        ProtocolModelResult r;
+        {
+          py::gil_scoped_release rel;
+          r = run_protocol_model(nranks, blocks, n_ops, seed, use_done_chain, slow_rank);
+        }
+        py::dict d;
+        d["errors"] = r.errors;
+        d["timeouts"] = r.timeouts;
+        d["ops"] = r.ops;
+        return d;
+      },
+      py::arg("nranks"), py::arg("blocks"), py::arg("n_ops"), py::arg("seed") = 0, py::arg("use_done_chain") = true,
+      py::arg("slow_rank") = -1,
+      "Runs the host-thread model of the fused kernels' signalling protocol and reports wrong sums / timeouts.");
   m.def(
       "debug_wait_timeout",
       [](int device, double wait_ms) {

@@ -125,6 +125,7 @@ class BaguaBucket:
 def _comms(pg, hierarchical: bool):
     if not hierarchical:
         return pg.global_comm, None
+    pg.ensure_hierarchical()
     if pg.intra_comm is None:
         raise RuntimeError("hierarchical communication needs intra-node / inter-node communicators")
     return pg.inter_comm, pg.intra_comm

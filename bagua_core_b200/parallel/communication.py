@@ -57,6 +57,7 @@ class BaguaProcessGroup:
     intra_comm: Optional[BaguaSingleCommunicatorPy] = None
     inter_comm: Optional[BaguaSingleCommunicatorPy] = None
     _keep: list = field(default_factory=list)
+    _hier_done: bool = False
 
     @property
     def stream_ptr(self) -> int:
@@ -65,6 +66,26 @@ class BaguaProcessGroup:
     @property
     def is_cuda(self) -> bool:
         return self.device.type == "cuda"
+
+    def ensure_hierarchical(self):
+        """Create the intra-node / inter-node communicators on first use.  Collective over
+        all ranks (every rank reaches it when it builds a `hierarchical=True` op); kept lazy
+        so that the common flat case pays for one communicator only."""
+        if self._hier_done:
+            return
+        self._hier_done = True
+        world = self.world_size
+        local_size = max(1, min(get_local_size(), world))
+        if world < 2 or world % local_size != 0:
+            return
+        n_nodes = world // local_size
+        for node in range(n_nodes):
+            ranks = list(range(node * local_size, (node + 1) * local_size))
+            c = _new_comm(ranks, self.rank, self.device, self.stream_ptr, self._keep)
+            if c is not None:
+                self.intra_comm = c
+        leaders = [n * local_size for n in range(n_nodes)]
+        self.inter_comm = _new_comm(leaders, self.rank, self.device, self.stream_ptr, self._keep)
 
     def wait_comm_stream(self):
         """Make the current (compute) stream wait for everything queued on the comm stream."""
@@ -133,18 +154,7 @@ def init_process_group(device: Optional[torch.device] = None, schedule_channel_c
         backend = BaguaCommBackendPy(schedule_channel_cap, dev_id)
         all_ranks = list(range(world))
         global_comm = _new_comm(all_ranks, rank, device, stream_ptr, keep)
-        local_size = max(1, min(get_local_size(), world))
-        intra = inter = None
-        if world > 1 and world % local_size == 0:
-            n_nodes = world // local_size
-            for node in range(n_nodes):
-                ranks = list(range(node * local_size, (node + 1) * local_size))
-                c = _new_comm(ranks, rank, device, stream_ptr, keep)
-                if c is not None:
-                    intra = c
-            leaders = [n * local_size for n in range(n_nodes)]
-            inter = _new_comm(leaders, rank, device, stream_ptr, keep)
-        _state = BaguaProcessGroup(rank, world, device, backend, comm_stream, global_comm, intra, inter, keep)
+        _state = BaguaProcessGroup(rank, world, device, backend, comm_stream, global_comm, None, None, keep)
         return _state
 
 
