@@ -279,6 +279,8 @@ def main():
         }
         print(json.dumps(line))
     if args.impl != "ddp":
+        if hasattr(algo, "abort"):
+            algo.abort(fwd)  # stop the background averaging thread before tearing down
         P.destroy_process_group()
     if dist.is_initialized():
         dist.destroy_process_group()

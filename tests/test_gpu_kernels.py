@@ -149,6 +149,53 @@ def test_device_wait_runs_out_and_reports():
     assert float((x * 2).sum()) == 32.0
 
 
+@pytest.mark.parametrize("n", [1, 17, 4096, 65536 + 3, (1 << 20) + 16])
+@pytest.mark.parametrize("dt", DTYPES)
+def test_kernels_stay_inside_their_buffers(n, dt):
+    """Guard regions of a sentinel value on both sides of every operand must survive every
+    kernel (stand-in for a memory checker, which cannot be run on the GPU pool)."""
+    import bagua_core as bc
+    import bagua_core_b200.ops as ops
+
+    guard = 64
+    sentinel = 12345.0
+
+    def guarded(seed):
+        buf = torch.full((n + 2 * guard,), sentinel, dtype=dt, device="cuda")
+        buf[guard:guard + n] = _rand(n, dt, seed)
+        return buf, buf[guard:guard + n]
+
+    def intact(buf):
+        return bool((buf[:guard] == sentinel).all() and (buf[guard + n:] == sentinel).all())
+
+    bx, x = guarded(21)
+    by, y = guarded(22)
+    ops.add_inplace(x, y)
+    ops.addmul_inplace(x, y, 0.25)
+    ops.average_inplace(x, y)
+    ops.subtract_inplace(x, y)
+    ops.divide_inplace(x, 3.0)
+    if n % 2 == 0:
+        ops.reduce_chunk_inplace(x, 2, 1, average=True)
+    torch.cuda.synchronize()
+    assert intact(bx) and intact(by)
+    # compress into an engine buffer, decompress into a guarded output
+    chunks = 2 if n % 2 == 0 else 1
+    c = bc.BaguaTensorPy(x, "x").compress("MinMaxUInt8", chunks, -1)
+    bo, o = guarded(23)
+    bc.BaguaTensorPy(o, "o").decompress_from("MinMaxUInt8", chunks, c)
+    torch.cuda.synchronize()
+    assert intact(bx) and intact(bo)
+    if dt == torch.float32:
+        bm, mbuf = guarded(24)
+        mbuf.zero_()
+        ops.sgd_momentum_flat(x, y, mbuf, 0.01, 0.9)
+        bt, t = guarded(25)
+        ops.async_model_average(t, x, y, 4)
+        torch.cuda.synchronize()
+        assert intact(bx) and intact(by) and intact(bm) and intact(bt)
+
+
 def test_pool_reuses_blocks():
     import bagua_core as bc
     import bagua_core_b200 as bb
