@@ -41,6 +41,7 @@ SOURCES = [
     "kernels/fused_allreduce.cu",
     "kernels/fused_bytegrad.cu",
     "kernels/fused_gossip.cu",
+    "kernels/fused_emu.cc",
     "kernels/no_alloc.cu",
 ]
 
@@ -55,6 +56,14 @@ def _nccl_paths():
     if os.path.exists(os.path.join(inc, "nccl.h")) and os.path.exists(os.path.join(lib, "libnccl.so.2")):
         return inc, lib
     return "/usr/include", "/usr/lib/x86_64-linux-gnu"
+
+
+def _shared_libstdcxx_flags():
+    """Linker flags that pin the system's shared libstdc++.so.6 (empty if it cannot be found)."""
+    for d in ("/usr/lib/x86_64-linux-gnu", "/usr/lib64", "/lib/x86_64-linux-gnu", "/usr/lib/aarch64-linux-gnu"):
+        if os.path.exists(os.path.join(d, "libstdc++.so.6")):
+            return [f"-L{d}", "-l:libstdc++.so.6"]
+    return []
 
 
 def sources():
@@ -95,7 +104,12 @@ def build(verbose: bool = False, force: bool = False) -> str:
             "-fvisibility=hidden",
         ],
         extra_include_paths=[nccl_inc, CSRC],
-        extra_ldflags=[f"-L{nccl_lib}", "-l:libnccl.so.2", f"-Wl,-rpath,{nccl_lib}", "-lcudart"],
+        # The shared C++ runtime is named explicitly and first.  Some toolchain wrappers
+        # resolve a bare -lstdc++ to the static archive; an extension carrying its own copy
+        # of libstdc++ next to the one torch uses has two sets of locale facets, and the
+        # first number streamed into a std::ostream crashes.
+        extra_ldflags=_shared_libstdcxx_flags()
+        + [f"-L{nccl_lib}", "-l:libnccl.so.2", f"-Wl,-rpath,{nccl_lib}", "-lcudart"],
         build_directory=BUILD_DIR,
         with_cuda=True,
         is_python_module=False,

@@ -16,6 +16,7 @@
 #include "comm/arena.h"
 #include "comm/communicator.h"
 #include "kernels/fused.h"
+#include "kernels/fused_emu.h"
 #include "kernels/kernels.h"
 #include "ops/comm_op.h"
 #include "pool/resource_pool.h"
@@ -523,6 +524,80 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("param"), py::arg("grad"), py::arg("momentum_buffer"), py::arg("lr"), py::arg("momentum"),
       py::arg("dampening"), py::arg("weight_decay"), py::arg("nesterov"), py::arg("first_step"), py::arg("stream"));
+
+  // ---- single-GPU emulation of the fused kernels (all ranks in one cooperative launch) ----
+  py::class_<fused::EmulatedArena>(m, "EmulatedArena")
+      .def(py::init<int, int, size_t>(), py::arg("nranks"), py::arg("device"), py::arg("staging_bytes"))
+      .def("nranks", &fused::EmulatedArena::nranks)
+      .def("epoch", &fused::EmulatedArena::epoch)
+      .def("set_deadline_ms", &fused::EmulatedArena::set_deadline_ms)
+      .def(
+          "allreduce",
+          [](fused::EmulatedArena& a, std::vector<at::Tensor> in, std::vector<at::Tensor> out, bool average,
+             const std::string& mode, int blocks) {
+            BAGUA_CHECK(!in.empty() && in.size() == out.size(), Tensor, "one input and one output per rank");
+            std::vector<const void*> pi;
+            std::vector<void*> po;
+            for (size_t r = 0; r < in.size(); ++r) {
+              check_pair(in[r], out[r]);
+              check_pair(in[0], in[r]);
+              pi.push_back(in[r].data_ptr());
+              po.push_back(out[r].data_ptr());
+            }
+            const auto md = mode == "oneshot"   ? fused::EmuAllreduceMode::OneShot
+                            : mode == "twoshot" ? fused::EmuAllreduceMode::TwoShot
+                                                : fused::EmuAllreduceMode::Symmetric;
+            py::gil_scoped_release rel;
+            a.allreduce(pi, po, in[0].numel(), dtype_from_torch(in[0].scalar_type()),
+                        average ? 1.0f / (float)a.nranks() : 1.0f, md, blocks);
+          },
+          py::arg("inputs"), py::arg("outputs"), py::arg("average"), py::arg("mode"), py::arg("blocks"))
+      .def(
+          "pair_average",
+          [](fused::EmulatedArena& a, std::vector<at::Tensor> in, std::vector<at::Tensor> out, std::vector<int> peers,
+             int blocks) {
+            std::vector<const void*> pi;
+            std::vector<void*> po;
+            for (size_t r = 0; r < in.size(); ++r) {
+              check_pair(in[r], out[r]);
+              pi.push_back(in[r].data_ptr());
+              po.push_back(out[r].data_ptr());
+            }
+            py::gil_scoped_release rel;
+            a.pair_average(pi, po, in[0].numel(), dtype_from_torch(in[0].scalar_type()), peers, blocks);
+          },
+          py::arg("inputs"), py::arg("outputs"), py::arg("peers"), py::arg("blocks"))
+      .def(
+          "bytegrad",
+          [](fused::EmulatedArena& a, std::vector<at::Tensor> buckets, bool average, int blocks) {
+            std::vector<void*> p;
+            for (auto& t : buckets) {
+              check_pair(buckets[0], t);
+              p.push_back(t.data_ptr());
+            }
+            py::gil_scoped_release rel;
+            a.bytegrad(p, buckets[0].numel(), dtype_from_torch(buckets[0].scalar_type()), average, blocks);
+          },
+          py::arg("buckets"), py::arg("average"), py::arg("blocks"))
+      .def(
+          "lp_ring",
+          [](fused::EmulatedArena& a, std::vector<at::Tensor> x, std::vector<at::Tensor> w, std::vector<at::Tensor> l,
+             std::vector<at::Tensor> r, int blocks) {
+            std::vector<void*> px, pw, pl, pr;
+            for (size_t k = 0; k < x.size(); ++k) {
+              check_pair(x[0], x[k]);
+              check_pair(x[k], w[k]);
+              check_pair(x[k], l[k]);
+              check_pair(x[k], r[k]);
+              px.push_back(x[k].data_ptr());
+              pw.push_back(w[k].data_ptr());
+              pl.push_back(l[k].data_ptr());
+              pr.push_back(r[k].data_ptr());
+            }
+            py::gil_scoped_release rel;
+            a.lp_ring(px, pw, pl, pr, x[0].numel(), dtype_from_torch(x[0].scalar_type()), blocks);
+          },
+          py::arg("x"), py::arg("weight"), py::arg("left"), py::arg("right"), py::arg("blocks"));
 
   m.def(
       "protocol_model_check",

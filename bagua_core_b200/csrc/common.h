@@ -172,10 +172,8 @@ inline uint64_t now_us_steady() {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Floating-point values are formatted with snprintf, never streamed: inserting a double
-// into a std::ostream goes through locale facets of the C++ runtime, which crashed in
-// this build when the extension was compiled and loaded against different libstdc++
-// versions.
+// Compact "%g" formatting for log and error messages (ostream's default would print
+// 120000 as 120000 but 1e-07 style values less readably, and needs no locale lookup).
 inline std::string fmt_double(double v) {
   char buf[48];
   std::snprintf(buf, sizeof(buf), "%g", v);

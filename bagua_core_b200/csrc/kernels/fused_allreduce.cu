@@ -12,14 +12,18 @@
 //             q's staging), owner sums chunk `me` in rank order, scales, and stores the
 //             result both locally and into every peer's all-gather area; peers copy it
 //             out of their own staging.  Wire per GPU: 2(N-1)/N·S out.  Two hops.
+//   symmetric (large buffers in the symmetric heap): no staging; rank r loads chunk r of
+//             all N inputs directly, reduces, and stores into chunk r of all N outputs.
 //
-// Accumulation is fp32 for every dtype, rounded once.  Remote traffic is stores only;
-// every load is from local HBM/L2.
+// Accumulation is fp32 for every dtype, rounded once.  Each algorithm is a `*_body`
+// device function; the `__global__` kernels only supply the block's position (`Launch`),
+// which lets the single-GPU emulation run exactly the same code for all ranks at once.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "fused.h"
+#include "fused_emu.h"
 #include "peer_sync.cuh"
 
 namespace bagua {
@@ -28,6 +32,7 @@ namespace fused {
 namespace {
 
 constexpr int kThreads = 512;
+using psync::Launch;
 
 template <typename T>
 struct VecOps;
@@ -108,21 +113,21 @@ __device__ __forceinline__ void copy_vecs(uint4* __restrict__ dst, const uint4* 
 // one-shot
 // ---------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
-    allreduce_oneshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec,
-                             int64_t slot_vecs, float scale) {
+__device__ __forceinline__ void allreduce_oneshot_body(const ArenaView& v, const Launch& L,
+                                                       const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                       int64_t nvec, int64_t slot_vecs, float scale) {
   using O = VecOps<T>;
   const int me = v.rank, N = v.nranks;
-  const int64_t lo = nvec * blockIdx.x / gridDim.x, hi = nvec * (blockIdx.x + 1) / gridDim.x;
-  bool ok = psync::cta_wait_prev_done(v);
+  const int64_t lo = nvec * L.block / L.grid, hi = nvec * (L.block + 1) / L.grid;
+  bool ok = psync::cta_wait_prev_done(v, L);
   if (ok) {
     for (int i = 1; i < N; ++i) {
       const int q = (me + i) % N;
       uint4* dst = reinterpret_cast<uint4*>(v.staging[q]) + (int64_t)me * slot_vecs;
       copy_vecs(dst, in, lo, hi);
     }
-    psync::cta_signal_phase(v, 0, all_peers_mask(v));
-    ok = psync::cta_wait_phase(v, 0, all_peers_mask(v));
+    psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
   }
   if (ok) {
     const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
@@ -137,19 +142,19 @@ __global__ void __launch_bounds__(kThreads)
       out[i] = O::pack(a, scale);
     }
   }
-  psync::cta_finish_op(v);
+  psync::cta_finish_op(v, L);
 }
 
 // ---------------------------------------------------------------------------------
-// two-shot
+// two-shot through staging
 // ---------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
-    allreduce_twoshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec,
-                             int64_t max_chunk_vecs, float scale) {
+__device__ __forceinline__ void allreduce_twoshot_body(const ArenaView& v, const Launch& L,
+                                                       const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                       int64_t nvec, int64_t max_chunk_vecs, float scale) {
   using O = VecOps<T>;
   const int me = v.rank, N = v.nranks;
-  const int G = gridDim.x, b = blockIdx.x;
+  const int G = L.grid, b = L.block;
   auto chunk_lo = [&](int c) { return nvec * c / N; };
   // block slice inside chunk c
   auto slice = [&](int c, int64_t& lo, int64_t& hi) {
@@ -159,7 +164,7 @@ __global__ void __launch_bounds__(kThreads)
   };
   const int64_t ag_base = (int64_t)N * max_chunk_vecs;  // all-gather area follows the N reduce-scatter slots
 
-  bool ok = psync::cta_wait_prev_done(v);
+  bool ok = psync::cta_wait_prev_done(v, L);
   if (ok) {
     // step A: push my slice of chunk q into slot[me] of q
     for (int i = 1; i < N; ++i) {
@@ -171,8 +176,8 @@ __global__ void __launch_bounds__(kThreads)
     }
     // one fence for all peers: a system-scope fence waits for every outstanding remote
     // store, so fencing per peer would serialise N-1 NVLink round trips
-    psync::cta_signal_phase(v, 0, all_peers_mask(v));
-    ok = psync::cta_wait_phase(v, 0, all_peers_mask(v));
+    psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
   }
   if (ok) {
     // step B: reduce my chunk in rank order, scale, store locally and to every peer
@@ -195,8 +200,8 @@ __global__ void __launch_bounds__(kThreads)
         reinterpret_cast<uint4*>(v.staging[q])[ag_base + i] = res;
       }
     }
-    psync::cta_signal_phase(v, 1, all_peers_mask(v));
-    ok = psync::cta_wait_phase(v, 1, all_peers_mask(v));
+    psync::cta_signal_phase(v, L, 1, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
   }
   if (ok) {
     // step C: collect the other chunks from my own all-gather area
@@ -208,7 +213,7 @@ __global__ void __launch_bounds__(kThreads)
       copy_vecs(out, ag, lo, hi);
     }
   }
-  psync::cta_finish_op(v);
+  psync::cta_finish_op(v, L);
 }
 
 // ---------------------------------------------------------------------------------
@@ -225,18 +230,17 @@ struct SymPtrs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
-    allreduce_sym_kernel(const __grid_constant__ ArenaView v, const __grid_constant__ SymPtrs p, int64_t nvec,
-                         float scale) {
+__device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Launch& L, const SymPtrs& p,
+                                                   int64_t nvec, float scale) {
   using O = VecOps<T>;
   const int me = v.rank, N = v.nranks;
-  const int G = gridDim.x, b = blockIdx.x;
+  const int G = L.grid, b = L.block;
   const int64_t c0 = nvec * me / N, len = nvec * (me + 1) / N - c0;
   const int64_t lo = c0 + len * b / G, hi = c0 + len * (b + 1) / G;
 
   // round 0: every peer's block b has started, i.e. that peer's input is final
-  psync::cta_signal_phase(v, 0, all_peers_mask(v));
-  bool ok = psync::cta_wait_phase(v, 0, all_peers_mask(v));
+  psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+  bool ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
   if (ok) {
     constexpr int U = 2;  // vectors per thread per iteration: 2·N loads in flight
     int64_t i = lo + threadIdx.x;
@@ -270,25 +274,25 @@ __global__ void __launch_bounds__(kThreads)
       for (int r = 0; r < N; ++r) p.out[r][i] = res;
     }
     // round 1: my stores into everyone's output are complete / theirs into mine
-    psync::cta_signal_phase(v, 1, all_peers_mask(v));
-    ok = psync::cta_wait_phase(v, 1, all_peers_mask(v));
+    psync::cta_signal_phase(v, L, 1, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
   }
-  psync::cta_finish_op(v);
+  psync::cta_finish_op(v, L);
 }
 
 // ---------------------------------------------------------------------------------
 // pair average: out = (in + peer's in) / 2
 // ---------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
-    pair_average_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec, int peer) {
+__device__ __forceinline__ void pair_average_body(const ArenaView& v, const Launch& L, const uint4* __restrict__ in,
+                                                  uint4* __restrict__ out, int64_t nvec, int peer) {
   using O = VecOps<T>;
-  const int64_t lo = nvec * blockIdx.x / gridDim.x, hi = nvec * (blockIdx.x + 1) / gridDim.x;
-  bool ok = psync::cta_wait_prev_done(v);
+  const int64_t lo = nvec * L.block / L.grid, hi = nvec * (L.block + 1) / L.grid;
+  bool ok = psync::cta_wait_prev_done(v, L);
   if (ok) {
     copy_vecs(reinterpret_cast<uint4*>(v.staging[peer]), in, lo, hi);
-    psync::cta_signal_phase(v, 0, 1u << peer);
-    ok = psync::cta_wait_phase(v, 0, 1u << peer);
+    psync::cta_signal_phase(v, L, 0, 1u << peer);
+    ok = psync::cta_wait_phase(v, L, 0, 1u << peer);
   }
   if (ok) {
     const uint4* got = reinterpret_cast<const uint4*>(v.staging[v.rank]);
@@ -301,12 +305,66 @@ __global__ void __launch_bounds__(kThreads)
       out[i] = O::pack(a, 0.5f);
     }
   }
-  psync::cta_finish_op(v);
+  psync::cta_finish_op(v, L);
+}
+
+// ---- real kernels: one launch per rank ---------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    allreduce_oneshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in,
+                             uint4* __restrict__ out, int64_t nvec, int64_t slot_vecs, float scale) {
+  allreduce_oneshot_body<T>(v, psync::real_launch(), in, out, nvec, slot_vecs, scale);
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    allreduce_twoshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in,
+                             uint4* __restrict__ out, int64_t nvec, int64_t max_chunk_vecs, float scale) {
+  allreduce_twoshot_body<T>(v, psync::real_launch(), in, out, nvec, max_chunk_vecs, scale);
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    allreduce_sym_kernel(const __grid_constant__ ArenaView v, const __grid_constant__ SymPtrs p, int64_t nvec,
+                         float scale) {
+  allreduce_sym_body<T>(v, psync::real_launch(), p, nvec, scale);
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    pair_average_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out,
+                        int64_t nvec, int peer) {
+  pair_average_body<T>(v, psync::real_launch(), in, out, nvec, peer);
+}
+
+// ---- emulation kernels: the grids of all ranks in one cooperative launch ------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    allreduce_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int mode, int64_t nvec, int64_t aux_vecs,
+                         float scale) {
+  const EmuRank& e = ranks[blockIdx.x / blocks];
+  const Launch L{(int)(blockIdx.x % blocks), blocks};
+  if (mode == (int)EmuAllreduceMode::OneShot) {
+    allreduce_oneshot_body<T>(e.view, L, (const uint4*)e.in, (uint4*)e.out, nvec, aux_vecs, scale);
+  } else if (mode == (int)EmuAllreduceMode::TwoShot) {
+    allreduce_twoshot_body<T>(e.view, L, (const uint4*)e.in, (uint4*)e.out, nvec, aux_vecs, scale);
+  } else {
+    SymPtrs p;
+    for (int r = 0; r < kArenaMaxRanks; ++r) {
+      p.in[r] = (const uint4*)e.sym_in[r];
+      p.out[r] = (uint4*)e.sym_out[r];
+    }
+    allreduce_sym_body<T>(e.view, L, p, nvec, scale);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    pair_average_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int64_t nvec) {
+  const EmuRank& e = ranks[blockIdx.x / blocks];
+  pair_average_body<T>(e.view, Launch{(int)(blockIdx.x % blocks), blocks}, (const uint4*)e.in, (uint4*)e.out, nvec,
+                       e.peer);
 }
 
 __global__ void wait_probe_kernel(ArenaView v) {
   // waits for a phase signal from "rank 1" that nobody will ever send
-  psync::cta_wait_phase(v, 0, 1u << 1);
+  psync::cta_wait_phase(v, psync::real_launch(), 0, 1u << 1);
 }
 
 int pick_grid(const PeerArena& arena, size_t bytes) {
@@ -371,6 +429,18 @@ bool pair_average_t(PeerArena& arena, const void* in, void* out, int64_t n, int 
   return true;
 }
 
+template <typename K, typename... Args>
+void coop_launch(K kernel, int grid, Args... args) {
+  int per_sm = 0, sms = 0, dev = 0;
+  BAGUA_CUDA_CHECK(cudaGetDevice(&dev));
+  BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+  BAGUA_CHECK(grid <= per_sm * sms, Communicator,
+              "emulation needs " << grid << " co-resident blocks, the device holds " << per_sm * sms);
+  void* argv[] = {(void*)&args...};
+  BAGUA_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(kThreads), argv, 0, 0));
+}
+
 }  // namespace
 
 bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream) {
@@ -389,6 +459,30 @@ bool pair_average(PeerArena& arena, const void* in, void* out, int64_t n, DType 
     case DType::F16: return pair_average_t<__half>(arena, in, out, n, peer, stream);
     case DType::BF16: return pair_average_t<__nv_bfloat16>(arena, in, out, n, peer, stream);
     default: return false;
+  }
+}
+
+void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
+                          EmuAllreduceMode mode, int64_t aux_vecs) {
+  const int grid = nranks * blocks;
+  const int m = (int)mode;
+  switch (dt) {
+    case DType::F32: coop_launch(allreduce_emu_kernel<float>, grid, dev, blocks, m, n * 4 / 16, aux_vecs, scale); break;
+    case DType::F16: coop_launch(allreduce_emu_kernel<__half>, grid, dev, blocks, m, n * 2 / 16, aux_vecs, scale); break;
+    case DType::BF16:
+      coop_launch(allreduce_emu_kernel<__nv_bfloat16>, grid, dev, blocks, m, n * 2 / 16, aux_vecs, scale);
+      break;
+    default: throw BaguaError(ErrorKind::Tensor, "emulated all-reduce: unsupported dtype");
+  }
+}
+
+void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt) {
+  const int grid = nranks * blocks;
+  switch (dt) {
+    case DType::F32: coop_launch(pair_average_emu_kernel<float>, grid, dev, blocks, n * 4 / 16); break;
+    case DType::F16: coop_launch(pair_average_emu_kernel<__half>, grid, dev, blocks, n * 2 / 16); break;
+    case DType::BF16: coop_launch(pair_average_emu_kernel<__nv_bfloat16>, grid, dev, blocks, n * 2 / 16); break;
+    default: throw BaguaError(ErrorKind::Tensor, "emulated pair average: unsupported dtype");
   }
 }
 

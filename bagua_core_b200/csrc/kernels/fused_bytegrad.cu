@@ -26,6 +26,7 @@
 #include <cfloat>
 
 #include "fused.h"
+#include "fused_emu.h"
 #include "minmax_device.cuh"
 #include "peer_sync.cuh"
 
@@ -72,10 +73,9 @@ __device__ __forceinline__ void fold_partials(const float2* part, int G, float& 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
-    bytegrad_kernel(const __grid_constant__ ArenaView v, T* __restrict__ x, int64_t chunk, size_t slot_bytes,
-                    size_t scratch_off, float scale) {
-  const int me = v.rank, N = v.nranks, G = gridDim.x, b = blockIdx.x;
+__device__ __forceinline__ void bytegrad_body(const ArenaView& v, const psync::Launch& L, T* __restrict__ x,
+                                              int64_t chunk, size_t slot_bytes, size_t scratch_off, float scale) {
+  const int me = v.rank, N = v.nranks, G = L.grid, b = L.block;
   const int64_t groups = chunk / 16;
   const int64_t lo = groups * b / G * 16, hi = groups * (b + 1) / G * 16;
   uint8_t* my_stage = v.staging[me];
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ mmdev::Grid s_grid[kArenaMaxRanks];
   __shared__ float s_lut[kArenaMaxRanks * 256];  // dequantiser tables, one per source chunk
 
-  bool ok = psync::cta_wait_prev_done(v);
+  bool ok = psync::cta_wait_prev_done(v, L);
 
   // ---- P1 ----
   if (ok) {
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(kThreads)
       if (threadIdx.x == 0) part1[(size_t)c * G + b] = make_float2(mn, mx);
     }
   }
-  ok = psync::grid_barrier(v, 0) && ok;
+  ok = psync::grid_barrier(v, L, 0) && ok;
 
   // ---- P2 ----
   if (ok) {
@@ -125,8 +125,8 @@ __global__ void __launch_bounds__(kThreads)
       }
     }
     // one system-scope fence for all peers instead of N-1 serialised NVLink round trips
-    psync::cta_signal_phase(v, 0, peers_mask(v));
-    ok = psync::cta_wait_phase(v, 0, peers_mask(v));
+    psync::cta_signal_phase(v, L, 0, peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 0, peers_mask(v));
   }
 
   // ---- P3 ----
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(kThreads)
   }
   mmdev::block_minmax<kThreads>(mn2, mx2);
   if (threadIdx.x == 0) part2[b] = make_float2(mn2, mx2);
-  ok = psync::grid_barrier(v, 1) && ok;
+  ok = psync::grid_barrier(v, L, 1) && ok;
 
   // ---- P4 ----
   if (ok) {
@@ -176,8 +176,8 @@ __global__ void __launch_bounds__(kThreads)
         *reinterpret_cast<uint4*>(v.staging[q] + ag_off + (size_t)me * slot_bytes + kHdr + i) = packed;
       }
     }
-    psync::cta_signal_phase(v, 1, peers_mask(v));
-    ok = psync::cta_wait_phase(v, 1, peers_mask(v));
+    psync::cta_signal_phase(v, L, 1, peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 1, peers_mask(v));
   }
 
   // ---- P5 ----
@@ -196,7 +196,25 @@ __global__ void __launch_bounds__(kThreads)
       }
     }
   }
-  psync::cta_finish_op(v);
+  psync::cta_finish_op(v, L);
+}
+
+// one launch per rank
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    bytegrad_kernel(const __grid_constant__ ArenaView v, T* __restrict__ x, int64_t chunk, size_t slot_bytes,
+                    size_t scratch_off, float scale) {
+  bytegrad_body<T>(v, psync::real_launch(), x, chunk, slot_bytes, scratch_off, scale);
+}
+
+// single-GPU emulation: the grids of all ranks in one cooperative launch
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    bytegrad_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int64_t chunk, size_t slot_bytes,
+                        size_t scratch_off, float scale) {
+  const EmuRank& e = ranks[blockIdx.x / blocks];
+  bytegrad_body<T>(e.view, psync::Launch{(int)(blockIdx.x % blocks), blocks}, (T*)e.in, chunk, slot_bytes, scratch_off,
+                   scale);
 }
 
 template <typename T>
@@ -234,7 +252,33 @@ bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStr
   return true;
 }
 
+template <typename T>
+void emu_bytegrad_t(const EmuRank* dev, int nranks, int blocks, int64_t n, float scale, size_t slot_bytes,
+                    size_t scratch_off) {
+  int per_sm = 0, sms = 0, device = 0;
+  BAGUA_CUDA_CHECK(cudaGetDevice(&device));
+  BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, bytegrad_emu_kernel<T>, kThreads, 0));
+  const int grid = nranks * blocks;
+  BAGUA_CHECK(grid <= per_sm * sms, Communicator,
+              "emulation needs " << grid << " co-resident blocks, the device holds " << per_sm * sms);
+  int64_t chunk = n / nranks;
+  void* args[] = {(void*)&dev, (void*)&blocks, (void*)&chunk, (void*)&slot_bytes, (void*)&scratch_off, (void*)&scale};
+  BAGUA_CUDA_CHECK(
+      cudaLaunchCooperativeKernel((const void*)bytegrad_emu_kernel<T>, dim3(grid), dim3(kThreads), args, 0, 0));
+}
+
 }  // namespace
+
+void emu_launch_bytegrad(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
+                         size_t slot_bytes, size_t scratch_off) {
+  switch (dt) {
+    case DType::F32: emu_bytegrad_t<float>(dev, nranks, blocks, n, scale, slot_bytes, scratch_off); break;
+    case DType::F16: emu_bytegrad_t<__half>(dev, nranks, blocks, n, scale, slot_bytes, scratch_off); break;
+    case DType::BF16: emu_bytegrad_t<__nv_bfloat16>(dev, nranks, blocks, n, scale, slot_bytes, scratch_off); break;
+    default: throw BaguaError(ErrorKind::Tensor, "emulated ByteGrad: unsupported dtype");
+  }
+}
 
 bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream) {
   switch (dt) {

@@ -1,0 +1,84 @@
+// Single-GPU emulation of the fused communication kernels.
+//
+// Kernels whose blocks wait on blocks of other ranks cannot be tested on one GPU by
+// launching one kernel per rank (nothing guarantees that separate launches run at the
+// same time).  The emulation instead hosts the grids of all N ranks side by side in ONE
+// cooperative launch: block index / G selects the virtual rank, block index % G is the
+// block's position inside that rank's grid, and every virtual rank gets its own staging
+// buffer, signal pad and ArenaView on the same device.  The device code that runs is the
+// same `*_body` function the real kernels call; only the `Launch` position differs.
+// Used by the GPU tests on machines with fewer GPUs than ranks and for profiling a fused
+// kernel from a single process.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <vector>
+
+#include "../comm/arena.h"
+#include "../common.h"
+
+namespace bagua {
+namespace fused {
+
+struct EmuRank {
+  ArenaView view;
+  const void* in;   // all-reduce / pair-average input, ByteGrad bucket, lp-ring x
+  void* out;        // all-reduce / pair-average output
+  void* w;          // lp-ring replicas
+  void* l;
+  void* r;
+  const void* sym_in[kArenaMaxRanks];  // symmetric all-reduce: every rank's input / output
+  void* sym_out[kArenaMaxRanks];
+  int peer;         // pair-average partner
+};
+
+enum class EmuAllreduceMode { OneShot = 1, TwoShot = 2, Symmetric = 3 };
+
+class EmulatedArena {
+ public:
+  EmulatedArena(int nranks, int device, size_t staging_bytes);
+  ~EmulatedArena();
+  EmulatedArena(const EmulatedArena&) = delete;
+
+  int nranks() const { return nranks_; }
+  // Pointers are per rank (index = rank), all on this arena's device.  Calls are
+  // synchronous: they return after the kernel finished, and throw CommunicatorError if a
+  // device-side wait ran out.
+  void allreduce(const std::vector<const void*>& in, const std::vector<void*>& out, int64_t n, DType dt, float scale,
+                 EmuAllreduceMode mode, int blocks);
+  void bytegrad(const std::vector<void*>& buckets, int64_t n, DType dt, bool average, int blocks);
+  void pair_average(const std::vector<const void*>& in, const std::vector<void*>& out, int64_t n, DType dt,
+                    const std::vector<int>& peers, int blocks);
+  void lp_ring(const std::vector<void*>& x, const std::vector<void*>& w, const std::vector<void*>& l,
+               const std::vector<void*>& r, int64_t n, DType dt, int blocks);
+  void set_deadline_ms(double ms) { deadline_ns_ = (uint64_t)(ms * 1e6); }
+  uint32_t epoch() const { return epoch_; }
+
+ private:
+  // Fills one EmuRank per rank with the view of the next op; returns the device copy.
+  EmuRank* prepare(std::vector<EmuRank>& host, int blocks, int grid_barriers, size_t staging_needed);
+  void finish(const char* what);
+
+  int nranks_, device_;
+  size_t staging_bytes_;
+  std::vector<void*> staging_, signals_;
+  DeviceStatus* status_host_ = nullptr;
+  DeviceStatus* status_dev_ = nullptr;
+  EmuRank* dev_args_ = nullptr;
+  uint32_t epoch_ = 0;
+  uint64_t grid_bar_ = 0;
+  uint64_t deadline_ns_ = 5000000000ull;
+};
+
+// Launchers defined next to the kernels they start (cooperative, nranks*blocks CTAs).
+void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
+                          EmuAllreduceMode mode, int64_t aux_vecs);
+void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt);
+void emu_launch_bytegrad(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
+                         size_t slot_bytes, size_t scratch_off);
+void emu_launch_lp_ring(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, size_t slot_bytes,
+                        size_t scratch_off);
+
+}  // namespace fused
+}  // namespace bagua

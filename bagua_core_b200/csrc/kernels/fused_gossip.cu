@@ -17,6 +17,7 @@
 #include <cfloat>
 
 #include "fused.h"
+#include "fused_emu.h"
 #include "minmax_device.cuh"
 #include "peer_sync.cuh"
 
@@ -35,10 +36,10 @@ __device__ __forceinline__ float rt(float x) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
-    lp_ring_kernel(const __grid_constant__ ArenaView v, T* __restrict__ x, T* __restrict__ w, T* __restrict__ l,
-                   T* __restrict__ r, int64_t n, size_t slot_bytes, size_t scratch_off) {
-  const int me = v.rank, N = v.nranks, G = gridDim.x, b = blockIdx.x;
+__device__ __forceinline__ void lp_ring_body(const ArenaView& v, const psync::Launch& L, T* __restrict__ x,
+                                             T* __restrict__ w, T* __restrict__ l, T* __restrict__ r, int64_t n,
+                                             size_t slot_bytes, size_t scratch_off) {
+  const int me = v.rank, N = v.nranks, G = L.grid, b = L.block;
   const int left = (me + N - 1) % N, right = (me + 1) % N;
   const uint32_t nb_mask = (1u << left) | (1u << right);
   const int64_t groups = n / 16;
@@ -51,7 +52,7 @@ __global__ void __launch_bounds__(kThreads)
   const float third = 1.0f / 3.0f, m53 = -5.0f / 3.0f;
   __shared__ float s_lut[3 * 256];  // dequantiser tables: left, right, own
 
-  bool ok = psync::cta_wait_prev_done(v);
+  bool ok = psync::cta_wait_prev_done(v, L);
 
   // ---- P1: d = x + l/3 + r/3 - 5w/3 (stored in x), partial min/max ----
   float mn = FLT_MAX, mx = -FLT_MAX;
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(kThreads)
   }
   mmdev::block_minmax<kThreads>(mn, mx);
   if (threadIdx.x == 0) part[b] = make_float2(mn, mx);
-  ok = psync::grid_barrier(v, 0) && ok;
+  ok = psync::grid_barrier(v, L, 0) && ok;
 
   // ---- P2: quantise d, store to both neighbours and to my own slot ----
   mmdev::Grid g_own;
@@ -106,8 +107,8 @@ __global__ void __launch_bounds__(kThreads)
       *reinterpret_cast<uint4*>(to_right + kHdr + i) = packed;
       *reinterpret_cast<uint4*>(own + kHdr + i) = packed;
     }
-    psync::cta_signal_phase(v, 0, nb_mask);
-    ok = psync::cta_wait_phase(v, 0, nb_mask);
+    psync::cta_signal_phase(v, L, 0, nb_mask);
+    ok = psync::cta_wait_phase(v, L, 0, nb_mask);
   }
 
   // ---- P3: apply the three differences ----
@@ -141,7 +142,25 @@ __global__ void __launch_bounds__(kThreads)
       mmdev::store16(w + i, cur);
     }
   }
-  psync::cta_finish_op(v);
+  psync::cta_finish_op(v, L);
+}
+
+// one launch per rank
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    lp_ring_kernel(const __grid_constant__ ArenaView v, T* __restrict__ x, T* __restrict__ w, T* __restrict__ l,
+                   T* __restrict__ r, int64_t n, size_t slot_bytes, size_t scratch_off) {
+  lp_ring_body<T>(v, psync::real_launch(), x, w, l, r, n, slot_bytes, scratch_off);
+}
+
+// single-GPU emulation: the grids of all ranks in one cooperative launch
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    lp_ring_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int64_t n, size_t slot_bytes,
+                       size_t scratch_off) {
+  const EmuRank& e = ranks[blockIdx.x / blocks];
+  lp_ring_body<T>(e.view, psync::Launch{(int)(blockIdx.x % blocks), blocks}, (T*)e.in, (T*)e.w, (T*)e.l, (T*)e.r, n,
+                  slot_bytes, scratch_off);
 }
 
 template <typename T>
@@ -173,7 +192,31 @@ bool lp_ring_t(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, 
   return true;
 }
 
+template <typename T>
+void emu_lp_ring_t(const EmuRank* dev, int nranks, int blocks, int64_t n, size_t slot_bytes, size_t scratch_off) {
+  int per_sm = 0, sms = 0, device = 0;
+  BAGUA_CUDA_CHECK(cudaGetDevice(&device));
+  BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lp_ring_emu_kernel<T>, kThreads, 0));
+  const int grid = nranks * blocks;
+  BAGUA_CHECK(grid <= per_sm * sms, Communicator,
+              "emulation needs " << grid << " co-resident blocks, the device holds " << per_sm * sms);
+  void* args[] = {(void*)&dev, (void*)&blocks, (void*)&n, (void*)&slot_bytes, (void*)&scratch_off};
+  BAGUA_CUDA_CHECK(
+      cudaLaunchCooperativeKernel((const void*)lp_ring_emu_kernel<T>, dim3(grid), dim3(kThreads), args, 0, 0));
+}
+
 }  // namespace
+
+void emu_launch_lp_ring(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, size_t slot_bytes,
+                        size_t scratch_off) {
+  switch (dt) {
+    case DType::F32: emu_lp_ring_t<float>(dev, nranks, blocks, n, slot_bytes, scratch_off); break;
+    case DType::F16: emu_lp_ring_t<__half>(dev, nranks, blocks, n, slot_bytes, scratch_off); break;
+    case DType::BF16: emu_lp_ring_t<__nv_bfloat16>(dev, nranks, blocks, n, slot_bytes, scratch_off); break;
+    default: throw BaguaError(ErrorKind::Tensor, "emulated low-precision ring: unsupported dtype");
+  }
+}
 
 bool lp_ring(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, DType dt, cudaStream_t stream) {
   if (arena.nranks() < 2) return false;

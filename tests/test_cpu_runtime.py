@@ -308,6 +308,15 @@ def test_c_api_symbols_and_null_handling():
     assert lib.bagua_single_communicator_c_create(0, 1, 0, 0, None) is None
 
 
+def test_error_messages_with_numbers_reach_python():
+    """Formatting integers and floating-point values inside the extension must work (a build
+    that links a private static copy of the C++ runtime crashes here instead of raising)."""
+    with pytest.raises(RuntimeError, match="invalid rank 5 / 2"):
+        bc.BaguaSingleCommunicatorPy(5, 2, -1, 0, "c10d:no_such_group")
+    with pytest.raises(RuntimeError, match="device index 99 out of range"):
+        bb._C.pool_stats(99)
+
+
 def test_show_version_runs(capfd):
     bc.show_version()
     err = capfd.readouterr().err
