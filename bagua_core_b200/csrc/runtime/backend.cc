@@ -1,6 +1,7 @@
 #include "backend.h"
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include "../telemetry/telemetry.h"
 
@@ -43,6 +44,10 @@ void CommBackend::worker_loop() {
     }
     const uint64_t t0 = now_ms();
     std::string err;
+    // Optional NVTX range per bucket (BAGUA_B200_NVTX=1) so that profiler timelines line up
+    // with bucket names; a no-op when no tool is attached.
+    static const bool nvtx = env_long("BAGUA_B200_NVTX", 0) != 0;
+    if (nvtx) nvtxRangePushA(op.bucket->name().c_str());
     try {
       for (auto& o : op.ops) {
         o->execute_background_communication(op.bucket);
@@ -52,6 +57,7 @@ void CommBackend::worker_loop() {
       err = e.what();
       BAGUA_LOG(Error, "communication op on bucket `" << op.bucket->name() << "` failed: " << err);
     }
+    if (nvtx) nvtxRangePop();
     Telemetry::instance().record("bucket_executed", op.bucket->name(), t0, now_ms());
     if (err.empty())
       op.event.finish();
