@@ -555,7 +555,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def(
           "pair_average",
           [](fused::EmulatedArena& a, std::vector<at::Tensor> in, std::vector<at::Tensor> out, std::vector<int> peers,
-             int blocks) {
+             int blocks, bool symmetric) {
             std::vector<const void*> pi;
             std::vector<void*> po;
             for (size_t r = 0; r < in.size(); ++r) {
@@ -564,9 +564,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               po.push_back(out[r].data_ptr());
             }
             py::gil_scoped_release rel;
-            a.pair_average(pi, po, in[0].numel(), dtype_from_torch(in[0].scalar_type()), peers, blocks);
+            a.pair_average(pi, po, in[0].numel(), dtype_from_torch(in[0].scalar_type()), peers, blocks, symmetric);
           },
-          py::arg("inputs"), py::arg("outputs"), py::arg("peers"), py::arg("blocks"))
+          py::arg("inputs"), py::arg("outputs"), py::arg("peers"), py::arg("blocks"), py::arg("symmetric") = false)
       .def(
           "bytegrad",
           [](fused::EmulatedArena& a, std::vector<at::Tensor> buckets, bool average, int blocks) {

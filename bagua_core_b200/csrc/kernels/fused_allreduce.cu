@@ -308,7 +308,59 @@ __device__ __forceinline__ void pair_average_body(const ArenaView& v, const Laun
   psync::cta_finish_op(v, L);
 }
 
+// Pair average on symmetric buffers: the partner's weights are loaded straight from its
+// memory (no staging copy).  Round 0: both sides have started, so both inputs are final;
+// round 1: both sides are done reading, so either may overwrite its weights again.
+template <typename T>
+__device__ __forceinline__ void pair_average_sym_body(const ArenaView& v, const Launch& L,
+                                                      const uint4* __restrict__ in,
+                                                      const uint4* __restrict__ peer_in, uint4* __restrict__ out,
+                                                      int64_t nvec, int peer) {
+  using O = VecOps<T>;
+  const int64_t lo = nvec * L.block / L.grid, hi = nvec * (L.block + 1) / L.grid;
+  psync::cta_signal_phase(v, L, 0, 1u << peer);
+  bool ok = psync::cta_wait_phase(v, L, 0, 1u << peer);
+  if (ok) {
+    constexpr int U = 4;
+    int64_t i = lo + threadIdx.x;
+    for (; i + (U - 1) * kThreads < hi; i += U * kThreads) {
+      uint4 a[U], b[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        b[u] = peer_in[i + u * kThreads];
+        a[u] = in[i + u * kThreads];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float s[O::N];
+#pragma unroll
+        for (int k = 0; k < O::N; ++k) s[k] = 0.f;
+        O::acc(s, a[u]);
+        O::acc(s, b[u]);
+        out[i + u * kThreads] = O::pack(s, 0.5f);
+      }
+    }
+    for (; i < hi; i += kThreads) {
+      float s[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) s[k] = 0.f;
+      O::acc(s, in[i]);
+      O::acc(s, peer_in[i]);
+      out[i] = O::pack(s, 0.5f);
+    }
+    psync::cta_signal_phase(v, L, 1, 1u << peer);
+    ok = psync::cta_wait_phase(v, L, 1, 1u << peer);
+  }
+  psync::cta_finish_op(v, L);
+}
+
 // ---- real kernels: one launch per rank ---------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    pair_average_sym_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in,
+                            const uint4* __restrict__ peer_in, uint4* __restrict__ out, int64_t nvec, int peer) {
+  pair_average_sym_body<T>(v, psync::real_launch(), in, peer_in, out, nvec, peer);
+}
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     allreduce_oneshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in,
@@ -356,10 +408,13 @@ __global__ void __launch_bounds__(kThreads)
 }
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-    pair_average_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int64_t nvec) {
+    pair_average_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int64_t nvec, int symmetric) {
   const EmuRank& e = ranks[blockIdx.x / blocks];
-  pair_average_body<T>(e.view, Launch{(int)(blockIdx.x % blocks), blocks}, (const uint4*)e.in, (uint4*)e.out, nvec,
-                       e.peer);
+  const Launch L{(int)(blockIdx.x % blocks), blocks};
+  if (symmetric)
+    pair_average_sym_body<T>(e.view, L, (const uint4*)e.in, (const uint4*)e.sym_in[e.peer], (uint4*)e.out, nvec, e.peer);
+  else
+    pair_average_body<T>(e.view, L, (const uint4*)e.in, (uint4*)e.out, nvec, e.peer);
 }
 
 __global__ void wait_probe_kernel(ArenaView v) {
@@ -420,8 +475,18 @@ bool pair_average_t(PeerArena& arena, const void* in, void* out, int64_t n, int 
   const size_t bytes = (size_t)n * sizeof(T);
   if (bytes == 0) return true;
   if (bytes % 16 != 0 || (uintptr_t)in % 16 != 0 || (uintptr_t)out % 16 != 0) return false;
-  arena.ensure_staging(bytes);
   const int grid = pick_grid(arena, bytes);
+  void* pin[kArenaMaxRanks];
+  if (bytes > ((size_t)256 << 10) && arena.sym_translate(in, bytes, pin)) {
+    // weights live in the symmetric heap on every rank: read the partner's copy directly
+    ArenaView v = arena.next_view(grid, 0);
+    pair_average_sym_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (const uint4*)pin[peer],
+                                                               (uint4*)out, (int64_t)(bytes / 16), peer);
+    BAGUA_CUDA_CHECK(cudaGetLastError());
+    arena.count_launch();
+    return true;
+  }
+  arena.ensure_staging(bytes);
   ArenaView v = arena.next_view(grid, 0);
   pair_average_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, (int64_t)(bytes / 16), peer);
   BAGUA_CUDA_CHECK(cudaGetLastError());
@@ -476,12 +541,13 @@ void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n,
   }
 }
 
-void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt) {
+void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, bool symmetric) {
   const int grid = nranks * blocks;
+  const int sym = symmetric ? 1 : 0;
   switch (dt) {
-    case DType::F32: coop_launch(pair_average_emu_kernel<float>, grid, dev, blocks, n * 4 / 16); break;
-    case DType::F16: coop_launch(pair_average_emu_kernel<__half>, grid, dev, blocks, n * 2 / 16); break;
-    case DType::BF16: coop_launch(pair_average_emu_kernel<__nv_bfloat16>, grid, dev, blocks, n * 2 / 16); break;
+    case DType::F32: coop_launch(pair_average_emu_kernel<float>, grid, dev, blocks, n * 4 / 16, sym); break;
+    case DType::F16: coop_launch(pair_average_emu_kernel<__half>, grid, dev, blocks, n * 2 / 16, sym); break;
+    case DType::BF16: coop_launch(pair_average_emu_kernel<__nv_bfloat16>, grid, dev, blocks, n * 2 / 16, sym); break;
     default: throw BaguaError(ErrorKind::Tensor, "emulated pair average: unsupported dtype");
   }
 }

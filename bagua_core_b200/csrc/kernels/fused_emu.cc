@@ -111,7 +111,7 @@ void EmulatedArena::allreduce(const std::vector<const void*>& in, const std::vec
 }
 
 void EmulatedArena::pair_average(const std::vector<const void*>& in, const std::vector<void*>& out, int64_t n, DType dt,
-                                 const std::vector<int>& peers, int blocks) {
+                                 const std::vector<int>& peers, int blocks, bool symmetric) {
   const size_t bytes = (size_t)n * elem_bytes(dt);
   BAGUA_CHECK(bytes % 16 == 0 && (int)in.size() == nranks_ && (int)out.size() == nranks_ && (int)peers.size() == nranks_,
               Tensor, "emulated pair average: need one buffer and one peer per rank");
@@ -123,9 +123,10 @@ void EmulatedArena::pair_average(const std::vector<const void*>& in, const std::
     host[r].in = in[r];
     host[r].out = out[r];
     host[r].peer = peers[r];
+    for (int q = 0; q < nranks_; ++q) host[r].sym_in[q] = in[q];
   }
-  EmuRank* dev = prepare(host, blocks, 0, bytes);
-  emu_launch_pair_average(dev, nranks_, blocks, n, dt);
+  EmuRank* dev = prepare(host, blocks, 0, symmetric ? 0 : bytes);
+  emu_launch_pair_average(dev, nranks_, blocks, n, dt, symmetric);
   finish("pair average");
 }
 

@@ -48,8 +48,9 @@ class EmulatedArena {
   void allreduce(const std::vector<const void*>& in, const std::vector<void*>& out, int64_t n, DType dt, float scale,
                  EmuAllreduceMode mode, int blocks);
   void bytegrad(const std::vector<void*>& buckets, int64_t n, DType dt, bool average, int blocks);
+  // symmetric = true: partners load each other's input directly instead of going through staging
   void pair_average(const std::vector<const void*>& in, const std::vector<void*>& out, int64_t n, DType dt,
-                    const std::vector<int>& peers, int blocks);
+                    const std::vector<int>& peers, int blocks, bool symmetric = false);
   void lp_ring(const std::vector<void*>& x, const std::vector<void*>& w, const std::vector<void*>& l,
                const std::vector<void*>& r, int64_t n, DType dt, int blocks);
   void set_deadline_ms(double ms) { deadline_ns_ = (uint64_t)(ms * 1e6); }
@@ -74,7 +75,7 @@ class EmulatedArena {
 // Launchers defined next to the kernels they start (cooperative, nranks*blocks CTAs).
 void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
                           EmuAllreduceMode mode, int64_t aux_vecs);
-void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt);
+void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, bool symmetric);
 void emu_launch_bytegrad(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
                          size_t slot_bytes, size_t scratch_off);
 void emu_launch_lp_ring(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, size_t slot_bytes,

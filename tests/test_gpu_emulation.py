@@ -57,8 +57,9 @@ def test_emulated_mixed_ops_reuse_staging_safely():
     assert arena.epoch() == 20
 
 
+@pytest.mark.parametrize("symmetric", [False, True])
 @pytest.mark.parametrize("nranks", [2, 4, 8])
-def test_emulated_pair_average(nranks):
+def test_emulated_pair_average(nranks, symmetric):
     import bagua_core_b200 as bb
 
     arena = _arena(nranks)
@@ -67,7 +68,7 @@ def test_emulated_pair_average(nranks):
     for step in range(3):
         peers = [bb._C.shift_one_peer(r, nranks, step) for r in range(nranks)]
         outs = [torch.zeros_like(x) for x in xs]
-        arena.pair_average(xs, outs, peers, 4)
+        arena.pair_average(xs, outs, peers, 4, symmetric)
         for r in range(nranks):
             assert torch.allclose(outs[r], (xs[r] + xs[peers[r]]) / 2, atol=1e-6)
         xs = outs

@@ -312,3 +312,55 @@ def test_with_bagua_training_multi_gpu(algo):
         assert torch.equal(flat, res[0][0])
         tol = 2e-4 if algo == "allreduce" else 5e-2
         assert (flat - ref).abs().max().item() < tol
+
+
+def _sym_pair(rank, world):
+    """shift_one gossip on weights that live in the symmetric heap: partners read each other's
+    bucket directly."""
+    import bagua_core as bc
+    import bagua_core_b200 as bb
+
+    dev = torch.device("cuda", rank)
+    stream = torch.cuda.Stream()
+    comm = _mk_comm(rank, world, stream)
+    assert comm.fused_available()
+    comm.set_device_wait_ms(20000.0)
+    backend = bc.BaguaCommBackendPy(10, rank)
+    n = 16 * world * 8209  # > 256 KiB so that the direct-load kernel is chosen
+    x = comm.alloc_symmetric(n, torch.float32)
+    assert x is not None and comm.is_symmetric(x)
+    g = torch.Generator().manual_seed(40 + rank)
+    x.copy_(torch.randn(n, generator=g))
+    allx = [a.clone() for a in _gather_all(x.clone())]
+    peer = torch.zeros_like(x)
+    bt = bc.BaguaTensorPy(x, "w")
+    b = bc.BaguaBucketPy("sym_gossip", [bt])
+    b.append_decentralized_synchronous_op(comm, None, hierarchical=False, peer_selection_mode="shift_one",
+                                          peer_weight=bc.BaguaTensorPy(peer, "p"))
+    backend.register_ordered_buckets([b])
+    cur = allx
+    for step in range(3):
+        ev = torch.cuda.Event()
+        ev.record()
+        backend.mark_communication_ready(bt, ev.cuda_event)
+        backend.wait_pending_comm_ops()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        comm.check_device_status()
+        p = bb._C.shift_one_peer(rank, world, step)
+        assert torch.allclose(peer, (cur[rank] + cur[p]) / 2, atol=1e-6), step
+        cur = [(cur[r] + cur[bb._C.shift_one_peer(r, world, step)]) / 2 for r in range(world)]
+        x.copy_(peer)
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+    launches = comm.fused_launches()
+    backend.close()
+    return launches
+
+
+def test_symmetric_pair_average():
+    world = _world()
+    if world % 2:
+        pytest.skip("shift_one needs an even number of ranks")
+    res = run_ranks(_sym_pair, world, backend="nccl", timeout=300)
+    assert all(r == 3 for r in res)
