@@ -222,7 +222,7 @@ __device__ __forceinline__ void allreduce_twoshot_body(const ArenaView& v, const
 // `in` and `out` live in the symmetric heap, so every rank can address every rank's copy.
 // Rank r owns chunk r: it loads chunk r of all N inputs (N-1 of them over NVLink), sums in
 // rank order, scales, and stores the result into chunk r of all N outputs.  Two signalling
-// rounds: "my input is ready" before the loads, "my stores are done" after them.  Wire
+// exchanges: "my input is ready" before the loads, "my stores are done" after them.  Wire
 // per GPU: (N-1)/N·S in, (N-1)/N·S out; HBM traffic is the bucket itself, once.
 struct SymPtrs {
   const uint4* in[kArenaMaxRanks];
@@ -238,7 +238,7 @@ __device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Lau
   const int64_t c0 = nvec * me / N, len = nvec * (me + 1) / N - c0;
   const int64_t lo = c0 + len * b / G, hi = c0 + len * (b + 1) / G;
 
-  // round 0: every peer's block b has started, i.e. that peer's input is final
+  // first signal: every peer's block b has started, i.e. that peer's input is final
   psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
   bool ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
   if (ok) {
@@ -273,7 +273,7 @@ __device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Lau
       const uint4 res = O::pack(a, scale);
       for (int r = 0; r < N; ++r) p.out[r][i] = res;
     }
-    // round 1: my stores into everyone's output are complete / theirs into mine
+    // second signal: my stores into everyone's output are complete / theirs into mine
     psync::cta_signal_phase(v, L, 1, all_peers_mask(v));
     ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
   }
@@ -309,8 +309,8 @@ __device__ __forceinline__ void pair_average_body(const ArenaView& v, const Laun
 }
 
 // Pair average on symmetric buffers: the partner's weights are loaded straight from its
-// memory (no staging copy).  Round 0: both sides have started, so both inputs are final;
-// round 1: both sides are done reading, so either may overwrite its weights again.
+// memory (no staging copy).  First signal: both sides have started, so both inputs are final;
+// second signal: both sides are done reading, so either may overwrite its weights again.
 template <typename T>
 __device__ __forceinline__ void pair_average_sym_body(const ArenaView& v, const Launch& L,
                                                       const uint4* __restrict__ in,

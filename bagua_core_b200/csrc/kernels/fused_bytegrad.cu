@@ -225,8 +225,8 @@ bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStr
   const int64_t chunk = n / N;
   if ((chunk * (int64_t)sizeof(T)) % 16 != 0) return false;
   const size_t slot = (size_t)chunk + kHdr;
-  // one CTA per 32 Ki elements of the bucket, within the arena's budget (compute heavier
-  // than a plain copy, so it gets twice the CTA budget of the all-reduce)
+  // one CTA per 32 Ki elements of the bucket, up to the arena's limit for cooperative
+  // kernels (one per SM by default: several HBM passes plus quantiser math per element)
   int64_t g = (n + (32 << 10) - 1) / (32 << 10);
   int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, arena.max_coop_blocks()));
   static int coop_limit = 0;

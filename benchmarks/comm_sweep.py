@@ -3,7 +3,7 @@
 kernels versus the library (NCCL) path that replays the reference's call sequence.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        --master-port 29521 benchmarks/comm_sweep.py --out gpurun_out/sweep_8gpu.json
+        --master-port 29521 benchmarks/comm_sweep.py --out sweep_8gpu.json
 
 Ops: gradient_allreduce (O1, average), bytegrad (O2), shift_one (O3 pair average),
 lp_ring (O4), each on one fp32 bucket of 1 KB … 1 GB (powers of 4), values N(0,1) from

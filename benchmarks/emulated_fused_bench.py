@@ -9,7 +9,7 @@ script exists so that a fused kernel can be timed and captured by `ncu` from a s
 process, e.g. (after the same command line has exited 0 without ncu):
 
     ncu --set full --clock-control none -k regex:bytegrad_emu_kernel -c 1 \
-        -o gpurun_out/prof_bytegrad_emu python benchmarks/emulated_fused_bench.py --only bytegrad --iters 1 --warmup 1
+        -o prof_bytegrad_emu python benchmarks/emulated_fused_bench.py --only bytegrad --iters 1 --warmup 1
 
 Per-rank buffers default to 64 MB of fp32 (8 ranks: 512 MB of buckets plus staging, larger
 than the 126 MB L2, a few GB in total).
