@@ -65,6 +65,33 @@ def test_buckets_run_in_registered_order_whatever_the_ready_order():
     backend.close()
 
 
+def test_any_ready_order_yields_the_registered_bucket_order():
+    """Property: for random bucket shapes and random orders in which tensors become ready, over
+    several rounds, buckets execute exactly in registration order, once per round."""
+    import random
+
+    rng = random.Random(1234)
+    for trial in range(20):
+        backend = bc.BaguaCommBackendPy(rng.choice([1, 2, 100]), -1)
+        log = []
+        n_buckets = rng.randint(1, 6)
+        buckets, all_tensors = [], []
+        for b in range(n_buckets):
+            ts = [_tensor(name=f"x{trial}_{b}_{i}")[1] for i in range(rng.randint(1, 5))]
+            all_tensors += ts
+            buckets.append(_recording_bucket(f"b{b}", ts, log))
+        backend.register_ordered_buckets(buckets)
+        rounds = rng.randint(1, 4)
+        for _ in range(rounds):
+            order = all_tensors[:]
+            rng.shuffle(order)
+            for t in order:
+                backend.mark_communication_ready(t, 0)
+            assert backend.wait_pending_comm_ops() == n_buckets
+        assert log == [f"b{b}" for b in range(n_buckets)] * rounds
+        backend.close()
+
+
 def test_padding_tensors_are_always_ready_and_all_padding_bucket_is_rejected():
     backend = bc.BaguaCommBackendPy(10, -1)
     log = []
