@@ -41,6 +41,7 @@ SOURCES = [
     "kernels/fused_allreduce.cu",
     "kernels/fused_bytegrad.cu",
     "kernels/fused_gossip.cu",
+    "kernels/fused_collectives.cu",
     "kernels/fused_emu.cc",
     "kernels/no_alloc.cu",
 ]

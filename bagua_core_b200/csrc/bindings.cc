@@ -189,6 +189,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("transport", [](PyComm& c) { return std::string(c.inner->transport_kind()); })
       .def("set_fused", [](PyComm& c, bool on) { c.inner->set_fused(on); },
            "Enable/disable the fused peer-memory kernels for ops on this communicator.")
+      .def("set_p2p_collectives", [](PyComm& c, bool on) { c.inner->set_p2p_collectives(on); },
+           "Run this communicator's own collectives (allreduce SUM/AVG, allgather, alltoall, reduce_scatter SUM/AVG, "
+           "broadcast, barrier) as peer-memory kernels instead of library calls (also BAGUA_B200_P2P_COLLECTIVES=1). "
+           "Must be set identically on every rank.")
+      .def("p2p_collectives", [](PyComm& c) { return c.inner->p2p_collectives(); })
       .def("fused_available", [](PyComm& c) { return c.inner->arena() != nullptr; },
            py::call_guard<py::gil_scoped_release>(),
            "Collective: sets up the peer arena if needed and reports whether fused kernels can be used.")
@@ -597,15 +602,57 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
             py::gil_scoped_release rel;
             a.lp_ring(px, pw, pl, pr, x[0].numel(), dtype_from_torch(x[0].scalar_type()), blocks);
           },
-          py::arg("x"), py::arg("weight"), py::arg("left"), py::arg("right"), py::arg("blocks"));
+          py::arg("x"), py::arg("weight"), py::arg("left"), py::arg("right"), py::arg("blocks"))
+      .def(
+          "collective",
+          [](fused::EmulatedArena& a, const std::string& kind, std::vector<at::Tensor> in, std::vector<at::Tensor> out,
+             bool symmetric, int root, bool average, int blocks) {
+            fused::EmuCollective k;
+            if (kind == "allgather") k = fused::EmuCollective::AllGather;
+            else if (kind == "alltoall") k = fused::EmuCollective::AllToAll;
+            else if (kind == "reduce_scatter") k = fused::EmuCollective::ReduceScatter;
+            else if (kind == "broadcast_direct") k = fused::EmuCollective::BroadcastDirect;
+            else if (kind == "broadcast_twophase") k = fused::EmuCollective::BroadcastTwoPhase;
+            else if (kind == "barrier") k = fused::EmuCollective::Barrier;
+            else throw BaguaError(ErrorKind::Communicator, "unknown collective '" + kind + "'");
+            std::vector<const void*> pi;
+            std::vector<void*> po;
+            size_t chunk_bytes = 0;
+            DType dt = DType::F32;
+            if (k != fused::EmuCollective::Barrier) {
+              BAGUA_CHECK(!out.empty(), Tensor, "one output per rank expected");
+              for (auto& t : out) {
+                check_pair(out[0], t);
+                po.push_back(t.data_ptr());
+              }
+              for (auto& t : in) {
+                BAGUA_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == out[0].scalar_type(), Tensor,
+                            "inputs must be contiguous CUDA tensors of the outputs' dtype");
+                pi.push_back(t.data_ptr());
+              }
+              dt = dtype_from_torch(out[0].scalar_type());
+              const size_t n = (size_t)a.nranks();
+              if (k == fused::EmuCollective::AllGather) chunk_bytes = out[0].nbytes() / n;
+              else if (k == fused::EmuCollective::AllToAll) chunk_bytes = out[0].nbytes() / n;
+              else chunk_bytes = out[0].nbytes();  // reduce-scatter output / broadcast buffer
+              if (k == fused::EmuCollective::AllGather || k == fused::EmuCollective::AllToAll)
+                BAGUA_CHECK(out[0].nbytes() % n == 0, Tensor, "output size must be divisible by the number of ranks");
+            }
+            py::gil_scoped_release rel;
+            a.collective(k, pi, po, chunk_bytes, dt, average ? 1.0f / (float)a.nranks() : 1.0f, root, symmetric, blocks);
+          },
+          py::arg("kind"), py::arg("inputs"), py::arg("outputs"), py::arg("symmetric") = false, py::arg("root") = 0,
+          py::arg("average") = false, py::arg("blocks") = 4,
+          "Runs one of the communicator collectives (allgather, alltoall, reduce_scatter, broadcast_direct, "
+          "broadcast_twophase, barrier) for all virtual ranks in one cooperative launch.");
 
   m.def(
       "protocol_model_check",
-      [](int nranks, int blocks, int n_ops, uint32_t seed, bool use_done_chain, int slow_rank) {
+      [](int nranks, int blocks, int n_ops, uint32_t seed, bool use_done_chain, int slow_rank, bool mix) {
         ProtocolModelResult r;
         {
           py::gil_scoped_release rel;
-          r = run_protocol_model(nranks, blocks, n_ops, seed, use_done_chain, slow_rank);
+          r = run_protocol_model(nranks, blocks, n_ops, seed, use_done_chain, slow_rank, mix);
         }
         py::dict d;
         d["errors"] = r.errors;
@@ -614,8 +661,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return d;
       },
       py::arg("nranks"), py::arg("blocks"), py::arg("n_ops"), py::arg("seed") = 0, py::arg("use_done_chain") = true,
-      py::arg("slow_rank") = -1,
-      "Runs the host-thread model of the fused kernels' signalling protocol and reports wrong sums / timeouts.");
+      py::arg("slow_rank") = -1, py::arg("mix") = false,
+      "Runs the host-thread model of the fused kernels' signalling protocol and reports wrong values / timeouts "
+      "(mix=True draws the ops from every kernel of the communicator, not only the all-reduces).");
   m.def(
       "debug_wait_timeout",
       [](int device, double wait_ms) {

@@ -2,6 +2,7 @@
 
 #include <cuda_runtime.h>
 
+#include "../kernels/fused.h"
 #include "arena.h"
 
 namespace bagua {
@@ -25,6 +26,7 @@ SingleCommunicator::SingleCommunicator(int rank, int nranks, int device_id, uint
     transport_ = make_nccl_transport(rank, nranks, device_id, stream, unique_id);
   }
   fused_enabled_ = env_long("BAGUA_B200_FUSED", 1) != 0;
+  p2p_collectives_ = env_long("BAGUA_B200_P2P_COLLECTIVES", 0) != 0;
 }
 
 SingleCommunicator::~SingleCommunicator() {
@@ -59,6 +61,20 @@ PeerArena* SingleCommunicator::arena() {
   return arena_.get();
 }
 
+PeerArena* SingleCommunicator::p2p_arena() {
+  if (!p2p_collectives_ || group_depth_ > 0) return nullptr;
+  return arena();
+}
+
+namespace {
+// Scale of a reduction the peer-memory kernels implement; 0 when they do not.
+float p2p_scale(ReductionOp op, int nranks) {
+  if (op == ReductionOp::SUM) return 1.0f;
+  if (op == ReductionOp::AVG) return 1.0f / (float)nranks;
+  return 0.0f;
+}
+}  // namespace
+
 void SingleCommunicator::check_device_status() {
   std::lock_guard<std::mutex> g(arena_mu_);
   if (!arena_) return;
@@ -80,14 +96,29 @@ void SingleCommunicator::allreduce(const RawTensor& send, RawTensor& recv, Reduc
   same_kind(send, recv, "allreduce");
   BAGUA_CHECK(send.num_elements_allocated() == recv.num_elements_allocated(), Communicator,
               "allreduce: send and recv sizes differ");
+  if (PeerArena* a = p2p_arena()) {
+    const float scale = p2p_scale(op, nranks_);
+    if (scale != 0.0f && fused::allreduce(*a, send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(),
+                                          send.dtype(), scale, (cudaStream_t)stream_))
+      return;
+  }
   transport_->allreduce(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype(), op);
 }
 void SingleCommunicator::allreduce_inplace(RawTensor& t, ReductionOp op) {
   check_live();
+  if (PeerArena* a = p2p_arena()) {
+    const float scale = p2p_scale(op, nranks_);
+    if (scale != 0.0f && fused::allreduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,
+                                          (cudaStream_t)stream_))
+      return;
+  }
   transport_->allreduce(t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), op);
 }
 void SingleCommunicator::broadcast(RawTensor& t, int root) {
   check_live();
+  BAGUA_CHECK(root >= 0 && root < nranks_, Communicator, "broadcast: root rank " << root << " out of range");
+  if (PeerArena* a = p2p_arena())
+    if (fused::broadcast(*a, t.data_ptr(), t.bytes_allocated(), root, (cudaStream_t)stream_)) return;
   transport_->broadcast(t.data_ptr(), t.num_elements_allocated(), t.dtype(), root);
 }
 void SingleCommunicator::reduce(const RawTensor& send, RawTensor& recv, int dst, ReductionOp op) {
@@ -116,12 +147,19 @@ void SingleCommunicator::alltoall(const RawTensor& send, RawTensor& recv) {
               "alltoall: send and recv sizes differ");
   BAGUA_CHECK(send.num_elements_allocated() % nranks_ == 0, Communicator,
               "alltoall: tensor size must be divisible by the number of ranks");
+  if (PeerArena* a = p2p_arena())
+    if (fused::alltoall(*a, send.data_ptr(), recv.data_ptr(), send.bytes_allocated() / (size_t)nranks_,
+                        (cudaStream_t)stream_))
+      return;
   transport_->alltoall(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated() / nranks_, send.dtype());
 }
 void SingleCommunicator::alltoall_inplace(RawTensor& t) {
   check_live();
   BAGUA_CHECK(t.num_elements_allocated() % nranks_ == 0, Communicator,
               "alltoall: tensor size must be divisible by the number of ranks");
+  if (PeerArena* a = p2p_arena())
+    if (fused::alltoall(*a, t.data_ptr(), t.data_ptr(), t.bytes_allocated() / (size_t)nranks_, (cudaStream_t)stream_))
+      return;
   // Exchange out of a copy: slot p is both what goes to p and where p's data lands.
   auto tmp = PoolRawTensor::allocate(t.device_id(), t.dtype(), t.num_elements_allocated(), stream_);
   kernels::copy_bytes(tmp->data_ptr(), t.data_ptr(), t.bytes_allocated(), t.ctx(stream_));
@@ -148,6 +186,8 @@ void SingleCommunicator::allgather(const RawTensor& send, RawTensor& recv) {
   same_kind(send, recv, "allgather");
   BAGUA_CHECK(send.num_elements_allocated() * nranks_ == recv.num_elements_allocated(), Communicator,
               "allgather: recv must hold nranks * send elements");
+  if (PeerArena* a = p2p_arena())
+    if (fused::allgather(*a, send.data_ptr(), recv.data_ptr(), send.bytes_allocated(), (cudaStream_t)stream_)) return;
   transport_->allgather(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype());
 }
 void SingleCommunicator::allgather_inplace(RawTensor& t) {
@@ -156,6 +196,10 @@ void SingleCommunicator::allgather_inplace(RawTensor& t) {
               "allgather: tensor size must be divisible by the number of ranks");
   const int64_t count = t.num_elements_allocated() / nranks_;
   const size_t es = dtype_bytes(t.dtype());
+  if (PeerArena* a = p2p_arena())
+    if (fused::allgather(*a, (char*)t.data_ptr() + (size_t)rank_ * count * es, t.data_ptr(), (size_t)count * es,
+                         (cudaStream_t)stream_))
+      return;
   transport_->allgather((char*)t.data_ptr() + (size_t)rank_ * count * es, t.data_ptr(), count, t.dtype());
 }
 void SingleCommunicator::gather(const RawTensor& send, RawTensor& recv, int dst) {
@@ -201,6 +245,12 @@ void SingleCommunicator::reduce_scatter(const RawTensor& send, RawTensor& recv, 
   same_kind(send, recv, "reduce_scatter");
   BAGUA_CHECK(recv.num_elements_allocated() * nranks_ == send.num_elements_allocated(), Communicator,
               "reduce_scatter: send must hold nranks * recv elements");
+  if (PeerArena* a = p2p_arena()) {
+    const float scale = p2p_scale(op, nranks_);
+    if (scale != 0.0f && fused::reduce_scatter(*a, send.data_ptr(), recv.data_ptr(), recv.num_elements_allocated(),
+                                               send.dtype(), scale, (cudaStream_t)stream_))
+      return;
+  }
   transport_->reduce_scatter(send.data_ptr(), recv.data_ptr(), recv.num_elements_allocated(), send.dtype(), op);
 }
 void SingleCommunicator::reduce_scatter_inplace(RawTensor& t, ReductionOp op) {
@@ -209,10 +259,23 @@ void SingleCommunicator::reduce_scatter_inplace(RawTensor& t, ReductionOp op) {
               "reduce_scatter: tensor size must be divisible by the number of ranks");
   const int64_t count = t.num_elements_allocated() / nranks_;
   const size_t es = dtype_bytes(t.dtype());
+  if (PeerArena* a = p2p_arena()) {
+    const float scale = p2p_scale(op, nranks_);
+    if (scale != 0.0f && fused::reduce_scatter(*a, t.data_ptr(), (char*)t.data_ptr() + (size_t)rank_ * count * es, count,
+                                               t.dtype(), scale, (cudaStream_t)stream_))
+      return;
+  }
   transport_->reduce_scatter(t.data_ptr(), (char*)t.data_ptr() + (size_t)rank_ * count * es, count, t.dtype(), op);
 }
 void SingleCommunicator::barrier() {
   check_live();
+  if (PeerArena* a = p2p_arena())
+    if (fused::barrier(*a, (cudaStream_t)stream_)) {
+      // like the library barrier, return only once every rank has arrived
+      BAGUA_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_));
+      check_device_status();
+      return;
+    }
   transport_->barrier();
 }
 

@@ -59,8 +59,14 @@ class SingleCommunicator {
   void reduce_scatter(const RawTensor& send, RawTensor& recv, ReductionOp op);
   void reduce_scatter_inplace(RawTensor& t, ReductionOp op);
   void barrier();
-  void group_start() { transport_->group_start(); }
-  void group_end() { transport_->group_end(); }
+  void group_start() {
+    ++group_depth_;
+    transport_->group_start();
+  }
+  void group_end() {
+    transport_->group_end();
+    if (group_depth_ > 0) --group_depth_;
+  }
 
   // Fused path.  Null when the communicator is on the host, has one rank, was disabled
   // (BAGUA_B200_FUSED=0 or set_fused(false)) or peer mapping failed.
@@ -69,16 +75,26 @@ class SingleCommunicator {
   bool fused_enabled() const { return fused_enabled_; }
   // Throws CommunicatorError if a fused kernel reported a device-side wait that ran out.
   void check_device_status();
+  // Peer-memory kernels for the collectives above (all-reduce SUM/AVG, all-gather, all-to-all,
+  // reduce-scatter SUM/AVG, broadcast, barrier) instead of library calls.  Off unless
+  // BAGUA_B200_P2P_COLLECTIVES=1 or set_p2p_collectives(true); calls inside a
+  // group_start()/group_end() pair and ineligible layouts always take the library path.
+  void set_p2p_collectives(bool on) { p2p_collectives_ = on; }
+  bool p2p_collectives() const { return p2p_collectives_; }
 
   Transport& transport() { return *transport_; }
 
  private:
   void check_live() const;
+  // The arena when this call may run as a peer-memory kernel, else null.
+  PeerArena* p2p_arena();
   int rank_, nranks_, device_id_;
   uint64_t stream_;
   std::unique_ptr<Transport> transport_;
   std::atomic<bool> aborted_{false};
   bool fused_enabled_ = true;
+  bool p2p_collectives_ = false;
+  int group_depth_ = 0;
   bool arena_tried_ = false;
   std::unique_ptr<PeerArena> arena_;
   std::mutex arena_mu_;

@@ -36,6 +36,22 @@ bool pair_average(PeerArena& arena, const void* in, void* out, int64_t n, DType 
 // Low-precision ring gossip step on weights x with replicas w (own), l / r (neighbours').
 bool lp_ring(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, DType dt, cudaStream_t stream);
 
+// ---- the communicator's own collectives over peer memory (fused_collectives.cu) -----------
+// Chunks are `chunk_bytes` long (a multiple of 16, 16-byte aligned buffers).  The in-place
+// forms of the library calls are accepted: all-gather with in == out + rank*chunk,
+// all-to-all with in == out, reduce-scatter with out == in + rank*chunk.
+// out[r] = rank r's `in`.
+bool allgather(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, cudaStream_t stream);
+// out[r] = chunk `rank` of rank r's `in`.
+bool alltoall(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, cudaStream_t stream);
+// out = scale * sum_r (chunk `rank` of rank r's `in`); f32 / f16 / bf16.
+bool reduce_scatter(PeerArena& arena, const void* in, void* out, int64_t chunk_elems, DType dt, float scale,
+                    cudaStream_t stream);
+// buf on every rank = buf on `root`.
+bool broadcast(PeerArena& arena, void* buf, size_t bytes, int root, cudaStream_t stream);
+// Returns (on the stream) once every rank's stream has reached the call.
+bool barrier(PeerArena& arena, cudaStream_t stream);
+
 // Test hook: launches a one-CTA kernel that waits `wait_ms` for a signal nobody sends
 // and returns the status record the host read back (code != 0 expected).  Uses only
 // rank-local memory; needs no peers.

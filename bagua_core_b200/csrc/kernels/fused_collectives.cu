@@ -1,0 +1,467 @@
+// Peer-memory kernels for the communicator's own collectives (all-gather, all-to-all,
+// reduce-scatter, broadcast, barrier), sm_100a.  The reference forwards each of these to
+// one library call (bagua-core-internal/src/communicators/mod.rs:560-1040); here each is one
+// launch that moves the data with 16-byte stores over NVLink and synchronises with the
+// arena's signal words, using the same block-b-pairs-with-block-b scheme as the fused
+// all-reduce: block b of every rank owns slice b of every chunk.
+//
+//   exchange (all-gather, all-to-all)
+//       through staging: my chunk for q → slot[me] of q's staging, signal, wait, copy the
+//       N-1 slots out of my own staging;
+//       symmetric output: my chunk for q → straight into q's output, between a "started"
+//       and a "stores done" signal exchange (no staging copy).
+//   reduce-scatter
+//       through staging: chunk q of my input → slot[me] of q's staging, signal, wait, sum
+//       the N contributions to chunk `me` in rank order (fp32 accumulation, rounded once);
+//       symmetric input: chunk `me` of all N inputs is loaded directly.
+//   broadcast
+//       small: the root stores the buffer into every peer's staging;
+//       large: scatter + all-gather, so that the root sends 2(N-1)/N·S instead of (N-1)·S:
+//       the root stores chunk q into q's staging and its own chunk into everyone's, then
+//       every other rank forwards the chunk it owns to the remaining ranks.
+//   barrier
+//       one CTA: signal every peer, wait for every peer.
+#include <cuda_runtime.h>
+
+#include "fused.h"
+#include "fused_emu.h"
+#include "peer_sync.cuh"
+#include "vec_ops.cuh"
+
+namespace bagua {
+namespace fused {
+
+namespace {
+
+using psync::Launch;
+
+struct PeerPtrs {
+  uint4* p[kArenaMaxRanks];
+};
+
+// Vector range of block b inside a chunk of `len` vectors that starts at vector c0.
+__device__ __forceinline__ void block_slice(const Launch& L, int64_t c0, int64_t len, int64_t& lo, int64_t& hi) {
+  lo = c0 + len * L.block / L.grid;
+  hi = c0 + len * (L.block + 1) / L.grid;
+}
+
+// ---------------------------------------------------------------------------------
+// exchange: out[r] = chunk that rank r holds for me.  src_stride = 0: every peer gets
+// in[0..cvec) (all-gather); src_stride = 1: peer q gets in[q*cvec..) (all-to-all).
+// ---------------------------------------------------------------------------------
+// `in` and `out` may overlap (in-place forms), so neither is declared restrict.
+__device__ __forceinline__ void exchange_body(const ArenaView& v, const Launch& L, const uint4* in, uint4* out,
+                                              int64_t cvec, int src_stride, int skip_local) {
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, cvec, lo, hi);
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    for (int i = 1; i < N; ++i) {
+      const int q = (me + i) % N;
+      uint4* dst = reinterpret_cast<uint4*>(v.staging[q]) + (int64_t)me * cvec;
+      copy_vecs(dst, in + (int64_t)src_stride * q * cvec, lo, hi);
+    }
+    if (!skip_local) copy_vecs(out + (int64_t)me * cvec, in + (int64_t)src_stride * me * cvec, lo, hi);
+    psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+  }
+  if (ok) {
+    const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+    for (int i = 1; i < N; ++i) {
+      const int r = (me + i) % N;
+      copy_vecs(out + (int64_t)r * cvec, mine + (int64_t)r * cvec, lo, hi);
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
+// Output in the symmetric heap: store straight into every rank's output.  First signal:
+// the peer has started, so its output may be overwritten; second signal: all stores into
+// my output have landed.
+__device__ __forceinline__ void exchange_sym_body(const ArenaView& v, const Launch& L, const uint4* in,
+                                                  const PeerPtrs& out, int64_t cvec, int src_stride,
+                                                  int skip_local) {
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, cvec, lo, hi);
+  psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+  bool ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+  if (ok) {
+    for (int i = skip_local ? 1 : 0; i < N; ++i) {
+      const int q = (me + i) % N;
+      copy_vecs(out.p[q] + (int64_t)me * cvec, in + (int64_t)src_stride * q * cvec, lo, hi);
+    }
+    psync::cta_signal_phase(v, L, 1, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
+  }
+  psync::cta_finish_op(v, L);
+}
+
+// ---------------------------------------------------------------------------------
+// reduce-scatter: out[0..cvec) = scale * sum_r in_r[me*cvec ..)
+// ---------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void reduce_scatter_body(const ArenaView& v, const Launch& L, const uint4* in, uint4* out,
+                                                    int64_t cvec, float scale) {
+  using O = VecOps<T>;
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, cvec, lo, hi);
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    for (int i = 1; i < N; ++i) {
+      const int q = (me + i) % N;
+      uint4* dst = reinterpret_cast<uint4*>(v.staging[q]) + (int64_t)me * cvec;
+      copy_vecs(dst, in + (int64_t)q * cvec, lo, hi);
+    }
+    psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+  }
+  if (ok) {
+    const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+    const uint4* own = in + (int64_t)me * cvec;
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) {
+      float a[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+      for (int r = 0; r < N; ++r) {
+        const uint4 x = (r == me) ? own[i] : mine[(int64_t)r * cvec + i];
+        O::acc(a, x);
+      }
+      out[i] = O::pack(a, scale);  // may alias own[i] (in-place form): read above, same thread
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
+struct ConstPeerPtrs {
+  const uint4* p[kArenaMaxRanks];
+};
+
+// Input in the symmetric heap: load chunk `me` of every rank's input directly.  The second
+// signal tells the peers that their input is no longer being read.
+template <typename T>
+__device__ __forceinline__ void reduce_scatter_sym_body(const ArenaView& v, const Launch& L, const ConstPeerPtrs& in,
+                                                        uint4* out, int64_t cvec, float scale) {
+  using O = VecOps<T>;
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, cvec, lo, hi);
+  psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+  bool ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+  if (ok) {
+    const int64_t base = (int64_t)me * cvec;
+    constexpr int U = 2;
+    int64_t i = lo + threadIdx.x;
+    for (; i + (U - 1) * kThreads < hi; i += U * kThreads) {
+      uint4 x[U][kArenaMaxRanks];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int r = 0; r < kArenaMaxRanks; ++r)
+          if (r < N) x[u][r] = in.p[r][base + i + u * kThreads];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float a[O::N];
+#pragma unroll
+        for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kArenaMaxRanks; ++r)
+          if (r < N) O::acc(a, x[u][r]);
+        out[i + u * kThreads] = O::pack(a, scale);
+      }
+    }
+    for (; i < hi; i += kThreads) {
+      float a[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+      for (int r = 0; r < N; ++r) O::acc(a, in.p[r][base + i]);
+      out[i] = O::pack(a, scale);
+    }
+    psync::cta_signal_phase(v, L, 1, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
+  }
+  psync::cta_finish_op(v, L);
+}
+
+// ---------------------------------------------------------------------------------
+// broadcast (in place on `buf`)
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void broadcast_direct_body(const ArenaView& v, const Launch& L, uint4* buf, int64_t nvec,
+                                                      int root) {
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, nvec, lo, hi);
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    if (me == root) {
+      for (int i = 1; i < N; ++i) {
+        const int q = (me + i) % N;
+        copy_vecs(reinterpret_cast<uint4*>(v.staging[q]), buf, lo, hi);
+      }
+      psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    } else {
+      ok = psync::cta_wait_phase(v, L, 0, 1u << root);
+      if (ok) copy_vecs(buf, reinterpret_cast<const uint4*>(v.staging[me]), lo, hi);
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
+__device__ __forceinline__ void broadcast_twophase_body(const ArenaView& v, const Launch& L, uint4* buf, int64_t nvec,
+                                                        int root) {
+  const int me = v.rank, N = v.nranks;
+  auto chunk_lo = [&](int c) { return nvec * c / N; };
+  auto slice = [&](int c, int64_t& lo, int64_t& hi) {
+    const int64_t c0 = chunk_lo(c);
+    block_slice(L, c0, chunk_lo(c + 1) - c0, lo, hi);
+  };
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    if (me == root) {
+      // chunk q goes to q; the root's own chunk goes to everyone (staging mirrors buf's indexing)
+      for (int i = 1; i < N; ++i) {
+        const int q = (me + i) % N;
+        uint4* dst = reinterpret_cast<uint4*>(v.staging[q]);
+        int64_t lo, hi;
+        slice(q, lo, hi);
+        copy_vecs(dst, buf, lo, hi);
+        slice(root, lo, hi);
+        copy_vecs(dst, buf, lo, hi);
+      }
+      psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    } else {
+      const uint32_t others = all_peers_mask(v) & ~(1u << root);
+      ok = psync::cta_wait_phase(v, L, 0, 1u << root);
+      if (ok) {
+        // forward the chunk I own to everyone but the root
+        const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+        int64_t lo, hi;
+        slice(me, lo, hi);
+        for (int i = 1; i < N; ++i) {
+          const int q = (me + i) % N;
+          if (q == root) continue;
+          copy_vecs(reinterpret_cast<uint4*>(v.staging[q]), mine, lo, hi);
+        }
+        psync::cta_signal_phase(v, L, 1, others);
+        ok = psync::cta_wait_phase(v, L, 1, others);
+      }
+      if (ok) {
+        const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+        for (int c = 0; c < N; ++c) {
+          int64_t lo, hi;
+          slice(c, lo, hi);
+          copy_vecs(buf, mine, lo, hi);
+        }
+      }
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
+__device__ __forceinline__ void barrier_body(const ArenaView& v, const Launch& L) {
+  psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+  psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+  psync::cta_finish_op(v, L);
+}
+
+// ---- real kernels: one launch per rank ---------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+    exchange_kernel(const __grid_constant__ ArenaView v, const uint4* in, uint4* out, int64_t cvec, int src_stride,
+                    int skip_local) {
+  exchange_body(v, psync::real_launch(), in, out, cvec, src_stride, skip_local);
+}
+__global__ void __launch_bounds__(kThreads)
+    exchange_sym_kernel(const __grid_constant__ ArenaView v, const uint4* in, const __grid_constant__ PeerPtrs out,
+                        int64_t cvec, int src_stride, int skip_local) {
+  exchange_sym_body(v, psync::real_launch(), in, out, cvec, src_stride, skip_local);
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    reduce_scatter_kernel(const __grid_constant__ ArenaView v, const uint4* in, uint4* out, int64_t cvec, float scale) {
+  reduce_scatter_body<T>(v, psync::real_launch(), in, out, cvec, scale);
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    reduce_scatter_sym_kernel(const __grid_constant__ ArenaView v, const __grid_constant__ ConstPeerPtrs in, uint4* out,
+                              int64_t cvec, float scale) {
+  reduce_scatter_sym_body<T>(v, psync::real_launch(), in, out, cvec, scale);
+}
+__global__ void __launch_bounds__(kThreads)
+    broadcast_kernel(const __grid_constant__ ArenaView v, uint4* buf, int64_t nvec, int root, int two_phase) {
+  if (two_phase)
+    broadcast_twophase_body(v, psync::real_launch(), buf, nvec, root);
+  else
+    broadcast_direct_body(v, psync::real_launch(), buf, nvec, root);
+}
+__global__ void __launch_bounds__(kThreads) barrier_kernel(const __grid_constant__ ArenaView v) {
+  barrier_body(v, psync::real_launch());
+}
+
+// ---- emulation kernel: the grids of all ranks in one cooperative launch -------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    collective_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int kind, int64_t cvec, int aux, float scale) {
+  const EmuRank& e = ranks[blockIdx.x / blocks];
+  const Launch L{(int)(blockIdx.x % blocks), blocks};
+  switch ((EmuCollective)kind) {
+    case EmuCollective::AllGather:
+    case EmuCollective::AllToAll: {
+      const int stride = kind == (int)EmuCollective::AllToAll ? 1 : 0;
+      const int skip_local = (aux >> 1) & 1;
+      if (aux & 1) {
+        PeerPtrs p;
+        for (int r = 0; r < kArenaMaxRanks; ++r) p.p[r] = (uint4*)e.sym_out[r];
+        exchange_sym_body(e.view, L, (const uint4*)e.in, p, cvec, stride, skip_local);
+      } else {
+        exchange_body(e.view, L, (const uint4*)e.in, (uint4*)e.out, cvec, stride, skip_local);
+      }
+      break;
+    }
+    case EmuCollective::ReduceScatter:
+      if (aux & 1) {
+        ConstPeerPtrs p;
+        for (int r = 0; r < kArenaMaxRanks; ++r) p.p[r] = (const uint4*)e.sym_in[r];
+        reduce_scatter_sym_body<T>(e.view, L, p, (uint4*)e.out, cvec, scale);
+      } else {
+        reduce_scatter_body<T>(e.view, L, (const uint4*)e.in, (uint4*)e.out, cvec, scale);
+      }
+      break;
+    case EmuCollective::BroadcastDirect: broadcast_direct_body(e.view, L, (uint4*)e.out, cvec, aux); break;
+    case EmuCollective::BroadcastTwoPhase: broadcast_twophase_body(e.view, L, (uint4*)e.out, cvec, aux); break;
+    case EmuCollective::Barrier: barrier_body(e.view, L); break;
+  }
+}
+
+// Largest staging an exchange may ask for; bigger requests take the library path.
+constexpr size_t kMaxStaging = (size_t)2 << 30;
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+bool exchange(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, int src_stride, cudaStream_t stream) {
+  const int N = arena.nranks(), me = arena.rank();
+  if (chunk_bytes == 0) return true;
+  if (chunk_bytes % 16 != 0 || !aligned16(in) || !aligned16(out)) return false;
+  const int64_t cvec = (int64_t)(chunk_bytes / 16);
+  const char* local_src = (const char*)in + (size_t)src_stride * me * chunk_bytes;
+  const int skip_local = (local_src == (const char*)out + (size_t)me * chunk_bytes) ? 1 : 0;
+  const bool in_place_a2a = src_stride == 1 && in == out;
+  const int grid = grid_for_bytes(chunk_bytes * (size_t)N, arena.max_blocks());
+  void* pout[kArenaMaxRanks];
+  if (!in_place_a2a && chunk_bytes >= ((size_t)64 << 10) && arena.sym_translate(out, chunk_bytes * (size_t)N, pout)) {
+    PeerPtrs p;
+    std::memset(&p, 0, sizeof(p));
+    for (int r = 0; r < N; ++r) p.p[r] = (uint4*)pout[r];
+    ArenaView v = arena.next_view(grid, 0);
+    exchange_sym_kernel<<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, p, cvec, src_stride, skip_local);
+  } else {
+    if (chunk_bytes * (size_t)N > kMaxStaging) return false;
+    arena.ensure_staging(chunk_bytes * (size_t)N);
+    ArenaView v = arena.next_view(grid, 0);
+    exchange_kernel<<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, cvec, src_stride, skip_local);
+  }
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+template <typename T>
+bool reduce_scatter_t(PeerArena& arena, const void* in, void* out, int64_t chunk_elems, float scale,
+                      cudaStream_t stream) {
+  const int N = arena.nranks();
+  const size_t chunk_bytes = (size_t)chunk_elems * sizeof(T);
+  if (chunk_bytes == 0) return true;
+  if (chunk_bytes % 16 != 0 || !aligned16(in) || !aligned16(out)) return false;
+  const int64_t cvec = (int64_t)(chunk_bytes / 16);
+  const int grid = grid_for_bytes(chunk_bytes * (size_t)N, arena.max_blocks());
+  void* pin[kArenaMaxRanks];
+  if (chunk_bytes >= ((size_t)64 << 10) && arena.sym_translate(in, chunk_bytes * (size_t)N, pin)) {
+    ConstPeerPtrs p;
+    std::memset(&p, 0, sizeof(p));
+    for (int r = 0; r < N; ++r) p.p[r] = (const uint4*)pin[r];
+    ArenaView v = arena.next_view(grid, 0);
+    reduce_scatter_sym_kernel<T><<<grid, kThreads, 0, stream>>>(v, p, (uint4*)out, cvec, scale);
+  } else {
+    if (chunk_bytes * (size_t)N > kMaxStaging) return false;
+    arena.ensure_staging(chunk_bytes * (size_t)N);
+    ArenaView v = arena.next_view(grid, 0);
+    reduce_scatter_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, cvec, scale);
+  }
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+template <typename K, typename... Args>
+void coop_launch_all_ranks(K kernel, int grid, Args... args) {
+  int per_sm = 0, sms = 0, dev = 0;
+  BAGUA_CUDA_CHECK(cudaGetDevice(&dev));
+  BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+  BAGUA_CHECK(grid <= per_sm * sms, Communicator,
+              "emulation needs " << grid << " co-resident blocks, the device holds " << per_sm * sms);
+  void* argv[] = {(void*)&args...};
+  BAGUA_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(kThreads), argv, 0, 0));
+}
+
+}  // namespace
+
+bool allgather(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, cudaStream_t stream) {
+  return exchange(arena, in, out, chunk_bytes, 0, stream);
+}
+
+bool alltoall(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, cudaStream_t stream) {
+  return exchange(arena, in, out, chunk_bytes, 1, stream);
+}
+
+bool reduce_scatter(PeerArena& arena, const void* in, void* out, int64_t chunk_elems, DType dt, float scale,
+                    cudaStream_t stream) {
+  switch (dt) {
+    case DType::F32: return reduce_scatter_t<float>(arena, in, out, chunk_elems, scale, stream);
+    case DType::F16: return reduce_scatter_t<__half>(arena, in, out, chunk_elems, scale, stream);
+    case DType::BF16: return reduce_scatter_t<__nv_bfloat16>(arena, in, out, chunk_elems, scale, stream);
+    default: return false;
+  }
+}
+
+bool broadcast(PeerArena& arena, void* buf, size_t bytes, int root, cudaStream_t stream) {
+  const int N = arena.nranks();
+  if (root < 0 || root >= N) return false;
+  if (bytes == 0) return true;
+  if (bytes % 16 != 0 || !aligned16(buf) || bytes > kMaxStaging) return false;
+  const int64_t nvec = (int64_t)(bytes / 16);
+  // Direct: the root sends (N-1)·S in one hop.  Two-phase: 2(N-1)/N·S per GPU in two hops.
+  const int two_phase = (N > 2 && bytes * (size_t)(N - 1) > ((size_t)4 << 20)) ? 1 : 0;
+  const int grid = grid_for_bytes(bytes, arena.max_blocks());
+  arena.ensure_staging(bytes);
+  ArenaView v = arena.next_view(grid, 0);
+  broadcast_kernel<<<grid, kThreads, 0, stream>>>(v, (uint4*)buf, nvec, root, two_phase);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+bool barrier(PeerArena& arena, cudaStream_t stream) {
+  ArenaView v = arena.next_view(1, 0);
+  barrier_kernel<<<1, kThreads, 0, stream>>>(v);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+void emu_launch_collective(const EmuRank* dev, int nranks, int blocks, EmuCollective kind, int64_t cvec, DType dt,
+                           int aux, float scale) {
+  const int grid = nranks * blocks;
+  const int k = (int)kind;
+  switch (dt) {
+    case DType::F16: coop_launch_all_ranks(collective_emu_kernel<__half>, grid, dev, blocks, k, cvec, aux, scale); break;
+    case DType::BF16:
+      coop_launch_all_ranks(collective_emu_kernel<__nv_bfloat16>, grid, dev, blocks, k, cvec, aux, scale);
+      break;
+    default: coop_launch_all_ranks(collective_emu_kernel<float>, grid, dev, blocks, k, cvec, aux, scale); break;
+  }
+}
+
+}  // namespace fused
+}  // namespace bagua

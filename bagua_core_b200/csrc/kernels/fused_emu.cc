@@ -130,6 +130,52 @@ void EmulatedArena::pair_average(const std::vector<const void*>& in, const std::
   finish("pair average");
 }
 
+void EmulatedArena::collective(EmuCollective kind, const std::vector<const void*>& in, const std::vector<void*>& out,
+                               size_t chunk_bytes, DType dt, float scale, int root, bool symmetric, int blocks) {
+  std::vector<EmuRank> host((size_t)nranks_);
+  for (auto& h : host) std::memset(&h, 0, sizeof(h));
+  const size_t N = (size_t)nranks_;
+  size_t need = 0;
+  int aux = 0;
+  if (kind == EmuCollective::Barrier) {
+    blocks = 1;
+  } else {
+    BAGUA_CHECK(chunk_bytes > 0 && chunk_bytes % 16 == 0 && out.size() == N, Tensor,
+                "emulated collective: need one 16-byte-multiple buffer per rank");
+    const bool bcast = kind == EmuCollective::BroadcastDirect || kind == EmuCollective::BroadcastTwoPhase;
+    if (bcast) {
+      BAGUA_CHECK(root >= 0 && root < nranks_, Communicator, "emulated broadcast: root out of range");
+      need = chunk_bytes;
+      aux = root;
+    } else {
+      BAGUA_CHECK(in.size() == N, Tensor, "emulated collective: one input per rank expected");
+      need = symmetric ? 0 : N * chunk_bytes;
+      bool in_place = true;
+      for (size_t r = 0; r < N; ++r) {
+        const char* local = kind == EmuCollective::AllToAll ? (const char*)out[r] : (const char*)out[r] + r * chunk_bytes;
+        in_place = in_place && (const char*)in[r] == local;
+      }
+      if (kind == EmuCollective::ReduceScatter) in_place = false;
+      BAGUA_CHECK(!(symmetric && kind == EmuCollective::AllToAll && in_place), Tensor,
+                  "an in-place all-to-all cannot store into the peers' buffers directly");
+      aux = (symmetric ? 1 : 0) | (in_place ? 2 : 0);
+    }
+    for (size_t r = 0; r < N; ++r) {
+      BAGUA_CHECK((uintptr_t)out[r] % 16 == 0 && (bcast || (uintptr_t)in[r] % 16 == 0), Tensor,
+                  "buffers must be 16-byte aligned");
+      host[r].in = bcast ? nullptr : in[r];
+      host[r].out = out[r];
+      for (size_t q = 0; q < N; ++q) {
+        host[r].sym_in[q] = bcast ? nullptr : in[q];
+        host[r].sym_out[q] = out[q];
+      }
+    }
+  }
+  EmuRank* dev = prepare(host, blocks, 0, need);
+  emu_launch_collective(dev, nranks_, blocks, kind, (int64_t)(chunk_bytes / 16), dt, aux, scale);
+  finish("collective");
+}
+
 void EmulatedArena::bytegrad(const std::vector<void*>& buckets, int64_t n, DType dt, bool average, int blocks) {
   BAGUA_CHECK((int)buckets.size() == nranks_ && n % ((int64_t)16 * nranks_) == 0, Tensor,
               "emulated ByteGrad: n must be a multiple of 16 * nranks");

@@ -34,6 +34,7 @@ struct EmuRank {
 };
 
 enum class EmuAllreduceMode { OneShot = 1, TwoShot = 2, Symmetric = 3 };
+enum class EmuCollective { AllGather = 1, AllToAll = 2, ReduceScatter = 3, BroadcastDirect = 4, BroadcastTwoPhase = 5, Barrier = 6 };
 
 class EmulatedArena {
  public:
@@ -53,6 +54,13 @@ class EmulatedArena {
                     const std::vector<int>& peers, int blocks, bool symmetric = false);
   void lp_ring(const std::vector<void*>& x, const std::vector<void*>& w, const std::vector<void*>& l,
                const std::vector<void*>& r, int64_t n, DType dt, int blocks);
+  // The communicator's own collectives.  AllGather / AllToAll / ReduceScatter: `chunk_bytes`
+  // per chunk, in[r] / out[r] per rank (in-place forms allowed); `symmetric` selects the
+  // variants that store into (exchange) or load from (reduce-scatter) the peers' buffers
+  // directly.  Broadcast*: `out[r]` is rank r's buffer of `chunk_bytes`, `root` the source.
+  // Barrier: no buffers.
+  void collective(EmuCollective kind, const std::vector<const void*>& in, const std::vector<void*>& out,
+                  size_t chunk_bytes, DType dt, float scale, int root, bool symmetric, int blocks);
   void set_deadline_ms(double ms) { deadline_ns_ = (uint64_t)(ms * 1e6); }
   uint32_t epoch() const { return epoch_; }
 
@@ -76,6 +84,10 @@ class EmulatedArena {
 void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
                           EmuAllreduceMode mode, int64_t aux_vecs);
 void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, bool symmetric);
+// aux: bit 0 = symmetric variant, bit 1 = local chunk already in place (exchange);
+// the root rank for the broadcasts.
+void emu_launch_collective(const EmuRank* dev, int nranks, int blocks, EmuCollective kind, int64_t cvec, DType dt,
+                           int aux, float scale);
 void emu_launch_bytegrad(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
                          size_t slot_bytes, size_t scratch_off);
 void emu_launch_lp_ring(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, size_t slot_bytes,

@@ -2,14 +2,18 @@
 //
 // compute-sanitizer cannot be run on the GPU pool, so the protocol (epoch-valued phase
 // words, the `done` chain that guards staging reuse, block-to-block pairing) is restated
-// here with std::thread + std::atomic and the same acquire/release structure, and run
-// under randomised and adversarial schedules:
+// here with std::thread + std::atomic and the same acquire/release structure and the same
+// index arithmetic as the kernels, and run under randomised and adversarial schedules:
 //   * every (rank, block) pair is a thread; payload words are relaxed atomics (the GPU's
 //     weak accesses), signal words use release stores / acquire loads;
-//   * a run is a sequence of all-reduces that mixes the one-shot and the two-shot layout,
-//     so consecutive ops reuse the same staging addresses for different purposes;
+//   * a run is a sequence of ops.  With `mix = false` it alternates the one-shot and the
+//     two-shot all-reduce, so consecutive ops reuse the same staging addresses for different
+//     purposes; with `mix = true` it draws from every kernel of the communicator: the two
+//     all-reduces, all-gather, all-to-all and reduce-scatter through staging, all-gather into
+//     and reduce-scatter out of peer-visible ("symmetric") buffers, both broadcasts and the
+//     barrier;
 //   * inputs depend on (op, rank, index): any premature overwrite or stale read shows up
-//     as a wrong sum; every wait is bounded and counted when it runs out.
+//     as a wrong value; every wait is bounded and counted when it runs out.
 // With `use_done_chain = false` the model drops the wait on the peers' `done` words; an
 // adversarial delay then corrupts results, which shows that the chain is what makes the
 // reuse safe.
@@ -24,15 +28,30 @@ namespace bagua {
 
 namespace {
 
+enum class Kind {
+  TwoShot,
+  OneShot,
+  AllGather,
+  AllToAll,
+  ReduceScatter,
+  AllGatherSym,
+  ReduceScatterSym,
+  BroadcastDirect,
+  BroadcastTwoPhase,
+  Barrier,
+  kCount
+};
+
 struct RankMem {
   std::vector<std::atomic<uint32_t>> staging;
+  std::vector<std::atomic<uint32_t>> sym;     // peer-visible user buffer (symmetric heap)
   std::vector<std::atomic<uint32_t>> done;    // [nranks]
   std::vector<std::atomic<uint32_t>> phase;   // [2][nranks][blocks]
   std::atomic<uint32_t> counter{0};
-  std::vector<uint32_t> data;                 // the rank's bucket (only its own threads touch it)
-  RankMem(size_t stage_words, int nranks, int blocks)
-      : staging(stage_words), done((size_t)nranks), phase((size_t)2 * nranks * blocks) {
+  RankMem(size_t stage_words, size_t sym_words, int nranks, int blocks)
+      : staging(stage_words), sym(sym_words), done((size_t)nranks), phase((size_t)2 * nranks * blocks) {
     for (auto& a : staging) a.store(0xdeadbeefu);
+    for (auto& a : sym) a.store(0xfeedf00du);
     for (auto& a : done) a.store(0);
     for (auto& a : phase) a.store(0);
   }
@@ -65,116 +84,300 @@ struct Model {
 };
 
 struct OpDesc {
-  int64_t nvec;
-  bool oneshot;
+  Kind kind;
+  int64_t nvec;  // whole-buffer ops: words per rank; chunked ops: words per chunk
+  int root;
 };
 
-void block_thread(Model& m, int me, int b, const std::vector<OpDesc>& ops, uint32_t seed) {
-  std::mt19937 rng(seed);
-  auto jitter = [&](int max_us) {
+// One block of one rank running the whole op sequence.
+struct Block {
+  Model& m;
+  const int me, b, N, G;
+  RankMem& mine;
+  std::mt19937 rng;
+  uint32_t k = 0, epoch = 0;
+  uint64_t bad = 0;
+
+  Block(Model& model, int rank, int block, uint32_t seed)
+      : m(model), me(rank), b(block), N(model.N), G(model.G), mine(*model.mem[rank]), rng(seed) {}
+
+  void jitter(int max_us) {
     if (max_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(rng() % (uint32_t)max_us));
-  };
-  const int N = m.N, G = m.G;
-  RankMem& mine = *m.mem[me];
-  for (uint32_t k = 0; k < ops.size(); ++k) {
-    const uint32_t epoch = k + 1;
-    const int64_t nvec = ops[k].nvec;
-    // the bucket of this op (block 0 of each rank fills it; others wait for it via the counter trick
-    // of a real launch: here every block simply fills its own slice before use)
-    auto in = [&](int64_t i) { return Model::input(k, me, i); };
-    jitter(50);
-    // wait for the peers' previous op to be completely finished
-    if (m.use_done)
-      for (int q = 0; q < N; ++q)
-        if (q != me && !m.wait(mine.done[q], epoch - 1)) return;
-    uint64_t bad = 0;
-    if (ops[k].oneshot) {
-      const int64_t lo = nvec * b / G, hi = nvec * (b + 1) / G;
-      for (int s = 1; s < N; ++s) {
-        const int q = (me + s) % N;
-        for (int64_t i = lo; i < hi; ++i)
-          m.mem[q]->staging[(size_t)me * nvec + i].store(in(i), std::memory_order_relaxed);
+  }
+  uint32_t in(int64_t i) const { return Model::input(k, me, i); }
+  uint32_t all_peers() const { return ((1u << N) - 1u) & ~(1u << me); }
+  void signal(int ph, uint32_t mask) {
+    for (int q = 0; q < N; ++q)
+      if ((mask >> q) & 1u) m.phase(q, ph, me, b).store(epoch, std::memory_order_release);
+  }
+  bool wait_phase(int ph, uint32_t mask) {
+    for (int q = 0; q < N; ++q)
+      if (((mask >> q) & 1u) && !m.wait(m.phase(me, ph, q, b), epoch)) return false;
+    return true;
+  }
+  bool wait_prev_done() {
+    if (!m.use_done) return true;
+    for (int q = 0; q < N; ++q)
+      if (q != me && !m.wait(mine.done[q], epoch - 1)) return false;
+    return true;
+  }
+  void slice(int64_t c0, int64_t len, int64_t& lo, int64_t& hi) const {
+    lo = c0 + len * b / G;
+    hi = c0 + len * (b + 1) / G;
+  }
+  static void put(std::atomic<uint32_t>& w, uint32_t v) { w.store(v, std::memory_order_relaxed); }
+  static uint32_t get(const std::atomic<uint32_t>& w) { return w.load(std::memory_order_relaxed); }
+
+  bool oneshot(int64_t nvec) {
+    if (!wait_prev_done()) return false;
+    int64_t lo, hi;
+    slice(0, nvec, lo, hi);
+    for (int s = 1; s < N; ++s) {
+      const int q = (me + s) % N;
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)me * nvec + i], in(i));
+    }
+    signal(0, all_peers());
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    for (int64_t i = lo; i < hi; ++i) {
+      uint32_t sum = 0, expect = 0;
+      for (int r = 0; r < N; ++r) {
+        sum += (r == me) ? in(i) : get(mine.staging[(size_t)r * nvec + i]);
+        expect += Model::input(k, r, i);
       }
-      for (int q = 0; q < N; ++q)
-        if (q != me) m.phase(q, 0, me, b).store(epoch, std::memory_order_release);
-      for (int q = 0; q < N; ++q)
-        if (q != me && !m.wait(m.phase(me, 0, q, b), epoch)) return;
-      jitter(20);
+      if (sum != expect) ++bad;
+    }
+    return true;
+  }
+
+  bool twoshot(int64_t nvec) {
+    if (!wait_prev_done()) return false;
+    const int64_t max_chunk = (nvec + N - 1) / N, ag_base = (int64_t)N * max_chunk;
+    auto chunk_lo = [&](int c) { return nvec * c / N; };
+    auto cslice = [&](int c, int64_t& lo, int64_t& hi) { slice(chunk_lo(c), chunk_lo(c + 1) - chunk_lo(c), lo, hi); };
+    for (int s = 1; s < N; ++s) {  // step A
+      const int q = (me + s) % N;
+      int64_t lo, hi;
+      cslice(q, lo, hi);
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)(me * max_chunk + (i - chunk_lo(q)))], in(i));
+    }
+    signal(0, all_peers());
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    {  // step B
+      int64_t lo, hi;
+      cslice(me, lo, hi);
       for (int64_t i = lo; i < hi; ++i) {
         uint32_t sum = 0, expect = 0;
         for (int r = 0; r < N; ++r) {
-          sum += (r == me) ? in(i) : mine.staging[(size_t)r * nvec + i].load(std::memory_order_relaxed);
+          sum += (r == me) ? in(i) : get(mine.staging[(size_t)(r * max_chunk + (i - chunk_lo(me)))]);
           expect += Model::input(k, r, i);
         }
         if (sum != expect) ++bad;
-      }
-    } else {
-      const int64_t max_chunk = (nvec + N - 1) / N, ag_base = (int64_t)N * max_chunk;
-      auto chunk_lo = [&](int c) { return nvec * c / N; };
-      auto slice = [&](int c, int64_t& lo, int64_t& hi) {
-        const int64_t c0 = chunk_lo(c), len = chunk_lo(c + 1) - c0;
-        lo = c0 + len * b / G;
-        hi = c0 + len * (b + 1) / G;
-      };
-      for (int s = 1; s < N; ++s) {  // step A
-        const int q = (me + s) % N;
-        int64_t lo, hi;
-        slice(q, lo, hi);
-        for (int64_t i = lo; i < hi; ++i)
-          m.mem[q]->staging[(size_t)(me * max_chunk + (i - chunk_lo(q)))].store(in(i), std::memory_order_relaxed);
-      }
-      for (int q = 0; q < N; ++q)
-        if (q != me) m.phase(q, 0, me, b).store(epoch, std::memory_order_release);
-      for (int q = 0; q < N; ++q)
-        if (q != me && !m.wait(m.phase(me, 0, q, b), epoch)) return;
-      jitter(20);
-      {  // step B
-        int64_t lo, hi;
-        slice(me, lo, hi);
-        for (int64_t i = lo; i < hi; ++i) {
-          uint32_t sum = 0, expect = 0;
-          for (int r = 0; r < N; ++r) {
-            sum += (r == me) ? in(i)
-                             : mine.staging[(size_t)(r * max_chunk + (i - chunk_lo(me)))].load(std::memory_order_relaxed);
-            expect += Model::input(k, r, i);
-          }
-          if (sum != expect) ++bad;
-          for (int q = 0; q < N; ++q)
-            if (q != me) m.mem[q]->staging[(size_t)(ag_base + i)].store(sum, std::memory_order_relaxed);
-        }
-      }
-      for (int q = 0; q < N; ++q)
-        if (q != me) m.phase(q, 1, me, b).store(epoch, std::memory_order_release);
-      for (int q = 0; q < N; ++q)
-        if (q != me && !m.wait(m.phase(me, 1, q, b), epoch)) return;
-      if (me == m.slow_rank) std::this_thread::sleep_for(std::chrono::milliseconds(15));  // adversarial delay
-      for (int s = 1; s < N; ++s) {  // step C
-        const int q = (me + s) % N;
-        int64_t lo, hi;
-        slice(q, lo, hi);
-        for (int64_t i = lo; i < hi; ++i) {
-          uint32_t expect = 0;
-          for (int r = 0; r < N; ++r) expect += Model::input(k, r, i);
-          if (mine.staging[(size_t)(ag_base + i)].load(std::memory_order_relaxed) != expect) ++bad;
-        }
+        for (int q = 0; q < N; ++q)
+          if (q != me) put(m.mem[q]->staging[(size_t)(ag_base + i)], sum);
       }
     }
-    if (bad) m.errors += bad;
-    // the last block of the rank to finish tells every peer that this rank is done with the op
-    if (mine.counter.fetch_add(1, std::memory_order_acq_rel) == (uint32_t)G - 1) {
-      mine.counter.store(0, std::memory_order_relaxed);
-      for (int q = 0; q < N; ++q) m.mem[q]->done[me].store(epoch, std::memory_order_release);
+    signal(1, all_peers());
+    if (!wait_phase(1, all_peers())) return false;
+    if (me == m.slow_rank) std::this_thread::sleep_for(std::chrono::milliseconds(15));  // adversarial delay
+    for (int s = 1; s < N; ++s) {  // step C
+      const int q = (me + s) % N;
+      int64_t lo, hi;
+      cslice(q, lo, hi);
+      for (int64_t i = lo; i < hi; ++i) {
+        uint32_t expect = 0;
+        for (int r = 0; r < N; ++r) expect += Model::input(k, r, i);
+        if (get(mine.staging[(size_t)(ag_base + i)]) != expect) ++bad;
+      }
     }
-    // kernel boundary on the rank's stream: no block starts op k+1 before every block of
-    // the rank has finished op k (the rank's own slot of `done` stands in for it here)
-    if (!m.wait(mine.done[me], epoch)) return;
+    return true;
   }
-}
+
+  // all-gather (stride 0) / all-to-all (stride 1) through staging
+  bool exchange(int64_t cvec, int stride) {
+    if (!wait_prev_done()) return false;
+    int64_t lo, hi;
+    slice(0, cvec, lo, hi);
+    for (int s = 1; s < N; ++s) {
+      const int q = (me + s) % N;
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)(me * cvec + i)], in((int64_t)stride * q * cvec + i));
+    }
+    signal(0, all_peers());
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    for (int s = 1; s < N; ++s) {
+      const int r = (me + s) % N;
+      for (int64_t i = lo; i < hi; ++i)
+        if (get(mine.staging[(size_t)(r * cvec + i)]) != Model::input(k, r, (int64_t)stride * me * cvec + i)) ++bad;
+    }
+    return true;
+  }
+
+  // all-gather straight into every rank's peer-visible output
+  bool exchange_sym(int64_t cvec) {
+    int64_t lo, hi;
+    slice(0, cvec, lo, hi);
+    signal(0, all_peers());
+    if (!wait_phase(0, all_peers())) return false;
+    for (int s = 0; s < N; ++s) {
+      const int q = (me + s) % N;
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->sym[(size_t)(me * cvec + i)], in(i));
+    }
+    signal(1, all_peers());
+    if (!wait_phase(1, all_peers())) return false;
+    jitter(20);
+    for (int r = 0; r < N; ++r)
+      for (int64_t i = lo; i < hi; ++i)
+        if (get(mine.sym[(size_t)(r * cvec + i)]) != Model::input(k, r, i)) ++bad;
+    return true;
+  }
+
+  bool reduce_scatter(int64_t cvec) {
+    if (!wait_prev_done()) return false;
+    int64_t lo, hi;
+    slice(0, cvec, lo, hi);
+    for (int s = 1; s < N; ++s) {
+      const int q = (me + s) % N;
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)(me * cvec + i)], in((int64_t)q * cvec + i));
+    }
+    signal(0, all_peers());
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    for (int64_t i = lo; i < hi; ++i) {
+      uint32_t sum = 0, expect = 0;
+      for (int r = 0; r < N; ++r) {
+        sum += (r == me) ? in((int64_t)me * cvec + i) : get(mine.staging[(size_t)(r * cvec + i)]);
+        expect += Model::input(k, r, (int64_t)me * cvec + i);
+      }
+      if (sum != expect) ++bad;
+    }
+    return true;
+  }
+
+  // reduce-scatter that loads chunk `me` of every rank's peer-visible input
+  bool reduce_scatter_sym(int64_t cvec) {
+    int64_t lo, hi;
+    slice(0, cvec, lo, hi);
+    // the input is complete before the kernel starts; here block b provides slice b of every chunk
+    for (int c = 0; c < N; ++c)
+      for (int64_t i = lo; i < hi; ++i) put(mine.sym[(size_t)(c * cvec + i)], in((int64_t)c * cvec + i));
+    signal(0, all_peers());
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    for (int64_t i = lo; i < hi; ++i) {
+      uint32_t sum = 0, expect = 0;
+      for (int r = 0; r < N; ++r) {
+        sum += get(m.mem[r]->sym[(size_t)(me * cvec + i)]);
+        expect += Model::input(k, r, (int64_t)me * cvec + i);
+      }
+      if (sum != expect) ++bad;
+    }
+    signal(1, all_peers());
+    return wait_phase(1, all_peers());
+  }
+
+  bool broadcast_direct(int64_t nvec, int root) {
+    if (!wait_prev_done()) return false;
+    int64_t lo, hi;
+    slice(0, nvec, lo, hi);
+    if (me == root) {
+      for (int s = 1; s < N; ++s) {
+        const int q = (me + s) % N;
+        for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)i], in(i));
+      }
+      signal(0, all_peers());
+    } else {
+      if (!wait_phase(0, 1u << root)) return false;
+      jitter(20);
+      for (int64_t i = lo; i < hi; ++i)
+        if (get(mine.staging[(size_t)i]) != Model::input(k, root, i)) ++bad;
+    }
+    return true;
+  }
+
+  bool broadcast_twophase(int64_t nvec, int root) {
+    if (!wait_prev_done()) return false;
+    auto chunk_lo = [&](int c) { return nvec * c / N; };
+    auto cslice = [&](int c, int64_t& lo, int64_t& hi) { slice(chunk_lo(c), chunk_lo(c + 1) - chunk_lo(c), lo, hi); };
+    if (me == root) {
+      for (int s = 1; s < N; ++s) {
+        const int q = (me + s) % N;
+        int64_t lo, hi;
+        cslice(q, lo, hi);
+        for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)i], in(i));
+        cslice(root, lo, hi);
+        for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)i], in(i));
+      }
+      signal(0, all_peers());
+      return true;
+    }
+    const uint32_t others = all_peers() & ~(1u << root);
+    if (!wait_phase(0, 1u << root)) return false;
+    {
+      int64_t lo, hi;
+      cslice(me, lo, hi);
+      for (int s = 1; s < N; ++s) {
+        const int q = (me + s) % N;
+        if (q == root) continue;
+        for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)i], get(mine.staging[(size_t)i]));
+      }
+    }
+    signal(1, others);
+    if (!wait_phase(1, others)) return false;
+    jitter(20);
+    for (int c = 0; c < N; ++c) {
+      int64_t lo, hi;
+      cslice(c, lo, hi);
+      for (int64_t i = lo; i < hi; ++i)
+        if (get(mine.staging[(size_t)i]) != Model::input(k, root, i)) ++bad;
+    }
+    return true;
+  }
+
+  bool barrier() {
+    signal(0, all_peers());
+    return wait_phase(0, all_peers());
+  }
+
+  void run(const std::vector<OpDesc>& ops) {
+    for (k = 0; k < ops.size(); ++k) {
+      epoch = k + 1;
+      const OpDesc& d = ops[k];
+      bad = 0;
+      jitter(50);
+      bool ok = false;
+      switch (d.kind) {
+        case Kind::OneShot: ok = oneshot(d.nvec); break;
+        case Kind::TwoShot: ok = twoshot(d.nvec); break;
+        case Kind::AllGather: ok = exchange(d.nvec, 0); break;
+        case Kind::AllToAll: ok = exchange(d.nvec, 1); break;
+        case Kind::ReduceScatter: ok = reduce_scatter(d.nvec); break;
+        case Kind::AllGatherSym: ok = exchange_sym(d.nvec); break;
+        case Kind::ReduceScatterSym: ok = reduce_scatter_sym(d.nvec); break;
+        case Kind::BroadcastDirect: ok = broadcast_direct(d.nvec, d.root); break;
+        case Kind::BroadcastTwoPhase: ok = broadcast_twophase(d.nvec, d.root); break;
+        case Kind::Barrier: ok = barrier(); break;
+        default: break;
+      }
+      if (!ok) return;
+      if (bad) m.errors += bad;
+      // the last block of the rank to finish tells every peer that this rank is done with the op
+      if (mine.counter.fetch_add(1, std::memory_order_acq_rel) == (uint32_t)G - 1) {
+        mine.counter.store(0, std::memory_order_relaxed);
+        for (int q = 0; q < N; ++q) m.mem[q]->done[me].store(epoch, std::memory_order_release);
+      }
+      // kernel boundary on the rank's stream: no block starts op k+1 before every block of
+      // the rank has finished op k (the rank's own slot of `done` stands in for it here)
+      if (!m.wait(mine.done[me], epoch)) return;
+    }
+  }
+};
 
 }  // namespace
 
 ProtocolModelResult run_protocol_model(int nranks, int blocks, int n_ops, uint32_t seed, bool use_done_chain,
-                                       int slow_rank) {
+                                       int slow_rank, bool mix) {
   ProtocolModelResult res;
   if (nranks < 2 || nranks > 8 || blocks < 1 || blocks > 8 || n_ops < 1) {
     res.errors = 1;
@@ -182,13 +385,33 @@ ProtocolModelResult run_protocol_model(int nranks, int blocks, int n_ops, uint32
   }
   std::mt19937 rng(seed);
   std::vector<OpDesc> ops;
-  int64_t max_words = 0;
+  int64_t max_words = 0, max_sym = 1;
   for (int k = 0; k < n_ops; ++k) {
     OpDesc d;
+    d.root = (int)(rng() % (uint32_t)nranks);
     d.nvec = 32 + (int64_t)(rng() % 96);
-    d.oneshot = (k % 2 == 1);  // alternate layouts so that consecutive ops reuse addresses differently
-    if (slow_rank >= 0) d.nvec = 64;  // sizes chosen so the two layouts overlap exactly
-    const int64_t need = d.oneshot ? (int64_t)nranks * d.nvec : (int64_t)nranks * ((d.nvec + nranks - 1) / nranks) + d.nvec;
+    d.kind = (k % 2 == 1) ? Kind::OneShot : Kind::TwoShot;  // alternate layouts: consecutive ops reuse addresses differently
+    if (mix) d.kind = (Kind)(rng() % (uint32_t)Kind::kCount);
+    if (slow_rank >= 0) d.nvec = 64;  // sizes chosen so the two all-reduce layouts overlap exactly
+    int64_t need = 0;
+    switch (d.kind) {
+      case Kind::OneShot: need = (int64_t)nranks * d.nvec; break;
+      case Kind::TwoShot: need = (int64_t)nranks * ((d.nvec + nranks - 1) / nranks) + d.nvec; break;
+      case Kind::AllGather:
+      case Kind::AllToAll:
+      case Kind::ReduceScatter:
+        d.nvec = 3 + d.nvec / 4;  // words per chunk
+        need = (int64_t)nranks * d.nvec;
+        break;
+      case Kind::AllGatherSym:
+      case Kind::ReduceScatterSym:
+        d.nvec = 3 + d.nvec / 4;
+        max_sym = std::max(max_sym, (int64_t)nranks * d.nvec);
+        break;
+      case Kind::BroadcastDirect:
+      case Kind::BroadcastTwoPhase: need = d.nvec; break;
+      default: break;
+    }
     max_words = std::max(max_words, need);
     ops.push_back(d);
   }
@@ -197,13 +420,13 @@ ProtocolModelResult run_protocol_model(int nranks, int blocks, int n_ops, uint32
   m.G = blocks;
   m.use_done = use_done_chain;
   m.slow_rank = slow_rank;
-  for (int r = 0; r < nranks; ++r) m.mem.push_back(std::make_unique<RankMem>((size_t)max_words, nranks, blocks));
-  // a rank's own `done` word doubles as its kernel boundary: set by its last block
+  for (int r = 0; r < nranks; ++r)
+    m.mem.push_back(std::make_unique<RankMem>((size_t)std::max<int64_t>(max_words, 1), (size_t)max_sym, nranks, blocks));
   std::vector<std::thread> threads;
   for (int r = 0; r < nranks; ++r)
     for (int b = 0; b < blocks; ++b) threads.emplace_back([&m, r, b, &ops, seed] {
-      // wrap: make the rank's last-block signal also visible to its own blocks
-      block_thread(m, r, b, ops, seed * 131u + (uint32_t)(r * 17 + b));
+      Block blk(m, r, b, seed * 131u + (uint32_t)(r * 17 + b));
+      blk.run(ops);
     });
   for (auto& t : threads) t.join();
   res.errors = m.errors.load();

@@ -82,8 +82,9 @@ int main() {
       break;
     }
   // the signalling-protocol model (atomics only) must also be clean under the sanitizer
-  for (uint32_t seed = 0; seed < 3; ++seed) {
-    ProtocolModelResult r = run_protocol_model(4, 2, 30, seed, /*use_done_chain=*/true, /*slow_rank=*/-1);
+  for (uint32_t seed = 0; seed < 6; ++seed) {
+    ProtocolModelResult r =
+        run_protocol_model(4, 2, 30, seed, /*use_done_chain=*/true, /*slow_rank=*/-1, /*mix=*/seed >= 3);
     if (r.errors || r.timeouts) {
       std::fprintf(stderr, "protocol model: %llu errors, %llu timeouts\n", (unsigned long long)r.errors,
                    (unsigned long long)r.timeouts);
