@@ -11,11 +11,15 @@ seed=rank.  Every op runs through the public bucket API (`BaguaBucketPy.append_*
 `mark_communication_ready`, `wait_pending_comm_ops`).  Timing: CUDA events on the
 communication stream around `iters` back-to-back buckets after `warmup`, an L2 flush
 (192 MB memset) before each timed batch, max over ranks.  `raw_nccl` is a bare
-`ncclAllReduce` through the communicator for reference.
+`ncclAllReduce` through the communicator for reference.  `allgather`, `alltoall`,
+`reduce_scatter` and `broadcast` (not in the default list) time the communicator's own
+collectives on a buffer of the given total size, as peer-memory kernels (path `fused`) or
+library calls (path `library`), issued from a Python op inside a bucket.
 
 Bus bandwidth conventions (bytes that must cross each GPU's links, per direction):
   allreduce:  2(N-1)/N · S            bytegrad: 2(N-1)/N · (S/4 + 32N)
   shift_one:  S                        lp_ring:  2 · (S/4 + 32)
+  allgather / alltoall / reduce_scatter: (N-1)/N · S      broadcast: S
 Roofline fraction = busbw / 900 GB/s (nominal NVLink 5 per direction) and / 770 GB/s
 (measured peer copy on this pool).
 """
@@ -46,6 +50,10 @@ def wire_bytes(op, S, N):
         return S
     if op == "lp_ring":
         return 2 * (S / 4 + 32)
+    if op in ("allgather", "alltoall", "reduce_scatter"):
+        return (N - 1) / N * S
+    if op == "broadcast":
+        return S
     raise ValueError(op)
 
 
@@ -151,7 +159,22 @@ def main():
                         weight=bc.BaguaTensorPy(w, "w"), left_peer_weight=bc.BaguaTensorPy(l, "l"),
                         right_peer_weight=bc.BaguaTensorPy(r, "r"))
                 elif op == "raw_nccl":
+                    comm.set_p2p_collectives(False)
                     bucket.append_python_op(lambda _name, bt=bt: comm.allreduce_inplace(bt, 10))
+                elif op in ("allgather", "alltoall", "reduce_scatter", "broadcast"):
+                    comm.set_p2p_collectives(path != "library")
+                    part = torch.zeros(n // world, device=dev)
+                    other = torch.zeros(n, device=dev)
+                    keep += [part, other]
+                    pt, ot = bc.BaguaTensorPy(part, "part"), bc.BaguaTensorPy(other, "other")
+                    if op == "allgather":
+                        bucket.append_python_op(lambda _name, a=pt, b=bt: comm.allgather(a, b))
+                    elif op == "alltoall":
+                        bucket.append_python_op(lambda _name, a=bt, b=ot: comm.alltoall(a, b))
+                    elif op == "reduce_scatter":
+                        bucket.append_python_op(lambda _name, a=bt, b=pt: comm.reduce_scatter(a, b, 10))
+                    else:
+                        bucket.append_python_op(lambda _name, b=bt: comm.broadcast(b, 0))
                 us = time_bucket(bucket, bt, iters, args.warmup)
                 wb = wire_bytes(op, n * 4, world)
                 row = {"op": op, "path": path, "bytes": n * 4, "n_gpus": world, "latency_us": us,
@@ -162,6 +185,7 @@ def main():
                     print(json.dumps(row), flush=True)
                 del bucket, bt, x, keep
     bb._C.set_sync_per_bucket(False)
+    comm.set_p2p_collectives(False)
     if rank == 0 and args.out:
         os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
         with open(args.out, "w") as f:

@@ -57,6 +57,22 @@ def main():
         "bytegrad": (lambda: arena.bytegrad(xs, True, args.blocks), int(N * 3.75 * S)),
         "lp_ring": (lambda: arena.lp_ring(xs, aux[0], aux[1], aux[2], args.blocks), int(N * 13.75 * S)),
     }
+    # the communicator's collectives: every rank's buffer of S bytes is cut in N chunks of c = S/N
+    c = S // N
+    parts = [x[:n // N] for x in xs]
+    cases.update({
+        "allgather": (lambda: arena.collective("allgather", parts, aux[0], blocks=args.blocks),
+                      N * c * (4 * (N - 1) + 2)),
+        "allgather_symmetric": (lambda: arena.collective("allgather", parts, aux[0], symmetric=True, blocks=args.blocks),
+                                N * c * 2 * N),
+        "alltoall": (lambda: arena.collective("alltoall", xs, aux[0], blocks=args.blocks), N * c * (4 * (N - 1) + 2)),
+        "reduce_scatter": (lambda: arena.collective("reduce_scatter", xs, [a[:n // N] for a in aux[1]],
+                                                    blocks=args.blocks), N * c * (3 * (N - 1) + 2)),
+        "reduce_scatter_symmetric": (lambda: arena.collective("reduce_scatter", xs, [a[:n // N] for a in aux[1]],
+                                                              symmetric=True, blocks=args.blocks), N * c * (N + 1)),
+        "broadcast_twophase": (lambda: arena.collective("broadcast_twophase", [], aux[2], root=0, blocks=args.blocks),
+                               (N - 1) * S * 2 + (N - 1) * c * 2 * (N - 1)),
+    })
     only = [s for s in args.only.split(",") if s]
     for name, (fn, nbytes) in cases.items():
         if only and name not in only:
