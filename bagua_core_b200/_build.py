@@ -30,6 +30,7 @@ SOURCES = [
     "tensor/tensor.cc",
     "comm/communicator.cc",
     "comm/arena.cc",
+    "comm/nvls.cc",
     "comm/nccl_transport.cc",
     "comm/c10d_transport.cc",
     "ops/ops.cc",
@@ -42,6 +43,7 @@ SOURCES = [
     "kernels/fused_bytegrad.cu",
     "kernels/fused_gossip.cu",
     "kernels/fused_collectives.cu",
+    "kernels/fused_nvls.cu",
     "kernels/fused_emu.cc",
     "kernels/no_alloc.cu",
 ]

@@ -233,6 +233,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              void* peers[kArenaMaxRanks];
              return a && t.is_cuda() && a->sym_translate(t.data_ptr(), t.nbytes(), peers);
            })
+      .def("is_multicast",
+           [](PyComm& c, const at::Tensor& t) {
+             PeerArena* a = c.inner->arena();
+             return a && t.is_cuda() && a->sym_multicast(t.data_ptr(), t.nbytes()) != nullptr;
+           },
+           "True if the tensor lies in symmetric memory that also has an NVSwitch multicast mapping "
+           "(BAGUA_B200_NVLS=1 on a platform that supports it): its all-reduce runs inside the switch.")
       .def("fused_launches", [](PyComm& c) {
         auto* a = c.inner->arena();
         return a ? a->fused_launches() : (uint64_t)0;

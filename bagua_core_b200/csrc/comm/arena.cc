@@ -21,6 +21,7 @@ PeerArena::PeerArena(Transport& transport, int rank, int nranks, int device, cud
   deadline_ns_ = (uint64_t)(env_double("BAGUA_B200_DEVICE_WAIT_MS", 120000.0) * 1e6);
   max_blocks_ = (int)std::min<long>(std::max<long>(env_long("BAGUA_B200_COMM_CTAS", 64), 1), kArenaMaxBlocks);
   max_coop_blocks_ = (int)std::min<long>(std::max<long>(env_long("BAGUA_B200_COOP_CTAS", 148), 1), kArenaMaxBlocks);
+  nvls_ = env_long("BAGUA_B200_NVLS", 0) != 0;
   BAGUA_CUDA_CHECK(cudaSetDevice(device));
   // every peer must be reachable with peer access
   int ndev = 0;
@@ -42,7 +43,11 @@ PeerArena::~PeerArena() {
     if (peer_signals_[p]) cudaIpcCloseMemHandle(peer_signals_[p]);
   }
   for (void* p : retired_peer_) cudaIpcCloseMemHandle(p);
-  for (Slab& s : slabs_)
+  for (Slab& s : slabs_) {
+    if (s.vmm.impl) {
+      destroy_multicast_slab(s.vmm);
+      continue;
+    }
     for (int p = 0; p < nranks_; ++p) {
       if (!s.base[p]) continue;
       if (p == rank_)
@@ -50,6 +55,7 @@ PeerArena::~PeerArena() {
       else
         cudaIpcCloseMemHandle(s.base[p]);
     }
+  }
   if (local_staging_) cudaFree(local_staging_);
   for (void* p : retired_) cudaFree(p);
   if (local_signals_) cudaFree(local_signals_);
@@ -167,13 +173,30 @@ void* PeerArena::sym_alloc(size_t bytes) {
   if (slabs_.empty() || slabs_.back().used + bytes > slabs_.back().bytes) {
     static const size_t slab_min = (size_t)env_long("BAGUA_B200_SYM_SLAB_MB", 256) << 20;
     const size_t slab_bytes = align_up(std::max(bytes, slab_min), (size_t)2 << 20);
-    Slab s;
-    std::memset(&s, 0, sizeof(s));
-    void* local = nullptr;
-    void* peers[kArenaMaxRanks] = {};
-    exchange_block(slab_bytes, &local, peers);
-    for (int p = 0; p < nranks_; ++p) s.base[p] = (char*)peers[p];
-    s.bytes = slab_bytes;
+    Slab s{};
+    bool made = false;
+    if (nvls_) {
+      // Collective, and all ranks get the same answer: a slab with a multicast mapping or none.
+      std::string why;
+      BAGUA_CUDA_CHECK(cudaSetDevice(device_));
+      made = create_multicast_slab(transport_, rank_, nranks_, device_, stream_, slab_bytes, &s.vmm, &why);
+      if (made) {
+        for (int p = 0; p < nranks_; ++p) s.base[p] = s.vmm.base[p];
+        s.mc_base = s.vmm.mc_base;
+        s.bytes = s.vmm.bytes;
+        BAGUA_LOG(Info, "symmetric slab of " << (s.bytes >> 20) << " MiB with an NVSwitch multicast mapping");
+      } else {
+        BAGUA_LOG(Warn, "NVSwitch multicast is not usable, symmetric memory falls back to CUDA IPC: " << why);
+        nvls_ = false;
+      }
+    }
+    if (!made) {
+      void* local = nullptr;
+      void* peers[kArenaMaxRanks] = {};
+      exchange_block(slab_bytes, &local, peers);
+      for (int p = 0; p < nranks_; ++p) s.base[p] = (char*)peers[p];
+      s.bytes = slab_bytes;
+    }
     s.used = 0;
     slabs_.push_back(s);
   }
@@ -195,6 +218,16 @@ bool PeerArena::sym_translate(const void* p, size_t bytes, void* peers[kArenaMax
     }
   }
   return false;
+}
+
+void* PeerArena::sym_multicast(const void* p, size_t bytes) const {
+  std::lock_guard<std::mutex> g(sym_mu_);
+  const char* c = (const char*)p;
+  for (const Slab& s : slabs_) {
+    const char* b = s.base[rank_];
+    if (s.mc_base && c >= b && c + bytes <= b + s.used) return s.mc_base + (c - b);
+  }
+  return nullptr;
 }
 
 void PeerArena::ensure_staging(size_t bytes) {

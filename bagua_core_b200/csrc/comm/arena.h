@@ -28,6 +28,7 @@
 #include <cuda_runtime_api.h>
 
 #include "../common.h"
+#include "nvls.h"
 #include "transport.h"
 
 namespace bagua {
@@ -106,6 +107,11 @@ class PeerArena {
   // same offset (peers[rank] == p) and returns true.
   bool sym_translate(const void* p, size_t bytes, void* peers[kArenaMaxRanks]) const;
   size_t sym_bytes_in_use() const { return sym_used_; }
+  // If [p, p+bytes) lies inside a slab with an NVSwitch multicast mapping, the multicast
+  // address of the same offset (for multimem.ld_reduce / multimem.st); else null.  Slabs get
+  // such a mapping when BAGUA_B200_NVLS=1 and the platform supports it (see nvls.h).
+  void* sym_multicast(const void* p, size_t bytes) const;
+  bool nvls_enabled() const { return nvls_; }
 
  private:
   void allocate_and_exchange(size_t bytes);
@@ -116,6 +122,8 @@ class PeerArena {
     char* base[kArenaMaxRanks];  // this rank's mapping of every rank's slab
     size_t bytes;
     size_t used;
+    char* mc_base;               // multicast mapping, or null (CUDA-IPC slab)
+    MulticastSlab vmm;           // owner of a multicast slab's driver handles
   };
   std::vector<Slab> slabs_;
   size_t sym_used_ = 0;
@@ -138,6 +146,7 @@ class PeerArena {
   uint64_t deadline_ns_;
   int max_blocks_;
   int max_coop_blocks_;
+  bool nvls_ = false;
   uint64_t launches_ = 0;
 };
 

@@ -1,0 +1,358 @@
+#include "nvls.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <sys/syscall.h>
+#include <unistd.h>
+
+#include <cerrno>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#ifndef SYS_pidfd_open
+#define SYS_pidfd_open 434
+#endif
+#ifndef SYS_pidfd_getfd
+#define SYS_pidfd_getfd 438
+#endif
+
+namespace bagua {
+
+namespace {
+
+// Driver entry points, resolved through the runtime so that nothing links against libcuda.
+struct Driver {
+  CUresult (*DeviceGet)(CUdevice*, int) = nullptr;
+  CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice) = nullptr;
+  CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+  CUresult (*MemGetAllocationGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+  CUresult (*MemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+  CUresult (*MemRelease)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*MemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType,
+                                         unsigned long long) = nullptr;
+  CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+  CUresult (*MemAddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*MemAddressFree)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*MemMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*MemUnmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*MemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  CUresult (*MulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*) = nullptr;
+  CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice) = nullptr;
+  CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t,
+                               unsigned long long) = nullptr;
+  CUresult (*MulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t) = nullptr;
+  CUresult (*MulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags) = nullptr;
+
+  template <typename F>
+  bool get(const char* name, F*& fn, std::string* why) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult st;
+    cudaError_t e = cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &st);
+    if (e != cudaSuccess || st != cudaDriverEntryPointSuccess || !p) {
+      cudaGetLastError();
+      *why = std::string("driver entry point ") + name + " is not available";
+      return false;
+    }
+    fn = reinterpret_cast<F*>(p);
+    return true;
+  }
+  bool load(std::string* why) {
+    return get("cuDeviceGet", DeviceGet, why) && get("cuDeviceGetAttribute", DeviceGetAttribute, why) &&
+           get("cuGetErrorString", GetErrorString, why) &&
+           get("cuMemGetAllocationGranularity", MemGetAllocationGranularity, why) &&
+           get("cuMemCreate", MemCreate, why) && get("cuMemRelease", MemRelease, why) &&
+           get("cuMemExportToShareableHandle", MemExportToShareableHandle, why) &&
+           get("cuMemImportFromShareableHandle", MemImportFromShareableHandle, why) &&
+           get("cuMemAddressReserve", MemAddressReserve, why) && get("cuMemAddressFree", MemAddressFree, why) &&
+           get("cuMemMap", MemMap, why) && get("cuMemUnmap", MemUnmap, why) &&
+           get("cuMemSetAccess", MemSetAccess, why) && get("cuMulticastCreate", MulticastCreate, why) &&
+           get("cuMulticastAddDevice", MulticastAddDevice, why) && get("cuMulticastBindMem", MulticastBindMem, why) &&
+           get("cuMulticastUnbind", MulticastUnbind, why) &&
+           get("cuMulticastGetGranularity", MulticastGetGranularity, why);
+  }
+};
+
+struct Impl {
+  Driver drv;
+  CUdevice dev = 0;
+  int rank = 0, nranks = 0;
+  size_t bytes = 0;
+  CUmemGenericAllocationHandle mc = 0;
+  bool have_mc = false, bound = false;
+  CUmemGenericAllocationHandle mem[kMulticastMaxRanks] = {};
+  bool have_mem[kMulticastMaxRanks] = {};
+  CUdeviceptr va[kMulticastMaxRanks] = {};
+  bool reserved[kMulticastMaxRanks] = {}, mapped[kMulticastMaxRanks] = {};
+  CUdeviceptr mc_va = 0;
+  bool mc_reserved = false, mc_mapped = false;
+  int fd_mem = -1, fd_mc = -1;  // exported descriptors, open until every peer has imported them
+};
+
+void close_fds(Impl& s) {
+  if (s.fd_mem >= 0) close(s.fd_mem);
+  if (s.fd_mc >= 0) close(s.fd_mc);
+  s.fd_mem = s.fd_mc = -1;
+}
+
+void teardown(Impl& s) {
+  Driver& d = s.drv;
+  close_fds(s);
+  if (s.mc_mapped) d.MemUnmap(s.mc_va, s.bytes);
+  if (s.mc_reserved) d.MemAddressFree(s.mc_va, s.bytes);
+  if (s.bound) d.MulticastUnbind(s.mc, s.dev, 0, s.bytes);
+  for (int p = 0; p < s.nranks; ++p) {
+    if (s.mapped[p]) d.MemUnmap(s.va[p], s.bytes);
+    if (s.reserved[p]) d.MemAddressFree(s.va[p], s.bytes);
+    if (s.have_mem[p]) d.MemRelease(s.mem[p]);
+  }
+  if (s.have_mc) d.MemRelease(s.mc);
+  s.mc_mapped = s.mc_reserved = s.bound = s.have_mc = false;
+  for (int p = 0; p < kMulticastMaxRanks; ++p) s.mapped[p] = s.reserved[p] = s.have_mem[p] = false;
+}
+
+// One record per rank, all-gathered after every step.
+struct Note {
+  int32_t ok;
+  int32_t pid;
+  int32_t fd_mem;
+  int32_t fd_mc;
+  uint64_t bytes;
+};
+
+// All-gathers `mine` through device buffers on the transport (the same way the arena trades its IPC handles).
+bool gather_notes(Transport& t, int rank, int nranks, cudaStream_t stream, const Note& mine, std::vector<Note>* all) {
+  void* dev = nullptr;
+  if (cudaMalloc(&dev, sizeof(Note) * (size_t)nranks) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  all->assign((size_t)nranks, Note{});
+  bool ok = cudaMemcpyAsync((char*)dev + sizeof(Note) * (size_t)rank, &mine, sizeof(Note), cudaMemcpyHostToDevice,
+                            stream) == cudaSuccess;
+  if (ok) {
+    t.allgather((char*)dev + sizeof(Note) * (size_t)rank, dev, (int64_t)sizeof(Note), DType::U8);
+    ok = cudaMemcpyAsync(all->data(), dev, sizeof(Note) * (size_t)nranks, cudaMemcpyDeviceToHost, stream) ==
+             cudaSuccess &&
+         cudaStreamSynchronize(stream) == cudaSuccess;
+  }
+  cudaFree(dev);
+  if (!ok) cudaGetLastError();
+  return ok;
+}
+
+// Duplicates descriptor `fd` of process `pid` into this process.
+int steal_fd(int pid, int fd) {
+  const int pidfd = (int)syscall(SYS_pidfd_open, pid, 0);
+  if (pidfd < 0) return -1;
+  const int got = (int)syscall(SYS_pidfd_getfd, pidfd, fd, 0);
+  close(pidfd);
+  return got;
+}
+
+}  // namespace
+
+bool create_multicast_slab(Transport& transport, int rank, int nranks, int device, cudaStream_t stream, size_t bytes,
+                           MulticastSlab* out, std::string* why) {
+  *out = MulticastSlab{};
+  if (nranks < 2 || nranks > kMulticastMaxRanks) {
+    *why = "multicast slabs need 2.." + std::to_string(kMulticastMaxRanks) + " ranks";
+    return false;
+  }
+  auto impl = std::make_unique<Impl>();
+  Impl& s = *impl;
+  Driver& d = s.drv;
+  s.rank = rank;
+  s.nranks = nranks;
+  std::string local_why;
+  std::vector<Note> notes;
+
+  // Every step: do the local work, then trade {ok, ...}; the first rank that failed decides for all.
+  auto agree = [&](bool ok, const char* step, Note mine = Note{}) -> bool {
+    mine.ok = ok ? 1 : 0;
+    if (!gather_notes(transport, rank, nranks, stream, mine, &notes)) {
+      *why = std::string(step) + ": exchanging the result between ranks failed";
+      teardown(s);
+      return false;
+    }
+    for (int p = 0; p < nranks; ++p)
+      if (!notes[p].ok) {
+        *why = std::string(step) + " failed on rank " + std::to_string(p) + (p == rank ? ": " + local_why : std::string());
+        teardown(s);
+        return false;
+      }
+    return true;
+  };
+  auto check = [&](CUresult r, const char* what) -> bool {
+    if (r == CUDA_SUCCESS) return true;
+    const char* msg = nullptr;
+    if (d.GetErrorString) d.GetErrorString(r, &msg);
+    local_why = std::string(what) + ": " + (msg ? msg : "unknown driver error");
+    return false;
+  };
+
+  // 1. capability
+  bool ok = cudaSetDevice(device) == cudaSuccess && cudaFree(nullptr) == cudaSuccess && d.load(&local_why);
+  if (ok) ok = check(d.DeviceGet(&s.dev, device), "cuDeviceGet");
+  if (ok) {
+    int mc = 0, fd = 0;
+    ok = check(d.DeviceGetAttribute(&mc, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, s.dev), "query multicast support") &&
+         check(d.DeviceGetAttribute(&fd, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED, s.dev),
+               "query descriptor export support");
+    if (ok && (!mc || !fd)) {
+      ok = false;
+      local_why = mc ? "memory cannot be exported as a file descriptor" : "the device does not support multicast";
+    }
+  }
+  if (!ok) cudaGetLastError();
+  if (!agree(ok, "capability check")) return false;
+
+  // 2. size
+  CUmulticastObjectProp mprop;
+  std::memset(&mprop, 0, sizeof(mprop));
+  mprop.numDevices = (unsigned)nranks;
+  mprop.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  CUmemAllocationProp aprop;
+  std::memset(&aprop, 0, sizeof(aprop));
+  aprop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  aprop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  aprop.location.id = device;
+  aprop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  size_t gran_mc = 0, gran_mem = 0;
+  mprop.size = align_up(bytes, (size_t)2 << 20);
+  ok = check(d.MulticastGetGranularity(&gran_mc, &mprop, CU_MULTICAST_GRANULARITY_RECOMMENDED), "multicast granularity") &&
+       check(d.MemGetAllocationGranularity(&gran_mem, &aprop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED),
+             "allocation granularity");
+  size_t gran = 0;
+  if (ok) {
+    gran = std::max(gran_mc, gran_mem);
+    ok = gran > 0 && (gran % gran_mc == 0) && (gran % gran_mem == 0);
+    if (!ok) local_why = "multicast and allocation granularities do not nest";
+  }
+  if (ok) {
+    s.bytes = align_up(bytes, gran);
+    mprop.size = s.bytes;
+  }
+  {
+    Note n{};
+    n.bytes = s.bytes;
+    if (!agree(ok, "granularity query", n)) return false;
+    for (int p = 0; p < nranks; ++p)
+      if (notes[p].bytes != s.bytes) {
+        *why = "ranks disagree on the slab size";
+        teardown(s);
+        return false;
+      }
+  }
+
+  // 3. create: rank 0 the multicast object, every rank its memory; export both as descriptors
+  if (rank == 0) {
+    ok = check(d.MulticastCreate(&s.mc, &mprop), "cuMulticastCreate");
+    s.have_mc = ok;
+    if (ok)
+      ok = check(d.MemExportToShareableHandle(&s.fd_mc, s.mc, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
+                 "export the multicast object");
+  }
+  if (ok) {
+    ok = check(d.MemCreate(&s.mem[rank], s.bytes, &aprop, 0), "cuMemCreate");
+    s.have_mem[rank] = ok;
+  }
+  if (ok)
+    ok = check(d.MemExportToShareableHandle(&s.fd_mem, s.mem[rank], CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
+               "export the memory");
+  {
+    Note n{};
+    n.pid = (int32_t)getpid();
+    n.fd_mem = s.fd_mem;
+    n.fd_mc = s.fd_mc;
+    if (!agree(ok, "allocation", n)) return false;
+  }
+  const std::vector<Note> owners = notes;
+
+  // 4. import the peers' memory and, except on rank 0, the multicast object
+  for (int p = 0; p < nranks && ok; ++p) {
+    if (p == rank) continue;
+    const int fd = steal_fd(owners[p].pid, owners[p].fd_mem);
+    if (fd < 0) {
+      ok = false;
+      local_why = "pidfd_getfd on a peer's memory descriptor failed (errno " + std::to_string(errno) + ")";
+      break;
+    }
+    ok = check(d.MemImportFromShareableHandle(&s.mem[p], (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
+               "import a peer's memory");
+    s.have_mem[p] = ok;
+    close(fd);
+  }
+  if (ok && rank != 0) {
+    const int fd = steal_fd(owners[0].pid, owners[0].fd_mc);
+    if (fd < 0) {
+      ok = false;
+      local_why = "pidfd_getfd on the multicast descriptor failed (errno " + std::to_string(errno) + ")";
+    } else {
+      ok = check(d.MemImportFromShareableHandle(&s.mc, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
+                 "import the multicast object");
+      s.have_mc = ok;
+      close(fd);
+    }
+  }
+  if (!agree(ok, "import")) return false;
+  close_fds(s);  // every peer holds its own reference now
+
+  // 5. join the multicast team; all devices must have joined before anyone binds
+  ok = check(d.MulticastAddDevice(s.mc, s.dev), "cuMulticastAddDevice");
+  if (!agree(ok, "joining the multicast team")) return false;
+
+  // 6. bind this rank's memory at offset 0
+  ok = check(d.MulticastBindMem(s.mc, 0, s.mem[rank], 0, s.bytes, 0), "cuMulticastBindMem");
+  s.bound = ok;
+  if (!agree(ok, "binding memory to the multicast object")) return false;
+
+  // 7. map everything
+  CUmemAccessDesc access;
+  std::memset(&access, 0, sizeof(access));
+  access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  access.location.id = device;
+  access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  for (int p = 0; p < nranks && ok; ++p) {
+    ok = check(d.MemAddressReserve(&s.va[p], s.bytes, gran, 0, 0), "reserve an address range");
+    s.reserved[p] = ok;
+    if (ok) {
+      ok = check(d.MemMap(s.va[p], s.bytes, 0, s.mem[p], 0), "map memory");
+      s.mapped[p] = ok;
+    }
+    if (ok) ok = check(d.MemSetAccess(s.va[p], s.bytes, &access, 1), "enable access to memory");
+  }
+  if (ok) {
+    ok = check(d.MemAddressReserve(&s.mc_va, s.bytes, gran, 0, 0), "reserve the multicast address range");
+    s.mc_reserved = ok;
+  }
+  if (ok) {
+    ok = check(d.MemMap(s.mc_va, s.bytes, 0, s.mc, 0), "map the multicast object");
+    s.mc_mapped = ok;
+  }
+  if (ok) ok = check(d.MemSetAccess(s.mc_va, s.bytes, &access, 1), "enable access to the multicast mapping");
+  if (ok) {
+    ok = cudaMemsetAsync((void*)s.va[rank], 0, s.bytes, stream) == cudaSuccess &&
+         cudaStreamSynchronize(stream) == cudaSuccess;
+    if (!ok) {
+      local_why = std::string("clearing the slab: ") + cudaGetErrorString(cudaGetLastError());
+    }
+  }
+  if (!agree(ok, "mapping")) return false;
+
+  for (int p = 0; p < nranks; ++p) out->base[p] = (char*)(uintptr_t)s.va[p];
+  out->mc_base = (char*)(uintptr_t)s.mc_va;
+  out->bytes = s.bytes;
+  out->impl = impl.release();
+  return true;
+}
+
+void destroy_multicast_slab(MulticastSlab& slab) {
+  if (!slab.impl) return;
+  Impl* s = static_cast<Impl*>(slab.impl);
+  teardown(*s);
+  delete s;
+  slab = MulticastSlab{};
+}
+
+}  // namespace bagua

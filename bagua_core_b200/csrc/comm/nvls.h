@@ -1,0 +1,45 @@
+// Symmetric-heap slabs with an NVSwitch multicast mapping (NVLS).
+//
+// A slab is one physical allocation per rank made with the driver's virtual-memory-
+// management API, shared between the processes of one node as POSIX file descriptors, and
+// bound to one multicast object.  Every rank ends up with
+//   * base[q]  – an ordinary (unicast) mapping of rank q's memory, usable exactly like the
+//                CUDA-IPC slabs of the symmetric heap (peer loads and stores), and
+//   * mc_base  – the multicast mapping: a `multimem.st` to mc_base + off lands at offset
+//                off of every rank's memory, a `multimem.ld_reduce` from it returns the
+//                element-wise sum over all ranks, computed inside the switch.
+// An all-reduce on such memory moves S bytes per GPU and direction instead of 2(N-1)/N·S.
+//
+// The driver entry points are looked up at run time (cudaGetDriverEntryPoint), so the
+// extension does not link against libcuda and still loads on a machine without a driver.
+// Everything here is collective over the communicator's transport, and every step ends
+// with an agreement round: either all ranks get the slab or none does, in which case the
+// caller falls back to CUDA-IPC slabs.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <string>
+
+#include "transport.h"
+
+namespace bagua {
+
+constexpr int kMulticastMaxRanks = 8;
+
+struct MulticastSlab {
+  char* base[kMulticastMaxRanks] = {};
+  char* mc_base = nullptr;
+  size_t bytes = 0;
+  void* impl = nullptr;  // driver handles, for teardown
+};
+
+// Collective.  `bytes` is rounded up to the multicast granularity.  Returns false on every
+// rank alike, with the first failing step in `why`, and leaves nothing allocated.
+bool create_multicast_slab(Transport& transport, int rank, int nranks, int device, cudaStream_t stream, size_t bytes,
+                           MulticastSlab* out, std::string* why);
+
+// Unbinds, unmaps and releases.  Local; call on every rank before the transport goes away.
+void destroy_multicast_slab(MulticastSlab& slab);
+
+}  // namespace bagua

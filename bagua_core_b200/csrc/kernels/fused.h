@@ -27,6 +27,12 @@ namespace fused {
 // out = scale * sum_r in_r.  `in` and `out` may be the same buffer.
 bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream);
 
+// The same through the NVSwitch's reduction units (multimem.ld_reduce / multimem.st); only for
+// buffers inside a symmetric-heap slab that has a multicast mapping (BAGUA_B200_NVLS=1).
+// `allreduce` tries this first.
+bool allreduce_nvls(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale,
+                    cudaStream_t stream);
+
 // In-place ByteGrad on `bucket` (n elements, n % (16*nranks) == 0).
 bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream);
 

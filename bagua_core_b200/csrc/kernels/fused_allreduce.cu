@@ -432,6 +432,7 @@ void coop_launch(K kernel, int grid, Args... args) {
 }  // namespace
 
 bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream) {
+  if (arena.nvls_enabled() && allreduce_nvls(arena, in, out, n, dt, scale, stream)) return true;
   switch (dt) {
     case DType::F32: return allreduce_t<float>(arena, in, out, n, scale, stream);
     case DType::F16: return allreduce_t<__half>(arena, in, out, n, scale, stream);
