@@ -40,3 +40,17 @@ def _load():
 
 C = _load()
 SO_PATH = _build.SO_PATH
+
+
+def _drop_multicast_bindings():
+    # A process must not die while its memory is bound to an NVSwitch multicast object that
+    # other GPUs still use; communicators that were never destroyed are covered here.
+    try:
+        C.release_multicast_slabs()
+    except Exception:
+        pass
+
+
+import atexit  # noqa: E402
+
+atexit.register(_drop_multicast_bindings)

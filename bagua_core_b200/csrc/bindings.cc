@@ -653,6 +653,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "Runs one of the communicator collectives (allgather, alltoall, reduce_scatter, broadcast_direct, "
           "broadcast_twophase, barrier) for all virtual ranks in one cooperative launch.");
 
+  m.def("release_multicast_slabs", []() { return release_all_multicast_slabs(); },
+        "Drops every NVSwitch multicast binding this process holds (called at interpreter exit).");
   m.def(
       "protocol_model_check",
       [](int nranks, int blocks, int n_ops, uint32_t seed, bool use_done_chain, int slow_rank, bool mix) {

@@ -8,6 +8,7 @@
 #include <cerrno>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <vector>
 
 #ifndef SYS_pidfd_open
@@ -110,6 +111,11 @@ void teardown(Impl& s) {
   s.mc_mapped = s.mc_reserved = s.bound = s.have_mc = false;
   for (int p = 0; p < kMulticastMaxRanks; ++p) s.mapped[p] = s.reserved[p] = s.have_mem[p] = false;
 }
+
+// Slabs that are still bound, so that a process can drop its multicast bindings before it
+// exits even when the owning communicator is never destroyed.
+std::mutex g_live_mu;
+std::vector<Impl*> g_live;
 
 // One record per rank, all-gathered after every step.
 struct Note {
@@ -344,15 +350,38 @@ bool create_multicast_slab(Transport& transport, int rank, int nranks, int devic
   out->mc_base = (char*)(uintptr_t)s.mc_va;
   out->bytes = s.bytes;
   out->impl = impl.release();
+  {
+    std::lock_guard<std::mutex> g(g_live_mu);
+    g_live.push_back(static_cast<Impl*>(out->impl));
+  }
   return true;
 }
 
 void destroy_multicast_slab(MulticastSlab& slab) {
   if (!slab.impl) return;
   Impl* s = static_cast<Impl*>(slab.impl);
-  teardown(*s);
+  {
+    std::lock_guard<std::mutex> g(g_live_mu);
+    for (size_t i = 0; i < g_live.size(); ++i)
+      if (g_live[i] == s) {
+        g_live.erase(g_live.begin() + (long)i);
+        break;
+      }
+  }
+  teardown(*s);  // a no-op for what release_all_multicast_slabs() already dropped
   delete s;
   slab = MulticastSlab{};
+}
+
+int release_all_multicast_slabs() {
+  std::lock_guard<std::mutex> g(g_live_mu);
+  int n = 0;
+  for (Impl* s : g_live) {
+    teardown(*s);
+    ++n;
+  }
+  g_live.clear();
+  return n;
 }
 
 }  // namespace bagua

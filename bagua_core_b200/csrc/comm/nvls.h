@@ -42,4 +42,9 @@ bool create_multicast_slab(Transport& transport, int rank, int nranks, int devic
 // Unbinds, unmaps and releases.  Local; call on every rank before the transport goes away.
 void destroy_multicast_slab(MulticastSlab& slab);
 
+// Unbinds and unmaps every slab this process still holds (their pointers dangle afterwards)
+// and returns how many there were.  For process exit: a process should not die while its
+// memory is still bound to a multicast object that other GPUs use.
+int release_all_multicast_slabs();
+
 }  // namespace bagua
