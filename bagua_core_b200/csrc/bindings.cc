@@ -190,8 +190,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_fused", [](PyComm& c, bool on) { c.inner->set_fused(on); },
            "Enable/disable the fused peer-memory kernels for ops on this communicator.")
       .def("set_p2p_collectives", [](PyComm& c, bool on) { c.inner->set_p2p_collectives(on); },
-           "Run this communicator's own collectives (allreduce SUM/AVG, allgather, alltoall, reduce_scatter SUM/AVG, "
-           "broadcast, barrier) as peer-memory kernels instead of library calls (also BAGUA_B200_P2P_COLLECTIVES=1). "
+           "Run this communicator's own collectives (allreduce / reduce / reduce_scatter with SUM or AVG, allgather, "
+           "alltoall, gather, scatter, broadcast, barrier) as peer-memory kernels instead of library calls (also BAGUA_B200_P2P_COLLECTIVES=1). "
            "Must be set identically on every rank.")
       .def("p2p_collectives", [](PyComm& c) { return c.inner->p2p_collectives(); })
       .def("fused_available", [](PyComm& c) { return c.inner->arena() != nullptr; },
@@ -621,6 +621,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
             else if (kind == "broadcast_direct") k = fused::EmuCollective::BroadcastDirect;
             else if (kind == "broadcast_twophase") k = fused::EmuCollective::BroadcastTwoPhase;
             else if (kind == "barrier") k = fused::EmuCollective::Barrier;
+            else if (kind == "scatter") k = fused::EmuCollective::Scatter;
+            else if (kind == "gather") k = fused::EmuCollective::Gather;
+            else if (kind == "reduce_direct") k = fused::EmuCollective::ReduceDirect;
+            else if (kind == "reduce_twophase") k = fused::EmuCollective::ReduceTwoPhase;
             else throw BaguaError(ErrorKind::Communicator, "unknown collective '" + kind + "'");
             std::vector<const void*> pi;
             std::vector<void*> po;
@@ -641,7 +645,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               const size_t n = (size_t)a.nranks();
               if (k == fused::EmuCollective::AllGather) chunk_bytes = out[0].nbytes() / n;
               else if (k == fused::EmuCollective::AllToAll) chunk_bytes = out[0].nbytes() / n;
-              else chunk_bytes = out[0].nbytes();  // reduce-scatter output / broadcast buffer
+              else if (k == fused::EmuCollective::Gather) chunk_bytes = out[0].nbytes() / n;
+              else chunk_bytes = out[0].nbytes();  // reduce-scatter / scatter output, broadcast / reduce buffer
               if (k == fused::EmuCollective::AllGather || k == fused::EmuCollective::AllToAll)
                 BAGUA_CHECK(out[0].nbytes() % n == 0, Tensor, "output size must be divisible by the number of ranks");
             }
@@ -651,7 +656,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("kind"), py::arg("inputs"), py::arg("outputs"), py::arg("symmetric") = false, py::arg("root") = 0,
           py::arg("average") = false, py::arg("blocks") = 4,
           "Runs one of the communicator collectives (allgather, alltoall, reduce_scatter, broadcast_direct, "
-          "broadcast_twophase, barrier) for all virtual ranks in one cooperative launch.");
+          "broadcast_twophase, scatter, gather, reduce_direct, reduce_twophase, barrier) for all virtual ranks in "
+          "one cooperative launch.");
 
   m.def("release_multicast_slabs", []() { return release_all_multicast_slabs(); },
         "Drops every NVSwitch multicast binding this process holds (called at interpreter exit).");

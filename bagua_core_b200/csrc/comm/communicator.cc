@@ -126,10 +126,22 @@ void SingleCommunicator::reduce(const RawTensor& send, RawTensor& recv, int dst,
   same_kind(send, recv, "reduce");
   BAGUA_CHECK(send.num_elements_allocated() == recv.num_elements_allocated(), Communicator,
               "reduce: send and recv sizes differ");
+  if (PeerArena* a = p2p_arena()) {
+    const float scale = p2p_scale(op, nranks_);
+    if (scale != 0.0f && fused::reduce(*a, send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(),
+                                       send.dtype(), scale, dst, (cudaStream_t)stream_))
+      return;
+  }
   transport_->reduce(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype(), dst, op);
 }
 void SingleCommunicator::reduce_inplace(RawTensor& t, int dst, ReductionOp op) {
   check_live();
+  if (PeerArena* a = p2p_arena()) {
+    const float scale = p2p_scale(op, nranks_);
+    if (scale != 0.0f && fused::reduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,
+                                       dst, (cudaStream_t)stream_))
+      return;
+  }
   transport_->reduce(t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), dst, op);
 }
 void SingleCommunicator::send(const RawTensor& t, int peer) {
@@ -208,6 +220,8 @@ void SingleCommunicator::gather(const RawTensor& send, RawTensor& recv, int dst)
   if (rank_ == dst)
     BAGUA_CHECK(send.num_elements_allocated() * nranks_ == recv.num_elements_allocated(), Communicator,
                 "gather: recv on the root must hold nranks * send elements");
+  if (PeerArena* a = p2p_arena())
+    if (fused::gather(*a, send.data_ptr(), recv.data_ptr(), send.bytes_allocated(), dst, (cudaStream_t)stream_)) return;
   transport_->gather(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype(), dst);
 }
 void SingleCommunicator::gather_inplace(RawTensor& t, int64_t count, int dst) {
@@ -219,6 +233,8 @@ void SingleCommunicator::gather_inplace(RawTensor& t, int64_t count, int dst) {
     BAGUA_CHECK(t.num_elements_allocated() >= count, Communicator, "gather_inplace: tensor smaller than count");
   const size_t es = dtype_bytes(t.dtype());
   const void* src = rank_ == dst ? (char*)t.data_ptr() + (size_t)rank_ * count * es : t.data_ptr();
+  if (PeerArena* a = p2p_arena())
+    if (fused::gather(*a, src, t.data_ptr(), (size_t)count * es, dst, (cudaStream_t)stream_)) return;
   transport_->gather(src, t.data_ptr(), count, t.dtype(), dst);
 }
 void SingleCommunicator::scatter(const RawTensor& send, RawTensor& recv, int src) {
@@ -227,6 +243,8 @@ void SingleCommunicator::scatter(const RawTensor& send, RawTensor& recv, int src
   if (rank_ == src)
     BAGUA_CHECK(recv.num_elements_allocated() * nranks_ == send.num_elements_allocated(), Communicator,
                 "scatter: send on the root must hold nranks * recv elements");
+  if (PeerArena* a = p2p_arena())
+    if (fused::scatter(*a, send.data_ptr(), recv.data_ptr(), recv.bytes_allocated(), src, (cudaStream_t)stream_)) return;
   transport_->scatter(send.data_ptr(), recv.data_ptr(), recv.num_elements_allocated(), recv.dtype(), src);
 }
 void SingleCommunicator::scatter_inplace(RawTensor& t, int64_t count, int src) {
@@ -238,6 +256,8 @@ void SingleCommunicator::scatter_inplace(RawTensor& t, int64_t count, int src) {
     BAGUA_CHECK(t.num_elements_allocated() >= count, Communicator, "scatter_inplace: tensor smaller than count");
   const size_t es = dtype_bytes(t.dtype());
   void* dst = rank_ == src ? (char*)t.data_ptr() + (size_t)rank_ * count * es : t.data_ptr();
+  if (PeerArena* a = p2p_arena())
+    if (fused::scatter(*a, t.data_ptr(), dst, (size_t)count * es, src, (cudaStream_t)stream_)) return;
   transport_->scatter(t.data_ptr(), dst, count, t.dtype(), src);
 }
 void SingleCommunicator::reduce_scatter(const RawTensor& send, RawTensor& recv, ReductionOp op) {

@@ -75,8 +75,8 @@ class SingleCommunicator {
   bool fused_enabled() const { return fused_enabled_; }
   // Throws CommunicatorError if a fused kernel reported a device-side wait that ran out.
   void check_device_status();
-  // Peer-memory kernels for the collectives above (all-reduce SUM/AVG, all-gather, all-to-all,
-  // reduce-scatter SUM/AVG, broadcast, barrier) instead of library calls.  Off unless
+  // Peer-memory kernels for the collectives above (all-reduce / reduce / reduce-scatter with SUM or
+  // AVG, all-gather, all-to-all, gather, scatter, broadcast, barrier) instead of library calls.  Off unless
   // BAGUA_B200_P2P_COLLECTIVES=1 or set_p2p_collectives(true); calls inside a
   // group_start()/group_end() pair and ineligible layouts always take the library path.
   void set_p2p_collectives(bool on) { p2p_collectives_ = on; }

@@ -55,6 +55,13 @@ bool reduce_scatter(PeerArena& arena, const void* in, void* out, int64_t chunk_e
                     cudaStream_t stream);
 // buf on every rank = buf on `root`.
 bool broadcast(PeerArena& arena, void* buf, size_t bytes, int root, cudaStream_t stream);
+// Rank q's out = chunk q of root's `in` (in is only read on the root).
+bool scatter(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, int root, cudaStream_t stream);
+// Root's out[r] = rank r's `in` (out is only written on the root).
+bool gather(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, int root, cudaStream_t stream);
+// Root's out = scale * sum_r in_r; f32 / f16 / bf16.  `out` is only written on the root.
+bool reduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, int root,
+            cudaStream_t stream);
 // Returns (on the stream) once every rank's stream has reached the call.
 bool barrier(PeerArena& arena, cudaStream_t stream);
 

@@ -1,5 +1,5 @@
 // Peer-memory kernels for the communicator's own collectives (all-gather, all-to-all,
-// reduce-scatter, broadcast, barrier), sm_100a.  The reference forwards each of these to
+// reduce-scatter, broadcast, reduce, gather, scatter, barrier), sm_100a.  The reference forwards each of these to
 // one library call (bagua-core-internal/src/communicators/mod.rs:560-1040); here each is one
 // launch that moves the data with 16-byte stores over NVLink and synchronises with the
 // arena's signal words, using the same block-b-pairs-with-block-b scheme as the fused
@@ -19,6 +19,13 @@
 //       large: scatter + all-gather, so that the root sends 2(N-1)/N·S instead of (N-1)·S:
 //       the root stores chunk q into q's staging and its own chunk into everyone's, then
 //       every other rank forwards the chunk it owns to the remaining ranks.
+//   scatter / gather
+//       the root stores chunk q into q's staging / everyone stores its chunk into the
+//       root's staging; the receiving side copies out of its own staging.
+//   reduce (to one rank)
+//       small: everyone stores its input into the root's staging, the root sums in rank
+//       order; large: reduce-scatter among all ranks, then every rank hands its reduced
+//       chunk to the root (2(N-1)/N·S into the root instead of (N-1)·S).
 //   barrier
 //       one CTA: signal every peer, wait for every peer.
 #include <cuda_runtime.h>
@@ -260,6 +267,151 @@ __device__ __forceinline__ void broadcast_twophase_body(const ArenaView& v, cons
   psync::cta_finish_op(v, L);
 }
 
+// ---------------------------------------------------------------------------------
+// scatter / gather: one rank's N chunks to / from the N ranks
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void scatter_body(const ArenaView& v, const Launch& L, const uint4* in, uint4* out,
+                                             int64_t cvec, int root, int skip_local) {
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, cvec, lo, hi);
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    if (me == root) {
+      for (int i = 1; i < N; ++i) {
+        const int q = (me + i) % N;
+        copy_vecs(reinterpret_cast<uint4*>(v.staging[q]), in + (int64_t)q * cvec, lo, hi);
+      }
+      if (!skip_local) copy_vecs(out, in + (int64_t)me * cvec, lo, hi);
+      psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    } else {
+      ok = psync::cta_wait_phase(v, L, 0, 1u << root);
+      if (ok) copy_vecs(out, reinterpret_cast<const uint4*>(v.staging[me]), lo, hi);
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
+__device__ __forceinline__ void gather_body(const ArenaView& v, const Launch& L, const uint4* in, uint4* out,
+                                            int64_t cvec, int root, int skip_local) {
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, cvec, lo, hi);
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    if (me != root) {
+      copy_vecs(reinterpret_cast<uint4*>(v.staging[root]) + (int64_t)me * cvec, in, lo, hi);
+      psync::cta_signal_phase(v, L, 0, 1u << root);
+    } else {
+      if (!skip_local) copy_vecs(out + (int64_t)me * cvec, in, lo, hi);
+      ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+      if (ok) {
+        const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+        for (int i = 1; i < N; ++i) {
+          const int r = (me + i) % N;
+          copy_vecs(out + (int64_t)r * cvec, mine + (int64_t)r * cvec, lo, hi);
+        }
+      }
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
+// ---------------------------------------------------------------------------------
+// reduce to one rank: out (on root) = scale * sum_r in_r; other ranks' `out` is untouched
+// ---------------------------------------------------------------------------------
+// Small buffers: everyone stores its whole input into the root's staging.
+template <typename T>
+__device__ __forceinline__ void reduce_direct_body(const ArenaView& v, const Launch& L, const uint4* in, uint4* out,
+                                                   int64_t nvec, int root, float scale) {
+  using O = VecOps<T>;
+  const int me = v.rank, N = v.nranks;
+  int64_t lo, hi;
+  block_slice(L, 0, nvec, lo, hi);
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    if (me != root) {
+      copy_vecs(reinterpret_cast<uint4*>(v.staging[root]) + (int64_t)me * nvec, in, lo, hi);
+      psync::cta_signal_phase(v, L, 0, 1u << root);
+    } else {
+      ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+      if (ok) {
+        const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+        for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) {
+          float a[O::N];
+#pragma unroll
+          for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+          for (int r = 0; r < N; ++r) {
+            const uint4 x = (r == me) ? in[i] : mine[(int64_t)r * nvec + i];
+            O::acc(a, x);
+          }
+          out[i] = O::pack(a, scale);
+        }
+      }
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
+// Large buffers: reduce-scatter among all ranks, then every rank hands its reduced chunk to
+// the root, which receives 2(N-1)/N·S instead of (N-1)·S.  Staging layout as in the two-shot
+// all-reduce: N slots of max_chunk vectors, then an area that mirrors the buffer's indexing.
+template <typename T>
+__device__ __forceinline__ void reduce_twophase_body(const ArenaView& v, const Launch& L, const uint4* in, uint4* out,
+                                                     int64_t nvec, int64_t max_chunk_vecs, int root, float scale) {
+  using O = VecOps<T>;
+  const int me = v.rank, N = v.nranks;
+  auto chunk_lo = [&](int c) { return nvec * c / N; };
+  auto slice = [&](int c, int64_t& lo, int64_t& hi) {
+    const int64_t c0 = chunk_lo(c);
+    block_slice(L, c0, chunk_lo(c + 1) - c0, lo, hi);
+  };
+  const int64_t ag_base = (int64_t)N * max_chunk_vecs;
+  bool ok = psync::cta_wait_prev_done(v, L);
+  if (ok) {
+    for (int i = 1; i < N; ++i) {
+      const int q = (me + i) % N;
+      int64_t lo, hi;
+      slice(q, lo, hi);
+      uint4* dst = reinterpret_cast<uint4*>(v.staging[q]) + (int64_t)me * max_chunk_vecs - chunk_lo(q);
+      copy_vecs(dst, in, lo, hi);
+    }
+    psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+  }
+  if (ok) {
+    int64_t lo, hi;
+    slice(me, lo, hi);
+    const int64_t c0 = chunk_lo(me);
+    const uint4* mine = reinterpret_cast<const uint4*>(v.staging[me]);
+    uint4* dst = (me == root) ? out : reinterpret_cast<uint4*>(v.staging[root]) + ag_base;
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) {
+      float a[O::N];
+#pragma unroll
+      for (int k = 0; k < O::N; ++k) a[k] = 0.f;
+      for (int r = 0; r < N; ++r) {
+        const uint4 x = (r == me) ? in[i] : mine[(int64_t)r * max_chunk_vecs + (i - c0)];
+        O::acc(a, x);
+      }
+      dst[i] = O::pack(a, scale);
+    }
+    if (me != root) {
+      psync::cta_signal_phase(v, L, 1, 1u << root);
+    } else {
+      ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
+      if (ok) {
+        const uint4* ag = mine + ag_base;
+        for (int k = 1; k < N; ++k) {
+          const int q = (me + k) % N;
+          slice(q, lo, hi);
+          copy_vecs(out, ag, lo, hi);
+        }
+      }
+    }
+  }
+  psync::cta_finish_op(v, L);
+}
+
 __device__ __forceinline__ void barrier_body(const ArenaView& v, const Launch& L) {
   psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
   psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
@@ -294,6 +446,23 @@ __global__ void __launch_bounds__(kThreads)
     broadcast_twophase_body(v, psync::real_launch(), buf, nvec, root);
   else
     broadcast_direct_body(v, psync::real_launch(), buf, nvec, root);
+}
+__global__ void __launch_bounds__(kThreads)
+    scatter_gather_kernel(const __grid_constant__ ArenaView v, const uint4* in, uint4* out, int64_t cvec, int root,
+                          int skip_local, int gather) {
+  if (gather)
+    gather_body(v, psync::real_launch(), in, out, cvec, root, skip_local);
+  else
+    scatter_body(v, psync::real_launch(), in, out, cvec, root, skip_local);
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    reduce_kernel(const __grid_constant__ ArenaView v, const uint4* in, uint4* out, int64_t nvec, int64_t max_chunk_vecs,
+                  int root, float scale, int two_phase) {
+  if (two_phase)
+    reduce_twophase_body<T>(v, psync::real_launch(), in, out, nvec, max_chunk_vecs, root, scale);
+  else
+    reduce_direct_body<T>(v, psync::real_launch(), in, out, nvec, root, scale);
 }
 __global__ void __launch_bounds__(kThreads) barrier_kernel(const __grid_constant__ ArenaView v) {
   barrier_body(v, psync::real_launch());
@@ -331,6 +500,20 @@ __global__ void __launch_bounds__(kThreads)
     case EmuCollective::BroadcastDirect: broadcast_direct_body(e.view, L, (uint4*)e.out, cvec, aux); break;
     case EmuCollective::BroadcastTwoPhase: broadcast_twophase_body(e.view, L, (uint4*)e.out, cvec, aux); break;
     case EmuCollective::Barrier: barrier_body(e.view, L); break;
+    // aux = root | skip_local << 8 for the rooted collectives below
+    case EmuCollective::Scatter:
+      scatter_body(e.view, L, (const uint4*)e.in, (uint4*)e.out, cvec, aux & 0xff, (aux >> 8) & 1);
+      break;
+    case EmuCollective::Gather:
+      gather_body(e.view, L, (const uint4*)e.in, (uint4*)e.out, cvec, aux & 0xff, (aux >> 8) & 1);
+      break;
+    case EmuCollective::ReduceDirect:
+      reduce_direct_body<T>(e.view, L, (const uint4*)e.in, (uint4*)e.out, cvec, aux & 0xff, scale);
+      break;
+    case EmuCollective::ReduceTwoPhase:
+      reduce_twophase_body<T>(e.view, L, (const uint4*)e.in, (uint4*)e.out, cvec, (cvec + e.view.nranks - 1) / e.view.nranks,
+                              aux & 0xff, scale);
+      break;
   }
 }
 
@@ -440,6 +623,78 @@ bool broadcast(PeerArena& arena, void* buf, size_t bytes, int root, cudaStream_t
   BAGUA_CUDA_CHECK(cudaGetLastError());
   arena.count_launch();
   return true;
+}
+
+namespace {
+
+bool scatter_gather(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, int root, bool gather,
+                    cudaStream_t stream) {
+  const int N = arena.nranks(), me = arena.rank();
+  if (root < 0 || root >= N) return false;
+  if (chunk_bytes == 0) return true;
+  // Only the root's big buffer and every rank's chunk are touched; the root's pointers decide
+  // alignment on the root, the chunk pointers elsewhere.
+  const void* used_in = (gather || me == root) ? in : nullptr;
+  void* used_out = (!gather || me == root) ? out : nullptr;
+  if (chunk_bytes % 16 != 0 || !aligned16(used_in) || !aligned16(used_out)) return false;
+  const size_t need = gather ? chunk_bytes * (size_t)N : chunk_bytes;
+  if (need > kMaxStaging) return false;
+  int skip_local = 0;
+  if (me == root) {
+    const char* big = gather ? (const char*)out : (const char*)in;
+    const char* small = gather ? (const char*)in : (const char*)out;
+    skip_local = (small == big + (size_t)me * chunk_bytes) ? 1 : 0;
+  }
+  const int grid = grid_for_bytes(chunk_bytes * (size_t)N, arena.max_blocks());
+  arena.ensure_staging(need);
+  ArenaView v = arena.next_view(grid, 0);
+  scatter_gather_kernel<<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, (int64_t)(chunk_bytes / 16),
+                                                       root, skip_local, gather ? 1 : 0);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+template <typename T>
+bool reduce_t(PeerArena& arena, const void* in, void* out, int64_t n, int root, float scale, cudaStream_t stream) {
+  const int N = arena.nranks(), me = arena.rank();
+  const size_t bytes = (size_t)n * sizeof(T);
+  if (bytes == 0) return true;
+  if (bytes % 16 != 0 || !aligned16(in) || (me == root && !aligned16(out))) return false;
+  const int64_t nvec = (int64_t)(bytes / 16);
+  const int two_phase = (N > 2 && bytes * (size_t)(N - 1) > ((size_t)4 << 20)) ? 1 : 0;
+  const int64_t max_chunk = (nvec + N - 1) / N;
+  const size_t need = two_phase ? ((size_t)N * (size_t)max_chunk + (size_t)nvec) * 16 : (size_t)N * bytes;
+  if (need > kMaxStaging) return false;
+  const int grid = grid_for_bytes(bytes, arena.max_blocks());
+  arena.ensure_staging(need);
+  ArenaView v = arena.next_view(grid, 0);
+  reduce_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, nvec, max_chunk, root, scale,
+                                                  two_phase);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
+}
+
+}  // namespace
+
+bool scatter(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, int root, cudaStream_t stream) {
+  return scatter_gather(arena, in, out, chunk_bytes, root, false, stream);
+}
+
+bool gather(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, int root, cudaStream_t stream) {
+  return scatter_gather(arena, in, out, chunk_bytes, root, true, stream);
+}
+
+bool reduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, int root,
+            cudaStream_t stream) {
+  if (root < 0 || root >= arena.nranks()) return false;
+  switch (dt) {
+    case DType::F32: return reduce_t<float>(arena, in, out, n, root, scale, stream);
+    case DType::F16: return reduce_t<__half>(arena, in, out, n, root, scale, stream);
+    case DType::BF16: return reduce_t<__nv_bfloat16>(arena, in, out, n, root, scale, stream);
+    default: return false;
+  }
 }
 
 bool barrier(PeerArena& arena, cudaStream_t stream) {

@@ -143,10 +143,29 @@ void EmulatedArena::collective(EmuCollective kind, const std::vector<const void*
     BAGUA_CHECK(chunk_bytes > 0 && chunk_bytes % 16 == 0 && out.size() == N, Tensor,
                 "emulated collective: need one 16-byte-multiple buffer per rank");
     const bool bcast = kind == EmuCollective::BroadcastDirect || kind == EmuCollective::BroadcastTwoPhase;
+    const bool rooted = kind == EmuCollective::Scatter || kind == EmuCollective::Gather ||
+                        kind == EmuCollective::ReduceDirect || kind == EmuCollective::ReduceTwoPhase;
     if (bcast) {
       BAGUA_CHECK(root >= 0 && root < nranks_, Communicator, "emulated broadcast: root out of range");
       need = chunk_bytes;
       aux = root;
+    } else if (rooted) {
+      BAGUA_CHECK(root >= 0 && root < nranks_ && in.size() == N, Communicator,
+                  "emulated rooted collective: root out of range or inputs missing");
+      const size_t nvec = chunk_bytes / 16;
+      bool in_place = false;
+      if (kind == EmuCollective::Scatter) {
+        need = chunk_bytes;
+        in_place = (const char*)out[(size_t)root] == (const char*)in[(size_t)root] + (size_t)root * chunk_bytes;
+      } else if (kind == EmuCollective::Gather) {
+        need = N * chunk_bytes;
+        in_place = (const char*)in[(size_t)root] == (const char*)out[(size_t)root] + (size_t)root * chunk_bytes;
+      } else if (kind == EmuCollective::ReduceDirect) {
+        need = N * chunk_bytes;
+      } else {
+        need = (N * ((nvec + N - 1) / N) + nvec) * 16;
+      }
+      aux = root | (in_place ? 1 << 8 : 0);
     } else {
       BAGUA_CHECK(in.size() == N, Tensor, "emulated collective: one input per rank expected");
       need = symmetric ? 0 : N * chunk_bytes;

@@ -34,7 +34,18 @@ struct EmuRank {
 };
 
 enum class EmuAllreduceMode { OneShot = 1, TwoShot = 2, Symmetric = 3 };
-enum class EmuCollective { AllGather = 1, AllToAll = 2, ReduceScatter = 3, BroadcastDirect = 4, BroadcastTwoPhase = 5, Barrier = 6 };
+enum class EmuCollective {
+  AllGather = 1,
+  AllToAll = 2,
+  ReduceScatter = 3,
+  BroadcastDirect = 4,
+  BroadcastTwoPhase = 5,
+  Barrier = 6,
+  Scatter = 7,
+  Gather = 8,
+  ReduceDirect = 9,
+  ReduceTwoPhase = 10
+};
 
 class EmulatedArena {
  public:
@@ -58,7 +69,9 @@ class EmulatedArena {
   // per chunk, in[r] / out[r] per rank (in-place forms allowed); `symmetric` selects the
   // variants that store into (exchange) or load from (reduce-scatter) the peers' buffers
   // directly.  Broadcast*: `out[r]` is rank r's buffer of `chunk_bytes`, `root` the source.
-  // Barrier: no buffers.
+  // Scatter: in[r] holds N chunks (read on the root), out[r] one.  Gather: in[r] one chunk,
+  // out[r] N chunks (written on the root).  Reduce*: in[r] and out[r] of `chunk_bytes`, the
+  // sum lands in out[root].  Barrier: no buffers.
   void collective(EmuCollective kind, const std::vector<const void*>& in, const std::vector<void*>& out,
                   size_t chunk_bytes, DType dt, float scale, int root, bool symmetric, int blocks);
   void set_deadline_ms(double ms) { deadline_ns_ = (uint64_t)(ms * 1e6); }
@@ -85,7 +98,7 @@ void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n,
                           EmuAllreduceMode mode, int64_t aux_vecs);
 void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, bool symmetric);
 // aux: bit 0 = symmetric variant, bit 1 = local chunk already in place (exchange);
-// the root rank for the broadcasts.
+// the root rank for the broadcasts; root | in_place << 8 for scatter, gather and reduce.
 void emu_launch_collective(const EmuRank* dev, int nranks, int blocks, EmuCollective kind, int64_t cvec, DType dt,
                            int aux, float scale);
 void emu_launch_bytegrad(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,

@@ -39,6 +39,10 @@ enum class Kind {
   BroadcastDirect,
   BroadcastTwoPhase,
   Barrier,
+  Scatter,
+  Gather,
+  ReduceDirect,
+  ReduceTwoPhase,
   kCount
 };
 
@@ -340,6 +344,111 @@ struct Block {
     return wait_phase(0, all_peers());
   }
 
+  bool scatter(int64_t cvec, int root) {
+    if (!wait_prev_done()) return false;
+    int64_t lo, hi;
+    slice(0, cvec, lo, hi);
+    if (me == root) {
+      for (int s = 1; s < N; ++s) {
+        const int q = (me + s) % N;
+        for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)i], in((int64_t)q * cvec + i));
+      }
+      signal(0, all_peers());
+      return true;
+    }
+    if (!wait_phase(0, 1u << root)) return false;
+    jitter(20);
+    for (int64_t i = lo; i < hi; ++i)
+      if (get(mine.staging[(size_t)i]) != Model::input(k, root, (int64_t)me * cvec + i)) ++bad;
+    return true;
+  }
+
+  bool gather(int64_t cvec, int root) {
+    if (!wait_prev_done()) return false;
+    int64_t lo, hi;
+    slice(0, cvec, lo, hi);
+    if (me != root) {
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[root]->staging[(size_t)(me * cvec + i)], in(i));
+      signal(0, 1u << root);
+      return true;
+    }
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    for (int s = 1; s < N; ++s) {
+      const int r = (me + s) % N;
+      for (int64_t i = lo; i < hi; ++i)
+        if (get(mine.staging[(size_t)(r * cvec + i)]) != Model::input(k, r, i)) ++bad;
+    }
+    return true;
+  }
+
+  bool reduce_direct(int64_t nvec, int root) {
+    if (!wait_prev_done()) return false;
+    int64_t lo, hi;
+    slice(0, nvec, lo, hi);
+    if (me != root) {
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[root]->staging[(size_t)(me * nvec + i)], in(i));
+      signal(0, 1u << root);
+      return true;
+    }
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    for (int64_t i = lo; i < hi; ++i) {
+      uint32_t sum = 0, expect = 0;
+      for (int r = 0; r < N; ++r) {
+        sum += (r == me) ? in(i) : get(mine.staging[(size_t)(r * nvec + i)]);
+        expect += Model::input(k, r, i);
+      }
+      if (sum != expect) ++bad;
+    }
+    return true;
+  }
+
+  bool reduce_twophase(int64_t nvec, int root) {
+    if (!wait_prev_done()) return false;
+    const int64_t max_chunk = (nvec + N - 1) / N, ag_base = (int64_t)N * max_chunk;
+    auto chunk_lo = [&](int c) { return nvec * c / N; };
+    auto cslice = [&](int c, int64_t& lo, int64_t& hi) { slice(chunk_lo(c), chunk_lo(c + 1) - chunk_lo(c), lo, hi); };
+    for (int s = 1; s < N; ++s) {
+      const int q = (me + s) % N;
+      int64_t lo, hi;
+      cslice(q, lo, hi);
+      for (int64_t i = lo; i < hi; ++i) put(m.mem[q]->staging[(size_t)(me * max_chunk + (i - chunk_lo(q)))], in(i));
+    }
+    signal(0, all_peers());
+    if (!wait_phase(0, all_peers())) return false;
+    jitter(20);
+    {
+      int64_t lo, hi;
+      cslice(me, lo, hi);
+      for (int64_t i = lo; i < hi; ++i) {
+        uint32_t sum = 0, expect = 0;
+        for (int r = 0; r < N; ++r) {
+          sum += (r == me) ? in(i) : get(mine.staging[(size_t)(r * max_chunk + (i - chunk_lo(me)))]);
+          expect += Model::input(k, r, i);
+        }
+        if (sum != expect) ++bad;
+        if (me != root) put(m.mem[root]->staging[(size_t)(ag_base + i)], sum);
+      }
+    }
+    if (me != root) {
+      signal(1, 1u << root);
+      return true;
+    }
+    if (!wait_phase(1, all_peers())) return false;
+    for (int s = 1; s < N; ++s) {
+      const int q = (me + s) % N;
+      int64_t lo, hi;
+      cslice(q, lo, hi);
+      for (int64_t i = lo; i < hi; ++i) {
+        uint32_t expect = 0;
+        for (int r = 0; r < N; ++r) expect += Model::input(k, r, i);
+        if (get(mine.staging[(size_t)(ag_base + i)]) != expect) ++bad;
+      }
+    }
+    return true;
+  }
+
   void run(const std::vector<OpDesc>& ops) {
     for (k = 0; k < ops.size(); ++k) {
       epoch = k + 1;
@@ -358,6 +467,10 @@ struct Block {
         case Kind::BroadcastDirect: ok = broadcast_direct(d.nvec, d.root); break;
         case Kind::BroadcastTwoPhase: ok = broadcast_twophase(d.nvec, d.root); break;
         case Kind::Barrier: ok = barrier(); break;
+        case Kind::Scatter: ok = scatter(d.nvec, d.root); break;
+        case Kind::Gather: ok = gather(d.nvec, d.root); break;
+        case Kind::ReduceDirect: ok = reduce_direct(d.nvec, d.root); break;
+        case Kind::ReduceTwoPhase: ok = reduce_twophase(d.nvec, d.root); break;
         default: break;
       }
       if (!ok) return;
@@ -410,6 +523,16 @@ ProtocolModelResult run_protocol_model(int nranks, int blocks, int n_ops, uint32
         break;
       case Kind::BroadcastDirect:
       case Kind::BroadcastTwoPhase: need = d.nvec; break;
+      case Kind::Scatter:
+        d.nvec = 3 + d.nvec / 4;
+        need = d.nvec;
+        break;
+      case Kind::Gather:
+        d.nvec = 3 + d.nvec / 4;
+        need = (int64_t)nranks * d.nvec;
+        break;
+      case Kind::ReduceDirect: need = (int64_t)nranks * d.nvec; break;
+      case Kind::ReduceTwoPhase: need = (int64_t)nranks * ((d.nvec + nranks - 1) / nranks) + d.nvec; break;
       default: break;
     }
     max_words = std::max(max_words, need);

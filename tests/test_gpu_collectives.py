@@ -1,5 +1,5 @@
 """Peer-memory kernels for the communicator's own collectives (all-gather, all-to-all,
-reduce-scatter, broadcast, barrier): on one GPU through the single-launch emulation, and
+reduce-scatter, broadcast, reduce, gather, scatter, barrier): on one GPU through the single-launch emulation, and
 on several GPUs against the library (NCCL) results.
 
 These kernels are newer than the rest of the GPU suite and are off by default in the
@@ -114,6 +114,59 @@ def test_emulated_broadcast(nranks, kind):
                 assert torch.equal(b, ref)
 
 
+@pytest.mark.parametrize("nranks", [2, 3, 8])
+def test_emulated_scatter_and_gather(nranks):
+    arena = _arena(nranks)
+    for chunk, blocks in CASES:
+        for root in {0, nranks - 1}:
+            big = [_rand(chunk * nranks, torch.float32, 13 * chunk + r) for r in range(nranks)]
+            outs = [torch.zeros(chunk, device="cuda") for _ in range(nranks)]
+            arena.collective("scatter", big, outs, root=root, blocks=blocks)
+            for r in range(nranks):
+                assert torch.equal(outs[r], big[root][r * chunk:(r + 1) * chunk])
+            # gather them back into a fresh buffer on the root; other ranks' outputs stay as they were
+            back = [torch.full((chunk * nranks,), -1.0, device="cuda") for _ in range(nranks)]
+            arena.collective("gather", outs, back, root=root, blocks=blocks)
+            assert torch.equal(back[root], big[root])
+            for r in range(nranks):
+                if r != root:
+                    assert torch.equal(back[r], torch.full_like(back[r], -1.0))
+            # in-place forms on the root
+            ys = [b.clone() for b in big]
+            views = [ys[r][r * chunk:(r + 1) * chunk] if r == root else torch.zeros(chunk, device="cuda")
+                     for r in range(nranks)]
+            arena.collective("scatter", ys, views, root=root, blocks=blocks)
+            for r in range(nranks):
+                assert torch.equal(views[r], big[root][r * chunk:(r + 1) * chunk])
+            arena.collective("gather", views, ys, root=root, blocks=blocks)
+            assert torch.equal(ys[root], big[root])
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 8])
+@pytest.mark.parametrize("kind", ["reduce_direct", "reduce_twophase"])
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16])
+def test_emulated_reduce(nranks, kind, dt):
+    arena = _arena(nranks)
+    tol = 1e-6 if dt == torch.float32 else 2e-3
+    for n, blocks in [(8, 1), (4096 + 8, 3), (1 << 20, 8)]:
+        root = n % nranks
+        xs = [_rand(n, dt, 17 * n + r) for r in range(nranks)]
+        ref = torch.stack([x.float() for x in xs]).mean(0)
+        outs = [torch.full((n,), 7.0, dtype=dt, device="cuda") for _ in range(nranks)]
+        arena.collective(kind, xs, outs, root=root, average=True, blocks=blocks)
+        assert torch.allclose(outs[root].float(), ref, rtol=tol, atol=tol * max(1.0, ref.abs().max().item()))
+        for r in range(nranks):
+            if r != root:
+                assert torch.equal(outs[r], torch.full_like(outs[r], 7.0))
+        # in place: only the root's buffer changes
+        ys = [x.clone() for x in xs]
+        arena.collective(kind, ys, ys, root=root, blocks=blocks)
+        assert torch.allclose(ys[root].float(), ref * nranks, rtol=tol, atol=tol * nranks * max(1.0, ref.abs().max().item()))
+        for r in range(nranks):
+            if r != root:
+                assert torch.equal(ys[r], xs[r])
+
+
 def test_emulated_collectives_interleaved_with_allreduce():
     """Different kernels back to back over the same staging and signal words."""
     nranks = 4
@@ -226,6 +279,33 @@ def _p2p_vs_library(rank, world):
             comm.allreduce_inplace(T(buf, "b"), 10)
             return buf
 
+        def gather():
+            out = torch.full((chunk * world,), -1.0, device=dev)
+            comm.gather(T(x, "s"), T(out, "r"), world - 1)
+            return out if rank == world - 1 else torch.zeros(1, device=dev)
+
+        def scatter():
+            out = torch.zeros(chunk, device=dev)
+            comm.scatter(T(big, "s"), T(out, "r"), 0)
+            return out
+
+        def reduce():
+            buf = big.clone()
+            torch.cuda.synchronize()
+            comm.reduce_inplace(T(buf, "b"), 1 % world, 0)
+            return buf
+
+        for fn in (gather, scatter):
+            lib, p2p = both(fn)
+            assert torch.equal(lib, p2p), (fn.__name__, chunk)
+            checked += 1
+        lib, p2p = both(reduce)
+        if rank == 1 % world:
+            assert torch.allclose(lib, p2p, rtol=1e-5, atol=1e-5), ("reduce", chunk)
+        else:
+            assert torch.equal(p2p, big)  # only the root's buffer changes
+        checked += 1
+
         for fn in (allgather, allgather_inplace, alltoall, alltoall_inplace, broadcast):
             lib, p2p = both(fn)
             assert torch.equal(lib, p2p), (fn.__name__, chunk)
@@ -272,4 +352,4 @@ def _p2p_vs_library(rank, world):
 def test_p2p_collectives_match_the_library():
     world = min(torch.cuda.device_count(), int(os.environ.get("BAGUA_TEST_WORLD", "8")))
     res = run_ranks(_p2p_vs_library, world, backend="nccl", timeout=600)
-    assert all(r == 26 for r in res)
+    assert all(r == 35 for r in res)
