@@ -10,6 +10,28 @@ from .algorithms import (  # noqa: F401
     QAdamOptimizer,
 )
 from .bucket import BaguaBucket, BaguaTensor, split_into_buckets  # noqa: F401
+from .collectives import (  # noqa: F401
+    ReduceOp,
+    allgather,
+    allgather_inplace,
+    allreduce,
+    allreduce_inplace,
+    alltoall,
+    alltoall_inplace,
+    alltoall_v,
+    barrier,
+    broadcast,
+    gather,
+    gather_inplace,
+    recv,
+    reduce,
+    reduce_inplace,
+    reduce_scatter,
+    reduce_scatter_inplace,
+    scatter,
+    scatter_inplace,
+    send,
+)
 from .communication import (  # noqa: F401
     BaguaProcessGroup,
     destroy_process_group,
