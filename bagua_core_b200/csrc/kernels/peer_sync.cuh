@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include "../comm/arena.h"
+#include "host_emulation.h"
 
 namespace bagua {
 namespace psync {
@@ -32,6 +33,18 @@ struct Launch {
 };
 __device__ __forceinline__ Launch real_launch() { return Launch{(int)blockIdx.x, (int)gridDim.x}; }
 
+#ifdef BAGUA_HOST_EMULATION
+// The same five primitives for the host-thread emulation of the device code.
+inline uint64_t globaltimer_ns() {
+  timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return (uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec;
+}
+inline void st_release_sys(uint32_t* p, uint32_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
+inline uint32_t ld_acquire_sys(const uint32_t* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+inline uint32_t ld_relaxed_gpu(const uint32_t* p) { return __atomic_load_n(p, __ATOMIC_RELAXED); }
+inline uint64_t ld_acquire_gpu_u64(const unsigned long long* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+#else
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -55,6 +68,7 @@ __device__ __forceinline__ uint64_t ld_acquire_gpu_u64(const unsigned long long*
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+#endif
 
 __device__ __forceinline__ uint32_t* phase_word(uint32_t* pad, int phase, int src, int block) {
   return pad + kSigPhase + (phase * kArenaMaxRanks + src) * kArenaMaxBlocks + block;
@@ -134,7 +148,7 @@ __device__ __forceinline__ bool cta_wait_phase(const ArenaView& v, const Launch&
 // peer that this rank is done with the op (so they may overwrite its staging next op).
 __device__ __forceinline__ void cta_finish_op(const ArenaView& v, const Launch& L) {
   __syncthreads();
-  __shared__ int s_last;
+  BAGUA_SHARED(int, s_last, 0);
   uint32_t* pad = v.signals[v.rank];
   if (threadIdx.x == 0) {
     __threadfence();
@@ -157,7 +171,7 @@ __device__ __forceinline__ void cta_finish_op(const ArenaView& v, const Launch& 
 // (cooperative launch).  Returns false if the wait gave up.
 __device__ __forceinline__ bool grid_barrier(const ArenaView& v, const Launch& L, int index) {
   __syncthreads();
-  __shared__ int s_ok;
+  BAGUA_SHARED(int, s_ok, 1);
   if (threadIdx.x == 0) {
     unsigned long long* ctr = reinterpret_cast<unsigned long long*>(v.signals[v.rank] + kSigGridBar);
     const unsigned long long target = v.grid_bar_base + (unsigned long long)(index + 1) * (unsigned long long)L.grid;

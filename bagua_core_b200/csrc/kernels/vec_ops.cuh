@@ -8,11 +8,16 @@
 #include <cuda_runtime.h>
 
 #include "../comm/arena.h"
+#include "host_emulation.h"
 
 namespace bagua {
 namespace fused {
 
+#ifdef BAGUA_HOST_EMULATION
+constexpr int kThreads = 8;  // OS threads per emulated block; thread t talks to rank t, so at least kArenaMaxRanks
+#else
 constexpr int kThreads = 512;
+#endif
 
 template <typename T>
 struct VecOps;

@@ -1,0 +1,372 @@
+// The device bodies of the fused all-reduce, pair-average and collective kernels, compiled for the host
+// (-DBAGUA_HOST_EMULATION) and run with one OS thread per CUDA thread: N ranks x G blocks x
+// kThreads threads execute random sequences of these ops over per-rank staging buffers
+// and signal pads, every result is checked against the collective's definition, and the
+// whole program is meant to be built with -fsanitize=thread, so that a payload access that
+// the signalling does not order shows up as a data race.
+//
+// What it models of a GPU run: the kernel boundary on each rank's stream (a per-rank barrier
+// between ops, so ranks drift apart by whole ops), block b of every rank pairing with block
+// b of its peers, and the `done` chain that protects staging reuse.
+//
+//   device_emulation [nranks] [blocks] [ops] [seed]
+#include <barrier>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <thread>
+#include <vector>
+
+#include "kernels/fused_allreduce_bodies.cuh"
+#include "kernels/fused_collectives_bodies.cuh"
+
+using namespace bagua;
+using namespace bagua::fused;
+using namespace bagua::fused::collectives;
+using namespace bagua::fused::allreduce_bodies;
+using bagua::psync::Launch;
+
+namespace {
+
+enum class Kind {
+  AllGather,
+  AllGatherInPlace,
+  AllGatherSym,
+  AllToAll,
+  AllToAllInPlace,
+  AllToAllSym,
+  ReduceScatter,
+  ReduceScatterInPlace,
+  ReduceScatterSym,
+  BroadcastDirect,
+  BroadcastTwoPhase,
+  Scatter,
+  Gather,
+  ReduceDirect,
+  ReduceTwoPhase,
+  Barrier,
+  AllReduceOneShot,
+  AllReduceTwoShot,
+  AllReduceTwoShotInPlace,
+  AllReduceSym,
+  PairAverage,
+  PairAverageSym,
+  kCount
+};
+
+struct Op {
+  Kind kind;
+  int64_t vecs;  // per chunk (chunked ops) or per buffer
+  int root;
+  float scale;
+};
+
+float value(uint32_t op, int rank, int64_t i) { return (float)((op * 31u + (uint32_t)rank * 7u + (uint32_t)i) % 1000u); }
+
+struct alignas(16) Vec {
+  float f[4];
+};
+
+struct Rank {
+  std::vector<Vec> staging, in, out;
+  std::vector<uint32_t> signals;
+  std::unique_ptr<std::barrier<>> bar;  // the rank's stream: all of its threads between ops
+  uint64_t errors = 0;
+};
+
+struct World {
+  int N, G;
+  std::vector<Op> ops;
+  std::vector<Rank> ranks;
+  DeviceStatus status{};
+  std::vector<std::unique_ptr<hostemu::BlockContext>> blocks;  // [rank * G + block]
+};
+
+ArenaView view_of(World& w, int rank, uint32_t epoch) {
+  ArenaView v;
+  std::memset(&v, 0, sizeof(v));
+  for (int q = 0; q < w.N; ++q) {
+    v.staging[q] = reinterpret_cast<uint8_t*>(w.ranks[q].staging.data());
+    v.signals[q] = w.ranks[q].signals.data();
+  }
+  v.status = &w.status;
+  v.staging_bytes = w.ranks[0].staging.size() * sizeof(Vec);
+  v.rank = rank;
+  v.nranks = w.N;
+  v.epoch = epoch;
+  v.deadline_ns = 60ull * 1000000000ull;
+  return v;
+}
+
+void fill(std::vector<Vec>& buf, uint32_t op, int rank, int64_t vecs) {
+  for (int64_t i = 0; i < vecs; ++i)
+    for (int l = 0; l < 4; ++l) buf[(size_t)i].f[l] = value(op, rank, 4 * i + l);
+}
+void poison(std::vector<Vec>& buf) {
+  for (auto& x : buf)
+    for (int l = 0; l < 4; ++l) x.f[l] = -12345.0f;
+}
+
+// Run by one thread of the rank before the op: inputs and poisoned outputs.
+void prepare(World& w, int me, uint32_t k) {
+  const Op& op = w.ops[k];
+  Rank& r = w.ranks[me];
+  const int N = w.N;
+  poison(r.out);
+  switch (op.kind) {
+    case Kind::AllGather:
+    case Kind::AllGatherSym:
+    case Kind::Gather: fill(r.in, k, me, op.vecs); break;
+    case Kind::AllGatherInPlace:
+      for (int64_t i = 0; i < op.vecs; ++i)
+        for (int l = 0; l < 4; ++l) r.out[(size_t)(me * op.vecs + i)].f[l] = value(k, me, 4 * i + l);
+      break;
+    case Kind::AllToAll:
+    case Kind::AllToAllSym:
+    case Kind::ReduceScatter:
+    case Kind::ReduceScatterInPlace:
+    case Kind::ReduceScatterSym:
+    case Kind::Scatter: fill(r.in, k, me, op.vecs * N); break;
+    case Kind::AllToAllInPlace: fill(r.out, k, me, op.vecs * N); break;
+    case Kind::BroadcastDirect:
+    case Kind::BroadcastTwoPhase: fill(r.out, k, me, op.vecs); break;  // only the root's content matters
+    case Kind::ReduceDirect:
+    case Kind::ReduceTwoPhase:
+    case Kind::AllReduceOneShot:
+    case Kind::AllReduceTwoShot:
+    case Kind::AllReduceSym:
+    case Kind::PairAverage:
+    case Kind::PairAverageSym: fill(r.in, k, me, op.vecs); break;
+    case Kind::AllReduceTwoShotInPlace: fill(r.out, k, me, op.vecs); break;
+    default: break;
+  }
+}
+
+// Run by every thread of the rank: the device body.
+void run_body(World& w, int me, int b, uint32_t k) {
+  const Op& op = w.ops[k];
+  Rank& r = w.ranks[me];
+  const ArenaView v = view_of(w, me, k + 1);
+  const Launch L{b, w.G};
+  const uint4* in = reinterpret_cast<const uint4*>(r.in.data());
+  uint4* out = reinterpret_cast<uint4*>(r.out.data());
+  PeerPtrs outs;
+  ConstPeerPtrs ins;
+  for (int q = 0; q < kArenaMaxRanks; ++q) {
+    outs.p[q] = q < w.N ? reinterpret_cast<uint4*>(w.ranks[q].out.data()) : nullptr;
+    ins.p[q] = q < w.N ? reinterpret_cast<const uint4*>(w.ranks[q].in.data()) : nullptr;
+  }
+  const int64_t c = op.vecs;
+  switch (op.kind) {
+    case Kind::AllGather: exchange_body(v, L, in, out, c, 0, 0); break;
+    case Kind::AllGatherInPlace: exchange_body(v, L, out + me * c, out, c, 0, 1); break;
+    case Kind::AllGatherSym: exchange_sym_body(v, L, in, outs, c, 0, 0); break;
+    case Kind::AllToAll: exchange_body(v, L, in, out, c, 1, 0); break;
+    case Kind::AllToAllInPlace: exchange_body(v, L, out, out, c, 1, 1); break;
+    case Kind::AllToAllSym: exchange_sym_body(v, L, in, outs, c, 1, 0); break;
+    case Kind::ReduceScatter: reduce_scatter_body<float>(v, L, in, out, c, op.scale); break;
+    case Kind::ReduceScatterInPlace: {
+      uint4* io = reinterpret_cast<uint4*>(r.in.data());
+      reduce_scatter_body<float>(v, L, io, io + me * c, c, op.scale);
+      break;
+    }
+    case Kind::ReduceScatterSym: reduce_scatter_sym_body<float>(v, L, ins, out, c, op.scale); break;
+    case Kind::BroadcastDirect: broadcast_direct_body(v, L, out, c, op.root); break;
+    case Kind::BroadcastTwoPhase: broadcast_twophase_body(v, L, out, c, op.root); break;
+    case Kind::Scatter: scatter_body(v, L, in, out, c, op.root, 0); break;
+    case Kind::Gather: gather_body(v, L, in, out, c, op.root, 0); break;
+    case Kind::ReduceDirect: reduce_direct_body<float>(v, L, in, out, c, op.root, op.scale); break;
+    case Kind::ReduceTwoPhase:
+      reduce_twophase_body<float>(v, L, in, out, c, (c + w.N - 1) / w.N, op.root, op.scale);
+      break;
+    case Kind::Barrier: barrier_body(v, L); break;
+    case Kind::AllReduceOneShot: allreduce_oneshot_body<float>(v, L, in, out, c, c, op.scale); break;
+    case Kind::AllReduceTwoShot: allreduce_twoshot_body<float>(v, L, in, out, c, (c + w.N - 1) / w.N, op.scale); break;
+    case Kind::AllReduceTwoShotInPlace:
+      allreduce_twoshot_body<float>(v, L, out, out, c, (c + w.N - 1) / w.N, op.scale);
+      break;
+    case Kind::AllReduceSym: {
+      SymPtrs p;
+      for (int q = 0; q < kArenaMaxRanks; ++q) {
+        p.in[q] = ins.p[q];
+        p.out[q] = outs.p[q];
+      }
+      allreduce_sym_body<float>(v, L, p, c, op.scale);
+      break;
+    }
+    case Kind::PairAverage: pair_average_body<float>(v, L, in, out, c, me ^ 1); break;
+    case Kind::PairAverageSym: pair_average_sym_body<float>(v, L, in, ins.p[me ^ 1], out, c, me ^ 1); break;
+    default: break;
+  }
+}
+
+// Run by one thread of the rank after the op (its kernel has finished).
+uint64_t verify(World& w, int me, uint32_t k) {
+  const Op& op = w.ops[k];
+  Rank& r = w.ranks[me];
+  const int N = w.N;
+  const int64_t c = op.vecs;
+  uint64_t bad = 0;
+  auto expect = [&](const std::vector<Vec>& buf, int64_t vec, float want_l0, float want_l1, float want_l2, float want_l3) {
+    const Vec& x = buf[(size_t)vec];
+    if (x.f[0] != want_l0 || x.f[1] != want_l1 || x.f[2] != want_l2 || x.f[3] != want_l3) ++bad;
+  };
+  auto val4 = [&](int rank, int64_t vec, float* o) {
+    for (int l = 0; l < 4; ++l) o[l] = value(k, rank, 4 * vec + l);
+  };
+  auto sum4 = [&](int64_t vec, float scale, float* o) {
+    for (int l = 0; l < 4; ++l) {
+      float s = 0.f;
+      for (int q = 0; q < N; ++q) s += value(k, q, 4 * vec + l);
+      o[l] = s * scale;
+    }
+  };
+  float e[4];
+  switch (op.kind) {
+    case Kind::AllGather:
+    case Kind::AllGatherInPlace:
+    case Kind::AllGatherSym:
+      for (int q = 0; q < N; ++q)
+        for (int64_t i = 0; i < c; ++i) {
+          val4(q, i, e);
+          expect(r.out, q * c + i, e[0], e[1], e[2], e[3]);
+        }
+      break;
+    case Kind::AllToAll:
+    case Kind::AllToAllInPlace:
+    case Kind::AllToAllSym:
+      for (int q = 0; q < N; ++q)
+        for (int64_t i = 0; i < c; ++i) {
+          val4(q, me * c + i, e);
+          expect(r.out, q * c + i, e[0], e[1], e[2], e[3]);
+        }
+      break;
+    case Kind::ReduceScatter:
+    case Kind::ReduceScatterSym:
+      for (int64_t i = 0; i < c; ++i) {
+        sum4(me * c + i, op.scale, e);
+        expect(r.out, i, e[0], e[1], e[2], e[3]);
+      }
+      break;
+    case Kind::ReduceScatterInPlace:
+      for (int64_t i = 0; i < c; ++i) {
+        sum4(me * c + i, op.scale, e);
+        expect(r.in, me * c + i, e[0], e[1], e[2], e[3]);
+      }
+      break;
+    case Kind::BroadcastDirect:
+    case Kind::BroadcastTwoPhase:
+      for (int64_t i = 0; i < c; ++i) {
+        val4(op.root, i, e);
+        expect(r.out, i, e[0], e[1], e[2], e[3]);
+      }
+      break;
+    case Kind::Scatter:
+      for (int64_t i = 0; i < c; ++i) {
+        val4(op.root, me * c + i, e);
+        expect(r.out, i, e[0], e[1], e[2], e[3]);
+      }
+      break;
+    case Kind::Gather:
+      if (me == op.root)
+        for (int q = 0; q < N; ++q)
+          for (int64_t i = 0; i < c; ++i) {
+            val4(q, i, e);
+            expect(r.out, q * c + i, e[0], e[1], e[2], e[3]);
+          }
+      else
+        for (int64_t i = 0; i < c * N; ++i) expect(r.out, i, -12345.0f, -12345.0f, -12345.0f, -12345.0f);
+      break;
+    case Kind::ReduceDirect:
+    case Kind::ReduceTwoPhase:
+      for (int64_t i = 0; i < c; ++i) {
+        if (me == op.root) {
+          sum4(i, op.scale, e);
+          expect(r.out, i, e[0], e[1], e[2], e[3]);
+        } else {
+          expect(r.out, i, -12345.0f, -12345.0f, -12345.0f, -12345.0f);
+        }
+      }
+      break;
+    case Kind::AllReduceOneShot:
+    case Kind::AllReduceTwoShot:
+    case Kind::AllReduceTwoShotInPlace:
+    case Kind::AllReduceSym:
+      for (int64_t i = 0; i < c; ++i) {
+        sum4(i, op.scale, e);
+        expect(r.out, i, e[0], e[1], e[2], e[3]);
+      }
+      break;
+    case Kind::PairAverage:
+    case Kind::PairAverageSym:
+      for (int64_t i = 0; i < c; ++i) {
+        for (int l = 0; l < 4; ++l) e[l] = (value(k, me, 4 * i + l) + value(k, me ^ 1, 4 * i + l)) * 0.5f;
+        expect(r.out, i, e[0], e[1], e[2], e[3]);
+      }
+      break;
+    default: break;
+  }
+  return bad;
+}
+
+void cuda_thread(World& w, int me, int b, int t) {
+  hostemu::bind_thread(w.blocks[(size_t)(me * w.G + b)].get(), (unsigned)t, (unsigned)b, (unsigned)w.G);
+  Rank& r = w.ranks[me];
+  const bool lead = b == 0 && t == 0;
+  for (uint32_t k = 0; k < w.ops.size(); ++k) {
+    if (lead) prepare(w, me, k);
+    r.bar->arrive_and_wait();  // inputs ready: the kernel starts on this rank
+    run_body(w, me, b, k);
+    r.bar->arrive_and_wait();  // kernel boundary: every block of this rank has finished
+    if (lead) r.errors += verify(w, me, k);
+  }
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  World w;
+  w.N = argc > 1 ? std::atoi(argv[1]) : 4;
+  w.G = argc > 2 ? std::atoi(argv[2]) : 2;
+  const int n_ops = argc > 3 ? std::atoi(argv[3]) : 64;
+  const uint32_t seed = argc > 4 ? (uint32_t)std::atoi(argv[4]) : 1;
+  if (w.N < 2 || w.N > kArenaMaxRanks || w.G < 1 || w.G > 8 || n_ops < 1) {
+    std::fprintf(stderr, "usage: device_emulation [nranks 2..8] [blocks 1..8] [ops] [seed]\n");
+    return 2;
+  }
+  std::mt19937 rng(seed);
+  int64_t max_vecs = 0;
+  for (int k = 0; k < n_ops; ++k) {
+    Op op;
+    op.kind = (Kind)(rng() % (uint32_t)Kind::kCount);
+    if ((op.kind == Kind::PairAverage || op.kind == Kind::PairAverageSym) && w.N % 2) op.kind = Kind::Barrier;  // pairs need an even world
+    op.vecs = 1 + (int64_t)(rng() % 40);
+    op.root = (int)(rng() % (uint32_t)w.N);
+    op.scale = (rng() & 1) ? 1.0f : 0.5f;
+    max_vecs = std::max(max_vecs, op.vecs);
+    w.ops.push_back(op);
+  }
+  const size_t buf_vecs = (size_t)max_vecs * (size_t)w.N;
+  w.ranks.resize((size_t)w.N);
+  for (auto& r : w.ranks) {
+    r.staging.assign(buf_vecs * 2 + 8, Vec{});  // N slots + the mirror area of the two-phase reduce
+    r.in.assign(buf_vecs, Vec{});
+    r.out.assign(buf_vecs, Vec{});
+    r.signals.assign((size_t)kSigWords, 0u);
+    r.bar = std::make_unique<std::barrier<>>(w.G * kThreads);
+  }
+  for (int i = 0; i < w.N * w.G; ++i) w.blocks.push_back(std::make_unique<hostemu::BlockContext>(kThreads));
+
+  std::vector<std::thread> threads;
+  for (int r = 0; r < w.N; ++r)
+    for (int b = 0; b < w.G; ++b)
+      for (int t = 0; t < kThreads; ++t) threads.emplace_back(cuda_thread, std::ref(w), r, b, t);
+  for (auto& t : threads) t.join();
+
+  uint64_t errors = 0;
+  for (auto& r : w.ranks) errors += r.errors;
+  const int failures = (errors != 0) + (w.status.code != 0);
+  std::printf("device emulation: %d ranks x %d blocks x %d threads, %d ops, %llu wrong vectors, wait status %u, %d failures\n",
+              w.N, w.G, kThreads, n_ops, (unsigned long long)errors, w.status.code, failures);
+  return failures ? 1 : 0;
+}
