@@ -9,7 +9,11 @@
 // between ops, so ranks drift apart by whole ops), block b of every rank pairing with block
 // b of its peers, and the `done` chain that protects staging reuse.
 //
-//   device_emulation [nranks] [blocks] [ops] [seed]
+//   device_emulation [nranks] [blocks] [ops] [seed] [absent_rank] [deadline_ms]
+//
+// With absent_rank >= 0 that rank never runs (a process that died between steps): the others'
+// waits must run out after deadline_ms, record what they waited for in the status record, and
+// return — the program then exits with code 3 instead of hanging.
 #include <barrier>
 #include <cstdio>
 #include <cstdlib>
@@ -80,6 +84,8 @@ struct World {
   std::vector<Rank> ranks;
   DeviceStatus status{};
   std::vector<std::unique_ptr<hostemu::BlockContext>> blocks;  // [rank * G + block]
+  int absent = -1;
+  uint64_t deadline_ns = 60ull * 1000000000ull;
 };
 
 ArenaView view_of(World& w, int rank, uint32_t epoch) {
@@ -94,7 +100,7 @@ ArenaView view_of(World& w, int rank, uint32_t epoch) {
   v.rank = rank;
   v.nranks = w.N;
   v.epoch = epoch;
-  v.deadline_ns = 60ull * 1000000000ull;
+  v.deadline_ns = w.deadline_ns;
   return v;
 }
 
@@ -313,12 +319,13 @@ void cuda_thread(World& w, int me, int b, int t) {
   hostemu::bind_thread(w.blocks[(size_t)(me * w.G + b)].get(), (unsigned)t, (unsigned)b, (unsigned)w.G);
   Rank& r = w.ranks[me];
   const bool lead = b == 0 && t == 0;
+  if (me == w.absent) return;
   for (uint32_t k = 0; k < w.ops.size(); ++k) {
     if (lead) prepare(w, me, k);
     r.bar->arrive_and_wait();  // inputs ready: the kernel starts on this rank
     run_body(w, me, b, k);
     r.bar->arrive_and_wait();  // kernel boundary: every block of this rank has finished
-    if (lead) r.errors += verify(w, me, k);
+    if (lead && w.absent < 0) r.errors += verify(w, me, k);
   }
 }
 
@@ -330,8 +337,10 @@ int main(int argc, char** argv) {
   w.G = argc > 2 ? std::atoi(argv[2]) : 2;
   const int n_ops = argc > 3 ? std::atoi(argv[3]) : 64;
   const uint32_t seed = argc > 4 ? (uint32_t)std::atoi(argv[4]) : 1;
-  if (w.N < 2 || w.N > kArenaMaxRanks || w.G < 1 || w.G > 8 || n_ops < 1) {
-    std::fprintf(stderr, "usage: device_emulation [nranks 2..8] [blocks 1..8] [ops] [seed]\n");
+  w.absent = argc > 5 ? std::atoi(argv[5]) : -1;
+  if (argc > 6) w.deadline_ns = (uint64_t)std::atoll(argv[6]) * 1000000ull;
+  if (w.N < 2 || w.N > kArenaMaxRanks || w.G < 1 || w.G > 8 || n_ops < 1 || w.absent >= w.N) {
+    std::fprintf(stderr, "usage: device_emulation [nranks 2..8] [blocks 1..8] [ops] [seed] [absent_rank] [deadline_ms]\n");
     return 2;
   }
   std::mt19937 rng(seed);
@@ -365,6 +374,11 @@ int main(int argc, char** argv) {
 
   uint64_t errors = 0;
   for (auto& r : w.ranks) errors += r.errors;
+  if (w.absent >= 0) {
+    std::printf("device emulation: rank %d absent, every other rank returned; wait status code %u (phase %u, peer %u)\n",
+                w.absent, w.status.code, w.status.phase, w.status.peer);
+    return w.status.code != 0 ? 3 : 1;
+  }
   const int failures = (errors != 0) + (w.status.code != 0);
   std::printf("device emulation: %d ranks x %d blocks x %d threads, %d ops, %llu wrong vectors, wait status %u, %d failures\n",
               w.N, w.G, kThreads, n_ops, (unsigned long long)errors, w.status.code, failures);

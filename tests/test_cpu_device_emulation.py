@@ -50,6 +50,18 @@ def test_device_bodies_compute_every_collective_correctly(tmp_path):
         _run(exe, nranks, blocks, ops, seed)
 
 
+def test_a_missing_rank_makes_the_others_time_out_and_return(tmp_path):
+    """Failure detection of the device code without a GPU: one rank never runs; every wait of the
+    others is bounded, so they record what they waited for and return instead of hanging."""
+    exe = _build(tmp_path, None)
+    for nranks, absent in [(2, 1), (4, 2), (8, 0)]:
+        run = subprocess.run([exe, str(nranks), "2", "30", "1", str(absent), "300"], capture_output=True, text=True,
+                             timeout=120)
+        assert run.returncode == 3, run.stdout + run.stderr
+        assert f"rank {absent} absent, every other rank returned" in run.stdout
+        assert "wait status code 0" not in run.stdout
+
+
 def test_device_bodies_are_race_free_under_thread_sanitizer(tmp_path):
     exe = _build(tmp_path, "thread")
     for nranks, blocks, ops, seed in [(2, 1, 60, 1), (4, 2, 80, 2), (3, 3, 60, 3)]:
