@@ -46,6 +46,7 @@ SOURCES = [
     "kernels/fused_nvls.cu",
     "kernels/fused_emu.cc",
     "kernels/no_alloc.cu",
+    "kernels/model_ops.cu",
 ]
 
 

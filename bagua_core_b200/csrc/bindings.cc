@@ -18,6 +18,7 @@
 #include "kernels/fused.h"
 #include "kernels/fused_emu.h"
 #include "kernels/kernels.h"
+#include "kernels/model_ops.h"
 #include "ops/comm_op.h"
 #include "pool/resource_pool.h"
 #include "runtime/backend.h"
@@ -536,6 +537,52 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("param"), py::arg("grad"), py::arg("momentum_buffer"), py::arg("lr"), py::arg("momentum"),
       py::arg("dampening"), py::arg("weight_decay"), py::arg("nesterov"), py::arg("first_step"), py::arg("stream"));
+
+  // ---- fused bias + ReLU for channels-last bf16 activations (model-side kernels) ----
+  // An activation is either [rows, C] contiguous or [N, C, H, W] in channels-last memory format.
+  auto rows_and_channels = [](const at::Tensor& t, int64_t* rows, int* C) {
+    BAGUA_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, Tensor, "fused bias+ReLU works on CUDA bf16 tensors");
+    if (t.dim() == 2 && t.is_contiguous()) {
+      *rows = t.size(0);
+      *C = (int)t.size(1);
+    } else {
+      BAGUA_CHECK(t.dim() == 4 && t.is_contiguous(at::MemoryFormat::ChannelsLast), Tensor,
+                  "fused bias+ReLU needs a [rows, C] tensor or a channels-last [N, C, H, W] tensor");
+      *rows = t.size(0) * t.size(2) * t.size(3);
+      *C = (int)t.size(1);
+    }
+  };
+  m.def("k_bias_relu_supported", [](int64_t rows, int C) { return model_ops::bias_relu_supported(rows, C); });
+  m.def(
+      "k_bias_relu_",
+      [rows_and_channels](at::Tensor z, at::Tensor bias, uint64_t stream) {
+        int64_t rows;
+        int C;
+        rows_and_channels(z, &rows, &C);
+        BAGUA_CHECK(bias.is_cuda() && bias.scalar_type() == at::kBFloat16 && bias.is_contiguous() && bias.numel() == C,
+                    Tensor, "bias must be a contiguous bf16 vector with one entry per channel");
+        model_ops::bias_relu_inplace_bf16(z.data_ptr(), bias.data_ptr(), rows, C, (cudaStream_t)stream);
+      },
+      py::arg("activation"), py::arg("bias"), py::arg("stream"), "activation = max(activation + bias, 0), in place.");
+  m.def(
+      "k_bias_relu_backward",
+      [rows_and_channels](at::Tensor dy, at::Tensor y, at::Tensor dz, at::Tensor db, uint64_t stream) {
+        int64_t rows, r2, r3;
+        int C, C2, C3;
+        rows_and_channels(dy, &rows, &C);
+        rows_and_channels(y, &r2, &C2);
+        rows_and_channels(dz, &r3, &C3);
+        BAGUA_CHECK(rows == r2 && rows == r3 && C == C2 && C == C3, Tensor, "dy, y and dz must have the same shape");
+        BAGUA_CHECK(db.is_cuda() && db.scalar_type() == at::kFloat && db.is_contiguous() && db.numel() == C, Tensor,
+                    "db must be a contiguous fp32 vector with one entry per channel");
+        const size_t need = model_ops::bias_relu_backward_scratch_bytes(rows, C);
+        BAGUA_CHECK(need > 0, Tensor, "fused bias+ReLU backward: unsupported shape");
+        auto scratch = PoolRawTensor::allocate((int)dy.device().index(), DType::U8, (int64_t)need, stream);
+        model_ops::bias_relu_backward_bf16(dy.data_ptr(), y.data_ptr(), dz.data_ptr(), (float*)db.data_ptr(), rows, C,
+                                           scratch->data_ptr(), (cudaStream_t)stream);
+      },
+      py::arg("grad_output"), py::arg("output"), py::arg("grad_pre_activation"), py::arg("grad_bias"), py::arg("stream"),
+      "grad_pre_activation = grad_output * [output > 0]; grad_bias[c] = column sums of it (fp32).");
 
   // ---- single-GPU emulation of the fused kernels (all ranks in one cooperative launch) ----
   py::class_<fused::EmulatedArena>(m, "EmulatedArena")

@@ -1,0 +1,168 @@
+// Fused bias + ReLU (forward, in place) and its backward with the bias-gradient reduction,
+// on channels-last bf16 activations viewed as [rows, C]; see model_ops.h.
+//
+// Both kernels are pure streams over the activation: 16-byte vectors (8 channels), every
+// warp reads whole contiguous rows, grids are a small multiple of the 148 SMs and loop with a
+// grid stride.  The backward keeps one fp32 accumulator per channel of the thread's vector
+// across all rows it visits, folds the block's accumulators through shared memory and writes
+// one partial row per block; a second tiny kernel adds the partial rows in block order, so the
+// bias gradient is bit-reproducible.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../common.h"
+#include "model_ops.h"
+
+namespace bagua {
+namespace model_ops {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxBlocks = 148 * 4;
+
+__device__ __forceinline__ void unpack8(const uint4& x, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 v = __bfloat1622float2(h[k]);
+    f[2 * k] = v.x;
+    f[2 * k + 1] = v.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 r;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+  return r;
+}
+
+// ---- forward ----------------------------------------------------------------------
+__device__ __forceinline__ uint4 bias_relu_vec(const uint4& x, const float* b) {
+  float f[8];
+  unpack8(x, f);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) f[k] = fmaxf(f[k] + b[k], 0.f);
+  return pack8(f);
+}
+
+// cgroups = C / 8 vectors per row.
+__global__ void __launch_bounds__(kThreads)
+    bias_relu_kernel(uint4* __restrict__ z, const __nv_bfloat16* __restrict__ bias, int64_t nvec, int cgroups) {
+  extern __shared__ float s_bias[];
+  for (int c = threadIdx.x; c < cgroups * 8; c += kThreads) s_bias[c] = __bfloat162float(bias[c]);
+  __syncthreads();
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  for (; v + 3 * stride < nvec; v += 4 * stride) {
+    const uint4 a = z[v], b = z[v + stride], c = z[v + 2 * stride], d = z[v + 3 * stride];
+    z[v] = bias_relu_vec(a, s_bias + (int)(v % cgroups) * 8);
+    z[v + stride] = bias_relu_vec(b, s_bias + (int)((v + stride) % cgroups) * 8);
+    z[v + 2 * stride] = bias_relu_vec(c, s_bias + (int)((v + 2 * stride) % cgroups) * 8);
+    z[v + 3 * stride] = bias_relu_vec(d, s_bias + (int)((v + 3 * stride) % cgroups) * 8);
+  }
+  for (; v < nvec; v += stride) z[v] = bias_relu_vec(z[v], s_bias + (int)(v % cgroups) * 8);
+}
+
+// ---- backward ---------------------------------------------------------------------
+__device__ __forceinline__ uint4 relu_mask_acc(const uint4& dy, const uint4& y, float (&acc)[8]) {
+  float g[8], o[8];
+  unpack8(dy, g);
+  unpack8(y, o);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    g[k] = o[k] > 0.f ? g[k] : 0.f;
+    acc[k] += g[k];
+  }
+  return pack8(g);
+}
+
+// Threads are laid out [rows_per_iter][cgroups]: thread (ro, cg) visits rows ro, ro + R, ...
+// (R = gridDim.x * rows_per_iter apart) and always the same 8 channels.  cgroups divides kThreads.
+__global__ void __launch_bounds__(kThreads)
+    bias_relu_backward_kernel(const uint4* dy, const uint4* __restrict__ y, uint4* dz,
+                              float* __restrict__ partial, int64_t rows, int cgroups) {
+  __shared__ float s_acc[kThreads * 8];
+  const int rows_per_iter = kThreads / cgroups;
+  const int cg = threadIdx.x % cgroups, ro = threadIdx.x / cgroups;
+  const int64_t step = (int64_t)gridDim.x * rows_per_iter;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  int64_t row = (int64_t)blockIdx.x * rows_per_iter + ro;
+  for (; row + step < rows; row += 2 * step) {
+    const int64_t v0 = row * cgroups + cg, v1 = (row + step) * cgroups + cg;
+    const uint4 a0 = dy[v0], b0 = y[v0], a1 = dy[v1], b1 = y[v1];
+    dz[v0] = relu_mask_acc(a0, b0, acc);
+    dz[v1] = relu_mask_acc(a1, b1, acc);
+  }
+  for (; row < rows; row += step) {
+    const int64_t v0 = row * cgroups + cg;
+    dz[v0] = relu_mask_acc(dy[v0], y[v0], acc);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s_acc[threadIdx.x * 8 + k] = acc[k];
+  __syncthreads();
+  const int C = cgroups * 8;
+  for (int c = threadIdx.x; c < C; c += kThreads) {
+    const int g = c >> 3, k = c & 7;
+    float s = 0.f;
+    for (int r = 0; r < rows_per_iter; ++r) s += s_acc[(r * cgroups + g) * 8 + k];
+    partial[(size_t)blockIdx.x * C + c] = s;
+  }
+}
+
+__global__ void bias_grad_finish_kernel(const float* __restrict__ partial, float* __restrict__ db, int blocks, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int b = 0; b < blocks; ++b) s += partial[(size_t)b * C + c];
+  db[c] = s;
+}
+
+int backward_blocks(int64_t rows, int C) {
+  const int rows_per_iter = kThreads / (C / 8);
+  const int64_t want = (rows + rows_per_iter - 1) / rows_per_iter;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(want, kMaxBlocks));
+}
+
+}  // namespace
+
+bool bias_relu_supported(int64_t rows, int C) {
+  if (rows <= 0 || C < 8 || C > 2048 || C % 8 != 0) return false;
+  const int cgroups = C / 8;
+  return kThreads % cgroups == 0;  // the backward's thread layout
+}
+
+void bias_relu_inplace_bf16(void* z, const void* bias, int64_t rows, int C, cudaStream_t stream) {
+  BAGUA_CHECK(bias_relu_supported(rows, C) && (uintptr_t)z % 16 == 0, Tensor,
+              "fused bias+ReLU: unsupported shape [" << rows << ", " << C << "] or unaligned activation");
+  const int64_t nvec = rows * (C / 8);
+  const int64_t want = (nvec + (int64_t)kThreads * 4 - 1) / ((int64_t)kThreads * 4);
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, 148 * 8));
+  bias_relu_kernel<<<grid, kThreads, (size_t)C * sizeof(float), stream>>>((uint4*)z, (const __nv_bfloat16*)bias, nvec,
+                                                                         C / 8);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+}
+
+size_t bias_relu_backward_scratch_bytes(int64_t rows, int C) {
+  if (!bias_relu_supported(rows, C)) return 0;
+  return (size_t)backward_blocks(rows, C) * (size_t)C * sizeof(float);
+}
+
+void bias_relu_backward_bf16(const void* dy, const void* y, void* dz, float* db, int64_t rows, int C, void* scratch,
+                             cudaStream_t stream) {
+  BAGUA_CHECK(bias_relu_supported(rows, C) && (uintptr_t)dy % 16 == 0 && (uintptr_t)y % 16 == 0 &&
+                  (uintptr_t)dz % 16 == 0 && scratch != nullptr,
+              Tensor, "fused bias+ReLU backward: unsupported shape [" << rows << ", " << C << "] or unaligned buffers");
+  const int blocks = backward_blocks(rows, C);
+  bias_relu_backward_kernel<<<blocks, kThreads, 0, stream>>>((const uint4*)dy, (const uint4*)y, (uint4*)dz,
+                                                             (float*)scratch, rows, C / 8);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  bias_grad_finish_kernel<<<(C + 127) / 128, 128, 0, stream>>>((const float*)scratch, db, blocks, C);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace model_ops
+}  // namespace bagua

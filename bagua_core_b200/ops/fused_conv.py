@@ -1,0 +1,73 @@
+"""Convolution block with the element-wise tail fused: conv → (bias + ReLU) in one in-place pass,
+and in the backward one pass that applies the ReLU mask and reduces the bias gradient.
+
+The convolution itself stays a library call (cuDNN through `aten.convolution` /
+`aten.convolution_backward`).  What the framework would run around it — a bias add, a clamp, a
+ReLU-mask kernel and a separate column reduction for the bias gradient — is replaced by the two
+sm_100a kernels of `csrc/kernels/model_ops.cu`.  The fused path needs CUDA tensors computed in
+bf16 (bf16 autocast, or bf16 parameters and inputs); anything else takes the plain PyTorch
+composition, so `ConvBiasReLU` is a drop-in for `Conv2d` followed by `ReLU`.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .._native import C as _C
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _ConvBiasReLUFn(torch.autograd.Function):
+    """Inputs arrive as bf16 (cast by autocast where it is on)."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx, x, weight, bias, stride, padding, dilation, groups):
+        ctx.conf = (stride, padding, dilation, groups)
+        x = x.contiguous(memory_format=torch.channels_last)
+        z = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)
+        z = z.contiguous(memory_format=torch.channels_last)
+        _C.k_bias_relu_(z, bias.contiguous(), _stream(z))
+        ctx.save_for_backward(x, weight, z)
+        ctx.bias_dtype = bias.dtype
+        return z
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, dy):
+        stride, padding, dilation, groups = ctx.conf
+        x, weight, y = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dz = torch.empty_like(y)
+        db = torch.empty(weight.shape[0], dtype=torch.float32, device=y.device)
+        _C.k_bias_relu_backward(dy, y, dz, db, _stream(y))
+        dx, dw, _ = torch.ops.aten.convolution_backward(
+            dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
+            [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        return dx, dw, db.to(ctx.bias_dtype), None, None, None, None
+
+
+def _computes_in_bf16(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    if not x.is_cuda:
+        return False
+    if torch.is_autocast_enabled("cuda"):
+        return torch.get_autocast_dtype("cuda") == torch.bfloat16
+    return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+
+
+class ConvBiasReLU(nn.Conv2d):
+    """`nn.Conv2d` (with bias) followed by ReLU, with the same parameters and state dict as the
+    convolution alone."""
+
+    def forward(self, x):
+        fusable = (self.bias is not None and not isinstance(self.padding, str) and self.padding_mode == "zeros"
+                   and x.dim() == 4 and _computes_in_bf16(x, self.weight)
+                   and _C.k_bias_relu_supported(1, self.out_channels))
+        if not fusable:
+            return F.relu(super().forward(x))
+        return _ConvBiasReLUFn.apply(x, self.weight, self.bias, list(self.stride), list(self.padding),
+                                     list(self.dilation), self.groups)

@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch size")
     ap.add_argument("--bucket-mb", type=float, default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--fused-model-ops", action="store_true",
+                    help="VGG-16: conv+bias+ReLU blocks through this package's fused bias/ReLU kernels")
     return ap.parse_args()
 
 
@@ -64,13 +66,13 @@ def reference_arm(args):
     return 0
 
 
-def build_model(name, device):
+def build_model(name, device, fused_ops=False):
     import torch
 
     from bagua_core_b200 import models
 
     if name == "vgg16":
-        m = models.VGG16().to(device).to(memory_format=torch.channels_last)
+        m = models.VGG16(fused_ops=fused_ops).to(device).to(memory_format=torch.channels_last)
     elif name == "resnet50":
         m = models.ResNet50().to(device).to(memory_format=torch.channels_last)
     elif name == "bert_large":
@@ -147,7 +149,7 @@ def main():
         os.environ["BAGUA_B200_FUSED"] = "0"
         bb._C.set_sync_per_bucket(True)
 
-    model = build_model(args.model, device)
+    model = build_model(args.model, device, fused_ops=args.fused_model_ops)
     n_params = sum(p.numel() for p in model.parameters())
     lr = 0.01 if args.model != "bert_large" else 1e-4
     my_kernels = lambda: 0  # noqa: E731
@@ -271,6 +273,7 @@ def main():
                 "parallelism": f"dp{world}", "algorithm": algo_name, "bucket_mb": bucket_mb,
                 "optimizer": "sgd momentum 0.9" if algo_name != "qadam" else "qadam",
                 "precision": "bf16 autocast, fp32 master weights and gradients",
+                "fused_model_ops": bool(args.fused_model_ops),
                 "l2": "working set per step (fp32 weights+grads+momentum and activations) exceeds the 126 MB L2",
             },
             "clocks": clocks.summary(),

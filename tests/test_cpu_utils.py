@@ -46,3 +46,24 @@ def test_clock_sampler_without_nvidia_smi(monkeypatch, tmp_path):
 def test_measured_peaks_have_the_fields_the_benchmarks_use():
     p = load_measured_peaks()
     assert p["hbm_gbs"] > 1000 and p["bf16_tflops"] > 100 and p["source"] in ("measured", "fallback")
+
+
+def test_conv_bias_relu_module_is_a_drop_in_on_cpu():
+    """Off the fused path (CPU, fp32) the module is exactly Conv2d followed by ReLU, with Conv2d's state dict."""
+    import torch
+
+    from bagua_core_b200.models import VGG16
+    from bagua_core_b200.ops.fused_conv import ConvBiasReLU
+
+    torch.manual_seed(0)
+    fused = ConvBiasReLU(3, 8, 3, padding=1)
+    plain = torch.nn.Conv2d(3, 8, 3, padding=1)
+    plain.load_state_dict(fused.state_dict())
+    x = torch.randn(2, 3, 9, 9, requires_grad=True)
+    y = fused(x)
+    assert torch.equal(y, torch.relu(plain(x)))
+    y.sum().backward()
+    assert fused.bias.grad is not None and x.grad is not None
+    a, b = VGG16(num_classes=10, fused_ops=True), VGG16(num_classes=10)
+    assert sum(p.numel() for p in a.parameters()) == sum(p.numel() for p in b.parameters())
+    assert [tuple(p.shape) for p in a.parameters()] == [tuple(p.shape) for p in b.parameters()]

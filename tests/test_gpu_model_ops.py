@@ -1,0 +1,103 @@
+"""Fused bias + ReLU kernels of the convolution blocks (`csrc/kernels/model_ops.cu`,
+`bagua_core_b200/ops/fused_conv.py`) against plain fp32 PyTorch math, and the fused VGG-16
+against the unfused one.
+
+Newer than the rest of the GPU suite and off by default in the benchmark
+(`bench.py --fused-model-ops`); these cases run when BAGUA_B200_TEST_MODEL_OPS=1."""
+import os
+
+import pytest
+import torch
+
+pytestmark = [
+    pytest.mark.gpu,
+    pytest.mark.skipif(os.environ.get("BAGUA_B200_TEST_MODEL_OPS", "0") != "1",
+                       reason="set BAGUA_B200_TEST_MODEL_OPS=1 to run the fused model kernels"),
+]
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@pytest.mark.parametrize("rows,C", [(1, 8), (37, 64), (1000, 128), (4099, 256), (32 * 14 * 14, 512), (3, 2048)])
+def test_bias_relu_forward_and_backward_match_fp32_math(rows, C):
+    import bagua_core_b200 as bb
+
+    g = torch.Generator().manual_seed(rows + C)
+    z = torch.randn(rows, C, generator=g).to(torch.bfloat16).cuda()
+    bias = torch.randn(C, generator=g).to(torch.bfloat16).cuda()
+    ref = torch.relu(z.float() + bias.float())
+    y = z.clone()
+    bb._C.k_bias_relu_(y, bias, _stream())
+    assert torch.allclose(y.float(), ref, rtol=8e-3, atol=8e-3)
+    assert torch.equal(y > 0, ref.to(torch.bfloat16) > 0)
+
+    dy = torch.randn(rows, C, generator=g).to(torch.bfloat16).cuda()
+    dz = torch.empty_like(dy)
+    db = torch.empty(C, device="cuda")
+    bb._C.k_bias_relu_backward(dy, y, dz, db, _stream())
+    dz_ref = torch.where(y > 0, dy, torch.zeros_like(dy))
+    assert torch.equal(dz, dz_ref)
+    db_ref = dz_ref.double().sum(0)
+    assert torch.allclose(db.double(), db_ref, rtol=1e-4, atol=1e-3 * max(1.0, rows ** 0.5))
+    # bit-reproducible
+    db2 = torch.empty_like(db)
+    bb._C.k_bias_relu_backward(dy, y, torch.empty_like(dy), db2, _stream())
+    assert torch.equal(db, db2)
+
+
+def test_channels_last_activation_is_accepted_and_nchw_rejected():
+    import bagua_core_b200 as bb
+
+    z = torch.randn(4, 64, 6, 5).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    bias = torch.randn(64).to(torch.bfloat16).cuda()
+    ref = torch.relu(z.float() + bias.float().view(1, -1, 1, 1))
+    bb._C.k_bias_relu_(z, bias, _stream())
+    assert torch.allclose(z.float(), ref, rtol=8e-3, atol=8e-3)
+    with pytest.raises(RuntimeError, match="channels-last"):
+        bb._C.k_bias_relu_(torch.zeros(4, 64, 6, 5, dtype=torch.bfloat16, device="cuda"), bias, _stream())
+
+
+def test_conv_bias_relu_module_matches_conv_plus_relu_under_autocast():
+    from bagua_core_b200.ops.fused_conv import ConvBiasReLU
+
+    torch.manual_seed(0)
+    fused = ConvBiasReLU(16, 64, 3, padding=1).cuda().to(memory_format=torch.channels_last)
+    plain = torch.nn.Conv2d(16, 64, 3, padding=1).cuda().to(memory_format=torch.channels_last)
+    plain.load_state_dict(fused.state_dict())
+    x = torch.randn(8, 16, 20, 20, device="cuda").contiguous(memory_format=torch.channels_last)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        ya = fused(xa)
+        yb = torch.relu(plain(xb))
+    assert ya.dtype == torch.bfloat16 and torch.allclose(ya.float(), yb.float(), rtol=2e-2, atol=2e-2)
+    go = torch.randn_like(ya)
+    ya.backward(go)
+    yb.backward(go)
+    for a, b in [(xa.grad, xb.grad), (fused.weight.grad, plain.weight.grad), (fused.bias.grad, plain.bias.grad)]:
+        assert a.dtype == b.dtype == torch.float32
+        scale = b.abs().max().item() + 1e-6
+        assert (a - b).abs().max().item() <= 3e-2 * scale
+
+
+def test_fused_vgg16_step_matches_unfused():
+    from bagua_core_b200.models import VGG16
+
+    torch.manual_seed(1)
+    a = VGG16(num_classes=10, dropout=0.0, fused_ops=True).cuda().to(memory_format=torch.channels_last)
+    b = VGG16(num_classes=10, dropout=0.0).cuda().to(memory_format=torch.channels_last)
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        pb.data.copy_(pa.data)
+    x = torch.randn(4, 3, 64, 64, device="cuda").contiguous(memory_format=torch.channels_last)
+    t = torch.randint(0, 10, (4,), device="cuda")
+    losses = []
+    for m in (a, b):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = torch.nn.functional.cross_entropy(m(x).float(), t)
+        loss.backward()
+        losses.append(loss.item())
+    assert abs(losses[0] - losses[1]) <= 2e-2 * max(1.0, abs(losses[1]))
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        scale = pb.grad.abs().max().item() + 1e-6
+        assert (pa.grad - pb.grad).abs().max().item() <= 0.1 * scale
