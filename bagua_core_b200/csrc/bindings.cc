@@ -584,6 +584,43 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       py::arg("grad_output"), py::arg("output"), py::arg("grad_pre_activation"), py::arg("grad_bias"), py::arg("stream"),
       "grad_pre_activation = grad_output * [output > 0]; grad_bias[c] = column sums of it (fp32).");
 
+  // 2x2 / stride-2 max pooling on channels-last bf16 [N, C, H, W] tensors
+  auto nhwc_dims = [](const at::Tensor& t, int64_t* N, int64_t* H, int64_t* W, int* C) {
+    BAGUA_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 4 &&
+                    t.is_contiguous(at::MemoryFormat::ChannelsLast),
+                Tensor, "fused max-pool works on channels-last CUDA bf16 [N, C, H, W] tensors");
+    *N = t.size(0);
+    *C = (int)t.size(1);
+    *H = t.size(2);
+    *W = t.size(3);
+  };
+  m.def("k_maxpool2x2_supported",
+        [](int64_t N, int64_t H, int64_t W, int C) { return model_ops::maxpool2x2_supported(N, H, W, C); });
+  m.def(
+      "k_maxpool2x2_forward",
+      [nhwc_dims](at::Tensor x, at::Tensor y, uint64_t stream) {
+        int64_t N, H, W, N2, H2, W2;
+        int C, C2;
+        nhwc_dims(x, &N, &H, &W, &C);
+        nhwc_dims(y, &N2, &H2, &W2, &C2);
+        BAGUA_CHECK(N2 == N && C2 == C && H2 * 2 == H && W2 * 2 == W, Tensor, "y must be [N, C, H/2, W/2]");
+        model_ops::maxpool2x2_forward_bf16(x.data_ptr(), y.data_ptr(), N, H, W, C, (cudaStream_t)stream);
+      },
+      py::arg("input"), py::arg("output"), py::arg("stream"));
+  m.def(
+      "k_maxpool2x2_backward",
+      [nhwc_dims](at::Tensor x, at::Tensor dy, at::Tensor dx, uint64_t stream) {
+        int64_t N, H, W, N2, H2, W2, N3, H3, W3;
+        int C, C2, C3;
+        nhwc_dims(x, &N, &H, &W, &C);
+        nhwc_dims(dy, &N2, &H2, &W2, &C2);
+        nhwc_dims(dx, &N3, &H3, &W3, &C3);
+        BAGUA_CHECK(N2 == N && C2 == C && H2 * 2 == H && W2 * 2 == W && N3 == N && C3 == C && H3 == H && W3 == W, Tensor,
+                    "dy must be [N, C, H/2, W/2] and dx [N, C, H, W]");
+        model_ops::maxpool2x2_backward_bf16(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), N, H, W, C, (cudaStream_t)stream);
+      },
+      py::arg("input"), py::arg("grad_output"), py::arg("grad_input"), py::arg("stream"));
+
   // ---- single-GPU emulation of the fused kernels (all ranks in one cooperative launch) ----
   py::class_<fused::EmulatedArena>(m, "EmulatedArena")
       .def(py::init<int, int, size_t>(), py::arg("nranks"), py::arg("device"), py::arg("staging_bytes"))

@@ -121,6 +121,87 @@ __global__ void bias_grad_finish_kernel(const float* __restrict__ partial, float
   db[c] = s;
 }
 
+// ---- 2x2 / stride-2 max pooling -------------------------------------------------------
+// One thread per output vector (8 channels of one output pixel); vector indices are
+// [n][h][w][cg] with cg fastest, so a warp reads whole pixels of contiguous channels.
+struct PoolIndex {
+  int64_t x00;  // vector index of the window's top-left input pixel
+  int64_t dw, dh;  // vector strides to the right / lower neighbour
+};
+__device__ __forceinline__ PoolIndex pool_index(int64_t v, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
+  const int64_t cg = v % cgroups, p = v / cgroups;
+  const int64_t wo = p % Wo, q = p / Wo;
+  const int64_t ho = q % Ho, n = q / Ho;
+  PoolIndex r;
+  r.dw = cgroups;
+  r.dh = W * cgroups;
+  r.x00 = ((n * (2 * Ho) + 2 * ho) * W + 2 * wo) * cgroups + cg;
+  return r;
+}
+
+__global__ void __launch_bounds__(kThreads)
+    maxpool2x2_forward_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t nvec_out, int64_t Ho,
+                              int64_t Wo, int64_t W, int cgroups) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
+    const PoolIndex p = pool_index(v, Ho, Wo, W, cgroups);
+    const uint4 a = x[p.x00], b = x[p.x00 + p.dw], c = x[p.x00 + p.dh], d = x[p.x00 + p.dh + p.dw];
+    float fa[8], fb[8], fc[8], fd[8];
+    unpack8(a, fa);
+    unpack8(b, fb);
+    unpack8(c, fc);
+    unpack8(d, fd);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) fa[k] = fmaxf(fmaxf(fa[k], fb[k]), fmaxf(fc[k], fd[k]));
+    y[v] = pack8(fa);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+    maxpool2x2_backward_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ dx,
+                               int64_t nvec_out, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
+    const PoolIndex p = pool_index(v, Ho, Wo, W, cgroups);
+    const uint4 a = x[p.x00], b = x[p.x00 + p.dw], c = x[p.x00 + p.dh], d = x[p.x00 + p.dh + p.dw];
+    const uint4 g4 = dy[v];
+    float fa[8], fb[8], fc[8], fd[8], g[8];
+    unpack8(a, fa);
+    unpack8(b, fb);
+    unpack8(c, fc);
+    unpack8(d, fd);
+    unpack8(g4, g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      // first maximum in scan order (0,0) (0,1) (1,0) (1,1): a later element wins only if strictly larger
+      float m = fa[k];
+      int idx = 0;
+      if (fb[k] > m) {
+        m = fb[k];
+        idx = 1;
+      }
+      if (fc[k] > m) {
+        m = fc[k];
+        idx = 2;
+      }
+      if (fd[k] > m) idx = 3;
+      fa[k] = idx == 0 ? g[k] : 0.f;
+      fb[k] = idx == 1 ? g[k] : 0.f;
+      fc[k] = idx == 2 ? g[k] : 0.f;
+      fd[k] = idx == 3 ? g[k] : 0.f;
+    }
+    dx[p.x00] = pack8(fa);
+    dx[p.x00 + p.dw] = pack8(fb);
+    dx[p.x00 + p.dh] = pack8(fc);
+    dx[p.x00 + p.dh + p.dw] = pack8(fd);
+  }
+}
+
+int pool_grid(int64_t nvec_out) {
+  const int64_t want = (nvec_out + kThreads - 1) / kThreads;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(want, 148 * 8));
+}
+
 int backward_blocks(int64_t rows, int C) {
   const int rows_per_iter = kThreads / (C / 8);
   const int64_t want = (rows + rows_per_iter - 1) / rows_per_iter;
@@ -161,6 +242,32 @@ void bias_relu_backward_bf16(const void* dy, const void* y, void* dz, float* db,
                                                              (float*)scratch, rows, C / 8);
   BAGUA_CUDA_CHECK(cudaGetLastError());
   bias_grad_finish_kernel<<<(C + 127) / 128, 128, 0, stream>>>((const float*)scratch, db, blocks, C);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+}
+
+bool maxpool2x2_supported(int64_t N, int64_t H, int64_t W, int C) {
+  return N > 0 && H >= 2 && W >= 2 && H % 2 == 0 && W % 2 == 0 && C >= 8 && C % 8 == 0;
+}
+
+void maxpool2x2_forward_bf16(const void* x, void* y, int64_t N, int64_t H, int64_t W, int C, cudaStream_t stream) {
+  BAGUA_CHECK(maxpool2x2_supported(N, H, W, C) && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0, Tensor,
+              "fused max-pool: unsupported shape [" << N << ", " << H << ", " << W << ", " << C << "] or unaligned buffers");
+  const int64_t nvec_out = N * (H / 2) * (W / 2) * (C / 8);
+  maxpool2x2_forward_kernel<<<pool_grid(nvec_out), kThreads, 0, stream>>>((const uint4*)x, (uint4*)y, nvec_out, H / 2,
+                                                                          W / 2, W, C / 8);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+}
+
+void maxpool2x2_backward_bf16(const void* x, const void* dy, void* dx, int64_t N, int64_t H, int64_t W, int C,
+                              cudaStream_t stream) {
+  BAGUA_CHECK(maxpool2x2_supported(N, H, W, C) && (uintptr_t)x % 16 == 0 && (uintptr_t)dy % 16 == 0 &&
+                  (uintptr_t)dx % 16 == 0,
+              Tensor,
+              "fused max-pool backward: unsupported shape [" << N << ", " << H << ", " << W << ", " << C
+                                                             << "] or unaligned buffers");
+  const int64_t nvec_out = N * (H / 2) * (W / 2) * (C / 8);
+  maxpool2x2_backward_kernel<<<pool_grid(nvec_out), kThreads, 0, stream>>>((const uint4*)x, (const uint4*)dy, (uint4*)dx,
+                                                                           nvec_out, H / 2, W / 2, W, C / 8);
   BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 

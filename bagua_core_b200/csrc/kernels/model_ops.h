@@ -8,6 +8,7 @@
 //   forward   y = max(z + bias, 0), in place on the convolution's output;
 //   backward  dz = dy · [y > 0] and db[c] = Σ_rows dz[row, c] (fp32 accumulation, fixed
 //             summation order, no atomics), from one read of dy and y.
+// The pooling layers between the blocks get the same treatment (see below).
 // No counterpart in the reference, which has no model code.
 #pragma once
 
@@ -31,6 +32,16 @@ size_t bias_relu_backward_scratch_bytes(int64_t rows, int C);
 // dy, y, dz: [rows, C] bf16 (dz may alias dy); db: [C] fp32; scratch as sized above.
 void bias_relu_backward_bf16(const void* dy, const void* y, void* dz, float* db, int64_t rows, int C, void* scratch,
                              cudaStream_t stream);
+
+// ---- 2x2 / stride-2 max pooling on channels-last bf16 activations ---------------------
+// x: [N, H, W, C] (H, W even, C a multiple of 8), y: [N, H/2, W/2, C].  The forward stores no
+// index tensor; the backward recomputes each window's arg-max from x (first maximum in
+// (h, w) scan order, like the framework's kernel) and writes every element of dx exactly
+// once, so dx needs no zero-fill and no atomics.
+bool maxpool2x2_supported(int64_t N, int64_t H, int64_t W, int C);
+void maxpool2x2_forward_bf16(const void* x, void* y, int64_t N, int64_t H, int64_t W, int C, cudaStream_t stream);
+void maxpool2x2_backward_bf16(const void* x, const void* dy, void* dx, int64_t N, int64_t H, int64_t W, int C,
+                              cudaStream_t stream);
 
 }  // namespace model_ops
 }  // namespace bagua

@@ -51,6 +51,37 @@ class _ConvBiasReLUFn(torch.autograd.Function):
         return dx, dw, db.to(ctx.bias_dtype), None, None, None, None
 
 
+class _MaxPool2x2Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        n, c, h, w = x.shape
+        y = torch.empty((n, c, h // 2, w // 2), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        _C.k_maxpool2x2_forward(x, y, _stream(x))
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = torch.empty_like(x, memory_format=torch.channels_last)
+        _C.k_maxpool2x2_backward(x, dy, dx, _stream(x))
+        return dx
+
+
+class MaxPool2x2(nn.Module):
+    """`nn.MaxPool2d(2, 2)`.  Channels-last CUDA bf16 inputs with even height and width go through
+    this package's kernels: no index tensor in the forward, and a backward that recomputes the
+    arg-max and writes the whole input gradient in one pass (no zero-fill)."""
+
+    def forward(self, x):
+        if (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4
+                and x.is_contiguous(memory_format=torch.channels_last)
+                and _C.k_maxpool2x2_supported(x.shape[0], x.shape[2], x.shape[3], x.shape[1])):
+            return _MaxPool2x2Fn.apply(x)
+        return F.max_pool2d(x, 2, 2)
+
+
 def _computes_in_bf16(x: torch.Tensor, weight: torch.Tensor) -> bool:
     if not x.is_cuda:
         return False

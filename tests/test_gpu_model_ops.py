@@ -59,6 +59,33 @@ def test_channels_last_activation_is_accepted_and_nchw_rejected():
         bb._C.k_bias_relu_(torch.zeros(4, 64, 6, 5, dtype=torch.bfloat16, device="cuda"), bias, _stream())
 
 
+@pytest.mark.parametrize("shape", [(1, 8, 2, 2), (2, 64, 6, 10), (3, 128, 56, 56), (32, 512, 14, 14)])
+def test_maxpool2x2_matches_torch_bit_for_bit(shape):
+    from bagua_core_b200.ops.fused_conv import MaxPool2x2
+
+    g = torch.Generator().manual_seed(sum(shape))
+    # values on a coarse grid so that windows contain ties; half of them clamped to zero like a ReLU output
+    x = torch.relu((torch.randn(*shape, generator=g) * 4).round() / 4).to(torch.bfloat16).cuda()
+    x = x.contiguous(memory_format=torch.channels_last)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya = MaxPool2x2()(xa)
+    yb = torch.nn.functional.max_pool2d(xb, 2, 2)
+    assert ya.is_contiguous(memory_format=torch.channels_last)
+    assert torch.equal(ya, yb)
+    go = torch.randn(ya.shape, generator=g).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    ya.backward(go)
+    yb.backward(go)
+    assert torch.equal(xa.grad, xb.grad)
+
+
+def test_maxpool2x2_falls_back_for_odd_sizes_and_fp32():
+    from bagua_core_b200.ops.fused_conv import MaxPool2x2
+
+    for x in (torch.randn(2, 8, 5, 7, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last),
+              torch.randn(2, 8, 4, 4, device="cuda")):
+        assert torch.equal(MaxPool2x2()(x), torch.nn.functional.max_pool2d(x, 2, 2))
+
+
 def test_conv_bias_relu_module_matches_conv_plus_relu_under_autocast():
     from bagua_core_b200.ops.fused_conv import ConvBiasReLU
 
