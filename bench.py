@@ -184,7 +184,9 @@ def main():
 
         def my_kernels():
             s = bb._C.stats()
-            return int(s["fused_launches"]) + int(getattr(opt, "kernel_launches", 0))
+            from bagua_core_b200.ops import fused_conv
+
+            return int(s["fused_launches"]) + int(getattr(opt, "kernel_launches", 0)) + fused_conv.launches
 
     def step(x, y):
         zero()
