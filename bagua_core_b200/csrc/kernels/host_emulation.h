@@ -19,7 +19,10 @@
 #include <barrier>
 #include <cstdint>
 #include <cstring>
+#include <map>
 #include <memory>
+#include <mutex>
+#include <vector>
 
 namespace bagua {
 namespace hostemu {
@@ -31,6 +34,16 @@ struct BlockContext {
   std::barrier<> bar;
   int vote = 1;               // accumulator of __syncthreads_and
   alignas(16) char shared[256] = {};  // storage of BAGUA_SHARED variables, by slot
+  float lanes[32] = {};       // exchange buffer of the warp shuffles (a block is one warp)
+  std::mutex arrays_mu;
+  std::map<int, std::vector<uint64_t>> arrays;  // storage of BAGUA_SHARED_ARRAY variables, by slot
+
+  void* array(int slot, size_t bytes) {
+    std::lock_guard<std::mutex> g(arrays_mu);
+    auto& a = arrays[slot];
+    if (a.size() * 8 < bytes) a.resize((bytes + 7) / 8);
+    return a.data();
+  }
 };
 
 struct Dim {
@@ -41,12 +54,14 @@ inline thread_local BlockContext* t_block = nullptr;
 inline thread_local Dim t_thread_idx;
 inline thread_local Dim t_block_idx;
 inline thread_local Dim t_grid_dim;
+inline thread_local Dim t_block_dim;
 
 inline void bind_thread(BlockContext* b, unsigned tid, unsigned block, unsigned grid) {
   t_block = b;
   t_thread_idx.x = tid;
   t_block_idx.x = block;
   t_grid_dim.x = grid;
+  t_block_dim.x = (unsigned)b->nthreads;
 }
 
 inline void syncthreads() { t_block->bar.arrive_and_wait(); }
@@ -67,12 +82,31 @@ inline T& shared_slot(int slot) {
   return *reinterpret_cast<T*>(t_block->shared + 16 * slot);
 }
 
+template <typename T>
+inline T* shared_array(int slot, size_t count) {
+  return static_cast<T*>(t_block->array(slot, count * sizeof(T)));
+}
+
+// __shfl_xor_sync for a block that is exactly one warp and in which every thread takes part:
+// everyone publishes its value, reads its partner's, and waits until all have read.
+inline float shfl_xor(float v, int lane_mask) {
+  BlockContext* b = t_block;
+  const unsigned me = t_thread_idx.x;
+  b->lanes[me] = v;
+  b->bar.arrive_and_wait();
+  const float r = b->lanes[(me ^ (unsigned)lane_mask) % (unsigned)b->nthreads];
+  b->bar.arrive_and_wait();
+  return r;
+}
+
 }  // namespace hostemu
 }  // namespace bagua
 
 #define threadIdx (::bagua::hostemu::t_thread_idx)
 #define blockIdx (::bagua::hostemu::t_block_idx)
 #define gridDim (::bagua::hostemu::t_grid_dim)
+#define blockDim (::bagua::hostemu::t_block_dim)
+#define __shfl_xor_sync(mask, v, lane_mask) ::bagua::hostemu::shfl_xor((v), (lane_mask))
 #define __syncthreads() ::bagua::hostemu::syncthreads()
 #define __syncthreads_and(p) ::bagua::hostemu::syncthreads_and((p) ? 1 : 0)
 // ThreadSanitizer does not model stand-alone fences.  The protocol never relies on one for
@@ -105,11 +139,58 @@ inline unsigned __float_as_uint(float f) {
   return u;
 }
 
+// Chunk headers are written by every block of a rank with the same value, and a peer may read
+// one while a later block of the writer stores it again.  On the device these are plain word
+// accesses (one aligned word, same bits every time); here they are relaxed atomics, so that
+// ThreadSanitizer accepts exactly this pattern and nothing else.
+namespace bagua {
+template <typename T>
+inline void same_value_store(T* p, T v) {
+  static_assert(sizeof(T) == 2 || sizeof(T) == 4, "header words are 2 or 4 bytes");
+  if constexpr (sizeof(T) == 4) {
+    uint32_t bits;
+    std::memcpy(&bits, &v, 4);
+    __atomic_store_n(reinterpret_cast<uint32_t*>(p), bits, __ATOMIC_RELAXED);
+  } else {
+    uint16_t bits;
+    std::memcpy(&bits, &v, 2);
+    __atomic_store_n(reinterpret_cast<uint16_t*>(p), bits, __ATOMIC_RELAXED);
+  }
+}
+template <typename T>
+inline T same_value_load(const T* p) {
+  T v;
+  if constexpr (sizeof(T) == 4) {
+    const uint32_t bits = __atomic_load_n(reinterpret_cast<const uint32_t*>(p), __ATOMIC_RELAXED);
+    std::memcpy(&v, &bits, 4);
+  } else {
+    const uint16_t bits = __atomic_load_n(reinterpret_cast<const uint16_t*>(p), __ATOMIC_RELAXED);
+    std::memcpy(&v, &bits, 2);
+  }
+  return v;
+}
+}  // namespace bagua
+
 // `__shared__ T name;` of the device build: slot-indexed storage in the block's context.
 #define BAGUA_SHARED(T, name, slot) T& name = ::bagua::hostemu::shared_slot<T>(slot)
+// `__shared__ T name[count];`
+#define BAGUA_SHARED_ARRAY(T, name, count, slot) T* name = ::bagua::hostemu::shared_array<T>((slot), (count))
 
 #else  // device build
 
 #define BAGUA_SHARED(T, name, slot) __shared__ T name
+#define BAGUA_SHARED_ARRAY(T, name, count, slot) __shared__ T name[count]
+
+namespace bagua {
+// Plain accesses on the device; see the host branch above for why they have a name.
+template <typename T>
+__device__ __forceinline__ void same_value_store(T* p, T v) {
+  *p = v;
+}
+template <typename T>
+__device__ __forceinline__ T same_value_load(const T* p) {
+  return *p;
+}
+}  // namespace bagua
 
 #endif

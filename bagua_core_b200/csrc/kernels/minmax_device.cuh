@@ -8,6 +8,8 @@
 
 #include <cstdint>
 
+#include "host_emulation.h"
+
 namespace bagua {
 namespace kernels {
 namespace mmdev {
@@ -55,8 +57,8 @@ template <typename T>
 __device__ __forceinline__ void store_header(uint8_t* base, float mn, float mx) {
   T h[2] = {from_f<T>(mn), from_f<T>(mx)};
   if ((reinterpret_cast<uintptr_t>(base) % sizeof(T)) == 0) {
-    reinterpret_cast<T*>(base)[0] = h[0];
-    reinterpret_cast<T*>(base)[1] = h[1];
+    same_value_store(reinterpret_cast<T*>(base), h[0]);
+    same_value_store(reinterpret_cast<T*>(base) + 1, h[1]);
   } else {
     const uint8_t* src = reinterpret_cast<const uint8_t*>(h);
 #pragma unroll
@@ -67,8 +69,8 @@ template <typename T>
 __device__ __forceinline__ void load_header(const uint8_t* base, float& mn, float& mx) {
   T h[2];
   if ((reinterpret_cast<uintptr_t>(base) % sizeof(T)) == 0) {
-    h[0] = reinterpret_cast<const T*>(base)[0];
-    h[1] = reinterpret_cast<const T*>(base)[1];
+    h[0] = same_value_load(reinterpret_cast<const T*>(base));
+    h[1] = same_value_load(reinterpret_cast<const T*>(base) + 1);
   } else {
     uint8_t* dst = reinterpret_cast<uint8_t*>(h);
 #pragma unroll
@@ -270,8 +272,9 @@ __device__ __forceinline__ void lut_dq16(const uint8_t* q, float (&v)[16], const
 // Block-wide min/max; the result is valid in every thread.
 template <int kThreads>
 __device__ __forceinline__ void block_minmax(float& mn, float& mx) {
-  __shared__ float s_mn[kThreads / 32], s_mx[kThreads / 32];
-  __shared__ float s_out[2];
+  BAGUA_SHARED_ARRAY(float, s_mn, kThreads / 32, 2);
+  BAGUA_SHARED_ARRAY(float, s_mx, kThreads / 32, 3);
+  BAGUA_SHARED_ARRAY(float, s_out, 2, 4);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));

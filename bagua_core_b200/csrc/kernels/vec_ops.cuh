@@ -14,7 +14,7 @@ namespace bagua {
 namespace fused {
 
 #ifdef BAGUA_HOST_EMULATION
-constexpr int kThreads = 8;  // OS threads per emulated block; thread t talks to rank t, so at least kArenaMaxRanks
+constexpr int kThreads = 32;  // OS threads per emulated block: one warp (thread t talks to rank t, so at least kArenaMaxRanks)
 #else
 constexpr int kThreads = 512;
 #endif

@@ -21,8 +21,12 @@
 #include <thread>
 #include <vector>
 
+#include <cmath>
+
 #include "kernels/fused_allreduce_bodies.cuh"
+#include "kernels/fused_bytegrad_body.cuh"
 #include "kernels/fused_collectives_bodies.cuh"
+#include "kernels/fused_gossip_body.cuh"
 
 using namespace bagua;
 using namespace bagua::fused;
@@ -55,6 +59,8 @@ enum class Kind {
   AllReduceSym,
   PairAverage,
   PairAverageSym,
+  ByteGrad,
+  LpRing,
   kCount
 };
 
@@ -72,7 +78,7 @@ struct alignas(16) Vec {
 };
 
 struct Rank {
-  std::vector<Vec> staging, in, out;
+  std::vector<Vec> staging, in, out, w, l, r;  // w / l / r: the replicas of the low-precision ring
   std::vector<uint32_t> signals;
   std::unique_ptr<std::barrier<>> bar;  // the rank's stream: all of its threads between ops
   uint64_t errors = 0;
@@ -86,7 +92,45 @@ struct World {
   std::vector<std::unique_ptr<hostemu::BlockContext>> blocks;  // [rank * G + block]
   int absent = -1;
   uint64_t deadline_ns = 60ull * 1000000000ull;
+  std::vector<uint64_t> grid_bar_base;  // per op: grid barriers every rank has executed before it, times G
 };
+
+// ---- scalar restatement of MinMaxUInt8, independent of the device helpers ----------------
+struct Quantiser {
+  float scale, lower, upper;
+  Quantiser(float mn, float mx) {
+    const float denom = (mx - mn) + 1e-7f;
+    scale = (float)(255.0 / (double)denom);
+    upper = std::rint(mx * scale);
+    lower = upper - 255.0f;
+  }
+  float roundtrip(float x) const {
+    float level = std::fmin(std::rint(x * scale), upper);
+    const float q = (float)(uint8_t)std::fmin(std::fmax(level - lower, 0.f), 255.f);
+    return (q + lower) / scale;
+  }
+};
+Quantiser quantiser_of(const std::vector<float>& v) {
+  float mn = v[0], mx = v[0];
+  for (float x : v) {
+    mn = std::fmin(mn, x);
+    mx = std::fmax(mx, x);
+  }
+  return Quantiser(mn, mx);
+}
+
+// Inputs of the low-precision ring for op k on `rank`: x, w, l, r.
+float ring_input(uint32_t k, int rank, int which, int64_t i) { return value(k + 17u * (uint32_t)which, rank, i) * 0.125f; }
+std::vector<float> ring_difference(uint32_t k, int rank, int64_t n) {
+  std::vector<float> d((size_t)n);
+  const float third = 1.0f / 3.0f, m53 = -5.0f / 3.0f;
+  for (int64_t i = 0; i < n; ++i) {
+    float t = std::fmaf(ring_input(k, rank, 2, i), third, ring_input(k, rank, 0, i));
+    t = std::fmaf(ring_input(k, rank, 3, i), third, t);
+    d[(size_t)i] = std::fmaf(ring_input(k, rank, 1, i), m53, t);
+  }
+  return d;
+}
 
 ArenaView view_of(World& w, int rank, uint32_t epoch) {
   ArenaView v;
@@ -101,6 +145,7 @@ ArenaView view_of(World& w, int rank, uint32_t epoch) {
   v.nranks = w.N;
   v.epoch = epoch;
   v.deadline_ns = w.deadline_ns;
+  v.grid_bar_base = w.grid_bar_base[epoch - 1];
   return v;
 }
 
@@ -144,6 +189,16 @@ void prepare(World& w, int me, uint32_t k) {
     case Kind::PairAverage:
     case Kind::PairAverageSym: fill(r.in, k, me, op.vecs); break;
     case Kind::AllReduceTwoShotInPlace: fill(r.out, k, me, op.vecs); break;
+    case Kind::ByteGrad: fill(r.in, k, me, op.vecs * N); break;
+    case Kind::LpRing:
+      for (int64_t i = 0; i < op.vecs; ++i)
+        for (int l = 0; l < 4; ++l) {
+          r.in[(size_t)i].f[l] = ring_input(k, me, 0, 4 * i + l);
+          r.w[(size_t)i].f[l] = ring_input(k, me, 1, 4 * i + l);
+          r.l[(size_t)i].f[l] = ring_input(k, me, 2, 4 * i + l);
+          r.r[(size_t)i].f[l] = ring_input(k, me, 3, 4 * i + l);
+        }
+      break;
     default: break;
   }
 }
@@ -202,6 +257,24 @@ void run_body(World& w, int me, int b, uint32_t k) {
     }
     case Kind::PairAverage: pair_average_body<float>(v, L, in, out, c, me ^ 1); break;
     case Kind::PairAverageSym: pair_average_sym_body<float>(v, L, in, ins.p[me ^ 1], out, c, me ^ 1); break;
+    case Kind::ByteGrad: {
+      // bucket of N chunks of 4c floats, quantised to one byte each; slots hold a 32-byte header + payload
+      const int64_t chunk = 4 * c;
+      const size_t slot = (size_t)chunk + 32;
+      const size_t scratch_off = ((2 * (size_t)w.N * slot + 255) / 256) * 256;
+      bytegrad_bodies::bytegrad_body<float>(v, L, reinterpret_cast<float*>(r.in.data()), chunk, slot, scratch_off,
+                                            op.scale);
+      break;
+    }
+    case Kind::LpRing: {
+      const int64_t n = 4 * c;
+      const size_t slot = (size_t)n + 32;
+      const size_t scratch_off = ((3 * slot + 255) / 256) * 256;
+      gossip_bodies::lp_ring_body<float>(v, L, reinterpret_cast<float*>(r.in.data()), reinterpret_cast<float*>(r.w.data()),
+                                         reinterpret_cast<float*>(r.l.data()), reinterpret_cast<float*>(r.r.data()), n,
+                                         slot, scratch_off);
+      break;
+    }
     default: break;
   }
 }
@@ -310,6 +383,44 @@ uint64_t verify(World& w, int me, uint32_t k) {
         expect(r.out, i, e[0], e[1], e[2], e[3]);
       }
       break;
+    case Kind::ByteGrad: {
+      // every rank's chunk ch is quantised with its own grid, the owner sums the N dequantised
+      // contributions in rank order, scales, quantises the result once more; all ranks end up with that
+      const int64_t chunk = 4 * c;
+      const float* got = reinterpret_cast<const float*>(r.in.data());
+      for (int ch = 0; ch < N; ++ch) {
+        std::vector<float> reduced((size_t)chunk, 0.f);
+        for (int q = 0; q < N; ++q) {
+          std::vector<float> contrib((size_t)chunk);
+          for (int64_t i = 0; i < chunk; ++i) contrib[(size_t)i] = value(k, q, ch * chunk + i);
+          const Quantiser g = quantiser_of(contrib);
+          for (int64_t i = 0; i < chunk; ++i) reduced[(size_t)i] += g.roundtrip(contrib[(size_t)i]);
+        }
+        for (auto& x : reduced) x *= op.scale;
+        const Quantiser g2 = quantiser_of(reduced);
+        for (int64_t i = 0; i < chunk; ++i)
+          if (got[ch * chunk + i] != g2.roundtrip(reduced[(size_t)i])) ++bad;
+      }
+      break;
+    }
+    case Kind::LpRing: {
+      const int64_t n = 4 * c;
+      const int left = (me + N - 1) % N, right = (me + 1) % N;
+      const std::vector<float> d_me = ring_difference(k, me, n), d_l = ring_difference(k, left, n),
+                               d_r = ring_difference(k, right, n);
+      const Quantiser g_me = quantiser_of(d_me), g_l = quantiser_of(d_l), g_r = quantiser_of(d_r);
+      const float* x = reinterpret_cast<const float*>(r.in.data());
+      const float* wv = reinterpret_cast<const float*>(r.w.data());
+      const float* lv = reinterpret_cast<const float*>(r.l.data());
+      const float* rv = reinterpret_cast<const float*>(r.r.data());
+      for (int64_t i = 0; i < n; ++i) {
+        const float nw = g_me.roundtrip(d_me[(size_t)i]) + ring_input(k, me, 1, i);
+        if (x[i] != nw || wv[i] != nw) ++bad;
+        if (lv[i] != ring_input(k, me, 2, i) + g_l.roundtrip(d_l[(size_t)i])) ++bad;
+        if (rv[i] != ring_input(k, me, 3, i) + g_r.roundtrip(d_r[(size_t)i])) ++bad;
+      }
+      break;
+    }
     default: break;
   }
   return bad;
@@ -350,17 +461,26 @@ int main(int argc, char** argv) {
     op.kind = (Kind)(rng() % (uint32_t)Kind::kCount);
     if ((op.kind == Kind::PairAverage || op.kind == Kind::PairAverageSym) && w.N % 2) op.kind = Kind::Barrier;  // pairs need an even world
     op.vecs = 1 + (int64_t)(rng() % 40);
+    if (op.kind == Kind::ByteGrad || op.kind == Kind::LpRing) op.vecs = 4 * (1 + (int64_t)(rng() % 10));  // 16-element groups
     op.root = (int)(rng() % (uint32_t)w.N);
     op.scale = (rng() & 1) ? 1.0f : 0.5f;
     max_vecs = std::max(max_vecs, op.vecs);
+    w.grid_bar_base.push_back(w.grid_bar_base.empty() ? 0 : w.grid_bar_base.back());
+    if (!w.ops.empty()) {
+      const Kind prev = w.ops.back().kind;
+      w.grid_bar_base.back() += (uint64_t)w.G * (prev == Kind::ByteGrad ? 2u : prev == Kind::LpRing ? 1u : 0u);
+    }
     w.ops.push_back(op);
   }
   const size_t buf_vecs = (size_t)max_vecs * (size_t)w.N;
   w.ranks.resize((size_t)w.N);
   for (auto& r : w.ranks) {
-    r.staging.assign(buf_vecs * 2 + 8, Vec{});  // N slots + the mirror area of the two-phase reduce
+    r.staging.assign(buf_vecs * 2 + 64 + (size_t)(w.N + 1) * (size_t)w.G, Vec{});  // slots, mirror areas, min/max scratch
     r.in.assign(buf_vecs, Vec{});
     r.out.assign(buf_vecs, Vec{});
+    r.w.assign(buf_vecs, Vec{});
+    r.l.assign(buf_vecs, Vec{});
+    r.r.assign(buf_vecs, Vec{});
     r.signals.assign((size_t)kSigWords, 0u);
     r.bar = std::make_unique<std::barrier<>>(w.G * kThreads);
   }
