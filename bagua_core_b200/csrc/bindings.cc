@@ -234,7 +234,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              void* peers[kArenaMaxRanks];
              return a && t.is_cuda() && a->sym_translate(t.data_ptr(), t.nbytes(), peers);
            })
-      .def("is_multicast",
+      .def("is_nvls_mapped",
            [](PyComm& c, const at::Tensor& t) {
              PeerArena* a = c.inner->arena();
              return a && t.is_cuda() && a->sym_multicast(t.data_ptr(), t.nbytes()) != nullptr;

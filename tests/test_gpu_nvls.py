@@ -33,13 +33,13 @@ def _nvls_allreduce(rank, world):
     comm.set_device_wait_ms(20000.0)
     probe = comm.alloc_symmetric(1 << 20, torch.float32)
     assert probe is not None
-    if not comm.is_multicast(probe):
+    if not comm.is_nvls_mapped(probe):
         return "no multicast"  # the platform refused; the heap fell back to CUDA IPC on every rank
     checked = 0
     for dt, tol in ((torch.float32, 1e-5), (torch.float16, 2e-3), (torch.bfloat16, 1.6e-2)):
         for n in ((1 << 18) + 64, 6 << 20):
             buf = comm.alloc_symmetric(n, dt)
-            assert comm.is_multicast(buf)
+            assert comm.is_nvls_mapped(buf)
             x = torch.randn(n, generator=torch.Generator().manual_seed(31 * rank + n % 53)).to(dt).to(dev)
             allx = [torch.empty_like(x) for _ in range(world)]
             torch.distributed.all_gather(allx, x)
