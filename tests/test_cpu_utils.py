@@ -67,3 +67,25 @@ def test_conv_bias_relu_module_is_a_drop_in_on_cpu():
     a, b = VGG16(num_classes=10, fused_ops=True), VGG16(num_classes=10)
     assert sum(p.numel() for p in a.parameters()) == sum(p.numel() for p in b.parameters())
     assert [tuple(p.shape) for p in a.parameters()] == [tuple(p.shape) for p in b.parameters()]
+
+
+def test_prefetcher_and_lagged_reader_on_cpu():
+    """On a CPU device the pipelining helpers are plain pass-throughs with the same call pattern."""
+    import torch
+
+    from bagua_core_b200.utils.prefetch import DevicePrefetcher, LaggedScalarReader
+
+    pf, reader = DevicePrefetcher(torch.device("cpu")), LaggedScalarReader(torch.device("cpu"))
+    seen = []
+    pf.put(torch.tensor([1.0]), torch.tensor([2]))
+    for i in range(3):
+        x, y = pf.get()
+        pf.put(torch.tensor([float(i + 2)]), torch.tensor([i]))
+        seen.append(reader.push(x.sum()))
+    assert seen == [None, 1.0, 2.0]
+    assert reader.flush() == 3.0 and reader.flush() is None
+    import pytest
+
+    pf.get()
+    with pytest.raises(RuntimeError):
+        pf.get()
