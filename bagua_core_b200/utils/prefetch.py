@@ -88,7 +88,7 @@ class LaggedScalarReader:
     def push(self, scalar: torch.Tensor) -> Optional[float]:
         previous = self._take()
         if not self._cuda:
-            self._cpu_value = float(scalar)
+            self._cpu_value = float(scalar.detach())
             return previous
         k = self._i
         self._i ^= 1

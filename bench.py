@@ -45,6 +45,9 @@ def parse():
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch size")
     ap.add_argument("--bucket-mb", type=float, default=None)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu: dry run of the whole benchmark logic on host tensors (gloo, wall-clock timing); "
+                         "its numbers are not benchmark results")
     ap.add_argument("--fused-model-ops", action="store_true",
                     help="VGG-16: conv+bias+ReLU blocks through this package's fused bias/ReLU kernels")
     return ap.parse_args()
@@ -97,6 +100,8 @@ def make_batch(name, batch, seq, device, pinned=False):
         x = torch.randn(batch, 1024, generator=g)
         y = torch.randint(0, 1000, (batch,), generator=g)
     if pinned:
+        if device.type != "cuda":
+            return x, y
         return x.pin_memory(), y.pin_memory()
     x = x.to(device)
     if x.dim() == 4:
@@ -108,7 +113,10 @@ def loss_fn(name, model, x, y):
     import torch
     import torch.nn.functional as F
 
-    with torch.autocast("cuda", dtype=torch.bfloat16):
+    import contextlib
+
+    ctx = torch.autocast("cuda", dtype=torch.bfloat16) if x.is_cuda else contextlib.nullcontext()
+    with ctx:
         if name == "bert_large":
             return model(x, y[:, 0], y[:, 1])
         out = model(x)
@@ -138,12 +146,47 @@ def main():
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    torch.backends.cudnn.benchmark = True
-    torch.backends.cuda.matmul.allow_tf32 = True
-    torch.backends.cudnn.allow_tf32 = True
+    on_gpu = args.device == "cuda"
+    if on_gpu:
+        device = torch.device("cuda", local_rank)
+        torch.cuda.set_device(device)
+        torch.backends.cudnn.benchmark = True
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.backends.cudnn.allow_tf32 = True
+    else:
+        device = torch.device("cpu")
+        if args.impl != "ours":
+            raise SystemExit("--device cpu runs the default arm only")
     torch.manual_seed(0)
+
+    class _Mark:
+        """A point on the device's time line: a CUDA event, or the wall clock in a CPU dry run."""
+
+        def __init__(self):
+            self.ev = torch.cuda.Event(enable_timing=True) if on_gpu else None
+            self.t = 0.0
+
+        def record(self):
+            if on_gpu:
+                self.ev.record()
+            else:
+                self.t = time.perf_counter()
+
+        def elapsed_time(self, other):
+            return self.ev.elapsed_time(other.ev) if on_gpu else (other.t - self.t) * 1e3
+
+    class _NoClocks:
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *a):
+            return False
+
+        def mark(self):
+            pass
+
+        def summary(self):
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
 
     if args.impl == "baseline_nccl":
         os.environ["BAGUA_B200_FUSED"] = "0"
@@ -198,7 +241,8 @@ def main():
     def barrier():
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+        if on_gpu:
+            torch.cuda.synchronize()
 
     # ---- device-timed loop, inputs resident on the device -----------------------------
     x, y = make_batch(args.model, batch, seq, device)
@@ -206,8 +250,8 @@ def main():
         step(x, y)
     barrier()
     k0 = my_kernels()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
+    e0, e1 = _Mark(), _Mark()
+    with (ClockSampler(local_rank) if on_gpu else _NoClocks()) as clocks:
         clocks.mark()
         barrier()
         e0.record()
@@ -231,7 +275,7 @@ def main():
 
         def e2e_step():
             dx = hx.to(device, non_blocking=True)
-            if dx.dim() == 4:
+            if dx.dim() == 4 and on_gpu:
                 dx = dx.contiguous(memory_format=torch.channels_last)
             dy = hy.to(device, non_blocking=True)
             return float(step(dx, dy).item())  # 4-byte device→host read of the loss
@@ -294,7 +338,7 @@ def main():
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
-            "dtype": "bf16",
+            "dtype": "bf16" if on_gpu else "fp32 (cpu dry run)",
             "data": "synthetic (N(0,1) inputs, uniform labels), random-init weights",
             "impl": args.impl,
             "config": {
