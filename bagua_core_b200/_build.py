@@ -47,6 +47,7 @@ SOURCES = [
     "kernels/fused_emu.cc",
     "kernels/no_alloc.cu",
     "kernels/model_ops.cu",
+    "kernels/model_ops_cpu.cc",
 ]
 
 

@@ -541,7 +541,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // ---- fused bias + ReLU for channels-last bf16 activations (model-side kernels) ----
   // An activation is either [rows, C] contiguous or [N, C, H, W] in channels-last memory format.
   auto rows_and_channels = [](const at::Tensor& t, int64_t* rows, int* C) {
-    BAGUA_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, Tensor, "fused bias+ReLU works on CUDA bf16 tensors");
+    BAGUA_CHECK((t.is_cuda() || t.is_cpu()) && t.scalar_type() == at::kBFloat16, Tensor,
+                "fused bias+ReLU works on bf16 tensors (sm_100a kernels on CUDA, plain loops on the host)");
     if (t.dim() == 2 && t.is_contiguous()) {
       *rows = t.size(0);
       *C = (int)t.size(1);
@@ -559,9 +560,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         int64_t rows;
         int C;
         rows_and_channels(z, &rows, &C);
-        BAGUA_CHECK(bias.is_cuda() && bias.scalar_type() == at::kBFloat16 && bias.is_contiguous() && bias.numel() == C,
-                    Tensor, "bias must be a contiguous bf16 vector with one entry per channel");
-        model_ops::bias_relu_inplace_bf16(z.data_ptr(), bias.data_ptr(), rows, C, (cudaStream_t)stream);
+        BAGUA_CHECK(bias.device() == z.device() && bias.scalar_type() == at::kBFloat16 && bias.is_contiguous() &&
+                        bias.numel() == C,
+                    Tensor, "bias must be a contiguous bf16 vector with one entry per channel, on the activation's device");
+        if (z.is_cuda())
+          model_ops::bias_relu_inplace_bf16(z.data_ptr(), bias.data_ptr(), rows, C, (cudaStream_t)stream);
+        else
+          model_ops::bias_relu_inplace_bf16_host(z.data_ptr(), bias.data_ptr(), rows, C);
       },
       py::arg("activation"), py::arg("bias"), py::arg("stream"), "activation = max(activation + bias, 0), in place.");
   m.def(
@@ -573,8 +578,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         rows_and_channels(y, &r2, &C2);
         rows_and_channels(dz, &r3, &C3);
         BAGUA_CHECK(rows == r2 && rows == r3 && C == C2 && C == C3, Tensor, "dy, y and dz must have the same shape");
-        BAGUA_CHECK(db.is_cuda() && db.scalar_type() == at::kFloat && db.is_contiguous() && db.numel() == C, Tensor,
-                    "db must be a contiguous fp32 vector with one entry per channel");
+        BAGUA_CHECK(db.device() == dy.device() && y.device() == dy.device() && dz.device() == dy.device() &&
+                        db.scalar_type() == at::kFloat && db.is_contiguous() && db.numel() == C,
+                    Tensor, "db must be a contiguous fp32 vector with one entry per channel; all tensors on one device");
+        if (!dy.is_cuda()) {
+          model_ops::bias_relu_backward_bf16_host(dy.data_ptr(), y.data_ptr(), dz.data_ptr(), (float*)db.data_ptr(), rows, C);
+          return;
+        }
         const size_t need = model_ops::bias_relu_backward_scratch_bytes(rows, C);
         BAGUA_CHECK(need > 0, Tensor, "fused bias+ReLU backward: unsupported shape");
         auto scratch = PoolRawTensor::allocate((int)dy.device().index(), DType::U8, (int64_t)need, stream);
@@ -586,9 +596,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   // 2x2 / stride-2 max pooling on channels-last bf16 [N, C, H, W] tensors
   auto nhwc_dims = [](const at::Tensor& t, int64_t* N, int64_t* H, int64_t* W, int* C) {
-    BAGUA_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 4 &&
+    BAGUA_CHECK((t.is_cuda() || t.is_cpu()) && t.scalar_type() == at::kBFloat16 && t.dim() == 4 &&
                     t.is_contiguous(at::MemoryFormat::ChannelsLast),
-                Tensor, "fused max-pool works on channels-last CUDA bf16 [N, C, H, W] tensors");
+                Tensor, "fused max-pool works on channels-last bf16 [N, C, H, W] tensors");
     *N = t.size(0);
     *C = (int)t.size(1);
     *H = t.size(2);
@@ -604,7 +614,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         nhwc_dims(x, &N, &H, &W, &C);
         nhwc_dims(y, &N2, &H2, &W2, &C2);
         BAGUA_CHECK(N2 == N && C2 == C && H2 * 2 == H && W2 * 2 == W, Tensor, "y must be [N, C, H/2, W/2]");
-        model_ops::maxpool2x2_forward_bf16(x.data_ptr(), y.data_ptr(), N, H, W, C, (cudaStream_t)stream);
+        BAGUA_CHECK(x.device() == y.device(), Tensor, "input and output must be on one device");
+        if (x.is_cuda())
+          model_ops::maxpool2x2_forward_bf16(x.data_ptr(), y.data_ptr(), N, H, W, C, (cudaStream_t)stream);
+        else
+          model_ops::maxpool2x2_forward_bf16_host(x.data_ptr(), y.data_ptr(), N, H, W, C);
       },
       py::arg("input"), py::arg("output"), py::arg("stream"));
   m.def(
@@ -617,7 +631,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         nhwc_dims(dx, &N3, &H3, &W3, &C3);
         BAGUA_CHECK(N2 == N && C2 == C && H2 * 2 == H && W2 * 2 == W && N3 == N && C3 == C && H3 == H && W3 == W, Tensor,
                     "dy must be [N, C, H/2, W/2] and dx [N, C, H, W]");
-        model_ops::maxpool2x2_backward_bf16(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), N, H, W, C, (cudaStream_t)stream);
+        BAGUA_CHECK(x.device() == dy.device() && x.device() == dx.device(), Tensor, "all tensors must be on one device");
+        if (x.is_cuda())
+          model_ops::maxpool2x2_backward_bf16(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), N, H, W, C, (cudaStream_t)stream);
+        else
+          model_ops::maxpool2x2_backward_bf16_host(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), N, H, W, C);
       },
       py::arg("input"), py::arg("grad_output"), py::arg("grad_input"), py::arg("stream"));
 

@@ -43,5 +43,11 @@ void maxpool2x2_forward_bf16(const void* x, void* y, int64_t N, int64_t H, int64
 void maxpool2x2_backward_bf16(const void* x, const void* dy, void* dx, int64_t N, int64_t H, int64_t W, int C,
                               cudaStream_t stream);
 
+// ---- host restatements (model_ops_cpu.cc): same arguments, host pointers, any C ----------
+void bias_relu_inplace_bf16_host(void* z, const void* bias, int64_t rows, int C);
+void bias_relu_backward_bf16_host(const void* dy, const void* y, void* dz, float* db, int64_t rows, int C);
+void maxpool2x2_forward_bf16_host(const void* x, void* y, int64_t N, int64_t H, int64_t W, int C);
+void maxpool2x2_backward_bf16_host(const void* x, const void* dy, void* dx, int64_t N, int64_t H, int64_t W, int C);
+
 }  // namespace model_ops
 }  // namespace bagua

@@ -4,9 +4,11 @@ and in the backward one pass that applies the ReLU mask and reduces the bias gra
 The convolution itself stays a library call (cuDNN through `aten.convolution` /
 `aten.convolution_backward`).  What the framework would run around it — a bias add, a clamp, a
 ReLU-mask kernel and a separate column reduction for the bias gradient — is replaced by the two
-sm_100a kernels of `csrc/kernels/model_ops.cu`.  The fused path needs CUDA tensors computed in
-bf16 (bf16 autocast, or bf16 parameters and inputs); anything else takes the plain PyTorch
-composition, so `ConvBiasReLU` is a drop-in for `Conv2d` followed by `ReLU`.
+sm_100a kernels of `csrc/kernels/model_ops.cu`.  The fused path needs a block computed in bf16
+(bf16 autocast on CUDA, or bf16 parameters and inputs); anything else takes the plain PyTorch
+composition, so `ConvBiasReLU` is a drop-in for `Conv2d` followed by `ReLU`.  bf16 tensors on the
+CPU run the same Python path against a host restatement of the kernels
+(`csrc/kernels/model_ops_cpu.cc`), which is how the glue is tested without a GPU.
 """
 from __future__ import annotations
 
@@ -22,7 +24,7 @@ launches = 0
 
 
 def _stream(t: torch.Tensor) -> int:
-    return torch.cuda.current_stream(t.device).cuda_stream
+    return torch.cuda.current_stream(t.device).cuda_stream if t.is_cuda else 0
 
 
 def _count(n: int) -> None:
@@ -88,7 +90,7 @@ class MaxPool2x2(nn.Module):
     arg-max and writes the whole input gradient in one pass (no zero-fill)."""
 
     def forward(self, x):
-        if (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4
+        if (x.dtype == torch.bfloat16 and x.dim() == 4
                 and x.is_contiguous(memory_format=torch.channels_last)
                 and _C.k_maxpool2x2_supported(x.shape[0], x.shape[2], x.shape[3], x.shape[1])):
             return _MaxPool2x2Fn.apply(x)
@@ -96,9 +98,7 @@ class MaxPool2x2(nn.Module):
 
 
 def _computes_in_bf16(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    if not x.is_cuda:
-        return False
-    if torch.is_autocast_enabled("cuda"):
+    if x.is_cuda and torch.is_autocast_enabled("cuda"):
         return torch.get_autocast_dtype("cuda") == torch.bfloat16
     return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
 
