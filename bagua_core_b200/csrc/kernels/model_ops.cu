@@ -12,189 +12,38 @@
 
 #include "../common.h"
 #include "model_ops.h"
+#include "model_ops_bodies.cuh"
 
 namespace bagua {
 namespace model_ops {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kMaxBlocks = 148 * 4;
+using namespace bodies;
 
-__device__ __forceinline__ void unpack8(const uint4& x, float (&f)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 v = __bfloat1622float2(h[k]);
-    f[2 * k] = v.x;
-    f[2 * k + 1] = v.y;
-  }
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  uint4 r;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
-  return r;
-}
-
-// ---- forward ----------------------------------------------------------------------
-__device__ __forceinline__ uint4 bias_relu_vec(const uint4& x, const float* b) {
-  float f[8];
-  unpack8(x, f);
-#pragma unroll
-  for (int k = 0; k < 8; ++k) f[k] = fmaxf(f[k] + b[k], 0.f);
-  return pack8(f);
-}
-
-// cgroups = C / 8 vectors per row.
 __global__ void __launch_bounds__(kThreads)
     bias_relu_kernel(uint4* __restrict__ z, const __nv_bfloat16* __restrict__ bias, int64_t nvec, int cgroups) {
   extern __shared__ float s_bias[];
-  for (int c = threadIdx.x; c < cgroups * 8; c += kThreads) s_bias[c] = __bfloat162float(bias[c]);
-  __syncthreads();
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  for (; v + 3 * stride < nvec; v += 4 * stride) {
-    const uint4 a = z[v], b = z[v + stride], c = z[v + 2 * stride], d = z[v + 3 * stride];
-    z[v] = bias_relu_vec(a, s_bias + (int)(v % cgroups) * 8);
-    z[v + stride] = bias_relu_vec(b, s_bias + (int)((v + stride) % cgroups) * 8);
-    z[v + 2 * stride] = bias_relu_vec(c, s_bias + (int)((v + 2 * stride) % cgroups) * 8);
-    z[v + 3 * stride] = bias_relu_vec(d, s_bias + (int)((v + 3 * stride) % cgroups) * 8);
-  }
-  for (; v < nvec; v += stride) z[v] = bias_relu_vec(z[v], s_bias + (int)(v % cgroups) * 8);
+  bias_relu_body(z, bias, nvec, cgroups, s_bias);
 }
-
-// ---- backward ---------------------------------------------------------------------
-__device__ __forceinline__ uint4 relu_mask_acc(const uint4& dy, const uint4& y, float (&acc)[8]) {
-  float g[8], o[8];
-  unpack8(dy, g);
-  unpack8(y, o);
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    g[k] = o[k] > 0.f ? g[k] : 0.f;
-    acc[k] += g[k];
-  }
-  return pack8(g);
-}
-
-// Threads are laid out [rows_per_iter][cgroups]: thread (ro, cg) visits rows ro, ro + R, ...
-// (R = gridDim.x * rows_per_iter apart) and always the same 8 channels.  cgroups divides kThreads.
 __global__ void __launch_bounds__(kThreads)
-    bias_relu_backward_kernel(const uint4* dy, const uint4* __restrict__ y, uint4* dz,
-                              float* __restrict__ partial, int64_t rows, int cgroups) {
+    bias_relu_backward_kernel(const uint4* dy, const uint4* __restrict__ y, uint4* dz, float* __restrict__ partial,
+                              int64_t rows, int cgroups) {
   __shared__ float s_acc[kThreads * 8];
-  const int rows_per_iter = kThreads / cgroups;
-  const int cg = threadIdx.x % cgroups, ro = threadIdx.x / cgroups;
-  const int64_t step = (int64_t)gridDim.x * rows_per_iter;
-  float acc[8];
-#pragma unroll
-  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-  int64_t row = (int64_t)blockIdx.x * rows_per_iter + ro;
-  for (; row + step < rows; row += 2 * step) {
-    const int64_t v0 = row * cgroups + cg, v1 = (row + step) * cgroups + cg;
-    const uint4 a0 = dy[v0], b0 = y[v0], a1 = dy[v1], b1 = y[v1];
-    dz[v0] = relu_mask_acc(a0, b0, acc);
-    dz[v1] = relu_mask_acc(a1, b1, acc);
-  }
-  for (; row < rows; row += step) {
-    const int64_t v0 = row * cgroups + cg;
-    dz[v0] = relu_mask_acc(dy[v0], y[v0], acc);
-  }
-#pragma unroll
-  for (int k = 0; k < 8; ++k) s_acc[threadIdx.x * 8 + k] = acc[k];
-  __syncthreads();
-  const int C = cgroups * 8;
-  for (int c = threadIdx.x; c < C; c += kThreads) {
-    const int g = c >> 3, k = c & 7;
-    float s = 0.f;
-    for (int r = 0; r < rows_per_iter; ++r) s += s_acc[(r * cgroups + g) * 8 + k];
-    partial[(size_t)blockIdx.x * C + c] = s;
-  }
+  bias_relu_backward_body(dy, y, dz, partial, rows, cgroups, s_acc);
 }
-
 __global__ void bias_grad_finish_kernel(const float* __restrict__ partial, float* __restrict__ db, int blocks, int C) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float s = 0.f;
-  for (int b = 0; b < blocks; ++b) s += partial[(size_t)b * C + c];
-  db[c] = s;
+  bias_grad_finish_body(partial, db, blocks, C);
 }
-
-// ---- 2x2 / stride-2 max pooling -------------------------------------------------------
-// One thread per output vector (8 channels of one output pixel); vector indices are
-// [n][h][w][cg] with cg fastest, so a warp reads whole pixels of contiguous channels.
-struct PoolIndex {
-  int64_t x00;  // vector index of the window's top-left input pixel
-  int64_t dw, dh;  // vector strides to the right / lower neighbour
-};
-__device__ __forceinline__ PoolIndex pool_index(int64_t v, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
-  const int64_t cg = v % cgroups, p = v / cgroups;
-  const int64_t wo = p % Wo, q = p / Wo;
-  const int64_t ho = q % Ho, n = q / Ho;
-  PoolIndex r;
-  r.dw = cgroups;
-  r.dh = W * cgroups;
-  r.x00 = ((n * (2 * Ho) + 2 * ho) * W + 2 * wo) * cgroups + cg;
-  return r;
-}
-
 __global__ void __launch_bounds__(kThreads)
     maxpool2x2_forward_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t nvec_out, int64_t Ho,
                               int64_t Wo, int64_t W, int cgroups) {
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
-    const PoolIndex p = pool_index(v, Ho, Wo, W, cgroups);
-    const uint4 a = x[p.x00], b = x[p.x00 + p.dw], c = x[p.x00 + p.dh], d = x[p.x00 + p.dh + p.dw];
-    float fa[8], fb[8], fc[8], fd[8];
-    unpack8(a, fa);
-    unpack8(b, fb);
-    unpack8(c, fc);
-    unpack8(d, fd);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) fa[k] = fmaxf(fmaxf(fa[k], fb[k]), fmaxf(fc[k], fd[k]));
-    y[v] = pack8(fa);
-  }
+  maxpool2x2_forward_body(x, y, nvec_out, Ho, Wo, W, cgroups);
 }
-
 __global__ void __launch_bounds__(kThreads)
     maxpool2x2_backward_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ dx,
                                int64_t nvec_out, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
-    const PoolIndex p = pool_index(v, Ho, Wo, W, cgroups);
-    const uint4 a = x[p.x00], b = x[p.x00 + p.dw], c = x[p.x00 + p.dh], d = x[p.x00 + p.dh + p.dw];
-    const uint4 g4 = dy[v];
-    float fa[8], fb[8], fc[8], fd[8], g[8];
-    unpack8(a, fa);
-    unpack8(b, fb);
-    unpack8(c, fc);
-    unpack8(d, fd);
-    unpack8(g4, g);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      // first maximum in scan order (0,0) (0,1) (1,0) (1,1): a later element wins only if strictly larger
-      float m = fa[k];
-      int idx = 0;
-      if (fb[k] > m) {
-        m = fb[k];
-        idx = 1;
-      }
-      if (fc[k] > m) {
-        m = fc[k];
-        idx = 2;
-      }
-      if (fd[k] > m) idx = 3;
-      fa[k] = idx == 0 ? g[k] : 0.f;
-      fb[k] = idx == 1 ? g[k] : 0.f;
-      fc[k] = idx == 2 ? g[k] : 0.f;
-      fd[k] = idx == 3 ? g[k] : 0.f;
-    }
-    dx[p.x00] = pack8(fa);
-    dx[p.x00 + p.dw] = pack8(fb);
-    dx[p.x00 + p.dh] = pack8(fc);
-    dx[p.x00 + p.dh + p.dw] = pack8(fd);
-  }
+  maxpool2x2_backward_body(x, dy, dx, nvec_out, Ho, Wo, W, cgroups);
 }
 
 int pool_grid(int64_t nvec_out) {
@@ -210,11 +59,7 @@ int backward_blocks(int64_t rows, int C) {
 
 }  // namespace
 
-bool bias_relu_supported(int64_t rows, int C) {
-  if (rows <= 0 || C < 8 || C > 2048 || C % 8 != 0) return false;
-  const int cgroups = C / 8;
-  return kThreads % cgroups == 0;  // the backward's thread layout
-}
+static_assert(kThreads == kBlockThreads, "bias_relu_supported() assumes the kernels' block size");
 
 void bias_relu_inplace_bf16(void* z, const void* bias, int64_t rows, int C, cudaStream_t stream) {
   BAGUA_CHECK(bias_relu_supported(rows, C) && (uintptr_t)z % 16 == 0, Tensor,
@@ -243,10 +88,6 @@ void bias_relu_backward_bf16(const void* dy, const void* y, void* dz, float* db,
   BAGUA_CUDA_CHECK(cudaGetLastError());
   bias_grad_finish_kernel<<<(C + 127) / 128, 128, 0, stream>>>((const float*)scratch, db, blocks, C);
   BAGUA_CUDA_CHECK(cudaGetLastError());
-}
-
-bool maxpool2x2_supported(int64_t N, int64_t H, int64_t W, int C) {
-  return N > 0 && H >= 2 && W >= 2 && H % 2 == 0 && W % 2 == 0 && C >= 8 && C % 8 == 0;
 }
 
 void maxpool2x2_forward_bf16(const void* x, void* y, int64_t N, int64_t H, int64_t W, int C, cudaStream_t stream) {

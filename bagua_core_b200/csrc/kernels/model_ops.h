@@ -20,7 +20,10 @@
 namespace bagua {
 namespace model_ops {
 
-// C must be a multiple of 8, 8 <= C <= 2048; pointers 16-byte aligned.
+// Threads per block of the CUDA kernels.
+constexpr int kBlockThreads = 256;
+
+// C must be a multiple of 8, 8 <= C <= 2048, C / 8 a divisor of kBlockThreads; pointers 16-byte aligned.
 bool bias_relu_supported(int64_t rows, int C);
 
 // z: [rows, C] bf16 (in place), bias: [C] bf16.

@@ -30,6 +30,16 @@ inline uint16_t float_to_bf16(float f) {
 
 }  // namespace
 
+bool bias_relu_supported(int64_t rows, int C) {
+  if (rows <= 0 || C < 8 || C > 2048 || C % 8 != 0) return false;
+  const int cgroups = C / 8;
+  return kBlockThreads % cgroups == 0;  // the backward's thread layout: [rows per iteration][C / 8]
+}
+
+bool maxpool2x2_supported(int64_t N, int64_t H, int64_t W, int C) {
+  return N > 0 && H >= 2 && W >= 2 && H % 2 == 0 && W % 2 == 0 && C >= 8 && C % 8 == 0;
+}
+
 void bias_relu_inplace_bf16_host(void* z, const void* bias, int64_t rows, int C) {
   uint16_t* p = static_cast<uint16_t*>(z);
   const uint16_t* b = static_cast<const uint16_t*>(bias);

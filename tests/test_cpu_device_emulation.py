@@ -71,3 +71,19 @@ def test_device_bodies_are_race_free_under_thread_sanitizer(tmp_path):
     for nranks, blocks, ops, seed in [(2, 1, 80, 1), (4, 2, 80, 2), (3, 3, 60, 3)]:
         out = _run(exe, nranks, blocks, ops, seed)
         assert "WARNING: ThreadSanitizer" not in out, out[-3000:]
+
+
+def test_model_op_kernels_match_the_host_restatement(tmp_path):
+    """The fused bias+ReLU and max-pool kernels (`csrc/kernels/model_ops_bodies.cuh`), run thread for
+    thread on grids of a few blocks of 256 threads, against `csrc/kernels/model_ops_cpu.cc`."""
+    gxx = shutil.which("g++")
+    if gxx is None or not os.path.exists(os.path.join(CUDA_INC, "cuda_runtime.h")):
+        pytest.skip("needs g++ and the CUDA headers")
+    exe = str(tmp_path / "model_ops_emulation")
+    cmd = [gxx, "-std=c++20", "-O1", "-g", "-fno-strict-aliasing", "-DBAGUA_HOST_EMULATION", "-I", CSRC, "-I", CUDA_INC,
+           os.path.join(ROOT, "tests", "cpp", "model_ops_emulation.cc"), os.path.join(CSRC, "kernels", "model_ops_cpu.cc"),
+           "-o", exe, "-lpthread"]
+    build = subprocess.run(cmd, capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0 and "0 failures" in run.stdout, run.stdout + run.stderr
