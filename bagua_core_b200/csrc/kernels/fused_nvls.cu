@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include "fused.h"
+#include "fused_nvls_body.cuh"
 #include "peer_sync.cuh"
 #include "vec_ops.cuh"
 
@@ -26,90 +27,13 @@ namespace fused {
 namespace {
 
 using psync::Launch;
-
-template <typename T>
-struct Multimem;
-template <>
-struct Multimem<float> {
-  __device__ static uint4 ld_reduce(const uint4* mc) {
-    uint4 r;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(mc)
-                 : "memory");
-    return r;
-  }
-};
-template <>
-struct Multimem<__half> {
-  __device__ static uint4 ld_reduce(const uint4* mc) {
-    uint4 r;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(mc)
-                 : "memory");
-    return r;
-  }
-};
-template <>
-struct Multimem<__nv_bfloat16> {
-  __device__ static uint4 ld_reduce(const uint4* mc) {
-    uint4 r;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(mc)
-                 : "memory");
-    return r;
-  }
-};
-
-// The store is a 16-byte bit copy whatever the element type.
-__device__ __forceinline__ void multimem_st(uint4* mc, const uint4& x) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(x.x), "r"(x.y), "r"(x.z),
-               "r"(x.w)
-               : "memory");
-}
-
-template <typename T>
-__device__ __forceinline__ uint4 scaled(const uint4& x, float scale) {
-  using O = VecOps<T>;
-  float a[O::N];
-#pragma unroll
-  for (int k = 0; k < O::N; ++k) a[k] = 0.f;
-  O::acc(a, x);
-  return O::pack(a, scale);
-}
+using namespace nvls_bodies;
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     allreduce_nvls_kernel(const __grid_constant__ ArenaView v, const uint4* mc_in, uint4* mc_out, int64_t nvec,
                           float scale) {
-  const Launch L = psync::real_launch();
-  const int me = v.rank, N = v.nranks;
-  const int64_t c0 = nvec * me / N, len = nvec * (me + 1) / N - c0;
-  const int64_t lo = c0 + len * L.block / L.grid, hi = c0 + len * (L.block + 1) / L.grid;
-  const bool rescale = scale != 1.0f;
-
-  psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
-  bool ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
-  if (ok) {
-    constexpr int U = 4;  // reductions in flight per thread
-    int64_t i = lo + threadIdx.x;
-    for (; i + (U - 1) * kThreads < hi; i += U * kThreads) {
-      uint4 x[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) x[u] = Multimem<T>::ld_reduce(mc_in + i + u * kThreads);
-#pragma unroll
-      for (int u = 0; u < U; ++u) multimem_st(mc_out + i + u * kThreads, rescale ? scaled<T>(x[u], scale) : x[u]);
-    }
-    for (; i < hi; i += kThreads) {
-      const uint4 x = Multimem<T>::ld_reduce(mc_in + i);
-      multimem_st(mc_out + i, rescale ? scaled<T>(x, scale) : x);
-    }
-    psync::cta_signal_phase(v, L, 1, all_peers_mask(v));
-    ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
-  }
-  psync::cta_finish_op(v, L);
+  allreduce_nvls_body<T>(v, psync::real_launch(), mc_in, mc_out, nvec, scale);
 }
 
 template <typename T>

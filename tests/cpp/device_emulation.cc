@@ -27,6 +27,7 @@
 #include "kernels/fused_bytegrad_body.cuh"
 #include "kernels/fused_collectives_bodies.cuh"
 #include "kernels/fused_gossip_body.cuh"
+#include "kernels/fused_nvls_body.cuh"
 
 using namespace bagua;
 using namespace bagua::fused;
@@ -61,6 +62,7 @@ enum class Kind {
   PairAverageSym,
   ByteGrad,
   LpRing,
+  AllReduceNvls,
   kCount
 };
 
@@ -188,7 +190,8 @@ void prepare(World& w, int me, uint32_t k) {
     case Kind::AllReduceSym:
     case Kind::PairAverage:
     case Kind::PairAverageSym: fill(r.in, k, me, op.vecs); break;
-    case Kind::AllReduceTwoShotInPlace: fill(r.out, k, me, op.vecs); break;
+    case Kind::AllReduceTwoShotInPlace:
+    case Kind::AllReduceNvls: fill(r.out, k, me, op.vecs); break;
     case Kind::ByteGrad: fill(r.in, k, me, op.vecs * N); break;
     case Kind::LpRing:
       for (int64_t i = 0; i < op.vecs; ++i)
@@ -257,6 +260,13 @@ void run_body(World& w, int me, int b, uint32_t k) {
     }
     case Kind::PairAverage: pair_average_body<float>(v, L, in, out, c, me ^ 1); break;
     case Kind::PairAverageSym: pair_average_sym_body<float>(v, L, in, ins.p[me ^ 1], out, c, me ^ 1); break;
+    case Kind::AllReduceNvls: {
+      // in place on the `out` buffers, which stand for memory bound to one multicast object;
+      // the multicast address is the one inside rank 0's buffer
+      uint4* mc = reinterpret_cast<uint4*>(w.ranks[0].out.data());
+      nvls_bodies::allreduce_nvls_body<float>(v, L, mc, mc, c, op.scale);
+      break;
+    }
     case Kind::ByteGrad: {
       // bucket of N chunks of 4c floats, quantised to one byte each; slots hold a 32-byte header + payload
       const int64_t chunk = 4 * c;
@@ -371,6 +381,7 @@ uint64_t verify(World& w, int me, uint32_t k) {
     case Kind::AllReduceTwoShot:
     case Kind::AllReduceTwoShotInPlace:
     case Kind::AllReduceSym:
+    case Kind::AllReduceNvls:
       for (int64_t i = 0; i < c; ++i) {
         sum4(i, op.scale, e);
         expect(r.out, i, e[0], e[1], e[2], e[3]);
@@ -484,6 +495,8 @@ int main(int argc, char** argv) {
     r.signals.assign((size_t)kSigWords, 0u);
     r.bar = std::make_unique<std::barrier<>>(w.G * kThreads);
   }
+  nvls_bodies::g_host_multicast.nranks = w.N;
+  for (int q = 0; q < w.N; ++q) nvls_bodies::g_host_multicast.base[q] = reinterpret_cast<char*>(w.ranks[(size_t)q].out.data());
   for (int i = 0; i < w.N * w.G; ++i) w.blocks.push_back(std::make_unique<hostemu::BlockContext>(kThreads));
 
   std::vector<std::thread> threads;
