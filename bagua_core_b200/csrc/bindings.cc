@@ -639,6 +639,53 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("input"), py::arg("grad_output"), py::arg("grad_input"), py::arg("stream"));
 
+  // bias + ReLU followed by 2x2 pooling in one pass each way
+  m.def(
+      "k_bias_relu_pool_",
+      [nhwc_dims](at::Tensor y, at::Tensor p, at::Tensor bias, uint64_t stream) {
+        int64_t N, H, W, N2, H2, W2;
+        int C, C2;
+        nhwc_dims(y, &N, &H, &W, &C);
+        nhwc_dims(p, &N2, &H2, &W2, &C2);
+        BAGUA_CHECK(N2 == N && C2 == C && H2 * 2 == H && W2 * 2 == W && p.device() == y.device(), Tensor,
+                    "the pooled output must be [N, C, H/2, W/2] on the activation's device");
+        BAGUA_CHECK(bias.device() == y.device() && bias.scalar_type() == at::kBFloat16 && bias.is_contiguous() &&
+                        bias.numel() == C,
+                    Tensor, "bias must be a contiguous bf16 vector with one entry per channel, on the activation's device");
+        if (y.is_cuda())
+          model_ops::bias_relu_pool_bf16(y.data_ptr(), p.data_ptr(), bias.data_ptr(), N, H, W, C, (cudaStream_t)stream);
+        else
+          model_ops::bias_relu_pool_bf16_host(y.data_ptr(), p.data_ptr(), bias.data_ptr(), N, H, W, C);
+      },
+      py::arg("activation"), py::arg("pooled"), py::arg("bias"), py::arg("stream"),
+      "activation = max(activation + bias, 0) in place; pooled = its 2x2 / stride-2 maximum.");
+  m.def(
+      "k_bias_relu_pool_backward",
+      [nhwc_dims](at::Tensor dp, at::Tensor y, at::Tensor dz, at::Tensor db, uint64_t stream) {
+        int64_t N, H, W, N2, H2, W2, N3, H3, W3;
+        int C, C2, C3;
+        nhwc_dims(y, &N, &H, &W, &C);
+        nhwc_dims(dp, &N2, &H2, &W2, &C2);
+        nhwc_dims(dz, &N3, &H3, &W3, &C3);
+        BAGUA_CHECK(N2 == N && C2 == C && H2 * 2 == H && W2 * 2 == W && N3 == N && C3 == C && H3 == H && W3 == W, Tensor,
+                    "grad_pooled must be [N, C, H/2, W/2] and grad_pre_activation [N, C, H, W]");
+        BAGUA_CHECK(dp.device() == y.device() && dz.device() == y.device() && db.device() == y.device() &&
+                        db.scalar_type() == at::kFloat && db.is_contiguous() && db.numel() == C,
+                    Tensor, "db must be a contiguous fp32 vector with one entry per channel; all tensors on one device");
+        if (!y.is_cuda()) {
+          model_ops::bias_relu_pool_backward_bf16_host(dp.data_ptr(), y.data_ptr(), dz.data_ptr(), (float*)db.data_ptr(), N, H,
+                                                       W, C);
+          return;
+        }
+        const size_t need = model_ops::bias_relu_backward_scratch_bytes(N * (H / 2) * (W / 2), C);
+        BAGUA_CHECK(need > 0, Tensor, "fused bias+ReLU+pool backward: unsupported shape");
+        auto scratch = PoolRawTensor::allocate((int)y.device().index(), DType::U8, (int64_t)need, stream);
+        model_ops::bias_relu_pool_backward_bf16(dp.data_ptr(), y.data_ptr(), dz.data_ptr(), (float*)db.data_ptr(), N, H, W, C,
+                                                scratch->data_ptr(), (cudaStream_t)stream);
+      },
+      py::arg("grad_pooled"), py::arg("output"), py::arg("grad_pre_activation"), py::arg("grad_bias"), py::arg("stream"),
+      "Backward of k_bias_relu_pool_: routes grad_pooled to each window's first maximum where it is positive.");
+
   // ---- single-GPU emulation of the fused kernels (all ranks in one cooperative launch) ----
   py::class_<fused::EmulatedArena>(m, "EmulatedArena")
       .def(py::init<int, int, size_t>(), py::arg("nranks"), py::arg("device"), py::arg("staging_bytes"))

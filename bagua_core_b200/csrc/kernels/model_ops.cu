@@ -46,6 +46,20 @@ __global__ void __launch_bounds__(kThreads)
   maxpool2x2_backward_body(x, dy, dx, nvec_out, Ho, Wo, W, cgroups);
 }
 
+__global__ void __launch_bounds__(kThreads)
+    bias_relu_pool_kernel(uint4* __restrict__ y, uint4* __restrict__ p, const __nv_bfloat16* __restrict__ bias,
+                          int64_t nvec_out, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
+  extern __shared__ float s_bias[];
+  bias_relu_pool_body(y, p, bias, nvec_out, Ho, Wo, W, cgroups, s_bias);
+}
+__global__ void __launch_bounds__(kThreads)
+    bias_relu_pool_backward_kernel(const uint4* __restrict__ dp, const uint4* __restrict__ y, uint4* __restrict__ dz,
+                                   float* __restrict__ partial, int64_t pooled_rows, int64_t Ho, int64_t Wo, int64_t W,
+                                   int cgroups) {
+  __shared__ float s_acc[kThreads * 8];
+  bias_relu_pool_backward_body(dp, y, dz, partial, pooled_rows, Ho, Wo, W, cgroups, s_acc);
+}
+
 int pool_grid(int64_t nvec_out) {
   const int64_t want = (nvec_out + kThreads - 1) / kThreads;
   return (int)std::max<int64_t>(1, std::min<int64_t>(want, 148 * 8));
@@ -109,6 +123,34 @@ void maxpool2x2_backward_bf16(const void* x, const void* dy, void* dx, int64_t N
   const int64_t nvec_out = N * (H / 2) * (W / 2) * (C / 8);
   maxpool2x2_backward_kernel<<<pool_grid(nvec_out), kThreads, 0, stream>>>((const uint4*)x, (const uint4*)dy, (uint4*)dx,
                                                                            nvec_out, H / 2, W / 2, W, C / 8);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+}
+
+void bias_relu_pool_bf16(void* y, void* p, const void* bias, int64_t N, int64_t H, int64_t W, int C, cudaStream_t stream) {
+  BAGUA_CHECK(bias_relu_supported(N * H * W, C) && maxpool2x2_supported(N, H, W, C) && (uintptr_t)y % 16 == 0 &&
+                  (uintptr_t)p % 16 == 0,
+              Tensor,
+              "fused bias+ReLU+pool: unsupported shape [" << N << ", " << H << ", " << W << ", " << C
+                                                          << "] or unaligned buffers");
+  const int64_t nvec_out = N * (H / 2) * (W / 2) * (C / 8);
+  bias_relu_pool_kernel<<<pool_grid(nvec_out), kThreads, (size_t)C * sizeof(float), stream>>>(
+      (uint4*)y, (uint4*)p, (const __nv_bfloat16*)bias, nvec_out, H / 2, W / 2, W, C / 8);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+}
+
+void bias_relu_pool_backward_bf16(const void* dp, const void* y, void* dz, float* db, int64_t N, int64_t H, int64_t W,
+                                  int C, void* scratch, cudaStream_t stream) {
+  BAGUA_CHECK(bias_relu_supported(N * H * W, C) && maxpool2x2_supported(N, H, W, C) && (uintptr_t)dp % 16 == 0 &&
+                  (uintptr_t)y % 16 == 0 && (uintptr_t)dz % 16 == 0 && scratch != nullptr,
+              Tensor,
+              "fused bias+ReLU+pool backward: unsupported shape [" << N << ", " << H << ", " << W << ", " << C
+                                                                   << "] or unaligned buffers");
+  const int64_t pooled_rows = N * (H / 2) * (W / 2);
+  const int blocks = backward_blocks(pooled_rows, C);
+  bias_relu_pool_backward_kernel<<<blocks, kThreads, 0, stream>>>((const uint4*)dp, (const uint4*)y, (uint4*)dz,
+                                                                  (float*)scratch, pooled_rows, H / 2, W / 2, W, C / 8);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  bias_grad_finish_kernel<<<(C + 127) / 128, 128, 0, stream>>>((const float*)scratch, db, blocks, C);
   BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 

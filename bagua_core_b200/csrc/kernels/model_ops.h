@@ -46,11 +46,23 @@ void maxpool2x2_forward_bf16(const void* x, void* y, int64_t N, int64_t H, int64
 void maxpool2x2_backward_bf16(const void* x, const void* dy, void* dx, int64_t N, int64_t H, int64_t W, int C,
                               cudaStream_t stream);
 
+// ---- bias + ReLU followed by 2x2 pooling, as one forward and one backward pass ------------
+// y: [N, H, W, C] convolution output, overwritten with max(y + bias, 0); p: [N, H/2, W/2, C].
+// Needs both bias_relu_supported(N*H*W, C) and maxpool2x2_supported(N, H, W, C).
+void bias_relu_pool_bf16(void* y, void* p, const void* bias, int64_t N, int64_t H, int64_t W, int C, cudaStream_t stream);
+// dp: [N, H/2, W/2, C]; y as written by the forward; dz: [N, H, W, C] (every element written);
+// db: [C] fp32; scratch of bias_relu_backward_scratch_bytes(N*(H/2)*(W/2), C) bytes.
+void bias_relu_pool_backward_bf16(const void* dp, const void* y, void* dz, float* db, int64_t N, int64_t H, int64_t W,
+                                  int C, void* scratch, cudaStream_t stream);
+
 // ---- host restatements (model_ops_cpu.cc): same arguments, host pointers, any C ----------
 void bias_relu_inplace_bf16_host(void* z, const void* bias, int64_t rows, int C);
 void bias_relu_backward_bf16_host(const void* dy, const void* y, void* dz, float* db, int64_t rows, int C);
 void maxpool2x2_forward_bf16_host(const void* x, void* y, int64_t N, int64_t H, int64_t W, int C);
 void maxpool2x2_backward_bf16_host(const void* x, const void* dy, void* dx, int64_t N, int64_t H, int64_t W, int C);
+void bias_relu_pool_bf16_host(void* y, void* p, const void* bias, int64_t N, int64_t H, int64_t W, int C);
+void bias_relu_pool_backward_bf16_host(const void* dp, const void* y, void* dz, float* db, int64_t N, int64_t H,
+                                       int64_t W, int C);
 
 }  // namespace model_ops
 }  // namespace bagua

@@ -193,6 +193,99 @@ __device__ __forceinline__ void maxpool2x2_backward_body(const uint4* __restrict
   }
 }
 
+// ---- bias + ReLU with the 2x2 pooling that follows it -----------------------------------
+// Forward: y = max(z + bias, 0) in place on the [N, H, W, C] convolution output, and
+// p = 2x2 max of y, both from one read of z.  One thread per pooled vector.
+__device__ __forceinline__ void bias_relu_pool_body(uint4* __restrict__ y, uint4* __restrict__ p,
+                                                    const __nv_bfloat16* __restrict__ bias, int64_t nvec_out,
+                                                    int64_t Ho, int64_t Wo, int64_t W, int cgroups, float* s_bias) {
+  for (int c = threadIdx.x; c < cgroups * 8; c += kThreads) s_bias[c] = __bfloat162float(bias[c]);
+  __syncthreads();
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
+    const PoolIndex q = pool_index(v, Ho, Wo, W, cgroups);
+    const float* b = s_bias + (int)(v % cgroups) * 8;
+    const uint4 a0 = y[q.x00], a1 = y[q.x00 + q.dw], a2 = y[q.x00 + q.dh], a3 = y[q.x00 + q.dh + q.dw];
+    const uint4 r0 = bias_relu_vec(a0, b), r1 = bias_relu_vec(a1, b), r2 = bias_relu_vec(a2, b), r3 = bias_relu_vec(a3, b);
+    y[q.x00] = r0;
+    y[q.x00 + q.dw] = r1;
+    y[q.x00 + q.dh] = r2;
+    y[q.x00 + q.dh + q.dw] = r3;
+    float f0[8], f1[8], f2[8], f3[8];
+    unpack8(r0, f0);
+    unpack8(r1, f1);
+    unpack8(r2, f2);
+    unpack8(r3, f3);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f0[k] = fmaxf(fmaxf(f0[k], f1[k]), fmaxf(f2[k], f3[k]));
+    p[v] = pack8(f0);
+  }
+}
+
+// Backward of the pair: dz = dp routed to each window's first maximum of y, masked by y > 0,
+// zero elsewhere; db[c] = column sums of dz.  Thread (ro, cg) visits pooled pixels ro, ro + R, ...
+// and always the same 8 channels, like the un-pooled backward.
+__device__ __forceinline__ void bias_relu_pool_backward_body(const uint4* __restrict__ dp, const uint4* __restrict__ y,
+                                                             uint4* __restrict__ dz, float* __restrict__ partial,
+                                                             int64_t pooled_rows, int64_t Ho, int64_t Wo, int64_t W,
+                                                             int cgroups, float* s_acc) {
+  const int rows_per_iter = kThreads / cgroups;
+  const int cg = threadIdx.x % cgroups, ro = threadIdx.x / cgroups;
+  const int64_t step = (int64_t)gridDim.x * rows_per_iter;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  for (int64_t pr = (int64_t)blockIdx.x * rows_per_iter + ro; pr < pooled_rows; pr += step) {
+    const int64_t v = pr * cgroups + cg;
+    const PoolIndex q = pool_index(v, Ho, Wo, W, cgroups);
+    const uint4 a0 = y[q.x00], a1 = y[q.x00 + q.dw], a2 = y[q.x00 + q.dh], a3 = y[q.x00 + q.dh + q.dw];
+    const uint4 g4 = dp[v];
+    float f0[8], f1[8], f2[8], f3[8], g[8];
+    unpack8(a0, f0);
+    unpack8(a1, f1);
+    unpack8(a2, f2);
+    unpack8(a3, f3);
+    unpack8(g4, g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float m = f0[k];
+      int idx = 0;
+      if (f1[k] > m) {
+        m = f1[k];
+        idx = 1;
+      }
+      if (f2[k] > m) {
+        m = f2[k];
+        idx = 2;
+      }
+      if (f3[k] > m) {
+        m = f3[k];
+        idx = 3;
+      }
+      const float gv = m > 0.f ? g[k] : 0.f;  // the ReLU mask of the element the gradient goes to
+      acc[k] += gv;
+      f0[k] = idx == 0 ? gv : 0.f;
+      f1[k] = idx == 1 ? gv : 0.f;
+      f2[k] = idx == 2 ? gv : 0.f;
+      f3[k] = idx == 3 ? gv : 0.f;
+    }
+    dz[q.x00] = pack8(f0);
+    dz[q.x00 + q.dw] = pack8(f1);
+    dz[q.x00 + q.dh] = pack8(f2);
+    dz[q.x00 + q.dh + q.dw] = pack8(f3);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s_acc[threadIdx.x * 8 + k] = acc[k];
+  __syncthreads();
+  const int C = cgroups * 8;
+  for (int c = threadIdx.x; c < C; c += kThreads) {
+    const int g = c >> 3, k = c & 7;
+    float s = 0.f;
+    for (int r = 0; r < rows_per_iter; ++r) s += s_acc[(r * cgroups + g) * 8 + k];
+    partial[(size_t)blockIdx.x * C + c] = s;
+  }
+}
+
 }  // namespace bodies
 }  // namespace model_ops
 }  // namespace bagua

@@ -104,5 +104,18 @@ void maxpool2x2_backward_bf16_host(const void* x, const void* dy, void* dx, int6
         }
 }
 
+// The pooled pair is, by definition, the composition of the two single steps.
+void bias_relu_pool_bf16_host(void* y, void* p, const void* bias, int64_t N, int64_t H, int64_t W, int C) {
+  bias_relu_inplace_bf16_host(y, bias, N * H * W, C);
+  maxpool2x2_forward_bf16_host(y, p, N, H, W, C);
+}
+
+void bias_relu_pool_backward_bf16_host(const void* dp, const void* y, void* dz, float* db, int64_t N, int64_t H,
+                                       int64_t W, int C) {
+  std::vector<uint16_t> dy((size_t)(N * H * W * C));
+  maxpool2x2_backward_bf16_host(y, dp, dy.data(), N, H, W, C);
+  bias_relu_backward_bf16_host(dy.data(), y, dz, db, N * H * W, C);
+}
+
 }  // namespace model_ops
 }  // namespace bagua

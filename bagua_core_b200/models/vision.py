@@ -13,20 +13,22 @@ class VGG16(nn.Module):
     """13 convolutions + 3 fully connected layers, ReLU, max-pool, dropout in the classifier.
 
     `fused_ops=True` builds every conv+ReLU pair as one `ConvBiasReLU` module (bias add, ReLU and the
-    bias-gradient reduction in this package's own kernels) and every pooling layer as `MaxPool2x2`
-    (no index tensor, one-pass backward); parameter names change from `features.<2k>.weight` to
-    the fused module's index, values and shapes do not."""
+    bias-gradient reduction in this package's own kernels) and folds every pooling layer into the
+    block before it (`ConvBiasReLUPool`: no index tensor, one pass each way); parameter names change
+    from `features.<2k>.weight` to the fused module's index, values and shapes do not."""
 
     def __init__(self, num_classes: int = 1000, dropout: float = 0.5, fused_ops: bool = False):
         super().__init__()
         layers, c_in = [], 3
         if fused_ops:
-            from ..ops.fused_conv import ConvBiasReLU, MaxPool2x2
-        for v in _VGG16_CFG:
+            from ..ops.fused_conv import ConvBiasReLU, ConvBiasReLUPool
+        for i, v in enumerate(_VGG16_CFG):
             if v == "M":
-                layers.append(MaxPool2x2() if fused_ops else nn.MaxPool2d(2, 2))
+                if not fused_ops:
+                    layers.append(nn.MaxPool2d(2, 2))  # (fused: folded into the convolution block before it)
             elif fused_ops:
-                layers.append(ConvBiasReLU(c_in, v, 3, padding=1))
+                pooled = i + 1 < len(_VGG16_CFG) and _VGG16_CFG[i + 1] == "M"
+                layers.append((ConvBiasReLUPool if pooled else ConvBiasReLU)(c_in, v, 3, padding=1))
                 c_in = v
             else:
                 layers += [nn.Conv2d(c_in, v, 3, padding=1), nn.ReLU(inplace=True)]

@@ -64,6 +64,41 @@ class _ConvBiasReLUFn(torch.autograd.Function):
         return dx, dw, db.to(ctx.bias_dtype), None, None, None, None
 
 
+class _ConvBiasReLUPoolFn(torch.autograd.Function):
+    """conv → bias + ReLU → 2x2 max pooling; the full-resolution activation is kept only for the
+    backward, which produces the convolution's output gradient and the bias gradient in one pass."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx, x, weight, bias, stride, padding, dilation, groups):
+        ctx.conf = (stride, padding, dilation, groups)
+        x = x.contiguous(memory_format=torch.channels_last)
+        y = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)
+        y = y.contiguous(memory_format=torch.channels_last)
+        n, c, h, w = y.shape
+        p = torch.empty((n, c, h // 2, w // 2), dtype=y.dtype, device=y.device, memory_format=torch.channels_last)
+        _C.k_bias_relu_pool_(y, p, bias.contiguous(), _stream(y))
+        _count(1)
+        ctx.save_for_backward(x, weight, y)
+        ctx.bias_dtype = bias.dtype
+        return p
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, dp):
+        stride, padding, dilation, groups = ctx.conf
+        x, weight, y = ctx.saved_tensors
+        dp = dp.contiguous(memory_format=torch.channels_last)
+        dz = torch.empty_like(y)
+        db = torch.empty(weight.shape[0], dtype=torch.float32, device=y.device)
+        _C.k_bias_relu_pool_backward(dp, y, dz, db, _stream(y))
+        _count(2)
+        dx, dw, _ = torch.ops.aten.convolution_backward(
+            dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
+            [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        return dx, dw, db.to(ctx.bias_dtype), None, None, None, None
+
+
 class _MaxPool2x2Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):
@@ -115,3 +150,24 @@ class ConvBiasReLU(nn.Conv2d):
             return F.relu(super().forward(x))
         return _ConvBiasReLUFn.apply(x, self.weight, self.bias, list(self.stride), list(self.padding),
                                      list(self.dilation), self.groups)
+
+
+class ConvBiasReLUPool(nn.Conv2d):
+    """`nn.Conv2d` (with bias) followed by ReLU and `MaxPool2d(2, 2)`, with the convolution's
+    parameters and state dict.  On the fused path the pooling is folded into the bias + ReLU pass
+    in both directions, so the full-resolution activation is read once on the way forward and its
+    gradient is written once on the way back."""
+
+    def forward(self, x):
+        fusable = (self.bias is not None and not isinstance(self.padding, str) and self.padding_mode == "zeros"
+                   and x.dim() == 4 and _computes_in_bf16(x, self.weight)
+                   and _C.k_bias_relu_supported(1, self.out_channels))
+        if fusable:
+            # the convolution's output size decides whether the 2x2 windows tile it exactly
+            h = (x.shape[2] + 2 * self.padding[0] - self.dilation[0] * (self.kernel_size[0] - 1) - 1) // self.stride[0] + 1
+            w = (x.shape[3] + 2 * self.padding[1] - self.dilation[1] * (self.kernel_size[1] - 1) - 1) // self.stride[1] + 1
+            fusable = _C.k_maxpool2x2_supported(x.shape[0], h, w, self.out_channels)
+        if not fusable:
+            return F.max_pool2d(F.relu(super().forward(x)), 2, 2)
+        return _ConvBiasReLUPoolFn.apply(x, self.weight, self.bias, list(self.stride), list(self.padding),
+                                         list(self.dilation), self.groups)

@@ -114,6 +114,42 @@ int check_maxpool(int64_t N, int64_t H, int64_t W, int C, int blocks, std::mt199
          (std::memcmp(dx.data(), dx_want.data(), (size_t)nin * 16) != 0);
 }
 
+int check_bias_relu_pool(int64_t N, int64_t H, int64_t W, int C, int blocks, std::mt19937& rng) {
+  const int cgroups = C / 8;
+  const int64_t nin = N * H * W * cgroups, nout = N * (H / 2) * (W / 2) * cgroups;
+  Buf y((size_t)nin), p((size_t)nout), bias((size_t)cgroups), y_want, p_want((size_t)nout);
+  fill(y, rng, false);
+  fill(bias, rng, false);
+  y_want = y;
+  bias_relu_pool_bf16_host(raw(y_want), raw(p_want), raw(bias), N, H, W, C);
+  std::vector<std::vector<float>> smem((size_t)blocks, std::vector<float>((size_t)C));
+  launch(blocks, kThreads, [&] {
+    bias_relu_pool_body(reinterpret_cast<uint4*>(y.data()), reinterpret_cast<uint4*>(p.data()),
+                        reinterpret_cast<const __nv_bfloat16*>(raw(bias)), nout, H / 2, W / 2, W, cgroups,
+                        smem[hostemu::t_block_idx.x].data());
+  });
+  int bad = (std::memcmp(y.data(), y_want.data(), (size_t)nin * 16) != 0) +
+            (std::memcmp(p.data(), p_want.data(), (size_t)nout * 16) != 0);
+
+  Buf dp((size_t)nout), dz((size_t)nin), dz_want((size_t)nin);
+  fill(dp, rng, false);
+  for (auto& v : dz)
+    for (auto& h : v.h) h = 0x7fc0;  // every element must be overwritten
+  std::vector<float> db_want((size_t)C), db((size_t)C, -1.f), partial((size_t)blocks * (size_t)C, -1.f);
+  bias_relu_pool_backward_bf16_host(raw(dp), raw(y), raw(dz_want), db_want.data(), N, H, W, C);
+  std::vector<std::vector<float>> sacc((size_t)blocks, std::vector<float>((size_t)kThreads * 8));
+  launch(blocks, kThreads, [&] {
+    bias_relu_pool_backward_body(reinterpret_cast<const uint4*>(dp.data()), reinterpret_cast<const uint4*>(y.data()),
+                                 reinterpret_cast<uint4*>(dz.data()), partial.data(), N * (H / 2) * (W / 2), H / 2, W / 2,
+                                 W, cgroups, sacc[hostemu::t_block_idx.x].data());
+  });
+  launch((C + 127) / 128, 128, [&] { bias_grad_finish_body(partial.data(), db.data(), blocks, C); });
+  bad += std::memcmp(dz.data(), dz_want.data(), (size_t)nin * 16) != 0;
+  for (int c = 0; c < C; ++c)
+    if (std::fabs(db[(size_t)c] - db_want[(size_t)c]) > 1e-3f * (1.f + std::fabs(db_want[(size_t)c]))) ++bad;
+  return bad;
+}
+
 }  // namespace
 
 int main() {
@@ -143,6 +179,18 @@ int main() {
     if (bad)
       std::fprintf(stderr, "max-pool [%lld, %lld, %lld, %d] on %d blocks: mismatch\n", (long long)c.N, (long long)c.H,
                    (long long)c.W, c.C, c.blocks);
+    failures += bad != 0;
+    ++cases;
+  }
+  const struct {
+    int64_t N, H, W;
+    int C, blocks;
+  } bp[] = {{1, 2, 2, 8, 1}, {2, 6, 10, 64, 2}, {3, 8, 4, 128, 3}, {1, 14, 14, 512, 2}, {4, 4, 6, 16, 3}};
+  for (const auto& c : bp) {
+    const int bad = check_bias_relu_pool(c.N, c.H, c.W, c.C, c.blocks, rng);
+    if (bad)
+      std::fprintf(stderr, "bias+ReLU+pool [%lld, %lld, %lld, %d] on %d blocks: %d mismatches\n", (long long)c.N,
+                   (long long)c.H, (long long)c.W, c.C, c.blocks, bad);
     failures += bad != 0;
     ++cases;
   }

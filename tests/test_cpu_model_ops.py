@@ -82,6 +82,37 @@ def test_conv_bias_relu_function_matches_conv_plus_relu_on_cpu():
         assert (got.float() - ref).abs().max().item() <= 1e-2 * scale
 
 
+def test_conv_bias_relu_pool_function_on_cpu():
+    from bagua_core_b200.ops.fused_conv import ConvBiasReLU, ConvBiasReLUPool
+
+    torch.manual_seed(3)
+    pooled = ConvBiasReLUPool(16, 64, 3, padding=1).to(torch.bfloat16).to(memory_format=torch.channels_last)
+    single = ConvBiasReLU(16, 64, 3, padding=1).to(torch.bfloat16).to(memory_format=torch.channels_last)
+    single.load_state_dict(pooled.state_dict())
+    x = _cl(torch.randn(4, 16, 10, 12).to(torch.bfloat16))
+    xa = x.clone().requires_grad_(True)
+    pa = pooled(xa)
+    with torch.no_grad():
+        y = single(x)  # the same full-resolution activation the pooled block keeps for its backward
+    assert pa.shape == (4, 64, 5, 6) and torch.equal(pa, F.max_pool2d(y, 2, 2))
+    # backward against fp32 math on the block's own arg-max and ReLU masks
+    go = _cl(torch.randn_like(pa))
+    pa.backward(go)
+    yy = y.float().requires_grad_(True)
+    F.max_pool2d(yy, 2, 2).backward(go.float())
+    dz = torch.where(y > 0, yy.grad, torch.zeros_like(yy.grad))
+    refs = [torch.nn.grad.conv2d_input(x.shape, pooled.weight.detach().float(), dz, padding=1),
+            torch.nn.grad.conv2d_weight(x.float(), pooled.weight.shape, dz, padding=1),
+            dz.sum((0, 2, 3))]
+    for got, ref in zip([xa.grad, pooled.weight.grad, pooled.bias.grad], refs):
+        assert got.dtype == torch.bfloat16 and got.shape == ref.shape
+        scale = ref.abs().max().item() + 1e-6
+        assert (got.float() - ref).abs().max().item() <= 1e-2 * scale
+    # odd output sizes take the plain composition
+    x_odd = _cl(torch.randn(2, 16, 9, 9).to(torch.bfloat16))
+    assert torch.allclose(pooled(x_odd).float(), F.max_pool2d(single(x_odd), 2, 2).float(), rtol=2e-2, atol=2e-2)
+
+
 def test_fused_vgg16_matches_unfused_on_cpu_in_bf16():
     from bagua_core_b200.models import VGG16
 

@@ -133,3 +133,79 @@ def test_fused_vgg16_step_matches_unfused():
     for pa, pb in zip(a.parameters(), b.parameters()):
         scale = pb.grad.abs().max().item() + 1e-6
         assert (pa.grad - pb.grad).abs().max().item() <= 0.2 * scale  # ReLU masks flip here and there between two bf16 runs
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 2, 2), (2, 64, 6, 10), (4, 128, 28, 28), (32, 512, 14, 14), (8, 64, 56, 56)])
+def test_cuda_kernels_match_the_host_restatement_exactly(shape):
+    """Every model kernel on the GPU against the same binding on CPU tensors (plain loops)."""
+    import bagua_core_b200 as bb
+
+    C = bb._C
+    n, c, h, w = shape
+    g = torch.Generator().manual_seed(sum(shape))
+
+    def rnd(*s, relu=False):
+        t = (torch.randn(*s, generator=g) * 4).round() / 4
+        t = torch.relu(t) if relu else t
+        t = t.to(torch.bfloat16)
+        return t.contiguous(memory_format=torch.channels_last) if t.dim() == 4 else t
+
+    s = _stream()
+    # bias + ReLU
+    z, bias = rnd(n, c, h, w), rnd(c)
+    z_h, z_d = z.clone(), z.cuda()
+    C.k_bias_relu_(z_h, bias, 0)
+    C.k_bias_relu_(z_d, bias.cuda(), s)
+    assert torch.equal(z_d.cpu(), z_h)
+    dy = rnd(n, c, h, w)
+    dz_h, db_h = torch.empty_like(dy), torch.empty(c)
+    dz_d, db_d = torch.empty_like(dy).cuda(), torch.empty(c, device="cuda")
+    C.k_bias_relu_backward(dy, z_h, dz_h, db_h, 0)
+    C.k_bias_relu_backward(dy.cuda(), z_d, dz_d, db_d, s)
+    assert torch.equal(dz_d.cpu(), dz_h)
+    assert torch.allclose(db_d.cpu(), db_h, rtol=1e-4, atol=1e-2)
+    # max pooling
+    x = rnd(n, c, h, w, relu=True)
+    y_h = torch.empty((n, c, h // 2, w // 2), dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    y_d = y_h.cuda()
+    C.k_maxpool2x2_forward(x, y_h, 0)
+    C.k_maxpool2x2_forward(x.cuda(), y_d, s)
+    assert torch.equal(y_d.cpu(), y_h)
+    gy = rnd(n, c, h // 2, w // 2)
+    dx_h, dx_d = torch.empty_like(x), torch.empty_like(x).cuda()
+    C.k_maxpool2x2_backward(x, gy, dx_h, 0)
+    C.k_maxpool2x2_backward(x.cuda(), gy.cuda(), dx_d, s)
+    assert torch.equal(dx_d.cpu(), dx_h)
+    # bias + ReLU + pooling in one pass
+    a_h, a_d = z.clone(), z.cuda()
+    p_h, p_d = torch.empty_like(y_h), torch.empty_like(y_h).cuda()
+    C.k_bias_relu_pool_(a_h, p_h, bias, 0)
+    C.k_bias_relu_pool_(a_d, p_d, bias.cuda(), s)
+    assert torch.equal(a_d.cpu(), a_h) and torch.equal(p_d.cpu(), p_h)
+    dzp_h, dbp_h = torch.empty_like(z), torch.empty(c)
+    dzp_d, dbp_d = torch.empty_like(z).cuda(), torch.empty(c, device="cuda")
+    C.k_bias_relu_pool_backward(gy, a_h, dzp_h, dbp_h, 0)
+    C.k_bias_relu_pool_backward(gy.cuda(), a_d, dzp_d, dbp_d, s)
+    assert torch.equal(dzp_d.cpu(), dzp_h)
+    assert torch.allclose(dbp_d.cpu(), dbp_h, rtol=1e-4, atol=1e-2)
+
+
+def test_conv_bias_relu_pool_module_matches_the_composition_under_autocast():
+    from bagua_core_b200.ops.fused_conv import ConvBiasReLU, ConvBiasReLUPool
+
+    torch.manual_seed(0)
+    pooled = ConvBiasReLUPool(16, 64, 3, padding=1).cuda().to(memory_format=torch.channels_last)
+    single = ConvBiasReLU(16, 64, 3, padding=1).cuda().to(memory_format=torch.channels_last)
+    single.load_state_dict(pooled.state_dict())
+    x = torch.randn(8, 16, 20, 24, device="cuda").contiguous(memory_format=torch.channels_last)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        pa = pooled(xa)
+        pb = torch.nn.functional.max_pool2d(single(xb), 2, 2)
+    assert torch.allclose(pa.float(), pb.float(), rtol=2e-2, atol=2e-2)  # same math; the library may pick another conv algorithm
+    go = torch.randn_like(pa)
+    pa.backward(go)
+    pb.backward(go)
+    for a, b in [(xa.grad, xb.grad), (pooled.weight.grad, single.weight.grad), (pooled.bias.grad, single.bias.grad)]:
+        scale = b.abs().max().item() + 1e-6
+        assert (a - b).abs().max().item() <= 6e-2 * scale  # masks agree except where two conv algorithms round apart
