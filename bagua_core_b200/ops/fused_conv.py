@@ -45,7 +45,6 @@ class _ConvBiasReLUFn(torch.autograd.Function):
         _C.k_bias_relu_(z, bias.contiguous(), _stream(z))
         _count(1)
         ctx.save_for_backward(x, weight, z)
-        ctx.bias_dtype = bias.dtype
         return z
 
     @staticmethod
@@ -61,7 +60,7 @@ class _ConvBiasReLUFn(torch.autograd.Function):
         dx, dw, _ = torch.ops.aten.convolution_backward(
             dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
             [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
-        return dx, dw, db.to(ctx.bias_dtype), None, None, None, None
+        return dx, dw, db, None, None, None, None  # fp32; autograd casts it to the bias parameter's dtype
 
 
 class _ConvBiasReLUPoolFn(torch.autograd.Function):
@@ -80,7 +79,6 @@ class _ConvBiasReLUPoolFn(torch.autograd.Function):
         _C.k_bias_relu_pool_(y, p, bias.contiguous(), _stream(y))
         _count(1)
         ctx.save_for_backward(x, weight, y)
-        ctx.bias_dtype = bias.dtype
         return p
 
     @staticmethod
@@ -96,7 +94,7 @@ class _ConvBiasReLUPoolFn(torch.autograd.Function):
         dx, dw, _ = torch.ops.aten.convolution_backward(
             dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
             [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
-        return dx, dw, db.to(ctx.bias_dtype), None, None, None, None
+        return dx, dw, db, None, None, None, None  # fp32; autograd casts it to the bias parameter's dtype
 
 
 class _MaxPool2x2Fn(torch.autograd.Function):
