@@ -32,23 +32,34 @@ def _count(n: int) -> None:
     launches += n
 
 
+def _autocast_inputs(*tensors):
+    """What an autocast-aware op does with its inputs: inside an autocast region of the tensors'
+    device, floating-point inputs are cast to the region's dtype; elsewhere they pass through."""
+    dev = tensors[0].device.type
+    if not torch.is_autocast_enabled(dev):
+        return tensors
+    dtype = torch.get_autocast_dtype(dev)
+    return tuple(t.to(dtype) if t.is_floating_point() else t for t in tensors)
+
+
 class _ConvBiasReLUFn(torch.autograd.Function):
-    """Inputs arrive as bf16 (cast by autocast where it is on)."""
+    """Runs in the autocast dtype where autocast is on (parameters stay fp32 outside; autograd
+    casts the gradients returned here back to the parameters' dtype)."""
 
     @staticmethod
-    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
     def forward(ctx, x, weight, bias, stride, padding, dilation, groups):
         ctx.conf = (stride, padding, dilation, groups)
-        x = x.contiguous(memory_format=torch.channels_last)
-        z = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)
-        z = z.contiguous(memory_format=torch.channels_last)
+        x, weight, bias = _autocast_inputs(x, weight, bias)
+        with torch.autocast(x.device.type, enabled=False):
+            x = x.contiguous(memory_format=torch.channels_last)
+            z = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)
+            z = z.contiguous(memory_format=torch.channels_last)
         _C.k_bias_relu_(z, bias.contiguous(), _stream(z))
         _count(1)
         ctx.save_for_backward(x, weight, z)
         return z
 
     @staticmethod
-    @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, dy):
         stride, padding, dilation, groups = ctx.conf
         x, weight, y = ctx.saved_tensors
@@ -57,9 +68,10 @@ class _ConvBiasReLUFn(torch.autograd.Function):
         db = torch.empty(weight.shape[0], dtype=torch.float32, device=y.device)
         _C.k_bias_relu_backward(dy, y, dz, db, _stream(y))
         _count(2)  # mask + partial sums, then the fold of the partial sums
-        dx, dw, _ = torch.ops.aten.convolution_backward(
-            dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
-            [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        with torch.autocast(y.device.type, enabled=False):
+            dx, dw, _ = torch.ops.aten.convolution_backward(
+                dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
+                [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
         return dx, dw, db, None, None, None, None  # fp32; autograd casts it to the bias parameter's dtype
 
 
@@ -68,12 +80,13 @@ class _ConvBiasReLUPoolFn(torch.autograd.Function):
     backward, which produces the convolution's output gradient and the bias gradient in one pass."""
 
     @staticmethod
-    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
     def forward(ctx, x, weight, bias, stride, padding, dilation, groups):
         ctx.conf = (stride, padding, dilation, groups)
-        x = x.contiguous(memory_format=torch.channels_last)
-        y = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)
-        y = y.contiguous(memory_format=torch.channels_last)
+        x, weight, bias = _autocast_inputs(x, weight, bias)
+        with torch.autocast(x.device.type, enabled=False):
+            x = x.contiguous(memory_format=torch.channels_last)
+            y = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)
+            y = y.contiguous(memory_format=torch.channels_last)
         n, c, h, w = y.shape
         p = torch.empty((n, c, h // 2, w // 2), dtype=y.dtype, device=y.device, memory_format=torch.channels_last)
         _C.k_bias_relu_pool_(y, p, bias.contiguous(), _stream(y))
@@ -82,7 +95,6 @@ class _ConvBiasReLUPoolFn(torch.autograd.Function):
         return p
 
     @staticmethod
-    @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, dp):
         stride, padding, dilation, groups = ctx.conf
         x, weight, y = ctx.saved_tensors
@@ -91,9 +103,10 @@ class _ConvBiasReLUPoolFn(torch.autograd.Function):
         db = torch.empty(weight.shape[0], dtype=torch.float32, device=y.device)
         _C.k_bias_relu_pool_backward(dp, y, dz, db, _stream(y))
         _count(2)
-        dx, dw, _ = torch.ops.aten.convolution_backward(
-            dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
-            [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        with torch.autocast(y.device.type, enabled=False):
+            dx, dw, _ = torch.ops.aten.convolution_backward(
+                dz, x, weight, None, stride, padding, dilation, False, [0, 0], groups,
+                [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
         return dx, dw, db, None, None, None, None  # fp32; autograd casts it to the bias parameter's dtype
 
 
@@ -131,8 +144,8 @@ class MaxPool2x2(nn.Module):
 
 
 def _computes_in_bf16(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    if x.is_cuda and torch.is_autocast_enabled("cuda"):
-        return torch.get_autocast_dtype("cuda") == torch.bfloat16
+    if torch.is_autocast_enabled(x.device.type):
+        return torch.get_autocast_dtype(x.device.type) == torch.bfloat16
     return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
 
 

@@ -137,3 +137,31 @@ def test_fused_vgg16_matches_unfused_on_cpu_in_bf16():
             assert (pa.grad.float() - pb.grad.float()).abs().max().item() <= 0.15 * scale + 1e-6
             checked += 1
     assert checked >= 20
+
+
+def test_fused_blocks_under_cpu_autocast_keep_fp32_parameters_and_gradients():
+    """The benchmark's configuration, on the CPU: fp32 parameters and inputs inside a bf16 autocast
+    region.  The blocks compute in bf16; weight, bias and input gradients come back in fp32."""
+    from bagua_core_b200.ops.fused_conv import ConvBiasReLU, ConvBiasReLUPool
+
+    torch.manual_seed(5)
+    for cls, pool in ((ConvBiasReLU, False), (ConvBiasReLUPool, True)):
+        fused = cls(8, 32, 3, padding=1).to(memory_format=torch.channels_last)
+        plain = torch.nn.Conv2d(8, 32, 3, padding=1).to(memory_format=torch.channels_last)
+        plain.load_state_dict(fused.state_dict())
+        x = _cl(torch.randn(2, 8, 8, 8))
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        with torch.autocast("cpu", dtype=torch.bfloat16):
+            ya = fused(xa)
+            yb = torch.relu(plain(xb))
+            if pool:
+                yb = F.max_pool2d(yb, 2, 2)
+        assert ya.dtype == torch.bfloat16 and ya.shape == yb.shape
+        assert torch.allclose(ya.float(), yb.float(), rtol=3e-2, atol=3e-2)
+        go = torch.randn_like(ya)
+        ya.backward(go)
+        yb.backward(go)
+        for a, b in [(xa.grad, xb.grad), (fused.weight.grad, plain.weight.grad), (fused.bias.grad, plain.bias.grad)]:
+            assert a.dtype == torch.float32 and a.shape == b.shape
+            scale = b.abs().max().item() + 1e-6
+            assert (a - b).abs().max().item() <= 0.15 * scale  # bf16 math and a few flipped ReLU masks
