@@ -17,6 +17,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import bagua_core_b200.parallel as P  # noqa: E402
 from bagua_core_b200 import models  # noqa: E402
+from bagua_core_b200.utils import DevicePrefetcher, LaggedScalarReader  # noqa: E402
 
 
 def main():
@@ -55,15 +56,29 @@ def main():
         }[args.algorithm]()
     model = P.with_bagua(model, [opt], algo)
     g = torch.Generator().manual_seed(pg.rank)
+
+    def host_batch():
+        x = torch.randn(args.batch, *shape, generator=g)
+        y = torch.randint(0, classes, (args.batch,), generator=g)
+        return (x.pin_memory(), y.pin_memory()) if dev.type == "cuda" else (x, y)
+
+    # the next batch is copied on a side stream while this step computes; each loss is read one step
+    # late, so the launch thread never waits for the GPU
+    prefetch, losses = DevicePrefetcher(dev, channels_last=False), LaggedScalarReader(dev)
+    prefetch.put(*host_batch())
     for step in range(args.steps):
-        x = torch.randn(args.batch, *shape, generator=g).to(dev)
-        y = torch.randint(0, classes, (args.batch,), generator=g).to(dev)
+        x, y = prefetch.get()
+        if step + 1 < args.steps:
+            prefetch.put(*host_batch())
         opt.zero_grad(set_to_none=False)
         loss = torch.nn.functional.cross_entropy(model(x), y)
         loss.backward()
         opt.step()
-        if pg.rank == 0:
-            print(f"step {step}: loss {loss.item():.4f}")
+        previous = losses.push(loss)
+        if pg.rank == 0 and previous is not None:
+            print(f"step {step - 1}: loss {previous:.4f}")
+    if pg.rank == 0:
+        print(f"step {args.steps - 1}: loss {losses.flush():.4f}")
     if hasattr(algo, "abort"):
         algo.abort(model)
     P.destroy_process_group()
