@@ -6,7 +6,7 @@ kernels versus the library (NCCL) path that replays the reference's call sequenc
         --master-port 29521 benchmarks/comm_sweep.py --out sweep_8gpu.json
 
 Ops: gradient_allreduce (O1, average), bytegrad (O2), shift_one (O3 pair average),
-lp_ring (O4), each on one fp32 bucket of 1 KB … 1 GB (powers of 4), values N(0,1) from
+lp_ring (O4), qadam (the compressed all-reduce of a momentum buffer: the same op as bytegrad), each on one fp32 bucket of 1 KB … 1 GB (powers of 4), values N(0,1) from
 seed=rank.  Every op runs through the public bucket API (`BaguaBucketPy.append_*_op`,
 `mark_communication_ready`, `wait_pending_comm_ops`).  Timing: CUDA events on the
 communication stream around `iters` back-to-back buckets after `warmup`, an L2 flush
@@ -44,7 +44,7 @@ from bagua_core_b200.utils import flush_l2  # noqa: E402
 def wire_bytes(op, S, N):
     if op in ("gradient_allreduce", "raw_nccl"):
         return 2 * (N - 1) / N * S
-    if op == "bytegrad":
+    if op in ("bytegrad", "qadam"):
         return 2 * (N - 1) / N * (S / 4 + 32 * N)
     if op == "shift_one":
         return S
@@ -142,7 +142,9 @@ def main():
                 if op == "gradient_allreduce":
                     bucket.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True,
                                                              scattergather=False)
-                elif op == "bytegrad":
+                elif op in ("bytegrad", "qadam"):
+                    # QAdam's compression phase all-reduces the momentum buffer with the same compressed
+                    # op that ByteGrad applies to gradients
                     bucket.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True,
                                                              scattergather=True, compression="MinMaxUInt8")
                 elif op == "shift_one":
