@@ -6,8 +6,8 @@ kernels versus the library (NCCL) path that replays the reference's call sequenc
         --master-port 29521 benchmarks/comm_sweep.py --out sweep_8gpu.json
 
 Ops: gradient_allreduce (O1, average), bytegrad (O2), shift_one (O3 pair average),
-lp_ring (O4), qadam (the compressed all-reduce of a momentum buffer: the same op as bytegrad), each on one fp32 bucket of 1 KB … 1 GB (powers of 4), values N(0,1) from
-seed=rank.  Every op runs through the public bucket API (`BaguaBucketPy.append_*_op`,
+lp_ring (O4), qadam (the compressed all-reduce of a momentum buffer: the same op as
+bytegrad), each on one fp32 bucket of 1 KB … 1 GB (powers of 4), values N(0,1) from seed=rank.  Every op runs through the public bucket API (`BaguaBucketPy.append_*_op`,
 `mark_communication_ready`, `wait_pending_comm_ops`).  Timing: CUDA events on the
 communication stream around `iters` back-to-back buckets after `warmup`, an L2 flush
 (192 MB memset) before each timed batch, max over ranks.  `raw_nccl` is a bare
