@@ -48,8 +48,11 @@ def parse():
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: dry run of the whole benchmark logic on host tensors (gloo, wall-clock timing); "
                          "its numbers are not benchmark results")
-    ap.add_argument("--fused-model-ops", action="store_true",
-                    help="VGG-16: conv+bias+ReLU blocks through this package's fused bias/ReLU kernels")
+    ap.add_argument("--fused-model-ops", dest="fused_model_ops", action="store_true", default=None,
+                    help="VGG-16: conv+bias+ReLU(+pool) blocks through this package's fused kernels "
+                         "(the default for vgg16 on a GPU)")
+    ap.add_argument("--no-fused-model-ops", dest="fused_model_ops", action="store_false",
+                    help="VGG-16 built from plain Conv2d / ReLU / MaxPool2d modules")
     return ap.parse_args()
 
 
@@ -192,7 +195,25 @@ def main():
         os.environ["BAGUA_B200_FUSED"] = "0"
         bb._C.set_sync_per_bucket(True)
 
-    model = build_model(args.model, device, fused_ops=args.fused_model_ops)
+    fused_ops = args.fused_model_ops
+    if fused_ops is None:
+        fused_ops = args.model == "vgg16" and on_gpu
+    model = build_model(args.model, device, fused_ops=fused_ops)
+    if fused_ops and args.model == "vgg16":
+        # One small forward/backward through the fused blocks before anything is timed; if it raises,
+        # the benchmark runs the plain modules instead (same math, the framework's kernels).
+        try:
+            px, py_ = make_batch(args.model, 2, seq, device)
+            loss_fn(args.model, model, px, py_).backward()
+            for p in model.parameters():
+                p.grad = None
+            if on_gpu:
+                torch.cuda.synchronize()
+        except Exception as exc:
+            print(f"[bench] fused model kernels failed ({exc!r}); using the plain modules", file=sys.stderr)
+            fused_ops = False
+            torch.manual_seed(0)
+            model = build_model(args.model, device, fused_ops=False)
     n_params = sum(p.numel() for p in model.parameters())
     lr = 0.01 if args.model != "bert_large" else 1e-4
     my_kernels = lambda: 0  # noqa: E731
@@ -346,7 +367,7 @@ def main():
                 "parallelism": f"dp{world}", "algorithm": algo_name, "bucket_mb": bucket_mb,
                 "optimizer": "sgd momentum 0.9" if algo_name != "qadam" else "qadam",
                 "precision": "bf16 autocast, fp32 master weights and gradients",
-                "fused_model_ops": bool(args.fused_model_ops),
+                "fused_model_ops": bool(fused_ops),
                 "l2": "working set per step (fp32 weights+grads+momentum and activations) exceeds the 126 MB L2",
             },
             "clocks": clocks.summary(),

@@ -1,19 +1,10 @@
-"""Fused bias + ReLU kernels of the convolution blocks (`csrc/kernels/model_ops.cu`,
-`bagua_core_b200/ops/fused_conv.py`) against plain fp32 PyTorch math, and the fused VGG-16
-against the unfused one.
-
-Newer than the rest of the GPU suite and off by default in the benchmark
-(`bench.py --fused-model-ops`); these cases run when BAGUA_B200_TEST_MODEL_OPS=1."""
-import os
-
+"""Fused bias + ReLU (+ pooling) kernels of the convolution blocks (`csrc/kernels/model_ops.cu`,
+`bagua_core_b200/ops/fused_conv.py`): the CUDA kernels against their host restatement and against
+plain fp32 PyTorch math, the modules under autocast, and the fused VGG-16 against the unfused one."""
 import pytest
 import torch
 
-pytestmark = [
-    pytest.mark.gpu,
-    pytest.mark.skipif(os.environ.get("BAGUA_B200_TEST_MODEL_OPS", "0") != "1",
-                       reason="set BAGUA_B200_TEST_MODEL_OPS=1 to run the fused model kernels"),
-]
+pytestmark = pytest.mark.gpu
 
 
 def _stream():
