@@ -466,8 +466,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     d["pulls"] = s.pulls;
     d["bytes_reserved"] = s.bytes_reserved;
     d["bytes_in_use"] = s.bytes_in_use;
+    d["guard_violations"] = s.guard_violations;
     return d;
   });
+  m.def("pool_set_guard", [](bool on) { MemoryPool::set_guard(on); }, py::arg("on"),
+        "Guard regions around pool blocks allocated from now on (also: BAGUA_B200_POOL_GUARD=1).");
+  m.def("pool_guard", []() { return MemoryPool::guard(); });
+  m.def("pool_check_guards", [](int device) { return MemoryPool::for_device(device).check_guards(); }, py::arg("device"),
+        "Number of pool blocks on `device` (-1: host) whose guard regions were overwritten; synchronises the device.");
   m.def("pool_size_class", [](size_t bytes) { return MemoryPool::size_class(bytes); });
   m.def("pool_release_cached", [](int device) { MemoryPool::for_device(device).release_cached(); });
   m.def("shift_one_peer", &shift_one_peer, py::arg("rank"), py::arg("nranks"), py::arg("step"));

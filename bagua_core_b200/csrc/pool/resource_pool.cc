@@ -2,7 +2,32 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 namespace bagua {
+
+namespace {
+std::atomic<int> g_guard{-1};  // -1: not decided yet (environment), 0 / 1
+
+// Offset of the first byte of `p[0..n)` that is not the guard pattern, or -1.
+long first_damaged(const unsigned char* p, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    if (p[i] != MemoryPool::kGuardPattern) return (long)i;
+  return -1;
+}
+}  // namespace
+
+void MemoryPool::set_guard(bool on) { g_guard.store(on ? 1 : 0); }
+bool MemoryPool::guard() {
+  int g = g_guard.load();
+  if (g < 0) {
+    g = env_long("BAGUA_B200_POOL_GUARD", 0) != 0 ? 1 : 0;
+    int expected = -1;
+    g_guard.compare_exchange_strong(expected, g);
+    g = g_guard.load();
+  }
+  return g == 1;
+}
 
 void log_write(LogLevel l, const char* file, int line, const std::string& msg) {
   static const char* names[] = {"TRACE", "DEBUG", "INFO", "WARN", "ERROR", "OFF"};
@@ -45,15 +70,21 @@ std::shared_ptr<PoolBlock> MemoryPool::pull(size_t bytes, uint64_t tag) {
     }
   }
   if (!ptr) {
+    const bool guarded = guard();
+    const size_t raw = cls + (guarded ? 2 * kGuardBytes : 0);
     if (device_ >= 0) {
       int prev = -1;
       cudaGetDevice(&prev);
       if (prev != device_) cudaSetDevice(device_);
-      cudaError_t e = cudaMalloc(&ptr, cls);
+      cudaError_t e = cudaMalloc(&ptr, raw);
       if (e != cudaSuccess) {
         // give cached blocks back to the device and retry once
         release_cached();
-        e = cudaMalloc(&ptr, cls);
+        e = cudaMalloc(&ptr, raw);
+      }
+      if (e == cudaSuccess && guarded) {
+        cudaMemset(ptr, kGuardPattern, kGuardBytes);
+        e = cudaMemset(static_cast<char*>(ptr) + kGuardBytes + cls, kGuardPattern, kGuardBytes);
       }
       if (prev >= 0 && prev != device_) cudaSetDevice(prev);
       if (e != cudaSuccess) {
@@ -62,10 +93,18 @@ std::shared_ptr<PoolBlock> MemoryPool::pull(size_t bytes, uint64_t tag) {
                                                  std::to_string(device_) + " failed: " + cudaGetErrorString(e));
       }
     } else {
-      ptr = std::aligned_alloc(256, align_up(cls, 256));
+      ptr = std::aligned_alloc(256, align_up(raw, 256));
       if (!ptr) throw BaguaError(ErrorKind::MemPool, "host allocation of " + std::to_string(cls) + " bytes failed");
+      if (guarded) {
+        std::memset(ptr, kGuardPattern, kGuardBytes);
+        std::memset(static_cast<char*>(ptr) + kGuardBytes + cls, kGuardPattern, kGuardBytes);
+      }
     }
     std::lock_guard<std::mutex> g(mu_);
+    if (guarded) {
+      ptr = static_cast<char*>(ptr) + kGuardBytes;  // still 256-byte aligned
+      guarded_[ptr] = cls;
+    }
     stats_.device_allocs++;
     stats_.bytes_reserved += cls;
   }
@@ -78,6 +117,15 @@ std::shared_ptr<PoolBlock> MemoryPool::pull(size_t bytes, uint64_t tag) {
 
 void MemoryPool::give_back(void* ptr, size_t cls, uint64_t tag) {
   std::lock_guard<std::mutex> g(mu_);
+  if (device_ < 0 && guarded_.count(ptr)) {
+    // host memory can be looked at right away: a block is checked every time it comes back
+    const unsigned char* p = static_cast<const unsigned char*>(ptr);
+    if ((first_damaged(p - kGuardBytes, kGuardBytes) >= 0 || first_damaged(p + cls, kGuardBytes) >= 0) &&
+        reported_.insert(ptr).second) {
+      stats_.guard_violations++;
+      BAGUA_LOG(Error, "host pool block of " << cls << " bytes came back with an overwritten guard region");
+    }
+  }
   free_[{cls, tag}].push_back(ptr);
   stats_.bytes_in_use -= cls;
 }
@@ -87,7 +135,14 @@ void MemoryPool::release_cached() {
   {
     std::lock_guard<std::mutex> g(mu_);
     taken.swap(free_);
-    for (auto& kv : taken) stats_.bytes_reserved -= kv.first.first * kv.second.size();
+    for (auto& kv : taken) {
+      stats_.bytes_reserved -= kv.first.first * kv.second.size();
+      for (void*& p : kv.second)
+        if (guarded_.erase(p)) {  // the allocation starts at the front guard
+          reported_.erase(p);
+          p = static_cast<char*>(p) - kGuardBytes;
+        }
+    }
   }
   for (auto& kv : taken)
     for (void* p : kv.second) {
@@ -102,6 +157,46 @@ MemoryPool::~MemoryPool() {
   // Device memory is reclaimed by the driver at process exit; calling cudaFree from a
   // static destructor can run after the runtime has shut down.
   if (device_ < 0) release_cached();
+}
+
+size_t MemoryPool::check_guards() {
+  std::vector<std::pair<void*, size_t>> blocks;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    blocks.assign(guarded_.begin(), guarded_.end());
+  }
+  if (blocks.empty()) return 0;
+  int prev = -1;
+  if (device_ >= 0) {
+    cudaGetDevice(&prev);
+    if (prev != device_) cudaSetDevice(device_);
+    BAGUA_CUDA_CHECK(cudaDeviceSynchronize());
+  }
+  size_t damaged = 0;
+  unsigned char front[kGuardBytes], back[kGuardBytes];
+  for (auto& [ptr, cls] : blocks) {
+    const unsigned char* f = static_cast<const unsigned char*>(ptr) - kGuardBytes;
+    const unsigned char* b = static_cast<const unsigned char*>(ptr) + cls;
+    if (device_ >= 0) {
+      BAGUA_CUDA_CHECK(cudaMemcpy(front, f, kGuardBytes, cudaMemcpyDeviceToHost));
+      BAGUA_CUDA_CHECK(cudaMemcpy(back, b, kGuardBytes, cudaMemcpyDeviceToHost));
+      f = front;
+      b = back;
+    }
+    const long bad_front = first_damaged(f, kGuardBytes), bad_back = first_damaged(b, kGuardBytes);
+    if (bad_front < 0 && bad_back < 0) continue;
+    ++damaged;
+    std::lock_guard<std::mutex> g(mu_);
+    if (reported_.insert(ptr).second) {
+      stats_.guard_violations++;
+      BAGUA_LOG(Error, "pool block of " << cls << " bytes on device " << device_ << ": guard region overwritten "
+                                        << (bad_front >= 0 ? "before the block, " : "behind the block, ")
+                                        << (bad_front >= 0 ? (long)kGuardBytes - bad_front : bad_back)
+                                        << (bad_front >= 0 ? " bytes in front of its start" : " bytes past its capacity"));
+    }
+  }
+  if (device_ >= 0 && prev >= 0 && prev != device_) cudaSetDevice(prev);
+  return damaged;
 }
 
 PoolStats MemoryPool::stats() const {

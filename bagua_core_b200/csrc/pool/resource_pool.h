@@ -4,6 +4,10 @@
 // block returns to its class's free list instead of `cudaFree` (allocation on the
 // communication path must never synchronise the device).  Device index -1 is host
 // memory for the CPU backend.  Events: created with cudaEventDisableTiming and recycled.
+// With guards on (BAGUA_B200_POOL_GUARD=1 or set_guard(true)) every new block gets 256 bytes
+// of a fixed pattern in front of it and behind its capacity; check_guards() reports blocks
+// whose pattern was overwritten (the memory checker of the GPU pool being closed to tools,
+// this is how an out-of-range store of a kernel into pool memory is found after a test).
 // A lease owns its resource until destroyed — the reference copies the raw event out of
 // a pool guard that is dropped at once (bagua-core-internal/src/comm_ops/
 // decentralized_full_precision_asynchronous.rs:78,107), which this design rules out.
@@ -15,6 +19,7 @@
 
 #include <array>
 #include <map>
+#include <set>
 
 #include "../common.h"
 
@@ -46,6 +51,7 @@ struct PoolStats {
   uint64_t pulls = 0;           // leases handed out
   uint64_t bytes_reserved = 0;  // currently held from the device
   uint64_t bytes_in_use = 0;
+  uint64_t guard_violations = 0;  // blocks found with an overwritten guard region so far
 };
 
 class MemoryPool {
@@ -69,6 +75,17 @@ class MemoryPool {
   // device in [-1, kMaxDevices)
   static MemoryPool& for_device(int device);
 
+  // Guard regions around blocks allocated from now on (all pools).
+  static constexpr size_t kGuardBytes = 256;
+  static constexpr unsigned char kGuardPattern = 0xC5;
+  static void set_guard(bool on);
+  static bool guard();
+  // Checks the guard regions of every guarded block, leased or cached, and returns how many
+  // are damaged (each is logged once with the offset of its first damaged byte and counted in
+  // stats().guard_violations).  For a device pool this synchronises the device: call it
+  // between steps, not while a stream is being captured.
+  size_t check_guards();
+
  private:
   friend class PoolBlock;
   void give_back(void* ptr, size_t cls, uint64_t tag);
@@ -76,6 +93,8 @@ class MemoryPool {
   const int device_;
   mutable std::mutex mu_;
   std::map<std::pair<size_t, uint64_t>, std::vector<void*>> free_;
+  std::map<void*, size_t> guarded_;  // block -> capacity, for blocks that have guard regions
+  std::set<void*> reported_;         // guarded blocks already reported as damaged
   PoolStats stats_;
 };
 

@@ -434,6 +434,39 @@ uint64_t verify(World& w, int me, uint32_t k) {
     }
     default: break;
   }
+
+  // Stray stores: `out` was poisoned before the op, so everything past the op's output must
+  // still be poison; and an op that is not in place must leave its input as it was.
+  int64_t out_extent = 0, in_extent = 0;
+  switch (op.kind) {
+    case Kind::AllGather:
+    case Kind::AllGatherSym: out_extent = c * N, in_extent = c; break;
+    case Kind::AllGatherInPlace:
+    case Kind::AllToAllInPlace: out_extent = c * N; break;
+    case Kind::AllToAll:
+    case Kind::AllToAllSym: out_extent = c * N, in_extent = c * N; break;
+    case Kind::ReduceScatter:
+    case Kind::ReduceScatterSym: out_extent = c, in_extent = c * N; break;
+    case Kind::BroadcastDirect:
+    case Kind::BroadcastTwoPhase: out_extent = c; break;
+    case Kind::Scatter: out_extent = c, in_extent = me == op.root ? c * N : 0; break;
+    case Kind::Gather: out_extent = me == op.root ? c * N : 0, in_extent = c; break;
+    case Kind::ReduceDirect:
+    case Kind::ReduceTwoPhase: out_extent = me == op.root ? c : 0, in_extent = c; break;
+    case Kind::AllReduceOneShot:
+    case Kind::AllReduceTwoShot:
+    case Kind::AllReduceSym:
+    case Kind::PairAverage:
+    case Kind::PairAverageSym: out_extent = c, in_extent = c; break;
+    case Kind::AllReduceTwoShotInPlace:
+    case Kind::AllReduceNvls: out_extent = c; break;
+    default: break;  // ReduceScatterInPlace, ByteGrad, LpRing, Barrier: `out` is not touched
+  }
+  for (int64_t i = out_extent; i < (int64_t)r.out.size(); ++i) expect(r.out, i, -12345.0f, -12345.0f, -12345.0f, -12345.0f);
+  for (int64_t i = 0; i < in_extent; ++i) {
+    val4(me, i, e);
+    expect(r.in, i, e[0], e[1], e[2], e[3]);
+  }
   return bad;
 }
 

@@ -39,17 +39,33 @@ def _from_np(o):
     return o
 
 
+def _check_pool_guards(device):
+    """Every scratch block the engine took from its pools on this rank still has intact guard regions."""
+    import bagua_core_b200 as bb
+
+    damaged = bb._C.pool_check_guards(device)
+    seen = bb._C.pool_stats(device)["guard_violations"]
+    if damaged or seen:
+        raise RuntimeError(f"pool guard regions overwritten on device {device}: {damaged} now, {seen} in total")
+
+
 def _entry(rank, world, port, backend, fn, args, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["RANK"] = str(rank)
     os.environ["LOCAL_RANK"] = str(rank)
     os.environ["WORLD_SIZE"] = str(world)
+    # CPU ranks always run with guard regions around the engine's pool blocks; GPU ranks when asked to
+    guard = backend == "gloo" or os.environ.get("BAGUA_B200_POOL_GUARD") == "1"
+    if guard:
+        os.environ["BAGUA_B200_POOL_GUARD"] = "1"
     try:
         if backend == "nccl":
             torch.cuda.set_device(rank)
         dist.init_process_group(backend, rank=rank, world_size=world)
         out = fn(rank, world, *args)
+        if guard:
+            _check_pool_guards(rank if backend == "nccl" else -1)
         q.put((rank, "ok", _to_np(out)))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))

@@ -73,9 +73,21 @@ def test_device_bodies_are_race_free_under_thread_sanitizer(tmp_path):
         assert "WARNING: ThreadSanitizer" not in out, out[-3000:]
 
 
-def test_model_op_kernels_match_the_host_restatement(tmp_path):
+def test_device_bodies_stay_in_bounds_under_address_sanitizer(tmp_path):
+    """The memory checker for device code that needs no GPU: every buffer of the emulation is a heap
+    block of its own, so a load or store of a body outside staging, input or output is reported.  (Stores
+    inside a buffer but outside the op's extent are caught by the poison check of every run.)"""
+    exe = _build(tmp_path, "address")
+    for nranks, blocks, ops, seed in [(2, 1, 80, 11), (4, 2, 80, 12), (8, 2, 60, 13)]:
+        out = _run(exe, nranks, blocks, ops, seed)
+        assert "ERROR: AddressSanitizer" not in out, out[-3000:]
+
+
+@pytest.mark.parametrize("sanitizer", [None, "address"])
+def test_model_op_kernels_match_the_host_restatement(tmp_path, sanitizer):
     """The fused bias+ReLU and max-pool kernels (`csrc/kernels/model_ops_bodies.cuh`), run thread for
-    thread on grids of a few blocks of 256 threads, against `csrc/kernels/model_ops_cpu.cc`."""
+    thread on grids of a few blocks of 256 threads, against `csrc/kernels/model_ops_cpu.cc`; the second
+    build runs them under AddressSanitizer (every tensor is a heap block of exactly its size)."""
     gxx = shutil.which("g++")
     if gxx is None or not os.path.exists(os.path.join(CUDA_INC, "cuda_runtime.h")):
         pytest.skip("needs g++ and the CUDA headers")
@@ -83,7 +95,12 @@ def test_model_op_kernels_match_the_host_restatement(tmp_path):
     cmd = [gxx, "-std=c++20", "-O1", "-g", "-fno-strict-aliasing", "-DBAGUA_HOST_EMULATION", "-I", CSRC, "-I", CUDA_INC,
            os.path.join(ROOT, "tests", "cpp", "model_ops_emulation.cc"), os.path.join(CSRC, "kernels", "model_ops_cpu.cc"),
            "-o", exe, "-lpthread"]
+    if sanitizer:
+        cmd[1:1] = [f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
     build = subprocess.run(cmd, capture_output=True, text=True)
+    if build.returncode != 0 and "sanitize" in build.stderr and "cannot find" in build.stderr:
+        pytest.skip("sanitizer runtime not installed")
     assert build.returncode == 0, build.stderr[-3000:]
     run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert run.returncode == 0 and "0 failures" in run.stdout, run.stdout + run.stderr
+    assert "ERROR: AddressSanitizer" not in run.stdout + run.stderr

@@ -274,6 +274,45 @@ def test_pool_size_classes_and_reuse():
     assert s["device_allocs"] == a0 and s["bytes_in_use"] == 0
 
 
+def test_pool_guard_regions_catch_a_store_past_the_block():
+    """The memory checker that needs no tool: with guards on, a block has 256 pattern bytes in front of
+    it and behind its capacity, and `pool_check_guards` finds a block whose pattern was overwritten."""
+    import ctypes
+
+    C = bb._C
+    was = C.pool_guard()
+    C.pool_release_cached(-1)  # the next pulls allocate fresh (guarded) blocks
+    C.pool_set_guard(True)
+    try:
+        t = bc.BaguaTensorPy(torch.randn(3000), "x")
+        c = t.compress("MinMaxUInt8", 2, -1)
+        other = t.compress("MinMaxUInt8", 4, -1)
+        assert C.pool_check_guards(-1) == 0
+        v0 = C.pool_stats(-1)["guard_violations"]
+        cap = C.pool_size_class(c.num_elements_allocated())
+        rear = ctypes.c_ubyte.from_address(c.data_ptr() + cap + 3)
+        assert rear.value == 0xC5
+        rear.value = 0  # what a kernel that runs four bytes past the block would do
+        assert C.pool_check_guards(-1) == 1
+        assert C.pool_check_guards(-1) == 1  # still damaged, but counted once
+        assert C.pool_stats(-1)["guard_violations"] == v0 + 1
+        rear.value = 0xC5
+        front = ctypes.c_ubyte.from_address(other.data_ptr() - 1)
+        assert front.value == 0xC5
+        front.value = 7
+        assert C.pool_check_guards(-1) == 1
+        front.value = 0xC5
+        assert C.pool_check_guards(-1) == 0
+        del c, other
+    finally:
+        C.pool_release_cached(-1)
+        C.pool_set_guard(was)
+    # unguarded blocks are neither tracked nor checked
+    c = bc.BaguaTensorPy(torch.randn(3000), "y").compress("MinMaxUInt8", 2, -1)
+    assert C.pool_check_guards(-1) == 0
+    del c
+
+
 # ---- telemetry ---------------------------------------------------------------------------
 def test_telemetry_posts_reference_schema():
     received = []

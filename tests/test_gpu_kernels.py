@@ -207,3 +207,43 @@ def test_pool_reuses_blocks():
         bc.BaguaTensorPy(x, "x").compress("MinMaxUInt8", 1, -1)
     torch.cuda.synchronize()
     assert bb._C.pool_stats(0)["device_allocs"] == a
+
+
+@pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_POOL_GUARD") != "1",
+                    reason="guard regions of device pool blocks: set BAGUA_B200_TEST_POOL_GUARD=1 (first run on hardware pending)")
+def test_pool_guard_regions_stay_intact_under_the_kernels_and_catch_a_stray_store():
+    """Device pool blocks with guard regions: the compression kernels on ragged sizes leave every
+    guard intact, and four bytes stored just past a block's capacity are found."""
+    import bagua_core as bc
+    import bagua_core_b200 as bb
+
+    runtime = pytest.importorskip("cuda.bindings.runtime")
+    C = bb._C
+    was = C.pool_guard()
+    torch.cuda.synchronize()
+    C.pool_release_cached(0)
+    C.pool_set_guard(True)
+    try:
+        kept = []
+        for n in SIZES:
+            for dt in (torch.float32, torch.float16):
+                x = _rand(n, dt, n % 97)
+                t = bc.BaguaTensorPy(x, "x")
+                c = t.compress("MinMaxUInt8", 1, -1)
+                back = bc.BaguaTensorPy(torch.empty_like(x), "back")
+                back.decompress_from("MinMaxUInt8", 1, c)
+                kept.append(c)
+        assert C.pool_check_guards(0) == 0
+        c = kept[-1]
+        cap = C.pool_size_class(c.num_elements_allocated())
+        (err,) = runtime.cudaMemset(c.data_ptr() + cap, 0, 4)  # inside the allocation: the rear guard
+        assert int(err) == 0
+        assert C.pool_check_guards(0) == 1
+        (err,) = runtime.cudaMemset(c.data_ptr() + cap, 0xC5, 4)
+        assert int(err) == 0
+        assert C.pool_check_guards(0) == 0
+        del kept, c
+    finally:
+        torch.cuda.synchronize()
+        C.pool_release_cached(0)
+        C.pool_set_guard(was)
