@@ -182,3 +182,122 @@ def test_rank_raising_is_seen_by_its_peer():
     assert out[1][0] == "error" and "injected failure" in out[1][1]
     status, (result, elapsed) = out[0]
     assert status == "ok" and result == "error" and elapsed < 40
+
+
+def _killed_mid_step(rank, world):
+    """Rank 1 is killed (SIGKILL, no clean-up of any kind) while rank 0 is already inside the bucket's
+    collective of the second step."""
+    import signal
+
+    import bagua_core as bc
+
+    comm = _comm(rank, world)
+    backend = bc.BaguaCommBackendPy(10, -1)
+    t = bc.BaguaTensorPy(torch.ones(4096), "x")
+    b = bc.BaguaBucketPy("b", [t])
+    b.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True)
+    backend.register_ordered_buckets([b])
+    backend.mark_communication_ready(t, 0)
+    assert backend.wait_pending_comm_ops() == 1
+    if rank == 1:
+        time.sleep(1.0)  # rank 0 is waiting for this rank's contribution by now
+        os.kill(os.getpid(), signal.SIGKILL)
+    t0 = time.time()
+    backend.mark_communication_ready(t, 0)
+    try:
+        backend.wait_pending_comm_ops()
+        result = "no error"
+    except RuntimeError as e:
+        result = "error: " + str(e)[:200]
+    elapsed = time.time() - t0
+    backend.close()
+    return result, elapsed
+
+
+def test_rank_killed_while_its_peer_is_inside_the_collective():
+    out = _run(_killed_mid_step)
+    assert out[1][0] == "died", out
+    status, (result, elapsed) = out[0]
+    assert status == "ok", out[0]
+    assert result.startswith("error: "), result
+    assert elapsed < 30
+
+
+def _delayed_past_watchdog(rank, world):
+    """Rank 1 joins the bucket's collective three seconds late; rank 0's watchdog is set to half a
+    second, so rank 0 hears about the stuck bucket by name while its worker is still waiting, and the
+    collective itself completes once rank 1 arrives."""
+    import bagua_core as bc
+
+    comm = _comm(rank, world)
+    backend = bc.BaguaCommBackendPy(10, -1)
+    if rank == 0:
+        backend.set_watchdog_timeout(0.5)
+    x = torch.full((256,), float(rank + 1))
+    t = bc.BaguaTensorPy(x, "x")
+    b = bc.BaguaBucketPy("late_bucket", [t])
+    b.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True)
+    backend.register_ordered_buckets([b])
+    if rank == 1:
+        time.sleep(3.0)
+    backend.mark_communication_ready(t, 0)
+    report = ""
+    t0 = time.time()
+    try:
+        backend.wait_pending_comm_ops()
+    except RuntimeError as e:
+        report = str(e)
+    reported_after = time.time() - t0
+    # the late rank arrives; the worker finishes the collective and the backend shuts down cleanly
+    deadline = time.time() + 20
+    while x[0].item() != 1.5 and time.time() < deadline:
+        time.sleep(0.05)
+    backend.close()
+    return report[:300], reported_after, x[0].item()
+
+
+def test_rank_delayed_past_the_watchdog_is_reported_by_bucket_name():
+    out = _run(_delayed_past_watchdog)
+    status0, (report0, after0, value0) = out[0]
+    status1, (report1, after1, value1) = out[1]
+    assert status0 == "ok" and status1 == "ok", out
+    assert "watchdog" in report0 and "late_bucket" in report0, report0
+    assert after0 < 2.5  # long before the late rank arrived
+    assert report1 == ""
+    assert value0 == 1.5 and value1 == 1.5  # the collective still completed on both ranks
+
+
+def test_corrupted_chunk_header_does_not_make_decompression_leave_its_buffers():
+    """A compressed chunk whose header was overwritten (NaN, infinities, min > max) decompresses to
+    meaningless values, but the call returns, stays inside the output tensor (poison on both sides is
+    intact) and inside its pool blocks (guard regions intact)."""
+    import struct
+
+    import bagua_core as bc
+    import bagua_core_b200 as bb
+
+    C = bb._C
+    was = C.pool_guard()
+    C.pool_release_cached(-1)
+    C.pool_set_guard(True)
+    try:
+        src = torch.randn(1000)
+        c = bc.BaguaTensorPy(src, "src").compress("MinMaxUInt8", 4, -1)
+        import ctypes
+
+        stride = c.num_elements() // 4  # per chunk: 32-byte header {min, max, padding}, then the bytes
+        first = struct.unpack("<ff", bytes((ctypes.c_char * 8).from_address(c.data_ptr())))
+        assert first == (src[:250].min().item(), src[:250].max().item())
+        for lo, hi in [(float("nan"), 1.0), (float("inf"), float("-inf")), (5.0, -5.0), (0.0, 0.0), (-3e38, 3e38)]:
+            for chunk in range(4):
+                header = (ctypes.c_char * 8).from_address(c.data_ptr() + chunk * stride)
+                header[:] = struct.pack("<ff", lo, hi)
+            whole = torch.full((1000 + 64,), -777.0)
+            out = whole[32:1032]
+            bc.BaguaTensorPy(out, "out").decompress_from("MinMaxUInt8", 4, c)
+            assert torch.all(whole[:32] == -777.0) and torch.all(whole[1032:] == -777.0)
+            assert C.pool_check_guards(-1) == 0
+        del c
+    finally:
+        C.pool_release_cached(-1)
+        C.pool_set_guard(was)
