@@ -43,6 +43,10 @@ void SingleCommunicator::check_live() const {
   if (check_abort()) throw BaguaError(ErrorKind::Communicator, "communicator was aborted");
 }
 
+void SingleCommunicator::check_rank(int r, const char* what) const {
+  BAGUA_CHECK(r >= 0 && r < nranks_, Communicator, what << " rank " << r << " out of range (" << nranks_ << " ranks)");
+}
+
 PeerArena* SingleCommunicator::arena() {
   if (device_id_ < 0 || nranks_ < 2 || nranks_ > kArenaMaxRanks || !fused_enabled_) return nullptr;
   std::lock_guard<std::mutex> g(arena_mu_);
@@ -116,7 +120,7 @@ void SingleCommunicator::allreduce_inplace(RawTensor& t, ReductionOp op) {
 }
 void SingleCommunicator::broadcast(RawTensor& t, int root) {
   check_live();
-  BAGUA_CHECK(root >= 0 && root < nranks_, Communicator, "broadcast: root rank " << root << " out of range");
+  check_rank(root, "broadcast: root");
   if (PeerArena* a = p2p_arena())
     if (fused::broadcast(*a, t.data_ptr(), t.bytes_allocated(), root, (cudaStream_t)stream_)) return;
   transport_->broadcast(t.data_ptr(), t.num_elements_allocated(), t.dtype(), root);
@@ -124,6 +128,7 @@ void SingleCommunicator::broadcast(RawTensor& t, int root) {
 void SingleCommunicator::reduce(const RawTensor& send, RawTensor& recv, int dst, ReductionOp op) {
   check_live();
   same_kind(send, recv, "reduce");
+  check_rank(dst, "reduce: destination");
   BAGUA_CHECK(send.num_elements_allocated() == recv.num_elements_allocated(), Communicator,
               "reduce: send and recv sizes differ");
   if (PeerArena* a = p2p_arena()) {
@@ -136,6 +141,7 @@ void SingleCommunicator::reduce(const RawTensor& send, RawTensor& recv, int dst,
 }
 void SingleCommunicator::reduce_inplace(RawTensor& t, int dst, ReductionOp op) {
   check_live();
+  check_rank(dst, "reduce: destination");
   if (PeerArena* a = p2p_arena()) {
     const float scale = p2p_scale(op, nranks_);
     if (scale != 0.0f && fused::reduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,
@@ -146,10 +152,12 @@ void SingleCommunicator::reduce_inplace(RawTensor& t, int dst, ReductionOp op) {
 }
 void SingleCommunicator::send(const RawTensor& t, int peer) {
   check_live();
+  check_rank(peer, "send: peer");
   transport_->send(t.data_ptr(), t.num_elements_allocated(), t.dtype(), peer);
 }
 void SingleCommunicator::recv(RawTensor& t, int peer) {
   check_live();
+  check_rank(peer, "recv: peer");
   transport_->recv(t.data_ptr(), t.num_elements_allocated(), t.dtype(), peer);
 }
 void SingleCommunicator::alltoall(const RawTensor& send, RawTensor& recv) {
@@ -217,6 +225,7 @@ void SingleCommunicator::allgather_inplace(RawTensor& t) {
 void SingleCommunicator::gather(const RawTensor& send, RawTensor& recv, int dst) {
   check_live();
   same_kind(send, recv, "gather");
+  check_rank(dst, "gather: destination");
   if (rank_ == dst)
     BAGUA_CHECK(send.num_elements_allocated() * nranks_ == recv.num_elements_allocated(), Communicator,
                 "gather: recv on the root must hold nranks * send elements");
@@ -226,6 +235,8 @@ void SingleCommunicator::gather(const RawTensor& send, RawTensor& recv, int dst)
 }
 void SingleCommunicator::gather_inplace(RawTensor& t, int64_t count, int dst) {
   check_live();
+  check_rank(dst, "gather: destination");
+  BAGUA_CHECK(count >= 0, Communicator, "gather_inplace: negative count");
   if (rank_ == dst)
     BAGUA_CHECK(t.num_elements_allocated() == count * nranks_, Communicator,
                 "gather_inplace: the root tensor must hold count * nranks elements");
@@ -240,6 +251,7 @@ void SingleCommunicator::gather_inplace(RawTensor& t, int64_t count, int dst) {
 void SingleCommunicator::scatter(const RawTensor& send, RawTensor& recv, int src) {
   check_live();
   same_kind(send, recv, "scatter");
+  check_rank(src, "scatter: source");
   if (rank_ == src)
     BAGUA_CHECK(recv.num_elements_allocated() * nranks_ == send.num_elements_allocated(), Communicator,
                 "scatter: send on the root must hold nranks * recv elements");
@@ -249,6 +261,8 @@ void SingleCommunicator::scatter(const RawTensor& send, RawTensor& recv, int src
 }
 void SingleCommunicator::scatter_inplace(RawTensor& t, int64_t count, int src) {
   check_live();
+  check_rank(src, "scatter: source");
+  BAGUA_CHECK(count >= 0, Communicator, "scatter_inplace: negative count");
   if (rank_ == src)
     BAGUA_CHECK(t.num_elements_allocated() == count * nranks_, Communicator,
                 "scatter_inplace: the root tensor must hold count * nranks elements");

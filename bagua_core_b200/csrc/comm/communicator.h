@@ -86,6 +86,7 @@ class SingleCommunicator {
 
  private:
   void check_live() const;
+  void check_rank(int r, const char* what) const;
   // The arena when this call may run as a peer-memory kernel, else null.
   PeerArena* p2p_arena();
   int rank_, nranks_, device_id_;

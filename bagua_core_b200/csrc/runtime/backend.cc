@@ -163,6 +163,8 @@ size_t CommBackend::wait_pending_comm_ops() {
       if (!watchdog_error_.empty()) {
         std::string w = watchdog_error_;
         watchdog_error_.clear();
+        // the op is still running: a later wait must still see how it ended
+        not_waited_.send(*ev);
         throw BaguaError(ErrorKind::Backend, "watchdog: " + w);
       }
     }

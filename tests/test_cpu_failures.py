@@ -248,22 +248,21 @@ def _delayed_past_watchdog(rank, world):
     except RuntimeError as e:
         report = str(e)
     reported_after = time.time() - t0
-    # the late rank arrives; the worker finishes the collective and the backend shuts down cleanly
-    deadline = time.time() + 20
-    while x[0].item() != 1.5 and time.time() < deadline:
-        time.sleep(0.05)
+    # the late rank arrives and the worker finishes the collective: after a watchdog report the op is
+    # still owed to the caller, so a second wait returns it
+    waited_again = backend.wait_pending_comm_ops() if report else 0
     backend.close()
-    return report[:300], reported_after, x[0].item()
+    return report[:300], reported_after, x[0].item(), waited_again
 
 
 def test_rank_delayed_past_the_watchdog_is_reported_by_bucket_name():
     out = _run(_delayed_past_watchdog)
-    status0, (report0, after0, value0) = out[0]
-    status1, (report1, after1, value1) = out[1]
-    assert status0 == "ok" and status1 == "ok", out
+    assert out[0][0] == "ok" and out[1][0] == "ok", out
+    report0, after0, value0, again0 = out[0][1]
+    report1, after1, value1, again1 = out[1][1]
     assert "watchdog" in report0 and "late_bucket" in report0, report0
     assert after0 < 2.5  # long before the late rank arrived
-    assert report1 == ""
+    assert report1 == "" and again0 == 1 and again1 == 0
     assert value0 == 1.5 and value1 == 1.5  # the collective still completed on both ranks
 
 

@@ -286,6 +286,17 @@ def _collectives(rank, world):
         z = torch.zeros(8)
         comm.recv(T(z), 0)
         out["recv"] = z.clone()
+    # a root or peer outside the group is refused on the calling rank, before anything is sent
+    refused = 0
+    for call in (lambda: comm.broadcast(T(a.clone()), world), lambda: comm.reduce_inplace(T(a.clone()), -1, 0),
+                 lambda: comm.gather_inplace(T(torch.zeros(8 * world)), 8, world + 3),
+                 lambda: comm.scatter_inplace(T(torch.zeros(8 * world)), 8, -2),
+                 lambda: comm.send(T(a.clone()), world), lambda: comm.recv(T(a.clone()), -1)):
+        try:
+            call()
+        except RuntimeError as e:
+            refused += "out of range" in str(e)
+    out["refused"] = refused
     comm.barrier()
     return out
 
@@ -297,6 +308,7 @@ def test_collective_api():
     a = [base + 10 * r for r in range(world)]
     for r in range(world):
         o = res[r]
+        assert o["refused"] == 6
         assert torch.equal(o["allreduce_sum"], a[0] + a[1])
         assert torch.equal(o["allreduce_avg"], (a[0] + a[1]) / 2)
         assert torch.equal(o["broadcast"], a[1])
