@@ -23,19 +23,24 @@ PeerArena::PeerArena(Transport& transport, int rank, int nranks, int device, cud
   max_coop_blocks_ = (int)std::min<long>(std::max<long>(env_long("BAGUA_B200_COOP_CTAS", 148), 1), kArenaMaxBlocks);
   nvls_ = env_long("BAGUA_B200_NVLS", 0) != 0;
   BAGUA_CUDA_CHECK(cudaSetDevice(device));
-  // every peer must be reachable with peer access
-  int ndev = 0;
-  BAGUA_CUDA_CHECK(cudaGetDeviceCount(&ndev));
-  BAGUA_CUDA_CHECK(cudaMalloc(&local_signals_, kSigWords * sizeof(uint32_t)));
-  BAGUA_CUDA_CHECK(cudaMemset(local_signals_, 0, kSigWords * sizeof(uint32_t)));
-  BAGUA_CUDA_CHECK(cudaHostAlloc((void**)&status_host_, sizeof(DeviceStatus), cudaHostAllocMapped));
-  std::memset(status_host_, 0, sizeof(DeviceStatus));
-  BAGUA_CUDA_CHECK(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
-  BAGUA_CUDA_CHECK(cudaDeviceSynchronize());
-  allocate_and_exchange((size_t)env_long("BAGUA_B200_STAGING_MB", 64) << 20);
+  try {
+    BAGUA_CUDA_CHECK(cudaMalloc(&local_signals_, kSigWords * sizeof(uint32_t)));
+    BAGUA_CUDA_CHECK(cudaMemset(local_signals_, 0, kSigWords * sizeof(uint32_t)));
+    BAGUA_CUDA_CHECK(cudaHostAlloc((void**)&status_host_, sizeof(DeviceStatus), cudaHostAllocMapped));
+    std::memset(status_host_, 0, sizeof(DeviceStatus));
+    BAGUA_CUDA_CHECK(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
+    BAGUA_CUDA_CHECK(cudaDeviceSynchronize());
+    // fails when a peer cannot be mapped (no peer access between the devices, IPC disabled)
+    allocate_and_exchange((size_t)env_long("BAGUA_B200_STAGING_MB", 64) << 20);
+  } catch (...) {
+    release();  // a constructor that throws gets no destructor call
+    throw;
+  }
 }
 
-PeerArena::~PeerArena() {
+PeerArena::~PeerArena() { release(); }
+
+void PeerArena::release() {
   // Best effort; at interpreter shutdown the runtime may already be gone.
   for (int p = 0; p < nranks_; ++p) {
     if (p == rank_) continue;
@@ -56,10 +61,17 @@ PeerArena::~PeerArena() {
         cudaIpcCloseMemHandle(s.base[p]);
     }
   }
+  slabs_.clear();
+  retired_peer_.clear();
   if (local_staging_) cudaFree(local_staging_);
   for (void* p : retired_) cudaFree(p);
+  retired_.clear();
   if (local_signals_) cudaFree(local_signals_);
   if (status_host_) cudaFreeHost(status_host_);
+  local_staging_ = nullptr;
+  local_signals_ = nullptr;
+  status_host_ = nullptr;
+  for (int p = 0; p < kArenaMaxRanks; ++p) peer_staging_[p] = peer_signals_[p] = nullptr;
   cudaGetLastError();
 }
 
@@ -70,6 +82,13 @@ void PeerArena::allocate_and_exchange(size_t bytes) {
   BAGUA_CUDA_CHECK(cudaStreamSynchronize(stream_));
   void* fresh = nullptr;
   BAGUA_CUDA_CHECK(cudaMalloc(&fresh, bytes));
+  // until `fresh` becomes the arena's staging, an exception must give it back
+  struct FreeOnError {
+    void*& p;
+    ~FreeOnError() {
+      if (p) cudaFree(p);
+    }
+  } guard{fresh};
 
   HandlePair mine;
   std::memset(&mine, 0, sizeof(mine));
@@ -118,6 +137,7 @@ void PeerArena::allocate_and_exchange(size_t bytes) {
   if (local_staging_) retired_.push_back(local_staging_);
   local_staging_ = fresh;
   peer_staging_[rank_] = fresh;
+  fresh = nullptr;  // owned by the arena from here on
   peer_signals_[rank_] = local_signals_;
   staging_bytes_ = bytes;
   // Nobody may write into the new staging before every rank has mapped it.

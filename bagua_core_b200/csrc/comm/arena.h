@@ -135,6 +135,7 @@ class PeerArena {
   size_t staging_bytes_ = 0;
   void* local_staging_ = nullptr;
   void* local_signals_ = nullptr;
+  void release();  // frees and unmaps everything; the destructor, and a constructor that fails
   void* peer_staging_[kArenaMaxRanks] = {};
   void* peer_signals_[kArenaMaxRanks] = {};
   std::vector<void*> retired_;       // superseded local staging buffers, freed at destruction
