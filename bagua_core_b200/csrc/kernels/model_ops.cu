@@ -23,8 +23,7 @@ using namespace bodies;
 
 __global__ void __launch_bounds__(kThreads)
     bias_relu_kernel(uint4* __restrict__ z, const __nv_bfloat16* __restrict__ bias, int64_t nvec, int cgroups) {
-  extern __shared__ float s_bias[];
-  bias_relu_body(z, bias, nvec, cgroups, s_bias);
+  bias_relu_body(z, bias, nvec, cgroups);
 }
 __global__ void __launch_bounds__(kThreads)
     bias_relu_backward_kernel(const uint4* dy, const uint4* __restrict__ y, uint4* dz, float* __restrict__ partial,
@@ -36,28 +35,26 @@ __global__ void bias_grad_finish_kernel(const float* __restrict__ partial, float
   bias_grad_finish_body(partial, db, blocks, C);
 }
 __global__ void __launch_bounds__(kThreads)
-    maxpool2x2_forward_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t nvec_out, int64_t Ho,
-                              int64_t Wo, int64_t W, int cgroups) {
-  maxpool2x2_forward_body(x, y, nvec_out, Ho, Wo, W, cgroups);
+    maxpool2x2_forward_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t nvec_out, int64_t Wo,
+                              int64_t W, int cgroups) {
+  maxpool2x2_forward_body(x, y, nvec_out, Wo, W, cgroups);
 }
 __global__ void __launch_bounds__(kThreads)
     maxpool2x2_backward_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ dx,
-                               int64_t nvec_out, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
-  maxpool2x2_backward_body(x, dy, dx, nvec_out, Ho, Wo, W, cgroups);
+                               int64_t nvec_out, int64_t Wo, int64_t W, int cgroups) {
+  maxpool2x2_backward_body(x, dy, dx, nvec_out, Wo, W, cgroups);
 }
 
 __global__ void __launch_bounds__(kThreads)
     bias_relu_pool_kernel(uint4* __restrict__ y, uint4* __restrict__ p, const __nv_bfloat16* __restrict__ bias,
-                          int64_t nvec_out, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
-  extern __shared__ float s_bias[];
-  bias_relu_pool_body(y, p, bias, nvec_out, Ho, Wo, W, cgroups, s_bias);
+                          int64_t pooled_pixels, int64_t Wo, int64_t W, int cgroups) {
+  bias_relu_pool_body(y, p, bias, pooled_pixels, Wo, W, cgroups);
 }
 __global__ void __launch_bounds__(kThreads)
     bias_relu_pool_backward_kernel(const uint4* __restrict__ dp, const uint4* __restrict__ y, uint4* __restrict__ dz,
-                                   float* __restrict__ partial, int64_t pooled_rows, int64_t Ho, int64_t Wo, int64_t W,
-                                   int cgroups) {
+                                   float* __restrict__ partial, int64_t pooled_rows, int64_t Wo, int64_t W, int cgroups) {
   __shared__ float s_acc[kThreads * 8];
-  bias_relu_pool_backward_body(dp, y, dz, partial, pooled_rows, Ho, Wo, W, cgroups, s_acc);
+  bias_relu_pool_backward_body(dp, y, dz, partial, pooled_rows, Wo, W, cgroups, s_acc);
 }
 
 int pool_grid(int64_t nvec_out) {
@@ -81,8 +78,7 @@ void bias_relu_inplace_bf16(void* z, const void* bias, int64_t rows, int C, cuda
   const int64_t nvec = rows * (C / 8);
   const int64_t want = (nvec + (int64_t)kThreads * 4 - 1) / ((int64_t)kThreads * 4);
   const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, 148 * 8));
-  bias_relu_kernel<<<grid, kThreads, (size_t)C * sizeof(float), stream>>>((uint4*)z, (const __nv_bfloat16*)bias, nvec,
-                                                                         C / 8);
+  bias_relu_kernel<<<grid, kThreads, 0, stream>>>((uint4*)z, (const __nv_bfloat16*)bias, nvec, C / 8);
   BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -108,8 +104,8 @@ void maxpool2x2_forward_bf16(const void* x, void* y, int64_t N, int64_t H, int64
   BAGUA_CHECK(maxpool2x2_supported(N, H, W, C) && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0, Tensor,
               "fused max-pool: unsupported shape [" << N << ", " << H << ", " << W << ", " << C << "] or unaligned buffers");
   const int64_t nvec_out = N * (H / 2) * (W / 2) * (C / 8);
-  maxpool2x2_forward_kernel<<<pool_grid(nvec_out), kThreads, 0, stream>>>((const uint4*)x, (uint4*)y, nvec_out, H / 2,
-                                                                          W / 2, W, C / 8);
+  maxpool2x2_forward_kernel<<<pool_grid(nvec_out), kThreads, 0, stream>>>((const uint4*)x, (uint4*)y, nvec_out, W / 2, W,
+                                                                          C / 8);
   BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -122,7 +118,7 @@ void maxpool2x2_backward_bf16(const void* x, const void* dy, void* dx, int64_t N
                                                              << "] or unaligned buffers");
   const int64_t nvec_out = N * (H / 2) * (W / 2) * (C / 8);
   maxpool2x2_backward_kernel<<<pool_grid(nvec_out), kThreads, 0, stream>>>((const uint4*)x, (const uint4*)dy, (uint4*)dx,
-                                                                           nvec_out, H / 2, W / 2, W, C / 8);
+                                                                           nvec_out, W / 2, W, C / 8);
   BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -132,9 +128,9 @@ void bias_relu_pool_bf16(void* y, void* p, const void* bias, int64_t N, int64_t 
               Tensor,
               "fused bias+ReLU+pool: unsupported shape [" << N << ", " << H << ", " << W << ", " << C
                                                           << "] or unaligned buffers");
-  const int64_t nvec_out = N * (H / 2) * (W / 2) * (C / 8);
-  bias_relu_pool_kernel<<<pool_grid(nvec_out), kThreads, (size_t)C * sizeof(float), stream>>>(
-      (uint4*)y, (uint4*)p, (const __nv_bfloat16*)bias, nvec_out, H / 2, W / 2, W, C / 8);
+  const int64_t pooled_pixels = N * (H / 2) * (W / 2);
+  bias_relu_pool_kernel<<<pool_grid(pooled_pixels * (C / 8)), kThreads, 0, stream>>>(
+      (uint4*)y, (uint4*)p, (const __nv_bfloat16*)bias, pooled_pixels, W / 2, W, C / 8);
   BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -148,7 +144,7 @@ void bias_relu_pool_backward_bf16(const void* dp, const void* y, void* dz, float
   const int64_t pooled_rows = N * (H / 2) * (W / 2);
   const int blocks = backward_blocks(pooled_rows, C);
   bias_relu_pool_backward_kernel<<<blocks, kThreads, 0, stream>>>((const uint4*)dp, (const uint4*)y, (uint4*)dz,
-                                                                  (float*)scratch, pooled_rows, H / 2, W / 2, W, C / 8);
+                                                                  (float*)scratch, pooled_rows, W / 2, W, C / 8);
   BAGUA_CUDA_CHECK(cudaGetLastError());
   bias_grad_finish_kernel<<<(C + 127) / 128, 128, 0, stream>>>((const float*)scratch, db, blocks, C);
   BAGUA_CUDA_CHECK(cudaGetLastError());

@@ -44,21 +44,29 @@ __device__ __forceinline__ uint4 bias_relu_vec(const uint4& x, const float* b) {
   return pack8(f);
 }
 
-// cgroups = C / 8 vectors per row.
+// The 8 bias values of channel group cg.
+__device__ __forceinline__ void load_bias8(const __nv_bfloat16* __restrict__ bias, int cg, float (&b)[8]) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) b[k] = __bfloat162float(bias[cg * 8 + k]);
+}
+
+// cgroups = C / 8 vectors per row.  cgroups divides kThreads, hence the grid stride too, so all
+// vectors a thread visits belong to one channel group: its bias stays in registers and the loop
+// has no division.
 __device__ __forceinline__ void bias_relu_body(uint4* __restrict__ z, const __nv_bfloat16* __restrict__ bias,
-                                               int64_t nvec, int cgroups, float* s_bias) {
-  for (int c = threadIdx.x; c < cgroups * 8; c += kThreads) s_bias[c] = __bfloat162float(bias[c]);
-  __syncthreads();
+                                               int64_t nvec, int cgroups) {
+  float bs[8];
+  load_bias8(bias, (int)(threadIdx.x % cgroups), bs);
   const int64_t stride = (int64_t)gridDim.x * kThreads;
   int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   for (; v + 3 * stride < nvec; v += 4 * stride) {
     const uint4 a = z[v], b = z[v + stride], c = z[v + 2 * stride], d = z[v + 3 * stride];
-    z[v] = bias_relu_vec(a, s_bias + (int)(v % cgroups) * 8);
-    z[v + stride] = bias_relu_vec(b, s_bias + (int)((v + stride) % cgroups) * 8);
-    z[v + 2 * stride] = bias_relu_vec(c, s_bias + (int)((v + 2 * stride) % cgroups) * 8);
-    z[v + 3 * stride] = bias_relu_vec(d, s_bias + (int)((v + 3 * stride) % cgroups) * 8);
+    z[v] = bias_relu_vec(a, bs);
+    z[v + stride] = bias_relu_vec(b, bs);
+    z[v + 2 * stride] = bias_relu_vec(c, bs);
+    z[v + 3 * stride] = bias_relu_vec(d, bs);
   }
-  for (; v < nvec; v += stride) z[v] = bias_relu_vec(z[v], s_bias + (int)(v % cgroups) * 8);
+  for (; v < nvec; v += stride) z[v] = bias_relu_vec(z[v], bs);
 }
 
 // ---- backward ---------------------------------------------------------------------
@@ -118,29 +126,45 @@ __device__ __forceinline__ void bias_grad_finish_body(const float* __restrict__ 
 }
 
 // ---- 2x2 / stride-2 max pooling -------------------------------------------------------
-// One thread per output vector (8 channels of one output pixel); vector indices are
-// [n][h][w][cg] with cg fastest, so a warp reads whole pixels of contiguous channels.
+// Vector indices are [n][h][w][cg] with cg fastest, so a warp reads whole pixels of contiguous
+// channels.  Index arithmetic divides in 32 bits whenever the value fits: the 64-bit division
+// costs several times as many instructions, enough to show next to the handful of 16-byte
+// accesses a thread makes per output vector.
+__device__ __forceinline__ void div_mod(int64_t a, int64_t d, int64_t& quot, int64_t& rem) {
+  if (a <= 0xffffffffLL && d <= 0xffffffffLL) {
+    const uint32_t a32 = (uint32_t)a, d32 = (uint32_t)d, q32 = a32 / d32;
+    quot = q32;
+    rem = a32 - q32 * d32;
+  } else {
+    quot = a / d;
+    rem = a - quot * d;
+  }
+}
+
 struct PoolIndex {
   int64_t x00;  // vector index of the window's top-left input pixel
   int64_t dw, dh;  // vector strides to the right / lower neighbour
 };
-__device__ __forceinline__ PoolIndex pool_index(int64_t v, int64_t Ho, int64_t Wo, int64_t W, int cgroups) {
-  const int64_t cg = v % cgroups, p = v / cgroups;
-  const int64_t wo = p % Wo, q = p / Wo;
-  const int64_t ho = q % Ho, n = q / Ho;
+// Pooled pixel p = (n * Ho + ho) * Wo + wo of an [N, 2 Ho, W, C] input: its window starts at
+// input row 2 (n * Ho + ho), column 2 wo, so one division by Wo is all it takes.
+__device__ __forceinline__ PoolIndex pool_index(int64_t p, int64_t cg, int64_t Wo, int64_t W, int cgroups) {
+  int64_t q, wo;
+  div_mod(p, Wo, q, wo);
   PoolIndex r;
   r.dw = cgroups;
   r.dh = W * cgroups;
-  r.x00 = ((n * (2 * Ho) + 2 * ho) * W + 2 * wo) * cgroups + cg;
+  r.x00 = (2 * q * W + 2 * wo) * cgroups + cg;
   return r;
 }
 
+// One thread per output vector (8 channels of one output pixel); any number of channel groups.
 __device__ __forceinline__ void maxpool2x2_forward_body(const uint4* __restrict__ x, uint4* __restrict__ y,
-                                                        int64_t nvec_out, int64_t Ho, int64_t Wo, int64_t W,
-                                                        int cgroups) {
+                                                        int64_t nvec_out, int64_t Wo, int64_t W, int cgroups) {
   const int64_t stride = (int64_t)gridDim.x * kThreads;
   for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
-    const PoolIndex p = pool_index(v, Ho, Wo, W, cgroups);
+    int64_t pixel, cg;
+    div_mod(v, cgroups, pixel, cg);
+    const PoolIndex p = pool_index(pixel, cg, Wo, W, cgroups);
     const uint4 a = x[p.x00], b = x[p.x00 + p.dw], c = x[p.x00 + p.dh], d = x[p.x00 + p.dh + p.dw];
     float fa[8], fb[8], fc[8], fd[8];
     unpack8(a, fa);
@@ -154,11 +178,13 @@ __device__ __forceinline__ void maxpool2x2_forward_body(const uint4* __restrict_
 }
 
 __device__ __forceinline__ void maxpool2x2_backward_body(const uint4* __restrict__ x, const uint4* __restrict__ dy,
-                                                         uint4* __restrict__ dx, int64_t nvec_out, int64_t Ho,
-                                                         int64_t Wo, int64_t W, int cgroups) {
+                                                         uint4* __restrict__ dx, int64_t nvec_out, int64_t Wo,
+                                                         int64_t W, int cgroups) {
   const int64_t stride = (int64_t)gridDim.x * kThreads;
   for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
-    const PoolIndex p = pool_index(v, Ho, Wo, W, cgroups);
+    int64_t pixel, cg;
+    div_mod(v, cgroups, pixel, cg);
+    const PoolIndex p = pool_index(pixel, cg, Wo, W, cgroups);
     const uint4 a = x[p.x00], b = x[p.x00 + p.dw], c = x[p.x00 + p.dh], d = x[p.x00 + p.dh + p.dw];
     const uint4 g4 = dy[v];
     float fa[8], fb[8], fc[8], fd[8], g[8];
@@ -195,16 +221,19 @@ __device__ __forceinline__ void maxpool2x2_backward_body(const uint4* __restrict
 
 // ---- bias + ReLU with the 2x2 pooling that follows it -----------------------------------
 // Forward: y = max(z + bias, 0) in place on the [N, H, W, C] convolution output, and
-// p = 2x2 max of y, both from one read of z.  One thread per pooled vector.
+// p = 2x2 max of y, both from one read of z.  One thread per pooled vector; cgroups divides
+// kThreads, so a thread keeps its channel group (and its bias, in registers) and walks pooled
+// pixels that are a fixed number apart.
 __device__ __forceinline__ void bias_relu_pool_body(uint4* __restrict__ y, uint4* __restrict__ p,
-                                                    const __nv_bfloat16* __restrict__ bias, int64_t nvec_out,
-                                                    int64_t Ho, int64_t Wo, int64_t W, int cgroups, float* s_bias) {
-  for (int c = threadIdx.x; c < cgroups * 8; c += kThreads) s_bias[c] = __bfloat162float(bias[c]);
-  __syncthreads();
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nvec_out; v += stride) {
-    const PoolIndex q = pool_index(v, Ho, Wo, W, cgroups);
-    const float* b = s_bias + (int)(v % cgroups) * 8;
+                                                    const __nv_bfloat16* __restrict__ bias, int64_t pooled_pixels,
+                                                    int64_t Wo, int64_t W, int cgroups) {
+  const int cg = (int)(threadIdx.x % cgroups);
+  float b[8];
+  load_bias8(bias, cg, b);
+  const int64_t pixel_step = (int64_t)gridDim.x * (kThreads / cgroups);
+  for (int64_t px = (int64_t)blockIdx.x * (kThreads / cgroups) + threadIdx.x / cgroups; px < pooled_pixels;
+       px += pixel_step) {
+    const PoolIndex q = pool_index(px, cg, Wo, W, cgroups);
     const uint4 a0 = y[q.x00], a1 = y[q.x00 + q.dw], a2 = y[q.x00 + q.dh], a3 = y[q.x00 + q.dh + q.dw];
     const uint4 r0 = bias_relu_vec(a0, b), r1 = bias_relu_vec(a1, b), r2 = bias_relu_vec(a2, b), r3 = bias_relu_vec(a3, b);
     y[q.x00] = r0;
@@ -218,7 +247,7 @@ __device__ __forceinline__ void bias_relu_pool_body(uint4* __restrict__ y, uint4
     unpack8(r3, f3);
 #pragma unroll
     for (int k = 0; k < 8; ++k) f0[k] = fmaxf(fmaxf(f0[k], f1[k]), fmaxf(f2[k], f3[k]));
-    p[v] = pack8(f0);
+    p[px * cgroups + cg] = pack8(f0);
   }
 }
 
@@ -227,8 +256,8 @@ __device__ __forceinline__ void bias_relu_pool_body(uint4* __restrict__ y, uint4
 // and always the same 8 channels, like the un-pooled backward.
 __device__ __forceinline__ void bias_relu_pool_backward_body(const uint4* __restrict__ dp, const uint4* __restrict__ y,
                                                              uint4* __restrict__ dz, float* __restrict__ partial,
-                                                             int64_t pooled_rows, int64_t Ho, int64_t Wo, int64_t W,
-                                                             int cgroups, float* s_acc) {
+                                                             int64_t pooled_rows, int64_t Wo, int64_t W, int cgroups,
+                                                             float* s_acc) {
   const int rows_per_iter = kThreads / cgroups;
   const int cg = threadIdx.x % cgroups, ro = threadIdx.x / cgroups;
   const int64_t step = (int64_t)gridDim.x * rows_per_iter;
@@ -237,7 +266,7 @@ __device__ __forceinline__ void bias_relu_pool_backward_body(const uint4* __rest
   for (int k = 0; k < 8; ++k) acc[k] = 0.f;
   for (int64_t pr = (int64_t)blockIdx.x * rows_per_iter + ro; pr < pooled_rows; pr += step) {
     const int64_t v = pr * cgroups + cg;
-    const PoolIndex q = pool_index(v, Ho, Wo, W, cgroups);
+    const PoolIndex q = pool_index(pr, cg, Wo, W, cgroups);
     const uint4 a0 = y[q.x00], a1 = y[q.x00 + q.dw], a2 = y[q.x00 + q.dh], a3 = y[q.x00 + q.dh + q.dw];
     const uint4 g4 = dp[v];
     float f0[8], f1[8], f2[8], f3[8], g[8];

@@ -67,10 +67,8 @@ int check_bias_relu(int64_t rows, int C, int blocks, std::mt19937& rng) {
   fill(bias, rng, false);
   want = z;
   bias_relu_inplace_bf16_host(raw(want), raw(bias), rows, C);
-  std::vector<std::vector<float>> smem((size_t)blocks, std::vector<float>((size_t)C));
   launch(blocks, kThreads, [&] {
-    bias_relu_body(reinterpret_cast<uint4*>(z.data()), reinterpret_cast<const __nv_bfloat16*>(raw(bias)), nvec, cgroups,
-                   smem[hostemu::t_block_idx.x].data());
+    bias_relu_body(reinterpret_cast<uint4*>(z.data()), reinterpret_cast<const __nv_bfloat16*>(raw(bias)), nvec, cgroups);
   });
   int bad = std::memcmp(z.data(), want.data(), (size_t)nvec * 16) != 0;
 
@@ -103,12 +101,12 @@ int check_maxpool(int64_t N, int64_t H, int64_t W, int C, int blocks, std::mt199
   maxpool2x2_forward_bf16_host(raw(x), raw(y_want), N, H, W, C);
   maxpool2x2_backward_bf16_host(raw(x), raw(dy), raw(dx_want), N, H, W, C);
   launch(blocks, kThreads, [&] {
-    maxpool2x2_forward_body(reinterpret_cast<const uint4*>(x.data()), reinterpret_cast<uint4*>(y.data()), nout, H / 2, W / 2,
-                            W, cgroups);
+    maxpool2x2_forward_body(reinterpret_cast<const uint4*>(x.data()), reinterpret_cast<uint4*>(y.data()), nout, W / 2, W,
+                            cgroups);
   });
   launch(blocks, kThreads, [&] {
     maxpool2x2_backward_body(reinterpret_cast<const uint4*>(x.data()), reinterpret_cast<const uint4*>(dy.data()),
-                             reinterpret_cast<uint4*>(dx.data()), nout, H / 2, W / 2, W, cgroups);
+                             reinterpret_cast<uint4*>(dx.data()), nout, W / 2, W, cgroups);
   });
   return (std::memcmp(y.data(), y_want.data(), (size_t)nout * 16) != 0) +
          (std::memcmp(dx.data(), dx_want.data(), (size_t)nin * 16) != 0);
@@ -122,11 +120,9 @@ int check_bias_relu_pool(int64_t N, int64_t H, int64_t W, int C, int blocks, std
   fill(bias, rng, false);
   y_want = y;
   bias_relu_pool_bf16_host(raw(y_want), raw(p_want), raw(bias), N, H, W, C);
-  std::vector<std::vector<float>> smem((size_t)blocks, std::vector<float>((size_t)C));
   launch(blocks, kThreads, [&] {
     bias_relu_pool_body(reinterpret_cast<uint4*>(y.data()), reinterpret_cast<uint4*>(p.data()),
-                        reinterpret_cast<const __nv_bfloat16*>(raw(bias)), nout, H / 2, W / 2, W, cgroups,
-                        smem[hostemu::t_block_idx.x].data());
+                        reinterpret_cast<const __nv_bfloat16*>(raw(bias)), N * (H / 2) * (W / 2), W / 2, W, cgroups);
   });
   int bad = (std::memcmp(y.data(), y_want.data(), (size_t)nin * 16) != 0) +
             (std::memcmp(p.data(), p_want.data(), (size_t)nout * 16) != 0);
@@ -140,8 +136,8 @@ int check_bias_relu_pool(int64_t N, int64_t H, int64_t W, int C, int blocks, std
   std::vector<std::vector<float>> sacc((size_t)blocks, std::vector<float>((size_t)kThreads * 8));
   launch(blocks, kThreads, [&] {
     bias_relu_pool_backward_body(reinterpret_cast<const uint4*>(dp.data()), reinterpret_cast<const uint4*>(y.data()),
-                                 reinterpret_cast<uint4*>(dz.data()), partial.data(), N * (H / 2) * (W / 2), H / 2, W / 2,
-                                 W, cgroups, sacc[hostemu::t_block_idx.x].data());
+                                 reinterpret_cast<uint4*>(dz.data()), partial.data(), N * (H / 2) * (W / 2), W / 2, W,
+                                 cgroups, sacc[hostemu::t_block_idx.x].data());
   });
   launch((C + 127) / 128, 128, [&] { bias_grad_finish_body(partial.data(), db.data(), blocks, C); });
   bad += std::memcmp(dz.data(), dz_want.data(), (size_t)nin * 16) != 0;
@@ -191,6 +187,29 @@ int main() {
     if (bad)
       std::fprintf(stderr, "bias+ReLU+pool [%lld, %lld, %lld, %d] on %d blocks: %d mismatches\n", (long long)c.N,
                    (long long)c.H, (long long)c.W, c.C, c.blocks, bad);
+    failures += bad != 0;
+    ++cases;
+  }
+  // index arithmetic on both sides of the 32-bit limit, against plain 64-bit division
+  {
+    const int64_t big = (int64_t)1 << 32;
+    const int64_t as[] = {0, 1, 255, big - 1, big, big + 5, ((int64_t)1 << 40) + 123, ((int64_t)1 << 46) - 1};
+    const int64_t ds[] = {1, 3, 8, 112, ((int64_t)1 << 31), big - 1, big + 1};
+    int bad = 0;
+    for (int64_t a : as)
+      for (int64_t d : ds) {
+        int64_t q = -1, r = -1;
+        div_mod(a, d, q, r);
+        bad += q != a / d || r != a % d;
+      }
+    for (int64_t p : {(int64_t)0, (int64_t)111, (int64_t)112, big - 1, big, big + 113}) {
+      const int64_t Wo = 112, W = 224, cg = 5;
+      const int cgroups = 8;
+      const PoolIndex i = pool_index(p, cg, Wo, W, cgroups);
+      const int64_t wo = p % Wo, row = p / Wo;  // row = n * Ho + ho
+      bad += i.x00 != ((2 * row) * W + 2 * wo) * cgroups + cg || i.dw != cgroups || i.dh != W * cgroups;
+    }
+    if (bad) std::fprintf(stderr, "index arithmetic: %d mismatches\n", bad);
     failures += bad != 0;
     ++cases;
   }
