@@ -45,7 +45,7 @@ constexpr int kSigGridBar = kSigCounter + 2;                  // 64-bit local gr
 constexpr int kSigWords = kSigGridBar + 6;
 
 struct DeviceStatus {
-  uint32_t code;    // 0 = ok, 1 = wait on `done`, 2 = wait on a phase flag, 3 = grid barrier
+  uint32_t code;    // 0 = ok, 1 = wait on `done`, 2 = wait on a phase flag, 3 = grid barrier, 4 = alltoall_v sizes disagree
   uint32_t phase;
   uint32_t peer;
   uint32_t block;

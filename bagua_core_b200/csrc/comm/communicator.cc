@@ -86,6 +86,11 @@ void SingleCommunicator::check_device_status() {
   if (s.code == 0) return;
   aborted_.store(true, std::memory_order_release);
   std::ostringstream o;
+  if (s.code == 4) {
+    o << "alltoall_v: rank " << s.peer << " announced a segment of " << s.seen << " bytes for rank " << rank_
+      << ", which expected another size (op " << s.epoch << "); the communicator is now aborted";
+    throw BaguaError(ErrorKind::Communicator, o.str());
+  }
   static const char* what[] = {"", "wait for a peer to finish its previous op", "wait for a peer's data signal",
                                "grid barrier"};
   o << "a device-side " << (s.code < 4 ? what[s.code] : "wait") << " ran out after " << fmt_double(arena_->deadline_ms())
@@ -199,6 +204,10 @@ void SingleCommunicator::alltoall_v(const RawTensor& send, const std::vector<int
     BAGUA_CHECK(rc[p] >= 0 && rd[p] >= 0 && rd[p] + rc[p] <= recv.num_elements_allocated(), Communicator,
                 "alltoall_v: recv range of rank " << p << " is outside the tensor");
   }
+  if (PeerArena* a = p2p_arena())
+    if (fused::alltoall_v(*a, send.data_ptr(), send.bytes_allocated(), sc.data(), sd.data(), recv.data_ptr(),
+                          recv.bytes_allocated(), rc.data(), rd.data(), dtype_bytes(send.dtype()), (cudaStream_t)stream_))
+      return;
   transport_->alltoall_v(send.data_ptr(), sc, sd, recv.data_ptr(), rc, rd, send.dtype());
 }
 void SingleCommunicator::allgather(const RawTensor& send, RawTensor& recv) {

@@ -50,6 +50,13 @@ bool lp_ring(PeerArena& arena, void* x, void* w, void* l, void* r, int64_t n, DT
 bool allgather(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, cudaStream_t stream);
 // out[r] = chunk `rank` of rank r's `in`.
 bool alltoall(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, cudaStream_t stream);
+// All-to-all with per-pair sizes (counts and displacements in elements of `elem_bytes` bytes, one
+// entry per rank, as in the library call).  Peer-memory form only for a send buffer in the
+// symmetric heap — receivers pull their segments out of it —, which, like every symmetric
+// allocation, all ranks decide alike; `in` and `out` must not overlap.
+bool alltoall_v(PeerArena& arena, const void* in, size_t in_bytes, const int64_t* send_counts,
+                const int64_t* send_displs, void* out, size_t out_bytes, const int64_t* recv_counts,
+                const int64_t* recv_displs, size_t elem_bytes, cudaStream_t stream);
 // out = scale * sum_r (chunk `rank` of rank r's `in`); f32 / f16 / bf16.
 bool reduce_scatter(PeerArena& arena, const void* in, void* out, int64_t chunk_elems, DType dt, float scale,
                     cudaStream_t stream);

@@ -26,6 +26,10 @@
 //       small: everyone stores its input into the root's staging, the root sums in rank
 //       order; large: reduce-scatter among all ranks, then every rank hands its reduced
 //       chunk to the root (2(N-1)/N·S into the root instead of (N-1)·S).
+//   all-to-all with per-pair sizes (send buffer in the symmetric heap)
+//       every rank writes {offset, length} of each peer's segment into that peer's staging,
+//       signals, and pulls its own segments directly out of the peers' send buffers; a second
+//       signal exchange tells the senders that their buffers are no longer being read.
 //   barrier
 //       one CTA: signal every peer, wait for every peer.
 #include <cuda_runtime.h>
@@ -89,6 +93,11 @@ __global__ void __launch_bounds__(kThreads)
     reduce_twophase_body<T>(v, psync::real_launch(), in, out, nvec, max_chunk_vecs, root, scale);
   else
     reduce_direct_body<T>(v, psync::real_launch(), in, out, nvec, root, scale);
+}
+__global__ void __launch_bounds__(kThreads)
+    alltoall_v_sym_kernel(const __grid_constant__ ArenaView v, const __grid_constant__ ConstBytePtrs in, uint8_t* out,
+                          const __grid_constant__ VSegments seg) {
+  alltoall_v_sym_body(v, psync::real_launch(), in, out, seg);
 }
 __global__ void __launch_bounds__(kThreads) barrier_kernel(const __grid_constant__ ArenaView v) {
   barrier_body(v, psync::real_launch());
@@ -222,6 +231,40 @@ bool allgather(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, 
 
 bool alltoall(PeerArena& arena, const void* in, void* out, size_t chunk_bytes, cudaStream_t stream) {
   return exchange(arena, in, out, chunk_bytes, 1, stream);
+}
+
+bool alltoall_v(PeerArena& arena, const void* in, size_t in_bytes, const int64_t* send_counts,
+                const int64_t* send_displs, void* out, size_t out_bytes, const int64_t* recv_counts,
+                const int64_t* recv_displs, size_t elem_bytes, cudaStream_t stream) {
+  const int N = arena.nranks();
+  if (in_bytes == 0 || elem_bytes == 0) return false;
+  const char *a = (const char*)in, *b = (const char*)out;
+  if (a < b + out_bytes && b < a + in_bytes) return false;  // overlapping buffers: library path
+  void* pin[kArenaMaxRanks];
+  if (!arena.sym_translate(in, in_bytes, pin)) return false;
+  ConstBytePtrs p;
+  VSegments seg;
+  std::memset(&p, 0, sizeof(p));
+  std::memset(&seg, 0, sizeof(seg));
+  for (int r = 0; r < N; ++r) {
+    p.p[r] = (const uint8_t*)pin[r];
+    seg.send_off[r] = send_displs[r] * (int64_t)elem_bytes;
+    seg.send_bytes[r] = send_counts[r] * (int64_t)elem_bytes;
+    seg.recv_off[r] = recv_displs[r] * (int64_t)elem_bytes;
+    seg.recv_bytes[r] = recv_counts[r] * (int64_t)elem_bytes;
+    if (seg.send_off[r] < 0 || seg.send_bytes[r] < 0 || (size_t)(seg.send_off[r] + seg.send_bytes[r]) > in_bytes ||
+        seg.recv_off[r] < 0 || seg.recv_bytes[r] < 0 || (size_t)(seg.recv_off[r] + seg.recv_bytes[r]) > out_bytes)
+      throw BaguaError(ErrorKind::Communicator, "alltoall_v: a segment lies outside its tensor");
+  }
+  // Sizes differ from rank to rank, but block b of a rank pairs with block b of its peers: the
+  // grid must not depend on them.
+  const int grid = arena.max_blocks();
+  arena.ensure_staging((size_t)N * 16);
+  ArenaView v = arena.next_view(grid, 0);
+  alltoall_v_sym_kernel<<<grid, kThreads, 0, stream>>>(v, p, (uint8_t*)out, seg);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+  arena.count_launch();
+  return true;
 }
 
 bool reduce_scatter(PeerArena& arena, const void* in, void* out, int64_t chunk_elems, DType dt, float scale,

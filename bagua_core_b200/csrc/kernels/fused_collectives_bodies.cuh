@@ -384,6 +384,78 @@ __device__ __forceinline__ void reduce_twophase_body(const ArenaView& v, const L
   psync::cta_finish_op(v, L);
 }
 
+// ---------------------------------------------------------------------------------
+// all-to-all with per-pair sizes, send buffer in the symmetric heap (pull)
+// ---------------------------------------------------------------------------------
+// Byte offsets and lengths of the segments one rank sends to / receives from each rank.
+struct VSegments {
+  int64_t send_off[kArenaMaxRanks], send_bytes[kArenaMaxRanks];
+  int64_t recv_off[kArenaMaxRanks], recv_bytes[kArenaMaxRanks];
+};
+struct ConstBytePtrs {
+  const uint8_t* p[kArenaMaxRanks];
+};
+
+// Block b's share of a copy of `bytes` bytes, in the widest unit (16, 8, 4, 2 or 1 bytes) that
+// divides both addresses and the length: segments of whole 16-byte rows move as vectors, anything
+// else still arrives, only slower.
+template <typename U>
+__device__ __forceinline__ void copy_units(uint8_t* dst, const uint8_t* src, int64_t lo, int64_t hi) {
+  U* d = reinterpret_cast<U*>(dst);
+  const U* s = reinterpret_cast<const U*>(src);
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kThreads) d[i] = s[i];
+}
+__device__ __forceinline__ void copy_bytes_slice(const Launch& L, uint8_t* dst, const uint8_t* src, int64_t bytes) {
+  const uint64_t mix = (uint64_t)(uintptr_t)dst | (uint64_t)(uintptr_t)src | (uint64_t)bytes;
+  const int shift = (mix & 15) == 0 ? 4 : (mix & 7) == 0 ? 3 : (mix & 3) == 0 ? 2 : (mix & 1) == 0 ? 1 : 0;
+  int64_t lo, hi;
+  block_slice(L, 0, bytes >> shift, lo, hi);
+  switch (shift) {
+    case 4: copy_vecs(reinterpret_cast<uint4*>(dst), reinterpret_cast<const uint4*>(src), lo, hi); break;
+    case 3: copy_units<uint64_t>(dst, src, lo, hi); break;
+    case 2: copy_units<uint32_t>(dst, src, lo, hi); break;
+    case 1: copy_units<uint16_t>(dst, src, lo, hi); break;
+    default: copy_units<uint8_t>(dst, src, lo, hi); break;
+  }
+}
+
+// Every rank tells every peer where that peer's segment starts in its send buffer and how long
+// it is (two words in the peer's staging; only the receiver knows where the data goes), then
+// pulls its own segments straight out of the peers' send buffers.  First signal: "my table
+// entry for you is written and my send buffer is ready"; second signal: "I have finished
+// reading your send buffer".  A receiver that expected another length than the sender
+// announced moves the shorter of the two and reports status code 4.
+__device__ __forceinline__ void alltoall_v_sym_body(const ArenaView& v, const Launch& L, const ConstBytePtrs& in,
+                                                    uint8_t* out, const VSegments& seg) {
+  const int me = v.rank, N = v.nranks, t = threadIdx.x;
+  bool ok = psync::cta_wait_prev_done(v, L);  // the table lives in staging
+  if (ok) {
+    if (t < N && t != me) {
+      int64_t* entry = reinterpret_cast<int64_t*>(v.staging[t]) + 2 * me;
+      same_value_store(entry, seg.send_off[t]);  // every block writes the same two words
+      same_value_store(entry + 1, seg.send_bytes[t]);
+    }
+    psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
+  }
+  if (ok) {
+    const int64_t* table = reinterpret_cast<const int64_t*>(v.staging[me]);
+    for (int i = 0; i < N; ++i) {
+      const int r = (me + i) % N;
+      const int64_t off = r == me ? seg.send_off[me] : same_value_load(table + 2 * r);
+      int64_t bytes = r == me ? seg.send_bytes[me] : same_value_load(table + 2 * r + 1);
+      if (bytes != seg.recv_bytes[r]) {
+        if (t == 0) psync::record_timeout(v, 4, 0, (uint32_t)r, (uint32_t)bytes, (uint32_t)L.block);
+        bytes = bytes < seg.recv_bytes[r] ? bytes : seg.recv_bytes[r];
+      }
+      copy_bytes_slice(L, out + seg.recv_off[r], in.p[r] + off, bytes);
+    }
+    psync::cta_signal_phase(v, L, 1, all_peers_mask(v));
+    ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
+  }
+  psync::cta_finish_op(v, L);
+}
+
 __device__ __forceinline__ void barrier_body(const ArenaView& v, const Launch& L) {
   psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
   psync::cta_wait_phase(v, L, 0, all_peers_mask(v));

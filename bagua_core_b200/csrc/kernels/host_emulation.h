@@ -146,8 +146,12 @@ inline unsigned __float_as_uint(float f) {
 namespace bagua {
 template <typename T>
 inline void same_value_store(T* p, T v) {
-  static_assert(sizeof(T) == 2 || sizeof(T) == 4, "header words are 2 or 4 bytes");
-  if constexpr (sizeof(T) == 4) {
+  static_assert(sizeof(T) == 2 || sizeof(T) == 4 || sizeof(T) == 8, "header words are 2, 4 or 8 bytes");
+  if constexpr (sizeof(T) == 8) {
+    uint64_t bits;
+    std::memcpy(&bits, &v, 8);
+    __atomic_store_n(reinterpret_cast<uint64_t*>(p), bits, __ATOMIC_RELAXED);
+  } else if constexpr (sizeof(T) == 4) {
     uint32_t bits;
     std::memcpy(&bits, &v, 4);
     __atomic_store_n(reinterpret_cast<uint32_t*>(p), bits, __ATOMIC_RELAXED);
@@ -160,7 +164,10 @@ inline void same_value_store(T* p, T v) {
 template <typename T>
 inline T same_value_load(const T* p) {
   T v;
-  if constexpr (sizeof(T) == 4) {
+  if constexpr (sizeof(T) == 8) {
+    const uint64_t bits = __atomic_load_n(reinterpret_cast<const uint64_t*>(p), __ATOMIC_RELAXED);
+    std::memcpy(&v, &bits, 8);
+  } else if constexpr (sizeof(T) == 4) {
     const uint32_t bits = __atomic_load_n(reinterpret_cast<const uint32_t*>(p), __ATOMIC_RELAXED);
     std::memcpy(&v, &bits, 4);
   } else {

@@ -63,6 +63,7 @@ enum class Kind {
   ByteGrad,
   LpRing,
   AllReduceNvls,
+  AllToAllV,
   kCount
 };
 
@@ -134,6 +135,34 @@ std::vector<float> ring_difference(uint32_t k, int rank, int64_t n) {
   return d;
 }
 
+// All-to-all with per-pair sizes: op k moves a2av_bytes(k, s, d) bytes from s to d, in units of 16, 8,
+// 4, 2 or 1 bytes depending on the op, packed back to back on both sides.
+constexpr int kA2avMaxUnits = 37;
+int64_t a2av_unit(uint32_t k) { return (int64_t)16 >> (k % 5u); }
+int64_t a2av_bytes(uint32_t k, int s, int d) {
+  return a2av_unit(k) * (int64_t)((k * 7u + (uint32_t)s * 3u + (uint32_t)d * 5u) % (uint32_t)kA2avMaxUnits);
+}
+VSegments a2av_segments(uint32_t k, int me, int N) {
+  VSegments seg;
+  std::memset(&seg, 0, sizeof(seg));
+  int64_t so = 0, ro = 0;
+  for (int q = 0; q < N; ++q) {
+    seg.send_off[q] = so;
+    seg.send_bytes[q] = a2av_bytes(k, me, q);
+    so += seg.send_bytes[q];
+    seg.recv_off[q] = ro;
+    seg.recv_bytes[q] = a2av_bytes(k, q, me);
+    ro += seg.recv_bytes[q];
+  }
+  return seg;
+}
+uint8_t input_byte(uint32_t k, int rank, int64_t byte) {
+  const float f = value(k, rank, byte / 4);
+  uint8_t b[4];
+  std::memcpy(b, &f, 4);
+  return b[byte % 4];
+}
+
 ArenaView view_of(World& w, int rank, uint32_t epoch) {
   ArenaView v;
   std::memset(&v, 0, sizeof(v));
@@ -193,6 +222,7 @@ void prepare(World& w, int me, uint32_t k) {
     case Kind::AllReduceTwoShotInPlace:
     case Kind::AllReduceNvls: fill(r.out, k, me, op.vecs); break;
     case Kind::ByteGrad: fill(r.in, k, me, op.vecs * N); break;
+    case Kind::AllToAllV: fill(r.in, k, me, (int64_t)kA2avMaxUnits * N); break;
     case Kind::LpRing:
       for (int64_t i = 0; i < op.vecs; ++i)
         for (int l = 0; l < 4; ++l) {
@@ -265,6 +295,13 @@ void run_body(World& w, int me, int b, uint32_t k) {
       // the multicast address is the one inside rank 0's buffer
       uint4* mc = reinterpret_cast<uint4*>(w.ranks[0].out.data());
       nvls_bodies::allreduce_nvls_body<float>(v, L, mc, mc, c, op.scale);
+      break;
+    }
+    case Kind::AllToAllV: {
+      ConstBytePtrs src;
+      for (int q = 0; q < kArenaMaxRanks; ++q)
+        src.p[q] = q < w.N ? reinterpret_cast<const uint8_t*>(w.ranks[q].in.data()) : nullptr;
+      alltoall_v_sym_body(v, L, src, reinterpret_cast<uint8_t*>(r.out.data()), a2av_segments(k, me, w.N));
       break;
     }
     case Kind::ByteGrad: {
@@ -414,6 +451,27 @@ uint64_t verify(World& w, int me, uint32_t k) {
       }
       break;
     }
+    case Kind::AllToAllV: {
+      const VSegments seg = a2av_segments(k, me, N);
+      const uint8_t* got = reinterpret_cast<const uint8_t*>(r.out.data());
+      int64_t end = 0;
+      for (int q = 0; q < N; ++q) {
+        const VSegments theirs = a2av_segments(k, q, N);
+        for (int64_t j = 0; j < seg.recv_bytes[q]; ++j)
+          if (got[seg.recv_off[q] + j] != input_byte(k, q, theirs.send_off[me] + j)) ++bad;
+        end = seg.recv_off[q] + seg.recv_bytes[q];
+      }
+      // nothing behind the last segment may have been touched
+      const float poison_value = -12345.0f;
+      uint8_t pb[4];
+      std::memcpy(pb, &poison_value, 4);
+      for (int64_t j = end; j < (int64_t)(r.out.size() * sizeof(Vec)); ++j)
+        if (got[j] != pb[j % 4]) {
+          ++bad;
+          break;
+        }
+      break;
+    }
     case Kind::LpRing: {
       const int64_t n = 4 * c;
       const int left = (me + N - 1) % N, right = (me + 1) % N;
@@ -460,6 +518,7 @@ uint64_t verify(World& w, int me, uint32_t k) {
     case Kind::PairAverageSym: out_extent = c, in_extent = c; break;
     case Kind::AllReduceTwoShotInPlace:
     case Kind::AllReduceNvls: out_extent = c; break;
+    case Kind::AllToAllV: out_extent = (int64_t)r.out.size(), in_extent = (int64_t)kA2avMaxUnits * N; break;  // bytes checked above
     default: break;  // ReduceScatterInPlace, ByteGrad, LpRing, Barrier: `out` is not touched
   }
   for (int64_t i = out_extent; i < (int64_t)r.out.size(); ++i) expect(r.out, i, -12345.0f, -12345.0f, -12345.0f, -12345.0f);
@@ -506,6 +565,7 @@ int main(int argc, char** argv) {
     if ((op.kind == Kind::PairAverage || op.kind == Kind::PairAverageSym) && w.N % 2) op.kind = Kind::Barrier;  // pairs need an even world
     op.vecs = 1 + (int64_t)(rng() % 40);
     if (op.kind == Kind::ByteGrad || op.kind == Kind::LpRing) op.vecs = 4 * (1 + (int64_t)(rng() % 10));  // 16-element groups
+    if (op.kind == Kind::AllToAllV) op.vecs = kA2avMaxUnits;  // sizes the buffers; the op's own sizes come from a2av_bytes
     op.root = (int)(rng() % (uint32_t)w.N);
     op.scale = (rng() & 1) ? 1.0f : 0.5f;
     max_vecs = std::max(max_vecs, op.vecs);

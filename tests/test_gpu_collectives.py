@@ -340,6 +340,33 @@ def _p2p_vs_library(rank, world):
     assert torch.allclose(lib, p2p, rtol=1e-5, atol=1e-5)
     checked += 2
 
+    # all-to-all with per-pair sizes out of a symmetric send buffer: receivers pull their segments.
+    # Ragged element counts (16-byte rows do not line up) and a single-byte dtype (odd lengths).
+    def counts(src, dst, scale):
+        return scale * (1 + (3 * src + 5 * dst) % 7) + (src + dst) % 3
+
+    for dtype, scale in ((torch.float32, 1000), (torch.uint8, 333)):
+        send_all = sym_in if dtype == torch.float32 else comm.alloc_symmetric(8 * 7 * 400, torch.uint8)
+        if dtype == torch.uint8:
+            send_all.copy_(torch.randint(0, 255, (send_all.numel(),), generator=torch.Generator().manual_seed(rank),
+                                         dtype=torch.uint8))
+            torch.cuda.synchronize()
+            torch.distributed.barrier()
+        sc = [counts(rank, q, scale) for q in range(world)]
+        rc = [counts(q, rank, scale) for q in range(world)]
+        sd = [sum(sc[:q]) + q for q in range(world)]  # one element of slack between segments
+        rd = [sum(rc[:q]) for q in range(world)]
+        assert sd[-1] + sc[-1] <= send_all.numel()
+
+        def alltoall_v():
+            out = torch.zeros(sum(rc) + 5, dtype=dtype, device=dev)
+            comm.alltoall_v(T(send_all, "s"), sc, sd, T(out, "r"), rc, rd)
+            return out
+
+        lib, p2p = both(alltoall_v)
+        assert torch.equal(lib, p2p), ("alltoall_v", dtype)
+        checked += 1
+
     # barrier: returns only once every rank has arrived
     comm.set_p2p_collectives(True)
     for _ in range(3):
@@ -352,4 +379,4 @@ def _p2p_vs_library(rank, world):
 def test_p2p_collectives_match_the_library():
     world = min(torch.cuda.device_count(), int(os.environ.get("BAGUA_TEST_WORLD", "8")))
     res = run_ranks(_p2p_vs_library, world, backend="nccl", timeout=600)
-    assert all(r == 35 for r in res)
+    assert all(r == 37 for r in res)
