@@ -9,11 +9,13 @@
 // between ops, so ranks drift apart by whole ops), block b of every rank pairing with block
 // b of its peers, and the `done` chain that protects staging reuse.
 //
-//   device_emulation [nranks] [blocks] [ops] [seed] [absent_rank] [deadline_ms]
+//   device_emulation [nranks] [blocks] [ops] [seed] [absent_rank] [deadline_ms] [a2av_mismatch]
 //
 // With absent_rank >= 0 that rank never runs (a process that died between steps): the others'
 // waits must run out after deadline_ms, record what they waited for in the status record, and
-// return — the program then exits with code 3 instead of hanging.
+// return — the program then exits with code 3 instead of hanging.  With a2av_mismatch = 1 every op is
+// an all-to-all with per-pair sizes in which rank 0 announces a longer segment than rank 1 expects:
+// rank 1 must report status code 4 and still receive the bytes it asked for (run it with ops = 1).
 #include <barrier>
 #include <cstdio>
 #include <cstdlib>
@@ -142,6 +144,7 @@ int64_t a2av_unit(uint32_t k) { return (int64_t)16 >> (k % 5u); }
 int64_t a2av_bytes(uint32_t k, int s, int d) {
   return a2av_unit(k) * (int64_t)((k * 7u + (uint32_t)s * 3u + (uint32_t)d * 5u) % (uint32_t)kA2avMaxUnits);
 }
+bool g_a2av_mismatch = false;  // rank 0 announces one unit more for rank 1 than rank 1 expects
 VSegments a2av_segments(uint32_t k, int me, int N) {
   VSegments seg;
   std::memset(&seg, 0, sizeof(seg));
@@ -150,6 +153,7 @@ VSegments a2av_segments(uint32_t k, int me, int N) {
     seg.send_off[q] = so;
     seg.send_bytes[q] = a2av_bytes(k, me, q);
     so += seg.send_bytes[q];
+    if (g_a2av_mismatch && me == 0 && q == 1) seg.send_bytes[q] += a2av_unit(k);
     seg.recv_off[q] = ro;
     seg.recv_bytes[q] = a2av_bytes(k, q, me);
     ro += seg.recv_bytes[q];
@@ -553,6 +557,7 @@ int main(int argc, char** argv) {
   const uint32_t seed = argc > 4 ? (uint32_t)std::atoi(argv[4]) : 1;
   w.absent = argc > 5 ? std::atoi(argv[5]) : -1;
   if (argc > 6) w.deadline_ns = (uint64_t)std::atoll(argv[6]) * 1000000ull;
+  g_a2av_mismatch = argc > 7 && std::atoi(argv[7]) != 0;
   if (w.N < 2 || w.N > kArenaMaxRanks || w.G < 1 || w.G > 8 || n_ops < 1 || w.absent >= w.N) {
     std::fprintf(stderr, "usage: device_emulation [nranks 2..8] [blocks 1..8] [ops] [seed] [absent_rank] [deadline_ms]\n");
     return 2;
@@ -565,6 +570,7 @@ int main(int argc, char** argv) {
     if ((op.kind == Kind::PairAverage || op.kind == Kind::PairAverageSym) && w.N % 2) op.kind = Kind::Barrier;  // pairs need an even world
     op.vecs = 1 + (int64_t)(rng() % 40);
     if (op.kind == Kind::ByteGrad || op.kind == Kind::LpRing) op.vecs = 4 * (1 + (int64_t)(rng() % 10));  // 16-element groups
+    if (g_a2av_mismatch) op.kind = Kind::AllToAllV;
     if (op.kind == Kind::AllToAllV) op.vecs = kA2avMaxUnits;  // sizes the buffers; the op's own sizes come from a2av_bytes
     op.root = (int)(rng() % (uint32_t)w.N);
     op.scale = (rng() & 1) ? 1.0f : 0.5f;

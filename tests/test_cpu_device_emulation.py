@@ -6,7 +6,8 @@ The `*_body` device functions (`csrc/kernels/fused_allreduce_bodies.cuh`, `fused
 warp of 32 threads with a barrier, GCC atomics for the PTX release/acquire instructions, warp
 shuffles through a per-block exchange buffer) into tests/cpp/device_emulation.cc, which drives random
 sequences of all-reduce (one-shot, two-shot, symmetric), pair average, ByteGrad, the low-precision
-ring, all-gather, all-to-all, reduce-scatter, broadcast, scatter, gather, reduce and barrier —
+ring, all-gather, all-to-all (equal and per-pair sizes), reduce-scatter, broadcast, scatter, gather,
+reduce and barrier —
 staging and direct-peer-access forms, in-place forms — for N ranks x G blocks and checks every
 result exactly (the quantising kernels against a scalar restatement of MinMaxUInt8).  Built with
 -fsanitize=thread the same program checks that the signalling orders every payload access (no data
@@ -64,6 +65,17 @@ def test_a_missing_rank_makes_the_others_time_out_and_return(tmp_path):
         assert run.returncode == 3, run.stdout + run.stderr
         assert f"rank {absent} absent, every other rank returned" in run.stdout
         assert "wait status code 0" not in run.stdout
+
+
+def test_alltoall_v_reports_sizes_that_sender_and_receiver_disagree_on(tmp_path):
+    """Rank 0 announces a longer segment than rank 1 expects: rank 1 records status code 4 with the
+    sender's rank, still receives exactly the bytes it asked for, and every rank returns."""
+    exe = _build(tmp_path, None)
+    for nranks in (2, 5):
+        run = subprocess.run([exe, str(nranks), "2", "1", "3", "-1", "5000", "1"], capture_output=True, text=True,
+                             timeout=120)
+        assert run.returncode == 1, run.stdout + run.stderr
+        assert "0 wrong vectors, wait status 4, 1 failures" in run.stdout, run.stdout + run.stderr
 
 
 def test_device_bodies_are_race_free_under_thread_sanitizer(tmp_path):
