@@ -766,6 +766,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           },
           py::arg("x"), py::arg("weight"), py::arg("left"), py::arg("right"), py::arg("blocks"))
       .def(
+          "alltoall_v",
+          [](fused::EmulatedArena& a, std::vector<at::Tensor> in, std::vector<at::Tensor> out,
+             std::vector<int64_t> bytes) {
+            std::vector<const void*> pi;
+            std::vector<void*> po;
+            const size_t n = (size_t)a.nranks();
+            BAGUA_CHECK(in.size() == n && out.size() == n && bytes.size() == n * n, Tensor,
+                        "one input and one output per rank and an N x N table of byte counts expected");
+            for (size_t r = 0; r < n; ++r) {
+              BAGUA_CHECK(in[r].is_cuda() && in[r].is_contiguous() && out[r].is_cuda() && out[r].is_contiguous(), Tensor,
+                          "buffers must be contiguous CUDA tensors");
+              int64_t sent = 0, received = 0;
+              for (size_t q = 0; q < n; ++q) {
+                sent += bytes[r * n + q];
+                received += bytes[q * n + r];
+              }
+              BAGUA_CHECK((size_t)sent <= in[r].nbytes() && (size_t)received <= out[r].nbytes(), Tensor,
+                          "the size table does not fit the buffers of rank " << r);
+              pi.push_back(in[r].data_ptr());
+              po.push_back(out[r].data_ptr());
+            }
+            py::gil_scoped_release rel;
+            a.alltoall_v(pi, po, bytes, 4);
+          },
+          py::arg("inputs"), py::arg("outputs"), py::arg("bytes"),
+          "All-to-all with per-pair sizes: rank s sends bytes[s * N + d] bytes to rank d, segments packed back "
+          "to back on both sides.")
+      .def(
           "collective",
           [](fused::EmulatedArena& a, const std::string& kind, std::vector<at::Tensor> in, std::vector<at::Tensor> out,
              bool symmetric, int root, bool average, int blocks) {

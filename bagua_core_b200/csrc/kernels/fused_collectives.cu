@@ -152,6 +152,15 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+__global__ void __launch_bounds__(kThreads)
+    alltoall_v_emu_kernel(const EmuRank* __restrict__ ranks, const VSegments* __restrict__ segments, int blocks) {
+  const int rank = (int)blockIdx.x / blocks;
+  const EmuRank& e = ranks[rank];
+  ConstBytePtrs p;
+  for (int r = 0; r < kArenaMaxRanks; ++r) p.p[r] = (const uint8_t*)e.sym_in[r];
+  alltoall_v_sym_body(e.view, Launch{(int)(blockIdx.x % blocks), blocks}, p, (uint8_t*)e.out, segments[rank]);
+}
+
 // Largest staging an exchange may ask for; bigger requests take the library path.
 constexpr size_t kMaxStaging = (size_t)2 << 30;
 
@@ -372,6 +381,11 @@ bool barrier(PeerArena& arena, cudaStream_t stream) {
   BAGUA_CUDA_CHECK(cudaGetLastError());
   arena.count_launch();
   return true;
+}
+
+void emu_launch_alltoall_v(const EmuRank* dev, const void* segments, int nranks, int blocks) {
+  static_assert(sizeof(VSegments) == 4 * kArenaMaxRanks * sizeof(int64_t), "EmulatedArena::alltoall_v mirrors this layout");
+  coop_launch_all_ranks(alltoall_v_emu_kernel, nranks * blocks, dev, (const VSegments*)segments, blocks);
 }
 
 void emu_launch_collective(const EmuRank* dev, int nranks, int blocks, EmuCollective kind, int64_t cvec, DType dt,

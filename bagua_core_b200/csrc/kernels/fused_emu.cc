@@ -195,6 +195,51 @@ void EmulatedArena::collective(EmuCollective kind, const std::vector<const void*
   finish("collective");
 }
 
+void EmulatedArena::alltoall_v(const std::vector<const void*>& in, const std::vector<void*>& out,
+                               const std::vector<int64_t>& bytes, int blocks) {
+  const size_t N = (size_t)nranks_;
+  BAGUA_CHECK(in.size() == N && out.size() == N && bytes.size() == N * N, Tensor,
+              "emulated alltoall_v: one input and output per rank and an N x N size table expected");
+  // the layout of fused::collectives::VSegments: four arrays of kArenaMaxRanks 64-bit words
+  struct Segments {
+    int64_t send_off[kArenaMaxRanks], send_bytes[kArenaMaxRanks], recv_off[kArenaMaxRanks], recv_bytes[kArenaMaxRanks];
+  };
+  std::vector<Segments> seg(N);
+  std::vector<EmuRank> host(N);
+  for (auto& h : host) std::memset(&h, 0, sizeof(h));
+  for (size_t r = 0; r < N; ++r) {
+    std::memset(&seg[r], 0, sizeof(Segments));
+    int64_t so = 0, ro = 0;
+    for (size_t q = 0; q < N; ++q) {
+      BAGUA_CHECK(bytes[r * N + q] >= 0, Tensor, "emulated alltoall_v: negative size");
+      seg[r].send_off[q] = so;
+      seg[r].send_bytes[q] = bytes[r * N + q];
+      so += bytes[r * N + q];
+      seg[r].recv_off[q] = ro;
+      seg[r].recv_bytes[q] = bytes[q * N + r];
+      ro += bytes[q * N + r];
+    }
+    host[r].in = in[r];
+    host[r].out = out[r];
+    for (size_t q = 0; q < N; ++q) host[r].sym_in[q] = in[q];
+  }
+  EmuRank* dev = prepare(host, blocks, 0, N * 16);
+  void* dseg = nullptr;
+  BAGUA_CUDA_CHECK(cudaMalloc(&dseg, sizeof(Segments) * N));
+  cudaError_t e = cudaMemcpy(dseg, seg.data(), sizeof(Segments) * N, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) {
+    try {
+      emu_launch_alltoall_v(dev, dseg, nranks_, blocks);
+      finish("alltoall_v");
+    } catch (...) {
+      cudaFree(dseg);
+      throw;
+    }
+  }
+  cudaFree(dseg);
+  BAGUA_CUDA_CHECK(e);
+}
+
 void EmulatedArena::bytegrad(const std::vector<void*>& buckets, int64_t n, DType dt, bool average, int blocks) {
   BAGUA_CHECK((int)buckets.size() == nranks_ && n % ((int64_t)16 * nranks_) == 0, Tensor,
               "emulated ByteGrad: n must be a multiple of 16 * nranks");

@@ -74,6 +74,10 @@ class EmulatedArena {
   // sum lands in out[root].  Barrier: no buffers.
   void collective(EmuCollective kind, const std::vector<const void*>& in, const std::vector<void*>& out,
                   size_t chunk_bytes, DType dt, float scale, int root, bool symmetric, int blocks);
+  // All-to-all with per-pair sizes: rank s sends bytes[s * N + d] bytes to rank d; segments are
+  // packed back to back in in[s] (in destination order) and in out[d] (in source order).
+  void alltoall_v(const std::vector<const void*>& in, const std::vector<void*>& out,
+                  const std::vector<int64_t>& bytes, int blocks);
   void set_deadline_ms(double ms) { deadline_ns_ = (uint64_t)(ms * 1e6); }
   uint32_t epoch() const { return epoch_; }
 
@@ -101,6 +105,8 @@ void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t
 // the root rank for the broadcasts; root | in_place << 8 for scatter, gather and reduce.
 void emu_launch_collective(const EmuRank* dev, int nranks, int blocks, EmuCollective kind, int64_t cvec, DType dt,
                            int aux, float scale);
+// `segments`: device array of one fused::collectives::VSegments per rank.
+void emu_launch_alltoall_v(const EmuRank* dev, const void* segments, int nranks, int blocks);
 void emu_launch_bytegrad(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
                          size_t slot_bytes, size_t scratch_off);
 void emu_launch_lp_ring(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, size_t slot_bytes,

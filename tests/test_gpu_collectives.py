@@ -79,6 +79,30 @@ def test_emulated_alltoall(nranks, symmetric):
 
 
 @pytest.mark.parametrize("nranks", [2, 4, 8])
+@pytest.mark.parametrize("unit", [16, 4, 1])
+def test_emulated_alltoall_v(nranks, unit):
+    """Per-pair sizes in multiples of `unit` bytes (16: whole vectors; 4 and 1: the narrower copy paths),
+    some of them zero; receivers pull their segments out of the senders' buffers."""
+    arena = _arena(nranks)
+    for scale in (1, 300):
+        table = [unit * scale * ((3 * s + 5 * d + scale) % 7) for s in range(nranks) for d in range(nranks)]
+        sent = [sum(table[s * nranks:(s + 1) * nranks]) for s in range(nranks)]
+        received = [sum(table[s * nranks + d] for s in range(nranks)) for d in range(nranks)]
+        g = torch.Generator().manual_seed(scale + unit)
+        xs = [torch.randint(0, 256, (max(sent[r], 16),), generator=g, dtype=torch.uint8).cuda() for r in range(nranks)]
+        outs = [torch.full((received[r] + 32,), 7, dtype=torch.uint8, device="cuda") for r in range(nranks)]
+        arena.alltoall_v(xs, outs, table)
+        for d in range(nranks):
+            parts = []
+            for s in range(nranks):
+                start = sum(table[s * nranks:s * nranks + d])
+                parts.append(xs[s][start:start + table[s * nranks + d]])
+            ref = torch.cat(parts)
+            assert torch.equal(outs[d][:received[d]], ref), (nranks, unit, scale, d)
+            assert torch.all(outs[d][received[d]:] == 7)  # nothing behind the last segment was touched
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
 @pytest.mark.parametrize("symmetric", [False, True])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 def test_emulated_reduce_scatter(nranks, symmetric, dt):
