@@ -22,6 +22,40 @@ namespace bagua {
 
 namespace {
 
+// ---- the CUDA runtime as a MulticastPlatform ------------------------------------------
+bool cuda_select_device(int device) { return cudaSetDevice(device) == cudaSuccess && cudaFree(nullptr) == cudaSuccess; }
+void* cuda_driver_entry(const char* name) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult st;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &st) != cudaSuccess || st != cudaDriverEntryPointSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+void* cuda_scratch_alloc(size_t bytes) {
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+void cuda_scratch_free(void* p) { cudaFree(p); }
+bool cuda_to_scratch(void* dst, const void* src, size_t bytes, cudaStream_t stream) {
+  return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+}
+bool cuda_from_scratch(void* dst, const void* src, size_t bytes, cudaStream_t stream) {
+  return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream) == cudaSuccess &&
+         cudaStreamSynchronize(stream) == cudaSuccess;
+}
+bool cuda_clear(void* mapped, size_t bytes, cudaStream_t stream) {
+  return cudaMemsetAsync(mapped, 0, bytes, stream) == cudaSuccess && cudaStreamSynchronize(stream) == cudaSuccess;
+}
+const MulticastPlatform kCudaPlatform = {cuda_select_device, cuda_driver_entry, cuda_scratch_alloc, cuda_scratch_free,
+                                         cuda_to_scratch,    cuda_from_scratch, cuda_clear};
+const MulticastPlatform* g_platform = &kCudaPlatform;
+
 // Driver entry points, resolved through the runtime so that nothing links against libcuda.
 struct Driver {
   // pointer types come from the driver header's own declarations
@@ -46,11 +80,8 @@ struct Driver {
 
   template <typename F>
   bool get(const char* name, F*& fn, std::string* why) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult st;
-    cudaError_t e = cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &st);
-    if (e != cudaSuccess || st != cudaDriverEntryPointSuccess || !p) {
-      cudaGetLastError();
+    void* p = g_platform->driver_entry(name);
+    if (!p) {
       *why = std::string("driver entry point ") + name + " is not available";
       return false;
     }
@@ -127,22 +158,16 @@ struct Note {
 
 // All-gathers `mine` through device buffers on the transport (the same way the arena trades its IPC handles).
 bool gather_notes(Transport& t, int rank, int nranks, cudaStream_t stream, const Note& mine, std::vector<Note>* all) {
-  void* dev = nullptr;
-  if (cudaMalloc(&dev, sizeof(Note) * (size_t)nranks) != cudaSuccess) {
-    cudaGetLastError();
-    return false;
-  }
+  const MulticastPlatform& pf = *g_platform;
+  void* dev = pf.scratch_alloc(sizeof(Note) * (size_t)nranks);
+  if (!dev) return false;
   all->assign((size_t)nranks, Note{});
-  bool ok = cudaMemcpyAsync((char*)dev + sizeof(Note) * (size_t)rank, &mine, sizeof(Note), cudaMemcpyHostToDevice,
-                            stream) == cudaSuccess;
+  bool ok = pf.to_scratch((char*)dev + sizeof(Note) * (size_t)rank, &mine, sizeof(Note), stream);
   if (ok) {
     t.allgather((char*)dev + sizeof(Note) * (size_t)rank, dev, (int64_t)sizeof(Note), DType::U8);
-    ok = cudaMemcpyAsync(all->data(), dev, sizeof(Note) * (size_t)nranks, cudaMemcpyDeviceToHost, stream) ==
-             cudaSuccess &&
-         cudaStreamSynchronize(stream) == cudaSuccess;
+    ok = pf.from_scratch(all->data(), dev, sizeof(Note) * (size_t)nranks, stream);
   }
-  cudaFree(dev);
-  if (!ok) cudaGetLastError();
+  pf.scratch_free(dev);
   return ok;
 }
 
@@ -156,6 +181,8 @@ int steal_fd(int pid, int fd) {
 }
 
 }  // namespace
+
+void set_multicast_platform(const MulticastPlatform* platform) { g_platform = platform ? platform : &kCudaPlatform; }
 
 bool create_multicast_slab(Transport& transport, int rank, int nranks, int device, cudaStream_t stream, size_t bytes,
                            MulticastSlab* out, std::string* why) {
@@ -197,7 +224,9 @@ bool create_multicast_slab(Transport& transport, int rank, int nranks, int devic
   };
 
   // 1. capability
-  bool ok = cudaSetDevice(device) == cudaSuccess && cudaFree(nullptr) == cudaSuccess && d.load(&local_why);
+  bool ok = g_platform->select_device(device);
+  if (!ok) local_why = "the device cannot be selected";
+  ok = ok && d.load(&local_why);
   if (ok) ok = check(d.DeviceGet(&s.dev, device), "cuDeviceGet");
   if (ok) {
     int mc = 0, fd = 0;
@@ -209,7 +238,6 @@ bool create_multicast_slab(Transport& transport, int rank, int nranks, int devic
       local_why = mc ? "memory cannot be exported as a file descriptor" : "the device does not support multicast";
     }
   }
-  if (!ok) cudaGetLastError();
   if (!agree(ok, "capability check")) return false;
 
   // 2. size
@@ -337,11 +365,8 @@ bool create_multicast_slab(Transport& transport, int rank, int nranks, int devic
   }
   if (ok) ok = check(d.MemSetAccess(s.mc_va, s.bytes, &access, 1), "enable access to the multicast mapping");
   if (ok) {
-    ok = cudaMemsetAsync((void*)s.va[rank], 0, s.bytes, stream) == cudaSuccess &&
-         cudaStreamSynchronize(stream) == cudaSuccess;
-    if (!ok) {
-      local_why = std::string("clearing the slab: ") + cudaGetErrorString(cudaGetLastError());
-    }
+    ok = g_platform->clear((void*)(uintptr_t)s.va[rank], s.bytes, stream);
+    if (!ok) local_why = "clearing the slab failed";
   }
   if (!agree(ok, "mapping")) return false;
 

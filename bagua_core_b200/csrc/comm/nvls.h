@@ -34,6 +34,21 @@ struct MulticastSlab {
   void* impl = nullptr;  // driver handles, for teardown
 };
 
+// The CUDA runtime calls and the driver lookup that the setup uses, as a table: with a stand-in
+// for it the whole sequence — above all the agreement between ranks after every step and the
+// clean-up when a step fails — runs on a machine without a GPU (tests/cpp/nvls_setup.cc).
+struct MulticastPlatform {
+  bool (*select_device)(int device);
+  void* (*driver_entry)(const char* name);  // nullptr: the driver does not have it
+  void* (*scratch_alloc)(size_t bytes);     // memory the transport can all-gather through; nullptr on failure
+  void (*scratch_free)(void* p);
+  bool (*to_scratch)(void* dst, const void* src, size_t bytes, cudaStream_t stream);
+  bool (*from_scratch)(void* dst, const void* src, size_t bytes, cudaStream_t stream);  // finished on return
+  bool (*clear)(void* mapped, size_t bytes, cudaStream_t stream);                       // zero-fill, finished on return
+};
+// nullptr restores the CUDA runtime.  Call while no setup is running.
+void set_multicast_platform(const MulticastPlatform* platform);
+
 // Collective.  `bytes` is rounded up to the multicast granularity.  Returns false on every
 // rank alike, with the first failing step in `why`, and leaves nothing allocated.
 bool create_multicast_slab(Transport& transport, int rank, int nranks, int device, cudaStream_t stream, size_t bytes,
