@@ -544,6 +544,24 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       py::arg("param"), py::arg("grad"), py::arg("momentum_buffer"), py::arg("lr"), py::arg("momentum"),
       py::arg("dampening"), py::arg("weight_decay"), py::arg("nesterov"), py::arg("first_step"), py::arg("stream"));
 
+  m.def(
+      "k_sgd_momentum_flat_shadow",
+      [](at::Tensor p, at::Tensor g, at::Tensor buf, at::Tensor shadow, float lr, float momentum, float dampening,
+         float wd, bool nesterov, bool first_step, uint64_t stream) {
+        check_pair(p, g);
+        check_pair(p, buf);
+        BAGUA_CHECK(p.scalar_type() == at::kFloat, Tensor, "fused SGD works on float32 flat buffers");
+        BAGUA_CHECK(shadow.scalar_type() == at::kBFloat16 && shadow.is_contiguous() && shadow.numel() == p.numel() &&
+                        shadow.device() == p.device(),
+                    Tensor, "the shadow must be a contiguous bf16 tensor of the parameters' size on their device");
+        kernels::sgd_momentum_flat_shadow((float*)p.data_ptr(), (const float*)g.data_ptr(), (float*)buf.data_ptr(),
+                                          shadow.data_ptr(), p.numel(), lr, momentum, dampening, wd, nesterov,
+                                          first_step, ctx_of(p, stream));
+      },
+      py::arg("param"), py::arg("grad"), py::arg("momentum_buffer"), py::arg("bf16_shadow"), py::arg("lr"),
+      py::arg("momentum"), py::arg("dampening"), py::arg("weight_decay"), py::arg("nesterov"), py::arg("first_step"),
+      py::arg("stream"));
+
   // ---- fused bias + ReLU for channels-last bf16 activations (model-side kernels) ----
   // An activation is either [rows, C] contiguous or [N, C, H, W] in channels-last memory format.
   auto rows_and_channels = [](const at::Tensor& t, int64_t* rows, int* C) {

@@ -211,6 +211,13 @@ void sgd_momentum_flat(float* p, const float* g, float* buf, int64_t n, float lr
   }
 }
 
+void sgd_momentum_flat_shadow(float* p, const float* g, float* buf, void* shadow, int64_t n, float lr, float momentum,
+                              float dampening, float wd, bool nesterov, bool first_step) {
+  sgd_momentum_flat(p, g, buf, n, lr, momentum, dampening, wd, nesterov, first_step);
+  uint16_t* h = static_cast<uint16_t*>(shadow);
+  for (int64_t i = 0; i < n; ++i) h[i] = float_to_bf16(p[i]);
+}
+
 }  // namespace cpu
 
 // ---------------------------------------------------------------------------------
@@ -279,6 +286,14 @@ void sgd_momentum_flat(float* p, const float* g, float* buf, int64_t n, float lr
   if (n <= 0) return;
   c.is_cuda() ? cuda::sgd_momentum_flat(p, g, buf, n, lr, momentum, dampening, wd, nesterov, first_step, c.stream)
               : cpu::sgd_momentum_flat(p, g, buf, n, lr, momentum, dampening, wd, nesterov, first_step);
+}
+
+void sgd_momentum_flat_shadow(float* p, const float* g, float* buf, void* shadow, int64_t n, float lr, float momentum,
+                              float dampening, float wd, bool nesterov, bool first_step, const Ctx& c) {
+  if (n <= 0) return;
+  c.is_cuda()
+      ? cuda::sgd_momentum_flat_shadow(p, g, buf, shadow, n, lr, momentum, dampening, wd, nesterov, first_step, c.stream)
+      : cpu::sgd_momentum_flat_shadow(p, g, buf, shadow, n, lr, momentum, dampening, wd, nesterov, first_step);
 }
 
 }  // namespace kernels

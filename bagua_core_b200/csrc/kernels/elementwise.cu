@@ -234,6 +234,53 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// The same step with a bf16 copy of every updated parameter (a kernel of its own, so that the
+// plain step keeps its code): 4 parameters per thread-iteration, their bf16 values go out as
+// one 8-byte store.
+__global__ void __launch_bounds__(kThreads)
+    sgd_shadow_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ buf,
+                      __nv_bfloat16* __restrict__ shadow, int64_t n, float lr, float momentum, float dampening, float wd,
+                      bool nesterov, bool first, bool vec) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  auto upd = [&](float& pv, float gv, float& bv) {
+    float d = gv + wd * pv;
+    if (momentum != 0.f) {
+      float b = first ? d : momentum * bv + (1.f - dampening) * d;
+      bv = b;
+      d = nesterov ? d + momentum * b : b;
+    }
+    pv -= lr * d;
+  };
+  auto one = [&](int64_t i) {
+    float bv = (momentum != 0.f && !first) ? buf[i] : 0.f;
+    upd(p[i], g[i], bv);
+    if (momentum != 0.f) buf[i] = bv;
+    shadow[i] = __float2bfloat16_rn(p[i]);
+  };
+  if (vec) {
+    const int64_t nv = n / 4;
+    for (int64_t i = tid; i < nv; i += stride) {
+      float4 pv = reinterpret_cast<float4*>(p)[i];
+      float4 gv = reinterpret_cast<const float4*>(g)[i];
+      float4 bv = (momentum != 0.f && !first) ? reinterpret_cast<float4*>(buf)[i] : make_float4(0, 0, 0, 0);
+      upd(pv.x, gv.x, bv.x);
+      upd(pv.y, gv.y, bv.y);
+      upd(pv.z, gv.z, bv.z);
+      upd(pv.w, gv.w, bv.w);
+      reinterpret_cast<float4*>(p)[i] = pv;
+      if (momentum != 0.f) reinterpret_cast<float4*>(buf)[i] = bv;
+      uint2 h;
+      *reinterpret_cast<__nv_bfloat162*>(&h.x) = __floats2bfloat162_rn(pv.x, pv.y);
+      *reinterpret_cast<__nv_bfloat162*>(&h.y) = __floats2bfloat162_rn(pv.z, pv.w);
+      reinterpret_cast<uint2*>(shadow)[i] = h;
+    }
+    for (int64_t i = nv * 4 + tid; i < n; i += stride) one(i);
+  } else {
+    for (int64_t i = tid; i < n; i += stride) one(i);
+  }
+}
+
 }  // namespace
 
 void divide_inplace(void* x, DType dt, int64_t n, float d, cudaStream_t s) {
@@ -270,6 +317,15 @@ void sgd_momentum_flat(float* p, const float* g, float* buf, int64_t n, float lr
   const bool vec = ((uintptr_t)p % 16 == 0) && ((uintptr_t)g % 16 == 0) && ((uintptr_t)buf % 16 == 0);
   sgd_kernel<<<grid_for(vec ? n / 4 + 1 : n), kThreads, 0, s>>>(p, g, buf, n, lr, momentum, dampening, wd, nesterov,
                                                                  first_step, vec);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
+}
+
+void sgd_momentum_flat_shadow(float* p, const float* g, float* buf, void* shadow, int64_t n, float lr, float momentum,
+                              float dampening, float wd, bool nesterov, bool first_step, cudaStream_t s) {
+  const bool vec = ((uintptr_t)p % 16 == 0) && ((uintptr_t)g % 16 == 0) && ((uintptr_t)buf % 16 == 0) &&
+                   ((uintptr_t)shadow % 8 == 0);
+  sgd_shadow_kernel<<<grid_for(vec ? n / 4 + 1 : n), kThreads, 0, s>>>(p, g, buf, (__nv_bfloat16*)shadow, n, lr, momentum,
+                                                                        dampening, wd, nesterov, first_step, vec);
   BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 

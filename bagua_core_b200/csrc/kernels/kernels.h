@@ -73,6 +73,11 @@ MinMaxGrid minmax_grid(float mn, float mx);
 void sgd_momentum_flat(float* p, const float* g, float* buf, int64_t n, float lr, float momentum,
                        float dampening, float weight_decay, bool nesterov, bool first_step,
                        const Ctx& c);
+// The same step, which also writes every updated parameter rounded to bf16 into `shadow`
+// (n bf16 values): a model that computes in bf16 then reads its weights from there instead
+// of casting the fp32 master copy again in every forward pass.
+void sgd_momentum_flat_shadow(float* p, const float* g, float* buf, void* shadow, int64_t n, float lr, float momentum,
+                              float dampening, float weight_decay, bool nesterov, bool first_step, const Ctx& c);
 
 }  // namespace kernels
 }  // namespace bagua

@@ -22,6 +22,8 @@ void decompress_minmax_u8(const uint8_t* in, size_t in_bytes, int64_t chunk, int
                           cudaStream_t s);
 void sgd_momentum_flat(float* p, const float* g, float* buf, int64_t n, float lr, float momentum, float dampening,
                        float wd, bool nesterov, bool first_step, cudaStream_t s);
+void sgd_momentum_flat_shadow(float* p, const float* g, float* buf, void* shadow, int64_t n, float lr, float momentum,
+                              float dampening, float wd, bool nesterov, bool first_step, cudaStream_t s);
 
 }  // namespace cuda
 }  // namespace kernels

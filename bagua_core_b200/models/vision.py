@@ -15,7 +15,9 @@ class VGG16(nn.Module):
     `fused_ops=True` builds every conv+ReLU pair as one `ConvBiasReLU` module (bias add, ReLU and the
     bias-gradient reduction in this package's own kernels) and folds every pooling layer into the
     block before it (`ConvBiasReLUPool`: no index tensor, one pass each way); parameter names change
-    from `features.<2k>.weight` to the fused module's index, values and shapes do not."""
+    from `features.<2k>.weight` to the fused module's index, values and shapes do not.  The classifier's
+    layers become `ShadowLinear`, which is `nn.Linear` unless the optimizer maintains bf16 copies of the
+    weights (`FlatSGD(bf16_shadow=True)`)."""
 
     def __init__(self, num_classes: int = 1000, dropout: float = 0.5, fused_ops: bool = False):
         super().__init__()
@@ -35,10 +37,14 @@ class VGG16(nn.Module):
                 c_in = v
         self.features = nn.Sequential(*layers)
         self.avgpool = nn.AdaptiveAvgPool2d((7, 7))
+        if fused_ops:
+            from ..ops.fused_linear import ShadowLinear as Linear  # nn.Linear unless the optimizer keeps bf16 weights
+        else:
+            Linear = nn.Linear
         self.classifier = nn.Sequential(
-            nn.Linear(512 * 7 * 7, 4096), nn.ReLU(inplace=True), nn.Dropout(dropout),
-            nn.Linear(4096, 4096), nn.ReLU(inplace=True), nn.Dropout(dropout),
-            nn.Linear(4096, num_classes),
+            Linear(512 * 7 * 7, 4096), nn.ReLU(inplace=True), nn.Dropout(dropout),
+            Linear(4096, 4096), nn.ReLU(inplace=True), nn.Dropout(dropout),
+            Linear(4096, num_classes),
         )
         for m in self.modules():
             if isinstance(m, nn.Conv2d):

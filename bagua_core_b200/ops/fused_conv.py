@@ -17,6 +17,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .._native import C as _C
+from . import shadow as _shadow
 
 
 # Kernels of this module launched so far in this process (benchmarks report it).
@@ -42,6 +43,15 @@ def _autocast_inputs(*tensors):
     return tuple(t.to(dtype) if t.is_floating_point() else t for t in tensors)
 
 
+def _autocast_weight(weight: torch.Tensor) -> torch.Tensor:
+    """The weight in the autocast dtype; taken from the optimizer's bf16 copy when that is current
+    (`bagua_core_b200.ops.shadow`), so that the forward pass does not cast it again."""
+    dev = weight.device.type
+    if not torch.is_autocast_enabled(dev):
+        return weight
+    return _shadow.cast_weight(weight, torch.get_autocast_dtype(dev))
+
+
 class _ConvBiasReLUFn(torch.autograd.Function):
     """Runs in the autocast dtype where autocast is on (parameters stay fp32 outside; autograd
     casts the gradients returned here back to the parameters' dtype)."""
@@ -49,7 +59,8 @@ class _ConvBiasReLUFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, stride, padding, dilation, groups):
         ctx.conf = (stride, padding, dilation, groups)
-        x, weight, bias = _autocast_inputs(x, weight, bias)
+        x, bias = _autocast_inputs(x, bias)
+        weight = _autocast_weight(weight)
         with torch.autocast(x.device.type, enabled=False):
             x = x.contiguous(memory_format=torch.channels_last)
             z = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)
@@ -82,7 +93,8 @@ class _ConvBiasReLUPoolFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, stride, padding, dilation, groups):
         ctx.conf = (stride, padding, dilation, groups)
-        x, weight, bias = _autocast_inputs(x, weight, bias)
+        x, bias = _autocast_inputs(x, bias)
+        weight = _autocast_weight(weight)
         with torch.autocast(x.device.type, enabled=False):
             x = x.contiguous(memory_format=torch.channels_last)
             y = torch.ops.aten.convolution(x, weight, None, stride, padding, dilation, False, [0, 0], groups)

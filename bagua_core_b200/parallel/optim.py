@@ -32,10 +32,17 @@ class FlatSGD(torch.optim.Optimizer):
     """torch.optim.SGD semantics (momentum, dampening, weight decay, Nesterov).
 
     Before `with_bagua` attaches it (or for parameters outside any bucket) it updates
-    parameter by parameter with the same kernel."""
+    parameter by parameter with the same kernel.
+
+    `bf16_shadow=True`: for buckets of gradients (algorithms that do not communicate weights) the
+    step kernel also writes every updated parameter rounded to bf16 into a second flat buffer, and
+    each parameter gets a view of it (`bagua_core_b200.ops.shadow`); `ConvBiasReLU`,
+    `ConvBiasReLUPool` and `ShadowLinear` under bf16 autocast then read their weights from there
+    instead of casting the fp32 master weights in every forward pass.  After changing a parameter
+    by other means than this optimizer or torch's in-place ops, call `refresh_bf16()`."""
 
     def __init__(self, params, lr: float = 1e-3, momentum: float = 0.0, dampening: float = 0.0,
-                 weight_decay: float = 0.0, nesterov: bool = False):
+                 weight_decay: float = 0.0, nesterov: bool = False, bf16_shadow: bool = False):
         if nesterov and (momentum <= 0 or dampening != 0):
             raise ValueError("Nesterov momentum requires a momentum and zero dampening")
         defaults = dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay, nesterov=nesterov)
@@ -44,11 +51,19 @@ class FlatSGD(torch.optim.Optimizer):
         self._attached_ids = set()
         self._steps = 0
         self.kernel_launches = 0
+        # bf16 copies of the weights, written by the step kernel (see bagua_core_b200.ops.shadow)
+        self.bf16_shadow = bf16_shadow
+        self.shadows_valid = False
+        self._shadowed: List[torch.Tensor] = []
 
     # called by BaguaModule after it has built gradient buckets
     def bagua_attach(self, bm):
         self._flat.clear()
         self._attached_ids.clear()
+        for p in self._shadowed:
+            p._bagua_bf16 = None
+        self._shadowed.clear()
+        self.shadows_valid = False
         for b in bm.bagua_buckets:
             if b.flattened is not None and b.flattened.dtype == torch.float32 and all(
                     t.kind == "weight" for t in b.tensors):
@@ -80,7 +95,20 @@ class FlatSGD(torch.optim.Optimizer):
                     p.set_(flat_p.untyped_storage(), off, shape, stride)
                     self._attached_ids.add(id(p))
                     off += n
-            self._flat.append({"p": flat_p, "g": b.flattened, "m": torch.zeros_like(flat_p), "first": True})
+            entry = {"p": flat_p, "g": b.flattened, "m": torch.zeros_like(flat_p), "first": True}
+            if self.bf16_shadow:
+                from ..ops.shadow import BF16Shadow
+
+                flat_h = torch.zeros_like(flat_p, dtype=torch.bfloat16)
+                off = 0
+                for t in b.tensors:
+                    p = t.owner
+                    n = p.numel()
+                    p._bagua_bf16 = BF16Shadow(flat_h[off:off + n].as_strided(tuple(p.shape), tuple(p.stride())), self)
+                    self._shadowed.append(p)
+                    off += n
+                entry["h"] = flat_h
+            self._flat.append(entry)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -88,10 +116,16 @@ class FlatSGD(torch.optim.Optimizer):
         g0 = self.param_groups[0]
         stream = torch.cuda.current_stream().cuda_stream if (self._flat and self._flat[0]["p"].is_cuda) else 0
         for f in self._flat:
-            _C.k_sgd_momentum_flat(f["p"], f["g"], f["m"], g0["lr"], g0["momentum"], g0["dampening"],
-                                   g0["weight_decay"], g0["nesterov"], f["first"], stream)
+            if "h" in f:
+                _C.k_sgd_momentum_flat_shadow(f["p"], f["g"], f["m"], f["h"], g0["lr"], g0["momentum"], g0["dampening"],
+                                              g0["weight_decay"], g0["nesterov"], f["first"], stream)
+            else:
+                _C.k_sgd_momentum_flat(f["p"], f["g"], f["m"], g0["lr"], g0["momentum"], g0["dampening"],
+                                       g0["weight_decay"], g0["nesterov"], f["first"], stream)
             f["first"] = False
             self.kernel_launches += 1
+        if self._shadowed and not self.shadows_valid:
+            self._validate_shadows()
         for group in self.param_groups:
             for p in group["params"]:
                 if id(p) in self._attached_ids or p.grad is None:
@@ -125,6 +159,22 @@ class FlatSGD(torch.optim.Optimizer):
                 self.kernel_launches += 1
         self._steps += 1
         return loss
+
+    def _validate_shadows(self):
+        """The bf16 copies equal the parameters now: remember the parameters' versions."""
+        for p in self._shadowed:
+            p._bagua_bf16.version = p._version
+        self.shadows_valid = True
+
+    @torch.no_grad()
+    def refresh_bf16(self):
+        """Recomputes the bf16 copies from the parameters (after the weights were changed by something
+        the copies cannot notice, or to use them before the first step)."""
+        for f in self._flat:
+            if "h" in f:
+                f["h"].copy_(f["p"])
+        if self._shadowed:
+            self._validate_shadows()
 
     def zero_grad(self, set_to_none: bool = False):
         """Zero the flat gradient buffers with one memset per bucket; gradients stay views

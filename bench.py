@@ -53,6 +53,10 @@ def parse():
                          "(the default for vgg16 on a GPU)")
     ap.add_argument("--no-fused-model-ops", dest="fused_model_ops", action="store_false",
                     help="VGG-16 built from plain Conv2d / ReLU / MaxPool2d modules")
+    ap.add_argument("--bf16-shadow", action="store_true",
+                    help="the optimizer kernel also writes bf16 copies of the weights and the fused blocks read those "
+                         "instead of casting the fp32 master weights in every forward pass (same values; needs the "
+                         "fused model ops and the flat SGD optimizer; off by default until it has been timed)")
     return ap.parse_args()
 
 
@@ -233,7 +237,7 @@ def main():
             opt = P.QAdamOptimizer(model.parameters(), lr=1e-4, warmup_steps=2)
             algo = P.QAdamAlgorithm(opt)
         else:
-            opt = P.FlatSGD(model.parameters(), lr=lr, momentum=0.9)
+            opt = P.FlatSGD(model.parameters(), lr=lr, momentum=0.9, bf16_shadow=bool(args.bf16_shadow and fused_ops))
             algo = {
                 "gradient_allreduce": lambda: P.GradientAllReduceAlgorithm(),
                 "bytegrad": lambda: P.ByteGradAlgorithm(),
@@ -368,6 +372,7 @@ def main():
                 "optimizer": "sgd momentum 0.9" if algo_name != "qadam" else "qadam",
                 "precision": "bf16 autocast, fp32 master weights and gradients",
                 "fused_model_ops": bool(fused_ops),
+                "bf16_weight_copies": bool(args.bf16_shadow and fused_ops and args.impl != "ddp" and algo_name != "qadam"),
                 "l2": "working set per step (fp32 weights+grads+momentum and activations) exceeds the 126 MB L2",
             },
             "clocks": clocks.summary(),

@@ -46,6 +46,10 @@ void decompress_minmax_u8(const uint8_t*, size_t, int64_t, int, void*, DType, cu
 void sgd_momentum_flat(float*, const float*, float*, int64_t, float, float, float, float, bool, bool, cudaStream_t) {
   UNREACHABLE();
 }
+void sgd_momentum_flat_shadow(float*, const float*, float*, void*, int64_t, float, float, float, float, bool, bool,
+                              cudaStream_t) {
+  UNREACHABLE();
+}
 }  // namespace cuda
 }  // namespace kernels
 }  // namespace bagua

@@ -200,3 +200,76 @@ def test_conv_bias_relu_pool_module_matches_the_composition_under_autocast():
     for a, b in [(xa.grad, xb.grad), (pooled.weight.grad, single.weight.grad), (pooled.bias.grad, single.bias.grad)]:
         scale = b.abs().max().item() + 1e-6
         assert (a - b).abs().max().item() <= 6e-2 * scale  # masks agree except where two conv algorithms round apart
+
+
+_SHADOW = pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_BF16_SHADOW") != "1",
+                             reason="bf16 weight copies written by the optimizer kernel: set BAGUA_B200_TEST_BF16_SHADOW=1 "
+                                    "(first run on hardware pending)")
+
+
+@_SHADOW
+@pytest.mark.parametrize("n", [1, 7, 4096, (1 << 20) + 3])
+def test_sgd_step_with_bf16_copy_equals_the_plain_step(n):
+    import bagua_core_b200 as bb
+
+    C = bb._C
+    g = torch.Generator().manual_seed(n)
+    p, grad = torch.randn(n, generator=g).cuda(), torch.randn(n, generator=g).cuda()
+    m = torch.zeros(n, device="cuda")
+    p2, m2, h = p.clone(), m.clone(), torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    for step in range(3):
+        C.k_sgd_momentum_flat(p, grad, m, 0.1, 0.9, 0.0, 1e-4, True, step == 0, s)
+        C.k_sgd_momentum_flat_shadow(p2, grad, m2, h, 0.1, 0.9, 0.0, 1e-4, True, step == 0, s)
+        torch.cuda.synchronize()
+        assert torch.equal(p, p2) and torch.equal(m, m2) and torch.equal(h, p2.to(torch.bfloat16))
+    # an unaligned view takes the scalar path
+    if n > 8:
+        q = torch.randn(n + 1, generator=g).cuda()[1:]  # 4 bytes past a 16-byte boundary
+        q2 = torch.empty(n + 1, device="cuda")[1:].copy_(q)
+        hq = torch.zeros(n + 1, dtype=torch.bfloat16, device="cuda")[1:]
+        C.k_sgd_momentum_flat(q, grad, m, 0.1, 0.9, 0.0, 0.0, False, False, s)
+        C.k_sgd_momentum_flat_shadow(q2, grad, m2, hq, 0.1, 0.9, 0.0, 0.0, False, False, s)
+        torch.cuda.synchronize()
+        assert torch.equal(q, q2) and torch.equal(hq, q2.to(torch.bfloat16))
+
+
+@_SHADOW
+def test_vgg_training_with_bf16_weight_copies_is_bit_identical_to_casting():
+    """Same model, same data: lookups switched off (the blocks cast the fp32 weights in every forward pass) against
+    lookups on (they read the optimizer's copies)."""
+    import os
+
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import VGG16
+    from bagua_core_b200.ops import shadow as S
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29541")
+    dev = torch.device("cuda", 0)
+    results = []
+    for use_copies in (False, True):
+        S.enabled = use_copies
+        torch.manual_seed(0)
+        model = VGG16(num_classes=10, dropout=0.0, fused_ops=True).to(dev).to(memory_format=torch.channels_last)
+        P.init_process_group(dev)
+        opt = P.FlatSGD(model.parameters(), lr=0.01, momentum=0.9, bf16_shadow=True)
+        bm = P.with_bagua(model, [opt], P.GradientAllReduceAlgorithm(), bucket_bytes=10 << 20)
+        g = torch.Generator().manual_seed(5)
+        hits0, losses = S.hits, []
+        for _ in range(4):
+            x = torch.randn(4, 3, 64, 64, generator=g).to(dev).contiguous(memory_format=torch.channels_last)
+            y = torch.randint(0, 10, (4,), generator=g).to(dev)
+            opt.zero_grad()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = torch.nn.functional.cross_entropy(bm(x).float(), y)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        torch.cuda.synchronize()
+        results.append((losses, torch.cat([p.detach().reshape(-1) for p in model.parameters()]).clone(), S.hits - hits0))
+        P.destroy_process_group()
+    S.enabled = True
+    assert results[0][2] == 0 and results[1][2] == 3 * 16  # 13 convolutions + 3 linear layers, from the second step on
+    assert results[0][0] == results[1][0]
+    assert torch.equal(results[0][1], results[1][1])
