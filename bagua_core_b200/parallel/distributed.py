@@ -16,13 +16,13 @@ bagua-core-py/src/lib.rs:316-349):
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from .bucket import ALIGN_ELEMS_PER_RANK, BaguaBucket, BaguaTensor, split_into_buckets
+from .bucket import ALIGN_ELEMS_PER_RANK, BaguaBucket, BaguaTensor
 from .communication import BaguaProcessGroup, get_process_group
 
 

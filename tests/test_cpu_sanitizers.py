@@ -6,7 +6,6 @@ this covers the host half of the engine.)"""
 import os
 import shutil
 import subprocess
-import sys
 
 import pytest
 

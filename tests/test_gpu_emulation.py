@@ -2,7 +2,6 @@
 cooperative launch (`EmulatedArena`), executing the same device code as the multi-GPU
 kernels.  Results are checked against plain fp32 PyTorch math and against the host
 implementation of the MinMaxUInt8 compressor."""
-import numpy as np
 import pytest
 import torch
 

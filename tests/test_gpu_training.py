@@ -1,7 +1,5 @@
 """Single-GPU end-to-end: the flagship training step through `with_bagua` (world size 1)
 and the engine scheduler driving GPU buckets with CUDA events."""
-import os
-
 import pytest
 import torch
 
