@@ -329,10 +329,19 @@ def main():
         e2e_loop, e2e_mode = e2e_loop_pipelined, "pipelined"
         if os.environ.get("BAGUA_B200_BENCH_E2E", "pipelined") == "plain":
             e2e_loop, e2e_mode = e2e_loop_plain, "plain"
+        failed = 0
         try:
             e2e_loop(3)
         except Exception as exc:  # the plain loop is the known-good fallback
             print(f"[bench] pipelined end-to-end loop failed ({exc!r}); using the plain loop", file=sys.stderr)
+            failed = 1
+        if world > 1:
+            # Every rank takes the same loop: a rank that fell back alone would run three more
+            # warm-up steps than its peers, and their collectives would no longer pair up.
+            f = torch.tensor([failed], device=device, dtype=torch.int32)
+            dist.all_reduce(f, op=dist.ReduceOp.MAX)
+            failed = int(f.item())
+        if failed and e2e_mode != "plain":
             e2e_loop, e2e_mode = e2e_loop_plain, "plain"
             e2e_loop(3)
         barrier()
