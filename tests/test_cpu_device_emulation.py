@@ -24,6 +24,13 @@ CSRC = os.path.join(ROOT, "bagua_core_b200", "csrc")
 CUDA_INC = "/usr/local/cuda/include"
 
 
+def _sanitizer_flags(sanitizer):
+    flags = [f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
+    if sanitizer == "alignment":
+        flags.append("-fno-sanitize-recover=alignment")  # the first misaligned access ends the program
+    return flags
+
+
 def _build(tmp_path, sanitizer):
     gxx = shutil.which("g++")
     if gxx is None or not os.path.exists(os.path.join(CUDA_INC, "cuda_runtime.h")):
@@ -32,7 +39,7 @@ def _build(tmp_path, sanitizer):
     cmd = [gxx, "-std=c++20", "-O1", "-g", "-fno-strict-aliasing", "-DBAGUA_HOST_EMULATION", "-I", CSRC, "-I", CUDA_INC,
            os.path.join(ROOT, "tests", "cpp", "device_emulation.cc"), "-o", exe, "-lpthread"]
     if sanitizer:
-        cmd[1:1] = [f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
+        cmd[1:1] = _sanitizer_flags(sanitizer)
     build = subprocess.run(cmd, capture_output=True, text=True)
     if build.returncode != 0 and "sanitize" in build.stderr and "cannot find" in build.stderr:
         pytest.skip("sanitizer runtime not installed")
@@ -95,7 +102,19 @@ def test_device_bodies_stay_in_bounds_under_address_sanitizer(tmp_path):
         assert "ERROR: AddressSanitizer" not in out, out[-3000:]
 
 
-@pytest.mark.parametrize("sanitizer", [None, "address"])
+def test_device_bodies_keep_every_vector_access_aligned(tmp_path):
+    """A 16-byte load or store at an address that is not a multiple of 16 is a fault on the GPU and
+    passes silently on an x86 host.  The CUDA vector types keep their alignment under the host compiler
+    (`alignof(uint4) == 16`), so the alignment check of the undefined-behaviour sanitizer sees every
+    such access of the bodies: ragged sizes, odd chunk counts and the per-pair all-to-all offsets
+    included.  The build stops at the first report."""
+    exe = _build(tmp_path, "alignment")
+    for nranks, blocks, ops, seed in [(2, 1, 150, 21), (3, 3, 120, 22), (5, 1, 100, 23), (8, 2, 100, 24)]:
+        out = _run(exe, nranks, blocks, ops, seed)
+        assert "runtime error" not in out, out[-3000:]
+
+
+@pytest.mark.parametrize("sanitizer", [None, "address", "alignment"])
 def test_model_op_kernels_match_the_host_restatement(tmp_path, sanitizer):
     """The fused bias+ReLU and max-pool kernels (`csrc/kernels/model_ops_bodies.cuh`), run thread for
     thread on grids of a few blocks of 256 threads, against `csrc/kernels/model_ops_cpu.cc`; the second
@@ -108,7 +127,7 @@ def test_model_op_kernels_match_the_host_restatement(tmp_path, sanitizer):
            os.path.join(ROOT, "tests", "cpp", "model_ops_emulation.cc"), os.path.join(CSRC, "kernels", "model_ops_cpu.cc"),
            "-o", exe, "-lpthread"]
     if sanitizer:
-        cmd[1:1] = [f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
+        cmd[1:1] = _sanitizer_flags(sanitizer)
     build = subprocess.run(cmd, capture_output=True, text=True)
     if build.returncode != 0 and "sanitize" in build.stderr and "cannot find" in build.stderr:
         pytest.skip("sanitizer runtime not installed")
@@ -116,3 +135,4 @@ def test_model_op_kernels_match_the_host_restatement(tmp_path, sanitizer):
     run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert run.returncode == 0 and "0 failures" in run.stdout, run.stdout + run.stderr
     assert "ERROR: AddressSanitizer" not in run.stdout + run.stderr
+    assert "runtime error" not in run.stdout + run.stderr
