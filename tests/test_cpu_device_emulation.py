@@ -26,8 +26,8 @@ CUDA_INC = "/usr/local/cuda/include"
 
 def _sanitizer_flags(sanitizer):
     flags = [f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
-    if sanitizer == "alignment":
-        flags.append("-fno-sanitize-recover=alignment")  # the first misaligned access ends the program
+    if sanitizer == "undefined":
+        flags.append("-fno-sanitize-recover=undefined")  # the first report ends the program
     return flags
 
 
@@ -107,14 +107,15 @@ def test_device_bodies_keep_every_vector_access_aligned(tmp_path):
     passes silently on an x86 host.  The CUDA vector types keep their alignment under the host compiler
     (`alignof(uint4) == 16`), so the alignment check of the undefined-behaviour sanitizer sees every
     such access of the bodies: ragged sizes, odd chunk counts and the per-pair all-to-all offsets
-    included.  The build stops at the first report."""
-    exe = _build(tmp_path, "alignment")
+    included.  The other checks of that sanitizer (shift widths, signed overflow in index arithmetic,
+    indexing past a fixed-size array) come with it.  The program stops at the first report."""
+    exe = _build(tmp_path, "undefined")
     for nranks, blocks, ops, seed in [(2, 1, 150, 21), (3, 3, 120, 22), (5, 1, 100, 23), (8, 2, 100, 24)]:
         out = _run(exe, nranks, blocks, ops, seed)
         assert "runtime error" not in out, out[-3000:]
 
 
-@pytest.mark.parametrize("sanitizer", [None, "address", "alignment"])
+@pytest.mark.parametrize("sanitizer", [None, "address", "undefined"])
 def test_model_op_kernels_match_the_host_restatement(tmp_path, sanitizer):
     """The fused bias+ReLU and max-pool kernels (`csrc/kernels/model_ops_bodies.cuh`), run thread for
     thread on grids of a few blocks of 256 threads, against `csrc/kernels/model_ops_cpu.cc`; the second
