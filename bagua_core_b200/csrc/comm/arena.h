@@ -34,7 +34,9 @@
 namespace bagua {
 
 constexpr int kArenaMaxRanks = 8;
-constexpr int kArenaMaxBlocks = 160;
+// Room for two 512-thread CTAs on each of 148 SMs (the fused kernels stay at or under 64 registers
+// per thread, so two are co-resident); the defaults below use far fewer.
+constexpr int kArenaMaxBlocks = 320;
 constexpr int kArenaPhases = 2;
 
 // Word offsets inside a rank's signal pad.
@@ -43,6 +45,7 @@ constexpr int kSigPhase = 32;                                 // [phases][ranks]
 constexpr int kSigCounter = kSigPhase + kArenaPhases * kArenaMaxRanks * kArenaMaxBlocks;  // local CTA counter
 constexpr int kSigGridBar = kSigCounter + 2;                  // 64-bit local grid-barrier counter (2 words, 8 B aligned)
 constexpr int kSigWords = kSigGridBar + 6;
+static_assert(kSigGridBar % 2 == 0, "the 64-bit grid-barrier counter must sit on an 8-byte boundary");
 
 struct DeviceStatus {
   uint32_t code;    // 0 = ok, 1 = wait on `done`, 2 = wait on a phase flag, 3 = grid barrier, 4 = alltoall_v sizes disagree
