@@ -57,6 +57,10 @@ def parse():
                     help="the optimizer kernel also writes bf16 copies of the weights and the fused blocks read those "
                          "instead of casting the fp32 master weights in every forward pass (same values; needs the "
                          "fused model ops and the flat SGD optimizer; off by default until it has been timed)")
+    ap.add_argument("--fused-wgrad", action="store_true",
+                    help="linear layers of the fused VGG-16 add their weight gradient into the fp32 gradient bucket "
+                         "with the GEMM that computes it, instead of a bf16 product, a cast and a separate accumulation "
+                         "(needs the fused model ops; off by default until it has been timed)")
     return ap.parse_args()
 
 
@@ -202,6 +206,10 @@ def main():
     fused_ops = args.fused_model_ops
     if fused_ops is None:
         fused_ops = args.model == "vgg16" and on_gpu
+    if args.fused_wgrad and fused_ops:
+        from bagua_core_b200.ops import wgrad
+
+        wgrad.enabled = True
     model = build_model(args.model, device, fused_ops=fused_ops)
     if fused_ops and args.model == "vgg16":
         # One small forward/backward through the fused blocks before anything is timed; if it raises,
@@ -382,6 +390,7 @@ def main():
                 "precision": "bf16 autocast, fp32 master weights and gradients",
                 "fused_model_ops": bool(fused_ops),
                 "bf16_weight_copies": bool(args.bf16_shadow and fused_ops and args.impl != "ddp" and algo_name != "qadam"),
+                "fused_wgrad": _wgrad_report(args, fused_ops),
                 "l2": "working set per step (fp32 weights+grads+momentum and activations) exceeds the 126 MB L2",
             },
             "clocks": clocks.summary(),
@@ -396,6 +405,15 @@ def main():
     if dist.is_initialized():
         dist.destroy_process_group()
     return 0
+
+
+def _wgrad_report(args, fused_ops):
+    """False, or which library call accumulated the weight gradients and how often it did / declined."""
+    if not (args.fused_wgrad and fused_ops):
+        return False
+    from bagua_core_b200.ops import wgrad
+
+    return {"mode": wgrad.cuda_mode or "host", "accumulated": wgrad.accumulated, "declined": wgrad.declined}
 
 
 if __name__ == "__main__":

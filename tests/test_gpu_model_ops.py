@@ -273,3 +273,84 @@ def test_vgg_training_with_bf16_weight_copies_is_bit_identical_to_casting():
     assert results[0][2] == 0 and results[1][2] == 3 * 16  # 13 convolutions + 3 linear layers, from the second step on
     assert results[0][0] == results[1][0]
     assert torch.equal(results[0][1], results[1][1])
+
+
+_WGRAD = pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_FUSED_WGRAD") != "1",
+                            reason="weight gradients accumulated by the GEMM (bagua_core_b200.ops.wgrad): set "
+                                   "BAGUA_B200_TEST_FUSED_WGRAD=1 (first run on hardware pending)")
+
+
+@_WGRAD
+@pytest.mark.parametrize("rows,n_in,n_out", [(32, 25088, 4096), (32, 4096, 1000), (5, 72, 24)])
+def test_linear_weight_gradient_accumulated_in_place_is_the_fp32_product(rows, n_in, n_out):
+    """The library GEMM adds dyᵀ x (bf16 operands) into the fp32 gradient; compared with the same
+    operands multiplied in fp32 by plain PyTorch, twice in a row (the second call adds)."""
+    from bagua_core_b200.ops import wgrad as W
+    from bagua_core_b200.ops.fused_linear import ShadowLinear
+
+    saved, W.enabled = W.enabled, True
+    try:
+        torch.manual_seed(rows + n_in)
+        m = ShadowLinear(n_in, n_out).cuda()
+        for p in m.parameters():
+            p.grad = torch.zeros_like(p)
+        fired = []
+        m.weight.register_post_accumulate_grad_hook(lambda p: fired.append(1))
+        x = torch.randn(rows, n_in, device="cuda")
+        a0 = W.accumulated
+        for k in (1, 2):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = m(x)
+            dy = torch.randn_like(y)
+            y.backward(dy)
+            torch.cuda.synchronize()
+            assert W.accumulated == a0 + k and len(fired) == k, (W.accumulated, W.declined, W.cuda_mode)
+            want = k * (dy.to(torch.bfloat16).float().t() @ x.to(torch.bfloat16).float()) if k == 1 else want + \
+                dy.to(torch.bfloat16).float().t() @ x.to(torch.bfloat16).float()
+            scale = want.abs().max().item()
+            assert (m.weight.grad - want).abs().max().item() <= 2e-3 * scale + 1e-5
+        assert W.cuda_mode in ("addmm", "mm_add")
+    finally:
+        W.enabled = saved
+
+
+@_WGRAD
+def test_vgg_training_with_in_place_weight_gradients_agrees_with_the_ordinary_path():
+    import os
+
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import VGG16
+    from bagua_core_b200.ops import wgrad as W
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29543")
+    dev = torch.device("cuda", 0)
+    saved, results = W.enabled, []
+    try:
+        for inplace in (False, True):
+            W.enabled = inplace
+            torch.manual_seed(0)
+            model = VGG16(num_classes=10, dropout=0.0, fused_ops=True).to(dev).to(memory_format=torch.channels_last)
+            P.init_process_group(dev)
+            opt = P.FlatSGD(model.parameters(), lr=0.01, momentum=0.9)
+            bm = P.with_bagua(model, [opt], P.GradientAllReduceAlgorithm(), bucket_bytes=10 << 20)
+            g = torch.Generator().manual_seed(5)
+            a0, losses = W.accumulated, []
+            for _ in range(4):
+                x = torch.randn(4, 3, 64, 64, generator=g).to(dev).contiguous(memory_format=torch.channels_last)
+                y = torch.randint(0, 10, (4,), generator=g).to(dev)
+                opt.zero_grad()
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss = torch.nn.functional.cross_entropy(bm(x).float(), y)
+                loss.backward()
+                opt.step()
+                losses.append(loss.item())
+            torch.cuda.synchronize()
+            results.append((losses, torch.cat([p.detach().reshape(-1) for p in model.parameters()]).clone(),
+                            W.accumulated - a0))
+            P.destroy_process_group()
+    finally:
+        W.enabled = saved
+    assert results[0][2] == 0 and results[1][2] == 4 * 3  # three linear layers, four steps
+    assert all(abs(a - b) < 5e-2 for a, b in zip(results[0][0], results[1][0])), (results[0][0], results[1][0])
+    assert (results[0][1] - results[1][1]).abs().max().item() < 2e-2
