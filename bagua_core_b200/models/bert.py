@@ -1,7 +1,12 @@
 """BERT-large encoder with a span-prediction (SQuAD-style) head: 24 layers, hidden 1024,
 16 heads, FFN 4096, vocabulary 30522, post-LayerNorm, learned positions.  Attention goes
 through `torch.nn.functional.scaled_dot_product_attention` (library kernel).  Random
-initialisation only."""
+initialisation only.
+
+The encoder's projections are `ShadowLinear` modules: `nn.Linear` (same parameter names, same
+math) unless an optimizer keeps bf16 copies of the weights (`FlatSGD(bf16_shadow=True)`) or
+in-place weight-gradient accumulation is on (`bagua_core_b200.ops.wgrad.enabled`), in which case
+they skip the per-forward weight casts and the cast-and-add of every weight gradient."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -9,6 +14,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+from ..ops.fused_linear import ShadowLinear
 
 
 @dataclass
@@ -36,11 +43,11 @@ class _Layer(nn.Module):
     def __init__(self, c: BertConfig):
         super().__init__()
         self.heads = c.heads
-        self.qkv = nn.Linear(c.hidden, 3 * c.hidden)
-        self.proj = nn.Linear(c.hidden, c.hidden)
+        self.qkv = ShadowLinear(c.hidden, 3 * c.hidden)
+        self.proj = ShadowLinear(c.hidden, c.hidden)
         self.ln1 = nn.LayerNorm(c.hidden, eps=c.eps)
-        self.fc1 = nn.Linear(c.hidden, c.ffn)
-        self.fc2 = nn.Linear(c.ffn, c.hidden)
+        self.fc1 = ShadowLinear(c.hidden, c.ffn)
+        self.fc2 = ShadowLinear(c.ffn, c.hidden)
         self.ln2 = nn.LayerNorm(c.hidden, eps=c.eps)
         self.drop = nn.Dropout(c.dropout)
         self.p = c.dropout

@@ -55,12 +55,12 @@ def parse():
                     help="VGG-16 built from plain Conv2d / ReLU / MaxPool2d modules")
     ap.add_argument("--bf16-shadow", action="store_true",
                     help="the optimizer kernel also writes bf16 copies of the weights and the fused blocks read those "
-                         "instead of casting the fp32 master weights in every forward pass (same values; needs the "
-                         "fused model ops and the flat SGD optimizer; off by default until it has been timed)")
+                         "instead of casting the fp32 master weights in every forward pass (same values; fused VGG-16 "
+                         "and BERT, flat SGD optimizer; off by default until it has been timed)")
     ap.add_argument("--fused-wgrad", action="store_true",
                     help="linear layers of the fused VGG-16 add their weight gradient into the fp32 gradient bucket "
                          "with the GEMM that computes it, instead of a bf16 product, a cast and a separate accumulation "
-                         "(needs the fused model ops; off by default until it has been timed)")
+                         "(fused VGG-16 and BERT; off by default until it has been timed)")
     return ap.parse_args()
 
 
@@ -206,7 +206,9 @@ def main():
     fused_ops = args.fused_model_ops
     if fused_ops is None:
         fused_ops = args.model == "vgg16" and on_gpu
-    if args.fused_wgrad and fused_ops:
+    # the two linear-layer options need modules that honour them: the fused VGG-16 or BERT
+    linear_opts = bool(fused_ops) or args.model == "bert_large"
+    if args.fused_wgrad and linear_opts:
         from bagua_core_b200.ops import wgrad
 
         wgrad.enabled = True
@@ -224,6 +226,7 @@ def main():
         except Exception as exc:
             print(f"[bench] fused model kernels failed ({exc!r}); using the plain modules", file=sys.stderr)
             fused_ops = False
+            linear_opts = False  # the plain modules honour neither option
             torch.manual_seed(0)
             model = build_model(args.model, device, fused_ops=False)
     n_params = sum(p.numel() for p in model.parameters())
@@ -245,7 +248,7 @@ def main():
             opt = P.QAdamOptimizer(model.parameters(), lr=1e-4, warmup_steps=2)
             algo = P.QAdamAlgorithm(opt)
         else:
-            opt = P.FlatSGD(model.parameters(), lr=lr, momentum=0.9, bf16_shadow=bool(args.bf16_shadow and fused_ops))
+            opt = P.FlatSGD(model.parameters(), lr=lr, momentum=0.9, bf16_shadow=bool(args.bf16_shadow and linear_opts))
             algo = {
                 "gradient_allreduce": lambda: P.GradientAllReduceAlgorithm(),
                 "bytegrad": lambda: P.ByteGradAlgorithm(),
@@ -389,8 +392,8 @@ def main():
                 "optimizer": "sgd momentum 0.9" if algo_name != "qadam" else "qadam",
                 "precision": "bf16 autocast, fp32 master weights and gradients",
                 "fused_model_ops": bool(fused_ops),
-                "bf16_weight_copies": bool(args.bf16_shadow and fused_ops and args.impl != "ddp" and algo_name != "qadam"),
-                "fused_wgrad": _wgrad_report(args, fused_ops),
+                "bf16_weight_copies": bool(args.bf16_shadow and linear_opts and args.impl != "ddp" and algo_name != "qadam"),
+                "fused_wgrad": _wgrad_report(args, linear_opts),
                 "l2": "working set per step (fp32 weights+grads+momentum and activations) exceeds the 126 MB L2",
             },
             "clocks": clocks.summary(),
@@ -407,9 +410,9 @@ def main():
     return 0
 
 
-def _wgrad_report(args, fused_ops):
+def _wgrad_report(args, linear_opts):
     """False, or which library call accumulated the weight gradients and how often it did / declined."""
-    if not (args.fused_wgrad and fused_ops):
+    if not (args.fused_wgrad and linear_opts):
         return False
     from bagua_core_b200.ops import wgrad
 

@@ -174,3 +174,51 @@ def test_training_through_with_bagua_agrees_with_the_ordinary_path(algorithm):
         assert torch.allclose(plain[r][0], fused[r][0], rtol=0, atol=2e-2), (plain[r][0] - fused[r][0]).abs().max()
         assert all(abs(a - b) < 5e-2 for a, b in zip(plain[r][1], fused[r][1]))
     assert torch.equal(fused[0][0], fused[1][0])  # the ranks stay bit-identical to each other
+
+
+def _train_bert(rank, world, inplace, shadow, steps):
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import BertConfig, BertForQuestionAnswering
+    from bagua_core_b200.ops import wgrad as W
+
+    W.enabled = inplace
+    torch.manual_seed(11)
+    cfg = BertConfig.tiny()
+    cfg.dropout = 0.0
+    model = BertForQuestionAnswering(cfg)
+    P.init_process_group(torch.device("cpu"))
+    opt = P.FlatSGD(model.parameters(), lr=0.05, momentum=0.9, bf16_shadow=shadow)
+    bm = P.with_bagua(model, [opt], P.ByteGradAlgorithm(), bucket_bytes=64 << 10)
+    g = torch.Generator().manual_seed(7 + rank)
+    losses = []
+    for _ in range(steps):
+        ids = torch.randint(0, cfg.vocab_size, (2, 16), generator=g)
+        span = torch.randint(0, 16, (2, 2), generator=g)
+        opt.zero_grad()
+        with torch.autocast("cpu", dtype=torch.bfloat16):
+            loss = bm(ids, span[:, 0], span[:, 1])
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    counts = (W.accumulated, W.declined)
+    P.destroy_process_group()
+    return flat, losses, counts
+
+
+def test_bert_encoder_projections_take_both_options():
+    """The encoder's four projections per layer are `ShadowLinear`: with in-place weight gradients (and
+    bf16 weight copies on top) ByteGrad training of a two-layer BERT stays with the ordinary path."""
+    steps = 4
+    plain = run_ranks(_train_bert, 2, args=(False, False, steps))
+    fused = run_ranks(_train_bert, 2, args=(True, False, steps))
+    both = run_ranks(_train_bert, 2, args=(True, True, steps))
+    for r in range(2):
+        assert plain[r][2] == (0, 0)
+        assert fused[r][2] == (2 * 4 * steps, 0) and both[r][2] == (2 * 4 * steps, 0)
+        for other in (fused, both):
+            assert (plain[r][0] - other[r][0]).abs().max().item() < 2e-2
+            assert all(abs(a - b) < 5e-2 for a, b in zip(plain[r][1], other[r][1]))
+        # the bf16 copies hold the values the casts would produce: same training, bit for bit
+        assert torch.equal(fused[r][0], both[r][0]) and fused[r][1] == both[r][1]
+    assert torch.equal(both[0][0], both[1][0])
