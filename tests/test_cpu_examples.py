@@ -1,0 +1,26 @@
+"""The example scripts run as a user would run them, on host ranks: they are documentation, and
+documentation that does not run misleads."""
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(*argv, timeout=600):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", LOG_LEVEL="ERROR")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    run = subprocess.run([sys.executable, *argv], cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-3000:]
+    return run.stdout
+
+
+def test_low_level_api_example_averages_and_compresses_on_two_ranks():
+    out = _run("examples/low_level_api.py")
+    assert "average over 2 ranks: max error 0.00e+00" in out and "ByteGrad: max error" in out
+
+
+def test_training_example_runs_a_few_steps():
+    out = _run("examples/train_synthetic.py", "--model", "mlp", "--algorithm", "bytegrad", "--steps", "4")
+    assert "loss" in out.lower()
