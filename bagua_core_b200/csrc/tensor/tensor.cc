@@ -176,8 +176,12 @@ bool BaguaBucket::contiguous() const {
 }
 
 bool BaguaBucket::ready_for_comm() const {
-  for (auto& t : tensors_)
-    if (!t->ready_for_comm()) return false;
+  // Asked after every tensor that becomes ready.  A trainer lists a bucket's tensors in the order
+  // their gradients appear, so the ones at the back are the last to become ready: looking from the
+  // back meets an unready tensor at once, where looking from the front walks over all that are
+  // ready already (one lock each) before it finds one.
+  for (auto it = tensors_.rbegin(); it != tensors_.rend(); ++it)
+    if (!(*it)->ready_for_comm()) return false;
   return true;
 }
 void BaguaBucket::reset_comm_ready() {

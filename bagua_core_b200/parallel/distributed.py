@@ -78,11 +78,14 @@ class BaguaModule(nn.Module):
                 opt.bagua_attach(self)
         self.pg.backend.register_ordered_buckets([b.backend_bucket for b in self.bagua_buckets])
         # per-bucket bookkeeping for the one-event-per-bucket rule
-        self._bucket_of = {}
-        self._remaining = {}
+        # (the hooks run once per parameter per step on the thread that launches the backward kernels:
+        # they reach their bucket and its countdown through attributes, not through look-ups by name)
         for b in self.bagua_buckets:
+            b._pending = len(b.tensors)
             for t in b.tensors:
-                self._bucket_of[t.name] = b
+                t._bucket = b
+        self._mark_ready_native = self.pg.backend.mark_communication_ready
+        self._on_cuda = bool(self.pg.is_cuda)
         self._hooks.extend(algo.init_backward_hooks(self))
         self._hooks.extend(algo.init_forward_pre_hooks(self))
         self._post_backward = algo.init_post_backward_hook(self)
@@ -105,7 +108,8 @@ class BaguaModule(nn.Module):
         return self.pg.global_comm.alloc_symmetric(int(numel), dtype)
 
     def _arm(self):
-        self._remaining = {b.name: len(b.tensors) for b in self.bagua_buckets}
+        for b in self.bagua_buckets:
+            b._pending = len(b.tensors)
 
     def _wrap_optimizer_steps(self):
         for opt in self.bagua_optimizers:
@@ -125,16 +129,16 @@ class BaguaModule(nn.Module):
     # ---- the hot path ------------------------------------------------------------------
     def mark_ready(self, t: BaguaTensor):
         """Tell the engine `t` holds its final value for this step (called from hooks)."""
-        b = self._bucket_of[t.name]
-        self._remaining[b.name] -= 1
+        b = t._bucket
+        b._pending -= 1
         ev_ptr = 0
-        if self._remaining[b.name] == 0 and self.pg.is_cuda:
+        if b._pending == 0 and self._on_cuda:
             ev = self._events.get(b.name)
             if ev is None:
                 ev = self._events[b.name] = torch.cuda.Event(enable_timing=False, blocking=False)
             ev.record()
             ev_ptr = ev.cuda_event
-        self.pg.backend.mark_communication_ready(t.backend_tensor, ev_ptr)
+        self._mark_ready_native(t.backend_tensor, ev_ptr)
 
     def forward(self, *args, **kwargs):
         out = self.module(*args, **kwargs)

@@ -92,6 +92,25 @@ def test_any_ready_order_yields_the_registered_bucket_order():
         backend.close()
 
 
+def test_a_bucket_is_ready_only_when_every_tensor_is_whichever_comes_last():
+    """The readiness check looks at a bucket's tensors from the back (the usual last arrivals); the
+    answer must not depend on which tensor is the one still missing."""
+    for missing in range(5):
+        tensors = [_tensor(name=f"m{missing}_{i}")[1] for i in range(5)]
+        log = []
+        bucket = _recording_bucket(f"b{missing}", tensors, log)
+        backend = bc.BaguaCommBackendPy(10, -1)
+        backend.register_ordered_buckets([bucket])
+        for i, t in enumerate(tensors):
+            if i != missing:
+                backend.mark_communication_ready(t, 0)
+        assert not bucket.ready_for_comm() and backend.wait_pending_comm_ops() == 0 and log == []
+        backend.mark_communication_ready(tensors[missing], 0)
+        assert backend.wait_pending_comm_ops() == 1 and log == [f"b{missing}"]
+        assert not bucket.ready_for_comm()  # readiness is cleared when the bucket is scheduled
+        backend.close()
+
+
 def test_padding_tensors_are_always_ready_and_all_padding_bucket_is_rejected():
     backend = bc.BaguaCommBackendPy(10, -1)
     log = []
