@@ -225,24 +225,35 @@ class QAdamOptimizer(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
+        """One multi-tensor call per operation and parameter group instead of one small kernel per
+        operation and parameter (for BERT-large: 9 launches instead of about 1500 after warm-up);
+        the arithmetic per element is the same sequence of operations."""
         loss = closure() if closure is not None else None
         self.step_id += 1
+        warm = self.step_id <= self.warmup_steps
         for group in self.param_groups:
             lr, (b1, b2), eps, wd = group["lr"], group["betas"], group["eps"], group["weight_decay"]
-            for p in group["params"]:
-                st = self.state[p]
-                m, v = st["exp_avg"], st["exp_avg_sq"]
-                if self.step_id <= self.warmup_steps:
-                    if p.grad is None:
-                        continue
-                    g = p.grad if wd == 0 else p.grad.add(p, alpha=wd)
-                    m.mul_(b1).add_(g, alpha=1 - b1)
-                    v.mul_(b2).addcmul_(g, g, value=1 - b2)
-                # after warm-up `m` was updated (and averaged across ranks) by the algorithm
-                bc1 = 1 - b1 ** self.step_id
-                bc2 = 1 - b2 ** min(self.step_id, self.warmup_steps)
-                denom = (v.sqrt() / (bc2 ** 0.5)).add_(eps)
-                p.addcdiv_(m, denom, value=-lr / bc1)
+            # during warm-up a parameter without a gradient is left alone; afterwards `m` was updated
+            # (and averaged across ranks) by the algorithm, so every parameter moves
+            ps = [p for p in group["params"] if not warm or p.grad is not None]
+            if not ps:
+                continue
+            ms = [self.state[p]["exp_avg"] for p in ps]
+            vs = [self.state[p]["exp_avg_sq"] for p in ps]
+            if warm:
+                gs = [p.grad for p in ps]
+                if wd != 0:
+                    gs = torch._foreach_add(gs, ps, alpha=wd)
+                torch._foreach_mul_(ms, b1)
+                torch._foreach_add_(ms, gs, alpha=1 - b1)
+                torch._foreach_mul_(vs, b2)
+                torch._foreach_addcmul_(vs, gs, gs, value=1 - b2)
+            bc1 = 1 - b1 ** self.step_id
+            bc2 = 1 - b2 ** min(self.step_id, self.warmup_steps)
+            denom = torch._foreach_sqrt(vs)
+            torch._foreach_div_(denom, bc2 ** 0.5)
+            torch._foreach_add_(denom, eps)
+            torch._foreach_addcdiv_(ps, ms, denom, value=-lr / bc1)
         return loss
 
 
@@ -287,13 +298,28 @@ class QAdamAlgorithm(Algorithm):
         by_param = {id(t.owner): t for b in bm.bagua_buckets for t in b.tensors if t.owner is not None}
         b1 = self.optimizer.param_groups[0]["betas"][0]
 
+        # m = b1 m + (1 - b1) g for a whole bucket at once, when its last gradient has arrived: two
+        # multi-tensor launches per bucket instead of two small kernels per parameter.  Nothing is
+        # lost by waiting, a bucket is only communicated once all of its tensors are ready.
+        for b in bm.bagua_buckets:
+            b._qadam_owned = sum(1 for t in b.tensors if t.owner is not None)
+            b._qadam_arrived = []
+
         def make(t):
             def hook(param):
                 if bm._in_no_sync:
                     return
+                b = t._bucket
+                b._qadam_arrived.append((t, param.grad))
+                if len(b._qadam_arrived) < b._qadam_owned:
+                    return
+                arrived, b._qadam_arrived = b._qadam_arrived, []
                 with torch.no_grad():
-                    t.tensor.mul_(b1).add_(param.grad, alpha=1 - b1)
-                bm.mark_ready(t)
+                    ms = [a.tensor for a, _ in arrived]
+                    torch._foreach_mul_(ms, b1)
+                    torch._foreach_add_(ms, [g for _, g in arrived], alpha=1 - b1)
+                for a, _ in arrived:
+                    bm.mark_ready(a)
 
             return hook
 

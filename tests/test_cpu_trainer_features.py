@@ -108,3 +108,43 @@ def test_no_sync_and_regrown_gradients():
         assert scheduled == 0  # nothing communicated under no_sync
         assert torch.allclose(synced, mean_local, atol=1e-6)  # same data → all-reduced mean of the local grads
         assert views_ok
+
+
+def test_qadam_multi_tensor_step_equals_the_per_tensor_formulas():
+    """`QAdamOptimizer.step` runs one multi-tensor call per operation; element by element it must be
+    the sequence m = b1 m + (1-b1) g, v = b2 v + (1-b2) g², p -= lr/bc1 · m / (sqrt(v)/sqrt(bc2) + eps)
+    applied tensor by tensor — through warm-up (parameters without a gradient left alone) and after it
+    (second moment frozen, every parameter moves)."""
+    import bagua_core_b200.parallel as P
+
+    torch.manual_seed(0)
+    shapes = [(7, 5), (33,), (4, 4, 3), (1,)]
+    params = [torch.nn.Parameter(torch.randn(*s)) for s in shapes]
+    ref_p = [p.detach().clone() for p in params]
+    ref_m = [torch.zeros_like(p) for p in ref_p]
+    ref_v = [torch.zeros_like(p) for p in ref_p]
+    lr, b1, b2, eps, wd, warmup = 0.02, 0.9, 0.999, 1e-3, 0.01, 3
+    opt = P.QAdamOptimizer(params, lr=lr, warmup_steps=warmup, betas=(b1, b2), eps=eps, weight_decay=wd)
+    for step in range(1, 7):
+        grads = [torch.randn(*s) for s in shapes]
+        skip = 1 if step == 2 else None  # no gradient for one parameter in one warm-up step
+        for i, p in enumerate(params):
+            p.grad = None if i == skip else grads[i].clone()
+        if step > warmup:  # the algorithm updates the momentum itself after warm-up
+            for i, p in enumerate(params):
+                opt.state[p]["exp_avg"].mul_(b1).add_(grads[i], alpha=1 - b1)
+                ref_m[i].mul_(b1).add_(grads[i], alpha=1 - b1)
+        opt.step()
+        for i in range(len(shapes)):
+            if step <= warmup:
+                if i == skip:
+                    continue
+                g = grads[i].add(ref_p[i], alpha=wd)
+                ref_m[i].mul_(b1).add_(g, alpha=1 - b1)
+                ref_v[i].mul_(b2).addcmul_(g, g, value=1 - b2)
+            bc1, bc2 = 1 - b1 ** step, 1 - b2 ** min(step, warmup)
+            denom = (ref_v[i].sqrt() / (bc2 ** 0.5)).add_(eps)
+            ref_p[i].addcdiv_(ref_m[i], denom, value=-lr / bc1)
+        for i, p in enumerate(params):
+            assert torch.equal(p.detach(), ref_p[i]), (step, i)
+            assert torch.equal(opt.state[p]["exp_avg"], ref_m[i]) and torch.equal(opt.state[p]["exp_avg_sq"], ref_v[i])
