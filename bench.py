@@ -208,6 +208,8 @@ def main():
         fused_ops = args.model == "vgg16" and on_gpu
     # the two linear-layer options need modules that honour them: the fused VGG-16 or BERT
     linear_opts = bool(fused_ops) or args.model == "bert_large"
+    if args.impl == "ddp":
+        args.fused_wgrad = False  # DDP's reducer does not learn of gradients through post-accumulate hooks
     if args.fused_wgrad and linear_opts:
         from bagua_core_b200.ops import wgrad
 
