@@ -43,18 +43,26 @@ using namespace bytegrad_bodies;
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     bytegrad_kernel(const __grid_constant__ ArenaView v, T* __restrict__ x, int64_t chunk, size_t slot_bytes,
-                    size_t scratch_off, float scale) {
-  bytegrad_body<T>(v, psync::real_launch(), x, chunk, slot_bytes, scratch_off, scale);
+                    size_t scratch_off, float scale, int pipelined) {
+  bytegrad_body<T>(v, psync::real_launch(), x, chunk, slot_bytes, scratch_off, scale, pipelined != 0);
+}
+
+// Whether the reduced chunks travel back one destination at a time (see bytegrad_body): for chunks of
+// at least BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK bytes; unset or negative = never (the default until
+// the variant has been timed).  Read at every call, and the same on every rank, like all environment knobs.
+bool pipelined_for(size_t chunk_bytes) {
+  const long min_chunk = env_long("BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK", -1);
+  return min_chunk >= 0 && chunk_bytes >= (size_t)min_chunk;
 }
 
 // single-GPU emulation: the grids of all ranks in one cooperative launch
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     bytegrad_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int64_t chunk, size_t slot_bytes,
-                        size_t scratch_off, float scale) {
+                        size_t scratch_off, float scale, int pipelined) {
   const EmuRank& e = ranks[blockIdx.x / blocks];
   bytegrad_body<T>(e.view, psync::Launch{(int)(blockIdx.x % blocks), blocks}, (T*)e.in, chunk, slot_bytes, scratch_off,
-                   scale);
+                   scale, pipelined != 0);
 }
 
 template <typename T>
@@ -85,7 +93,8 @@ bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStr
   int64_t chunk_arg = chunk;
   size_t slot_arg = slot, scratch_arg = scratch_off;
   float scale = average ? 1.0f / (float)N : 1.0f;
-  void* args[] = {&v, &x, &chunk_arg, &slot_arg, &scratch_arg, &scale};
+  int pipelined = pipelined_for((size_t)chunk * sizeof(T)) ? 1 : 0;
+  void* args[] = {&v, &x, &chunk_arg, &slot_arg, &scratch_arg, &scale, &pipelined};
   BAGUA_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)bytegrad_kernel<T>, dim3(grid), dim3(kThreads), args, 0,
                                                stream));
   arena.count_launch();
@@ -103,7 +112,9 @@ void emu_bytegrad_t(const EmuRank* dev, int nranks, int blocks, int64_t n, float
   BAGUA_CHECK(grid <= per_sm * sms, Communicator,
               "emulation needs " << grid << " co-resident blocks, the device holds " << per_sm * sms);
   int64_t chunk = n / nranks;
-  void* args[] = {(void*)&dev, (void*)&blocks, (void*)&chunk, (void*)&slot_bytes, (void*)&scratch_off, (void*)&scale};
+  int pipelined = pipelined_for((size_t)chunk * sizeof(T)) ? 1 : 0;
+  void* args[] = {(void*)&dev, (void*)&blocks, (void*)&chunk, (void*)&slot_bytes, (void*)&scratch_off, (void*)&scale,
+                  (void*)&pipelined};
   BAGUA_CUDA_CHECK(
       cudaLaunchCooperativeKernel((const void*)bytegrad_emu_kernel<T>, dim3(grid), dim3(kThreads), args, 0, 0));
 }

@@ -58,9 +58,16 @@ __device__ __forceinline__ void fold_partials(const float2* part, int G, float& 
   if (mn > mx) mn = mx = 0.f;
 }
 
+// `pipelined` changes how the reduced chunks travel back (the last two phases): instead of storing
+// every 16 quantised bytes to all N ranks at once and waiting for all of them before dequantising
+// anything, a rank quantises its chunk once into its own slot, copies it to one destination after
+// the other — nearest successor first — and signals each destination as soon as that copy is
+// complete; the receiver waits for one source at a time, in the order in which they finish, and
+// dequantises a chunk while the next ones are still on the wire.  Same bytes, same values.
 template <typename T>
 __device__ __forceinline__ void bytegrad_body(const ArenaView& v, const psync::Launch& L, T* __restrict__ x,
-                                              int64_t chunk, size_t slot_bytes, size_t scratch_off, float scale) {
+                                              int64_t chunk, size_t slot_bytes, size_t scratch_off, float scale,
+                                              bool pipelined = false) {
   const int me = v.rank, N = v.nranks, G = L.grid, b = L.block;
   const int64_t groups = chunk / 16;
   const int64_t lo = groups * b / G * 16, hi = groups * (b + 1) / G * 16;
@@ -153,21 +160,58 @@ __device__ __forceinline__ void bytegrad_body(const ArenaView& v, const psync::L
     const mmdev::Grid g = mmdev::make_grid(round_through<T>(mn), round_through<T>(mx));
     if (threadIdx.x < N) write_header<T>(v.staging[threadIdx.x] + ag_off + (size_t)me * slot_bytes, mn, mx);
     const T* p = x + (int64_t)me * chunk;
-    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
-      float f[16];
-      mmdev::load16(p + i, f);
-      const uint4 packed = mmdev::pack_q16(f, g);
-      for (int k = 0; k < N; ++k) {
+    if (!pipelined) {
+      for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+        float f[16];
+        mmdev::load16(p + i, f);
+        const uint4 packed = mmdev::pack_q16(f, g);
+        for (int k = 0; k < N; ++k) {
+          const int q = (me + k) % N;
+          *reinterpret_cast<uint4*>(v.staging[q] + ag_off + (size_t)me * slot_bytes + kHdr + i) = packed;
+        }
+      }
+      psync::cta_signal_phase(v, L, 1, peers_mask(v));
+      ok = psync::cta_wait_phase(v, L, 1, peers_mask(v));
+    } else {
+      uint8_t* own = my_stage + ag_off + (size_t)me * slot_bytes + kHdr;
+      for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+        float f[16];
+        mmdev::load16(p + i, f);
+        mmdev::store_q16(own + i, f, g);
+      }
+      // every thread copies the vectors it has just written itself, so no barrier is needed here
+      for (int k = 1; k < N; ++k) {
         const int q = (me + k) % N;
-        *reinterpret_cast<uint4*>(v.staging[q] + ag_off + (size_t)me * slot_bytes + kHdr + i) = packed;
+        uint8_t* dst = v.staging[q] + ag_off + (size_t)me * slot_bytes + kHdr;
+        for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16)
+          *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(own + i);
+        psync::cta_signal_phase(v, L, 1, 1u << q);
       }
     }
-    psync::cta_signal_phase(v, L, 1, peers_mask(v));
-    ok = psync::cta_wait_phase(v, L, 1, peers_mask(v));
   }
 
   // ---- P5 ----
-  if (ok) {
+  if (ok && pipelined) {
+    for (int k = 0; k < N; ++k) {
+      const int c = (me - k + N) % N;  // own chunk, then the sources in the order in which they reach this rank
+      if (k > 0) {
+        ok = psync::cta_wait_phase(v, L, 1, 1u << c);
+        if (!ok) break;
+      }
+      if (threadIdx.x == 0) s_grid[0] = read_grid<T>(my_stage + ag_off + (size_t)c * slot_bytes);
+      __syncthreads();
+      mmdev::build_dequant_lut<T>(s_lut, s_grid[0]);
+      __syncthreads();
+      const uint8_t* q = my_stage + ag_off + (size_t)c * slot_bytes + kHdr;
+      T* out = x + (int64_t)c * chunk;
+      for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+        float f[16];
+        mmdev::lut_dq16(q + i, f, s_lut);
+        mmdev::store16(out + i, f);
+      }
+      __syncthreads();  // the table is rebuilt for the next chunk
+    }
+  } else if (ok) {
     if (threadIdx.x < N) s_grid[threadIdx.x] = read_grid<T>(my_stage + ag_off + (size_t)threadIdx.x * slot_bytes);
     __syncthreads();
     for (int c = 0; c < N; ++c) mmdev::build_dequant_lut<T>(s_lut + c * 256, s_grid[c]);

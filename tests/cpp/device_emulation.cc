@@ -313,8 +313,9 @@ void run_body(World& w, int me, int b, uint32_t k) {
       const int64_t chunk = 4 * c;
       const size_t slot = (size_t)chunk + 32;
       const size_t scratch_off = ((2 * (size_t)w.N * slot + 255) / 256) * 256;
+      // the op's (otherwise unused) root picks the variant: odd = chunks travel back one destination at a time
       bytegrad_bodies::bytegrad_body<float>(v, L, reinterpret_cast<float*>(r.in.data()), chunk, slot, scratch_off,
-                                            op.scale);
+                                            op.scale, (op.root & 1) != 0);
       break;
     }
     case Kind::LpRing: {

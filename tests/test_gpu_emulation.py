@@ -135,3 +135,25 @@ def test_emulated_arena_rejects_oversized_ops():
     xs = [torch.zeros(1 << 20, device="cuda") for _ in range(2)]
     with pytest.raises(RuntimeError, match="staging"):
         arena.allreduce(xs, xs, True, "oneshot", 2)
+
+
+@pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_BYTEGRAD_PIPELINE") != "1",
+                    reason="ByteGrad with the reduced chunks travelling back one destination at a time: set "
+                           "BAGUA_B200_TEST_BYTEGRAD_PIPELINE=1 (first run on hardware pending)")
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16])
+def test_emulated_bytegrad_pipelined_equals_the_default_variant(nranks, dt, monkeypatch):
+    """Same bytes and values, another schedule for the last two phases: the results must be bit-equal."""
+    arena = _arena(nranks)
+    n = 16 * nranks * 1031
+    xs = _inputs(nranks, n, dt, seed=13)
+    plain = [x.clone() for x in xs]
+    monkeypatch.delenv("BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK", raising=False)
+    arena.bytegrad(plain, True, 5)
+    piped = [x.clone() for x in xs]
+    monkeypatch.setenv("BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK", "0")
+    arena.bytegrad(piped, True, 5)
+    torch.cuda.synchronize()
+    for a, b in zip(plain, piped):
+        assert torch.equal(a, b)
+    assert not torch.equal(piped[0], xs[0])
