@@ -40,3 +40,48 @@ def test_scheduler_with_cuda_events_single_rank():
     # one rank: ByteGrad = quantise/dequantise twice
     assert (flat - orig).abs().max() <= 2 * (orig.max() - orig.min()) / 255
     backend.close()
+
+
+def test_bert_trains_with_a_bf16_residual_stream():
+    """A two-layer BERT through `with_bagua` with ByteGrad under bf16 autocast: the encoder's LayerNorms
+    take and return bf16 (statistics in fp32 inside the library kernel), so every projection sees a
+    bf16 input; losses stay finite and close to the model with stock fp32-in/fp32-out LayerNorms."""
+    import copy
+    import os
+
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import BertConfig, BertForQuestionAnswering
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29547")
+    dev = torch.device("cuda", 0)
+    losses = []
+    for stock in (False, True):
+        torch.manual_seed(0)
+        cfg = BertConfig.tiny()
+        cfg.dropout = 0.0
+        cfg = copy.copy(cfg)
+        cfg.fp32_layernorm_io = stock
+        model = BertForQuestionAnswering(cfg).to(dev)
+        seen = []
+        model.layers[1].qkv.register_forward_hook(lambda m, i, o: seen.append(i[0].dtype))
+        P.init_process_group(dev)
+        opt = P.FlatSGD(model.parameters(), lr=0.05, momentum=0.9)
+        bm = P.with_bagua(model, [opt], P.ByteGradAlgorithm(), bucket_bytes=64 << 10)
+        g = torch.Generator().manual_seed(3)
+        run = []
+        for _ in range(4):
+            ids = torch.randint(0, cfg.vocab_size, (4, 32), generator=g).to(dev)
+            span = torch.randint(0, 32, (4, 2), generator=g).to(dev)
+            opt.zero_grad()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = bm(ids, span[:, 0], span[:, 1])
+            loss.backward()
+            opt.step()
+            run.append(loss.item())
+        torch.cuda.synchronize()
+        P.destroy_process_group()
+        assert all(d == (torch.float32 if stock else torch.bfloat16) for d in seen), seen
+        assert all(torch.isfinite(torch.tensor(run)))
+        losses.append(run)
+    assert all(abs(a - b) < 5e-2 for a, b in zip(*losses)), losses
