@@ -14,7 +14,9 @@ communication stream around `iters` back-to-back buckets after `warmup`, an L2 f
 `ncclAllReduce` through the communicator for reference.  `allgather`, `alltoall`,
 `reduce_scatter` and `broadcast` (not in the default list) time the communicator's own
 collectives on a buffer of the given total size, as peer-memory kernels (path `fused`) or
-library calls (path `library`), issued from a Python op inside a bucket.
+library calls (path `library`), issued from a Python op inside a bucket.  Path `fused_pipelined`
+(ByteGrad and QAdam only) times the ByteGrad kernel's variant that sends the reduced chunks back
+one destination at a time.
 
 Bus bandwidth conventions (bytes that must cross each GPU's links, per direction):
   allreduce:  2(N-1)/N · S            bytegrad: 2(N-1)/N · (S/4 + 32N)
@@ -125,6 +127,14 @@ def main():
                     continue
                 if op == "shift_one" and world % 2:
                     continue
+                # fused_pipelined: ByteGrad with the reduced chunks sent back one destination at a time
+                # (the engine reads the variable at every call, so one process can time both variants)
+                if path == "fused_pipelined":
+                    if op not in ("bytegrad", "qadam"):
+                        continue
+                    os.environ["BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK"] = "0"
+                else:
+                    os.environ.pop("BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK", None)
                 if path == "fused_sym":
                     # bucket in symmetric memory: in-place two-shot without staging
                     if op != "gradient_allreduce":
@@ -188,6 +198,7 @@ def main():
                 del bucket, bt, x, keep
     bb._C.set_sync_per_bucket(False)
     comm.set_p2p_collectives(False)
+    os.environ.pop("BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK", None)
     if rank == 0 and args.out:
         os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
         with open(args.out, "w") as f:
