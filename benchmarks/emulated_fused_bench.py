@@ -57,6 +57,17 @@ def main():
         "bytegrad": (lambda: arena.bytegrad(xs, True, args.blocks), int(N * 3.75 * S)),
         "lp_ring": (lambda: arena.lp_ring(xs, aux[0], aux[1], aux[2], args.blocks), int(N * 13.75 * S)),
     }
+
+    def bytegrad_pipelined():
+        # the variant that sends the reduced chunks back one destination at a time (read per call)
+        os.environ["BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK"] = "0"
+        try:
+            arena.bytegrad(xs, True, args.blocks)
+        finally:
+            os.environ.pop("BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK", None)
+
+    # one more pass over a quantised chunk per destination (S/4 per rank) than the default
+    cases["bytegrad_pipelined"] = (bytegrad_pipelined, int(N * 4.0 * S))
     # the communicator's collectives: every rank's buffer of S bytes is cut in N chunks of c = S/N
     c = S // N
     parts = [x[:n // N] for x in xs]
