@@ -24,3 +24,15 @@ def test_low_level_api_example_averages_and_compresses_on_two_ranks():
 def test_training_example_runs_a_few_steps():
     out = _run("examples/train_synthetic.py", "--model", "mlp", "--algorithm", "bytegrad", "--steps", "4")
     assert "loss" in out.lower()
+
+
+def test_host_overhead_benchmark_runs_and_a_ready_mark_stays_cheap():
+    """`benchmarks/host_overhead.py` end to end.  A ready mark on a tensor of a 400-tensor bucket cost
+    10.7 us while the readiness check walked the bucket from the front and costs about 0.5 us now:
+    5 us tells the two apart with room for a busy host."""
+    import json
+
+    out = _run("benchmarks/host_overhead.py")
+    row = json.loads(out.strip().splitlines()[-1])
+    assert set(row) >= {"mark_us", "bucket_us", "wrapper_us"}
+    assert 0 < row["mark_us"] < 5.0, row
