@@ -25,7 +25,7 @@ BUILD_DIR = os.path.join(PKG_DIR, "build")
 SOURCES = [
     "bindings.cc",
     "runtime/backend.cc",
-    "runtime/protocol_model.cc",
+    "runtime/timeline.cc",
     "pool/resource_pool.cc",
     "tensor/tensor.cc",
     "comm/communicator.cc",

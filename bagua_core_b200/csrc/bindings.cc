@@ -22,7 +22,7 @@
 #include "ops/comm_op.h"
 #include "pool/resource_pool.h"
 #include "runtime/backend.h"
-#include "runtime/protocol_model.h"
+#include "runtime/timeline.h"
 #include "telemetry/telemetry.h"
 #include "tensor/tensor.h"
 
@@ -204,6 +204,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            },
            py::call_guard<py::gil_scoped_release>())
       .def("check_device_status", [](PyComm& c) { c.inner->check_device_status(); })
+      .def("set_comm_ctas",
+           [](PyComm& c, int ctas, int coop_ctas) {
+             if (auto* a = c.inner->arena()) {
+               if (ctas > 0) a->set_max_blocks(ctas);
+               if (coop_ctas > 0) a->set_max_coop_blocks(coop_ctas);
+             }
+           },
+           py::arg("ctas"), py::arg("coop_ctas") = 0, py::call_guard<py::gil_scoped_release>(),
+           "CTA budgets of this communicator's fused kernels (BAGUA_B200_COMM_CTAS / BAGUA_B200_COOP_CTAS); "
+           "0 leaves one unchanged.  Must be set identically on every rank.")
       .def(
           "alloc_symmetric",
           [](PyComm& c, int64_t numel, at::ScalarType dtype) -> py::object {
@@ -438,6 +448,47 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_sync_per_bucket", [](bool on) { EngineConfig::global().sync_per_bucket = on; },
         "Reference-faithful mode: synchronise the communication stream after every bucket.");
   m.def("get_sync_per_bucket", []() { return EngineConfig::global().sync_per_bucket; });
+  m.def(
+      "set_tuning",
+      [](const std::string& key, long value) {
+        BAGUA_CHECK(fused::Tuning::global().set(key, value), Backend, "unknown tuning key `" << key << "`");
+      },
+      py::arg("key"), py::arg("value"),
+      "Size thresholds and CTA budgets of the fused kernels (keys: oneshot_bytes, oneshot_sym_bytes, overlap_ctas, "
+      "nvls_overlap_ctas, bytes_per_cta; defaults from BAGUA_B200_<KEY>).  Must be set identically on every rank.");
+  m.def("get_tuning", []() {
+    py::dict d;
+    for (auto& kv : fused::Tuning::global().items()) d[py::str(kv.first)] = kv.second;
+    return d;
+  });
+  m.def("set_bucket_timing", [](bool on) { BucketTimeline::instance().set_enabled(on); }, py::arg("on"),
+        "Record two timing events per bucket on the communication stream (also BAGUA_B200_BUCKET_TIMING=1).");
+  m.def("bucket_timing", []() { return BucketTimeline::instance().enabled(); });
+  m.def("timeline_mark", [](const std::string& name, uint64_t stream) {
+    BucketTimeline::instance().mark(name, (cudaStream_t)stream);
+  }, py::arg("name"), py::arg("stream"), "Drops a named mark on `stream` into the bucket time line.");
+  m.def(
+      "timeline_collect",
+      []() {
+        std::vector<TimelineSpan> spans;
+        {
+          py::gil_scoped_release rel;
+          spans = BucketTimeline::instance().collect();
+        }
+        py::list out;
+        for (auto& sp : spans) {
+          py::dict d;
+          d["name"] = sp.name;
+          d["kind"] = sp.kind;
+          d["start_ms"] = sp.start_ms;
+          d["end_ms"] = sp.end_ms;
+          d["bytes"] = sp.bytes;
+          out.append(d);
+        }
+        return out;
+      },
+      "Waits for the recorded events and returns [{name, kind: bucket|mark, start_ms, end_ms, bytes}] relative to "
+      "the first recorded event; the record is emptied.");
   m.def("set_log_level", [](const std::string& s) { set_log_level(parse_log_level(s.c_str())); });
   m.def("stats", []() {
     auto& s = EngineStats::global();
@@ -862,24 +913,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   m.def("release_multicast_slabs", []() { return release_all_multicast_slabs(); },
         "Drops every NVSwitch multicast binding this process holds (called at interpreter exit).");
-  m.def(
-      "protocol_model_check",
-      [](int nranks, int blocks, int n_ops, uint32_t seed, bool use_done_chain, int slow_rank, bool mix) {
-        ProtocolModelResult r;
-        {
-          py::gil_scoped_release rel;
-          r = run_protocol_model(nranks, blocks, n_ops, seed, use_done_chain, slow_rank, mix);
-        }
-        py::dict d;
-        d["errors"] = r.errors;
-        d["timeouts"] = r.timeouts;
-        d["ops"] = r.ops;
-        return d;
-      },
-      py::arg("nranks"), py::arg("blocks"), py::arg("n_ops"), py::arg("seed") = 0, py::arg("use_done_chain") = true,
-      py::arg("slow_rank") = -1, py::arg("mix") = false,
-      "Runs the host-thread model of the fused kernels' signalling protocol and reports wrong values / timeouts "
-      "(mix=True draws the ops from every kernel of the communicator, not only the all-reduces).");
   m.def(
       "debug_wait_timeout",
       [](int device, double wait_ms) {

@@ -26,9 +26,12 @@ PeerArena::PeerArena(Transport& transport, int rank, int nranks, int device, cud
   try {
     BAGUA_CUDA_CHECK(cudaMalloc(&local_signals_, kSigWords * sizeof(uint32_t)));
     BAGUA_CUDA_CHECK(cudaMemset(local_signals_, 0, kSigWords * sizeof(uint32_t)));
-    BAGUA_CUDA_CHECK(cudaHostAlloc((void**)&status_host_, sizeof(DeviceStatus), cudaHostAllocMapped));
-    std::memset(status_host_, 0, sizeof(DeviceStatus));
+    static_assert(sizeof(DeviceStatus) <= 60, "the status record shares 64 bytes with the poison source word");
+    BAGUA_CUDA_CHECK(cudaHostAlloc((void**)&status_host_, 64, cudaHostAllocMapped));
+    std::memset(status_host_, 0, 64);
+    reinterpret_cast<uint32_t*>(status_host_)[15] = 1u;  // what poison() copies into the pad
     BAGUA_CUDA_CHECK(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
+    BAGUA_CUDA_CHECK(cudaStreamCreateWithFlags(&abort_stream_, cudaStreamNonBlocking));
     BAGUA_CUDA_CHECK(cudaDeviceSynchronize());
     // fails when a peer cannot be mapped (no peer access between the devices, IPC disabled)
     allocate_and_exchange((size_t)env_long("BAGUA_B200_STAGING_MB", 64) << 20);
@@ -66,6 +69,11 @@ void PeerArena::release() {
   if (local_staging_) cudaFree(local_staging_);
   for (void* p : retired_) cudaFree(p);
   retired_.clear();
+  if (abort_stream_) {
+    cudaStreamSynchronize(abort_stream_);  // a poison() copy still reads status_host_
+    cudaStreamDestroy(abort_stream_);
+    abort_stream_ = nullptr;
+  }
   if (local_signals_) cudaFree(local_signals_);
   if (status_host_) cudaFreeHost(status_host_);
   local_staging_ = nullptr;
@@ -281,5 +289,20 @@ DeviceStatus PeerArena::read_status() const {
   return s;
 }
 void PeerArena::clear_status() { std::memset(status_host_, 0, sizeof(DeviceStatus)); }
+
+void PeerArena::poison() {
+  if (!local_signals_ || !abort_stream_) return;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(device_);
+  // pinned source, stream of its own: queues behind nothing and does not wait for running kernels
+  cudaError_t e = cudaMemcpyAsync((uint32_t*)local_signals_ + kSigPoison, reinterpret_cast<uint32_t*>(status_host_) + 15,
+                                  sizeof(uint32_t), cudaMemcpyHostToDevice, abort_stream_);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    BAGUA_LOG(Warn, "could not raise the device-side abort word: " << cudaGetErrorString(e));
+  }
+  cudaSetDevice(prev);
+}
 
 }  // namespace bagua

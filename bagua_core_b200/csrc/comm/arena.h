@@ -43,6 +43,7 @@ constexpr int kArenaPhases = 2;
 constexpr int kSigDone = 0;                                   // [kArenaMaxRanks]
 constexpr int kSigPhase = 32;                                 // [phases][ranks][blocks]
 constexpr int kSigCounter = kSigPhase + kArenaPhases * kArenaMaxRanks * kArenaMaxBlocks;  // local CTA counter
+constexpr int kSigPoison = kSigCounter + 1;                   // rank-local: non-zero once a wait ran out or the host aborted
 constexpr int kSigGridBar = kSigCounter + 2;                  // 64-bit local grid-barrier counter (2 words, 8 B aligned)
 constexpr int kSigWords = kSigGridBar + 6;
 static_assert(kSigGridBar % 2 == 0, "the 64-bit grid-barrier counter must sit on an 8-byte boundary");
@@ -87,6 +88,8 @@ class PeerArena {
 
   // Max CTAs per fused kernel (BAGUA_B200_COMM_CTAS, default 64, at most kArenaMaxBlocks).
   int max_blocks() const { return max_blocks_; }
+  void set_max_blocks(int n) { max_blocks_ = n < 1 ? 1 : (n > kArenaMaxBlocks ? kArenaMaxBlocks : n); }
+  void set_max_coop_blocks(int n) { max_coop_blocks_ = n < 1 ? 1 : (n > kArenaMaxBlocks ? kArenaMaxBlocks : n); }
   // Max CTAs of the cooperative kernels (ByteGrad, low-precision ring), which do several
   // HBM passes and quantiser math per element (BAGUA_B200_COOP_CTAS, default 148 = one per SM).
   int max_coop_blocks() const { return max_coop_blocks_; }
@@ -96,6 +99,10 @@ class PeerArena {
   // Host view of the status record (all zero when healthy).
   DeviceStatus read_status() const;
   void clear_status();
+  // Raises this rank's poison word from the host, on a stream of its own, so that kernels of
+  // this rank that are spinning on a peer give up at their next poll (every 32 spins) instead of
+  // at their deadline.  Terminal: the word is never cleared, the communicator is finished.
+  void poison();
   uint32_t epoch() const { return epoch_; }
   uint64_t fused_launches() const { return launches_; }
   void count_launch() { ++launches_; }
@@ -143,8 +150,9 @@ class PeerArena {
   void* peer_signals_[kArenaMaxRanks] = {};
   std::vector<void*> retired_;       // superseded local staging buffers, freed at destruction
   std::vector<void*> retired_peer_;  // superseded peer mappings
-  DeviceStatus* status_host_ = nullptr;
+  DeviceStatus* status_host_ = nullptr;  // 64 pinned, mapped bytes: the record, and at word 15 a constant 1
   DeviceStatus* status_dev_ = nullptr;
+  cudaStream_t abort_stream_ = nullptr;  // carries poison(); never blocked by a spinning kernel
   uint32_t epoch_ = 0;
   uint64_t grid_bar_ = 0;
   uint64_t deadline_ns_;

@@ -8,6 +8,10 @@
 namespace bagua {
 
 namespace {
+// Live communicators, for check_all_device_status().
+std::mutex g_comms_mu;
+std::vector<SingleCommunicator*> g_comms;
+
 void same_kind(const RawTensor& a, const RawTensor& b, const char* what) {
   BAGUA_CHECK(a.dtype() == b.dtype(), Communicator, what << ": send and recv dtypes differ");
   BAGUA_CHECK(a.device_id() == b.device_id(), Communicator, what << ": send and recv devices differ");
@@ -27,16 +31,37 @@ SingleCommunicator::SingleCommunicator(int rank, int nranks, int device_id, uint
   }
   fused_enabled_ = env_long("BAGUA_B200_FUSED", 1) != 0;
   p2p_collectives_ = env_long("BAGUA_B200_P2P_COLLECTIVES", 0) != 0;
+  std::lock_guard<std::mutex> g(g_comms_mu);
+  g_comms.push_back(this);
 }
 
 SingleCommunicator::~SingleCommunicator() {
+  {
+    std::lock_guard<std::mutex> g(g_comms_mu);
+    for (size_t i = 0; i < g_comms.size(); ++i)
+      if (g_comms[i] == this) {
+        g_comms.erase(g_comms.begin() + (long)i);
+        break;
+      }
+  }
   arena_.reset();
   transport_.reset();
 }
 
 void SingleCommunicator::abort() {
   aborted_.store(true, std::memory_order_release);
+  {
+    // fused kernels of this rank that wait for a peer see the word at their next poll and return
+    // (reference: abort() also stops the in-flight NCCL kernels, communicators/mod.rs:456-471)
+    std::lock_guard<std::mutex> g(arena_mu_);
+    if (arena_) arena_->poison();
+  }
   transport_->abort();
+}
+
+void SingleCommunicator::check_all_device_status() {
+  std::lock_guard<std::mutex> g(g_comms_mu);
+  for (SingleCommunicator* c : g_comms) c->check_device_status();
 }
 
 void SingleCommunicator::check_live() const {
@@ -85,6 +110,7 @@ void SingleCommunicator::check_device_status() {
   DeviceStatus s = arena_->read_status();
   if (s.code == 0) return;
   aborted_.store(true, std::memory_order_release);
+  arena_->clear_status();  // reported once; from here on the communicator answers "aborted"
   std::ostringstream o;
   if (s.code == 4) {
     o << "alltoall_v: rank " << s.peer << " announced a segment of " << s.seen << " bytes for rank " << rank_

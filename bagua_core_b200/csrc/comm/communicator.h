@@ -73,8 +73,12 @@ class SingleCommunicator {
   PeerArena* arena();
   void set_fused(bool on) { fused_enabled_ = on; }
   bool fused_enabled() const { return fused_enabled_; }
-  // Throws CommunicatorError if a fused kernel reported a device-side wait that ran out.
+  // Throws CommunicatorError if a fused kernel reported a device-side wait that ran out; the
+  // communicator is marked aborted and the record is cleared, so the error is raised once and
+  // every later use fails with "communicator was aborted".  A plain load of host-mapped memory.
   void check_device_status();
+  // The same for every live communicator of this process (what `wait_pending_comm_ops` calls).
+  static void check_all_device_status();
   // Peer-memory kernels for the collectives above (all-reduce / reduce / reduce-scatter with SUM or
   // AVG, all-gather, all-to-all, gather, scatter, broadcast, barrier) instead of library calls.  Off unless
   // BAGUA_B200_P2P_COLLECTIVES=1 or set_p2p_collectives(true); calls inside a

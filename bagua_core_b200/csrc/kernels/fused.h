@@ -18,20 +18,42 @@
 
 #include <cuda_runtime_api.h>
 
+#include <atomic>
+#include <string>
+#include <utility>
+#include <vector>
+
 #include "../comm/arena.h"
 #include "../common.h"
 
 namespace bagua {
 namespace fused {
 
-// out = scale * sum_r in_r.  `in` and `out` may be the same buffer.
-bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream);
+// Size thresholds and CTA budgets of the fused kernels.  Defaults come from the environment
+// (BAGUA_B200_<KEY IN CAPITALS>); `set` changes them at run time for all later launches, which
+// every rank must do alike (the thresholds select the algorithm, and ranks must agree on it).
+struct Tuning {
+  std::atomic<long> oneshot_bytes{-1};         // staging path: one-shot up to this size (-1: by rank count)
+  std::atomic<long> oneshot_sym_bytes{128 << 10};  // symmetric buffers: one-shot up to this size
+  std::atomic<long> overlap_ctas{64};          // CTA budget of a bucket reduced under backward kernels
+  std::atomic<long> bytes_per_cta{64 << 10};   // payload per CTA below the budget
+  std::atomic<long> nvls_overlap_ctas{64};     // the overlap budget of the multimem all-reduce
+  static Tuning& global();
+  bool set(const std::string& key, long value);  // false: unknown key
+  std::vector<std::pair<std::string, long>> items() const;
+};
+
+// out = scale * sum_r in_r.  `in` and `out` may be the same buffer.  `overlapped`: the call runs
+// while compute kernels want the SMs (a gradient bucket during backward), so it takes the
+// overlap CTA budget instead of the arena's.
+bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream,
+               bool overlapped = false);
 
 // The same through the NVSwitch's reduction units (multimem.ld_reduce / multimem.st); only for
 // buffers inside a symmetric-heap slab that has a multicast mapping (BAGUA_B200_NVLS=1).
 // `allreduce` tries this first.
 bool allreduce_nvls(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale,
-                    cudaStream_t stream);
+                    cudaStream_t stream, bool overlapped = false);
 
 // In-place ByteGrad on `bucket` (n elements, n % (16*nranks) == 0).
 bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream);

@@ -44,14 +44,14 @@ __global__ void __launch_bounds__(kThreads)
 }
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-    allreduce_oneshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in,
-                             uint4* __restrict__ out, int64_t nvec, int64_t slot_vecs, float scale) {
+    allreduce_oneshot_kernel(const __grid_constant__ ArenaView v, const uint4* in, uint4* out, int64_t nvec,
+                             int64_t slot_vecs, float scale) {  // in == out for the in-place call
   allreduce_oneshot_body<T>(v, psync::real_launch(), in, out, nvec, slot_vecs, scale);
 }
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-    allreduce_twoshot_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in,
-                             uint4* __restrict__ out, int64_t nvec, int64_t max_chunk_vecs, float scale) {
+    allreduce_twoshot_kernel(const __grid_constant__ ArenaView v, const uint4* in, uint4* out, int64_t nvec,
+                             int64_t max_chunk_vecs, float scale) {  // in == out for the in-place call
   allreduce_twoshot_body<T>(v, psync::real_launch(), in, out, nvec, max_chunk_vecs, scale);
 }
 template <typename T>
@@ -103,34 +103,47 @@ __global__ void wait_probe_kernel(ArenaView v) {
   psync::cta_wait_phase(v, psync::real_launch(), 0, 1u << 1);
 }
 
-int pick_grid(const PeerArena& arena, size_t bytes) {
-  // one CTA per 64 KiB, at least 1, at most the arena's CTA budget
-  int64_t g = (int64_t)((bytes + (64 << 10) - 1) / (64 << 10));
-  g = std::max<int64_t>(1, std::min<int64_t>(g, arena.max_blocks()));
+int pick_grid(const PeerArena& arena, size_t bytes, bool overlapped = false) {
+  // one CTA per `bytes_per_cta` of payload, at least 1, at most the CTA budget: the arena's
+  // for a call that has the GPU to itself, the (smaller) overlap budget for a bucket that is
+  // reduced while backward kernels want the SMs
+  const Tuning& t = Tuning::global();
+  const int64_t per = std::max<int64_t>(t.bytes_per_cta.load(), 4096);
+  int64_t cap = arena.max_blocks();
+  if (overlapped) cap = std::min<int64_t>(cap, std::max<int64_t>(t.overlap_ctas.load(), 1));
+  int64_t g = (int64_t)((bytes + per - 1) / per);
+  g = std::max<int64_t>(1, std::min<int64_t>(g, cap));
   return (int)g;
 }
 
 template <typename T>
-bool allreduce_t(PeerArena& arena, const void* in, void* out, int64_t n, float scale, cudaStream_t stream) {
+bool allreduce_t(PeerArena& arena, const void* in, void* out, int64_t n, float scale, cudaStream_t stream,
+                 bool overlapped) {
   const size_t bytes = (size_t)n * sizeof(T);
   if (bytes == 0) return true;
   if (bytes % 16 != 0 || (uintptr_t)in % 16 != 0 || (uintptr_t)out % 16 != 0) return false;
   const int64_t nvec = (int64_t)(bytes / 16);
   const int N = arena.nranks();
-  // One-shot sends (N-1)·S per GPU in one hop, two-shot 2(N-1)/N·S in two hops: with two
-  // ranks the wire bytes are equal, so one-shot always wins; otherwise it wins while the
-  // extra bytes cost less than the extra hop (about 16 MB of wire traffic per GPU).
-  static const long oneshot_env = env_long("BAGUA_B200_ONESHOT_BYTES", -1);
-  const size_t oneshot_max = oneshot_env >= 0 ? (size_t)oneshot_env
-                             : N == 2         ? ((size_t)512 << 20)
-                                              : ((size_t)16 << 20) / (size_t)(N - 1);
-  const int grid = pick_grid(arena, bytes);
+  const Tuning& tune = Tuning::global();
+  const int grid = pick_grid(arena, bytes, overlapped);
+  // Buffers in the symmetric heap need no staging: above a small size (two signalling hops
+  // instead of one) every rank reduces its own 1/N of the peers' buffers in place.  That moves
+  // (N-1)/N·S per GPU and direction where the one-shot push moves (N-1)·S, also with two ranks.
+  void *pin[kArenaMaxRanks], *pout[kArenaMaxRanks];
+  const bool sym = arena.sym_translate(in, bytes, pin) && arena.sym_translate(out, bytes, pout);
+  // One-shot through staging sends (N-1)·S per GPU in one hop, two-shot 2(N-1)/N·S in two hops:
+  // with two ranks the wire bytes are equal, so one-shot always wins; otherwise it wins while
+  // the extra bytes cost less than the extra hop (about 16 MB of wire traffic per GPU).
+  const long oneshot_env = tune.oneshot_bytes.load();
+  const size_t oneshot_max = sym                ? (size_t)std::max<long>(tune.oneshot_sym_bytes.load(), 0)
+                             : oneshot_env >= 0 ? (size_t)oneshot_env
+                             : N == 2           ? ((size_t)512 << 20)
+                                                : ((size_t)16 << 20) / (size_t)(N - 1);
   if (bytes <= oneshot_max) {
     arena.ensure_staging((size_t)N * bytes);
     ArenaView v = arena.next_view(grid, 0);
     allreduce_oneshot_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (uint4*)out, nvec, nvec, scale);
-  } else if (void *pin[kArenaMaxRanks], *pout[kArenaMaxRanks];
-             arena.sym_translate(in, bytes, pin) && arena.sym_translate(out, bytes, pout)) {
+  } else if (sym) {
     SymPtrs p;
     std::memset(&p, 0, sizeof(p));
     for (int r = 0; r < N; ++r) {
@@ -189,12 +202,44 @@ void coop_launch(K kernel, int grid, Args... args) {
 
 }  // namespace
 
-bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream) {
-  if (arena.nvls_enabled() && allreduce_nvls(arena, in, out, n, dt, scale, stream)) return true;
+Tuning& Tuning::global() {
+  static Tuning t;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    t.oneshot_bytes = env_long("BAGUA_B200_ONESHOT_BYTES", -1);
+    t.oneshot_sym_bytes = env_long("BAGUA_B200_ONESHOT_SYM_BYTES", 128 << 10);
+    t.overlap_ctas = env_long("BAGUA_B200_OVERLAP_CTAS", 64);
+    t.bytes_per_cta = env_long("BAGUA_B200_BYTES_PER_CTA", 64 << 10);
+    t.nvls_overlap_ctas = env_long("BAGUA_B200_NVLS_OVERLAP_CTAS", 64);
+  });
+  return t;
+}
+
+bool Tuning::set(const std::string& key, long value) {
+  if (key == "oneshot_bytes") oneshot_bytes = value;
+  else if (key == "oneshot_sym_bytes") oneshot_sym_bytes = value;
+  else if (key == "overlap_ctas") overlap_ctas = value;
+  else if (key == "bytes_per_cta") bytes_per_cta = value;
+  else if (key == "nvls_overlap_ctas") nvls_overlap_ctas = value;
+  else return false;
+  return true;
+}
+
+std::vector<std::pair<std::string, long>> Tuning::items() const {
+  return {{"oneshot_bytes", oneshot_bytes.load()},
+          {"oneshot_sym_bytes", oneshot_sym_bytes.load()},
+          {"overlap_ctas", overlap_ctas.load()},
+          {"bytes_per_cta", bytes_per_cta.load()},
+          {"nvls_overlap_ctas", nvls_overlap_ctas.load()}};
+}
+
+bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream,
+               bool overlapped) {
+  if (arena.nvls_enabled() && allreduce_nvls(arena, in, out, n, dt, scale, stream, overlapped)) return true;
   switch (dt) {
-    case DType::F32: return allreduce_t<float>(arena, in, out, n, scale, stream);
-    case DType::F16: return allreduce_t<__half>(arena, in, out, n, scale, stream);
-    case DType::BF16: return allreduce_t<__nv_bfloat16>(arena, in, out, n, scale, stream);
+    case DType::F32: return allreduce_t<float>(arena, in, out, n, scale, stream, overlapped);
+    case DType::F16: return allreduce_t<__half>(arena, in, out, n, scale, stream, overlapped);
+    case DType::BF16: return allreduce_t<__nv_bfloat16>(arena, in, out, n, scale, stream, overlapped);
     default: return false;
   }
 }

@@ -19,7 +19,7 @@ using psync::Launch;
 // ---------------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ void allreduce_oneshot_body(const ArenaView& v, const Launch& L,
-                                                       const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                       const uint4* in, uint4* out,  // may be the same buffer
                                                        int64_t nvec, int64_t slot_vecs, float scale) {
   using O = VecOps<T>;
   const int me = v.rank, N = v.nranks;
@@ -55,7 +55,7 @@ __device__ __forceinline__ void allreduce_oneshot_body(const ArenaView& v, const
 // ---------------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ void allreduce_twoshot_body(const ArenaView& v, const Launch& L,
-                                                       const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                       const uint4* in, uint4* out,  // may be the same buffer
                                                        int64_t nvec, int64_t max_chunk_vecs, float scale) {
   using O = VecOps<T>;
   const int me = v.rank, N = v.nranks;
@@ -134,11 +134,16 @@ struct SymPtrs {
   uint4* out[kArenaMaxRanks];
 };
 
-template <typename T>
-__device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Launch& L, const SymPtrs& p,
-                                                   int64_t nvec, float scale) {
+// NR is the rank count when it is 2, 4 or 8 (the loops over ranks then unroll with no
+// predicates and U = 16 / NR vectors per thread keep 16 loads in flight whatever the rank
+// count), 0 for any other count (bound checks against v.nranks, U = 2).
+template <typename T, int NR>
+__device__ __forceinline__ void allreduce_sym_body_n(const ArenaView& v, const Launch& L, const SymPtrs& p,
+                                                     int64_t nvec, float scale) {
   using O = VecOps<T>;
-  const int me = v.rank, N = v.nranks;
+  constexpr int R = NR > 0 ? NR : kArenaMaxRanks;  // unrolled extent of the rank loops
+  constexpr int U = NR > 0 ? 16 / NR : 2;          // vectors per thread per iteration
+  const int me = v.rank, N = NR > 0 ? NR : v.nranks;
   const int G = L.grid, b = L.block;
   const int64_t c0 = nvec * me / N, len = nvec * (me + 1) / N - c0;
   const int64_t lo = c0 + len * b / G, hi = c0 + len * (b + 1) / G;
@@ -147,14 +152,13 @@ __device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Lau
   psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
   bool ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
   if (ok) {
-    constexpr int U = 2;  // vectors per thread per iteration: 2·N loads in flight
     int64_t i = lo + threadIdx.x;
     for (; i + (U - 1) * kThreads < hi; i += U * kThreads) {
-      uint4 x[U][kArenaMaxRanks];
+      uint4 x[U][R];
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int r = 0; r < kArenaMaxRanks; ++r)
+        for (int r = 0; r < R; ++r)
           if (r < N) x[u][r] = p.in[r][i + u * kThreads];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -162,11 +166,11 @@ __device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Lau
 #pragma unroll
         for (int k = 0; k < O::N; ++k) a[k] = 0.f;
 #pragma unroll
-        for (int r = 0; r < kArenaMaxRanks; ++r)
+        for (int r = 0; r < R; ++r)
           if (r < N) O::acc(a, x[u][r]);
         const uint4 res = O::pack(a, scale);
 #pragma unroll
-        for (int r = 0; r < kArenaMaxRanks; ++r)
+        for (int r = 0; r < R; ++r)
           if (r < N) p.out[r][i + u * kThreads] = res;
       }
     }
@@ -183,6 +187,17 @@ __device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Lau
     ok = psync::cta_wait_phase(v, L, 1, all_peers_mask(v));
   }
   psync::cta_finish_op(v, L);
+}
+
+template <typename T>
+__device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Launch& L, const SymPtrs& p,
+                                                   int64_t nvec, float scale) {
+  switch (v.nranks) {
+    case 2: allreduce_sym_body_n<T, 2>(v, L, p, nvec, scale); break;
+    case 4: allreduce_sym_body_n<T, 4>(v, L, p, nvec, scale); break;
+    case 8: allreduce_sym_body_n<T, 8>(v, L, p, nvec, scale); break;
+    default: allreduce_sym_body_n<T, 0>(v, L, p, nvec, scale); break;
+  }
 }
 
 // ---------------------------------------------------------------------------------

@@ -37,14 +37,21 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 template <typename T>
-bool allreduce_nvls_t(PeerArena& arena, const void* in, void* out, int64_t n, float scale, cudaStream_t stream) {
+bool allreduce_nvls_t(PeerArena& arena, const void* in, void* out, int64_t n, float scale, cudaStream_t stream,
+                      bool overlapped) {
   const size_t bytes = (size_t)n * sizeof(T);
   static const size_t min_bytes = (size_t)env_long("BAGUA_B200_NVLS_MIN_BYTES", 256 << 10);
   if (bytes < min_bytes || bytes % 16 != 0 || (uintptr_t)in % 16 != 0 || (uintptr_t)out % 16 != 0) return false;
   const void* mc_in = arena.sym_multicast(in, bytes);
   void* mc_out = arena.sym_multicast(out, bytes);
   if (!mc_in || !mc_out) return false;
-  const int grid = grid_for_bytes(bytes, arena.max_blocks());
+  // The switch does the additions and the fan-out, so an SM issues one load and one store per
+  // 16 bytes of its chunk whatever the rank count: a bucket reduced under backward kernels gets
+  // by with the small overlap budget.
+  const Tuning& t = Tuning::global();
+  int cap = arena.max_blocks();
+  if (overlapped) cap = (int)std::min<long>(cap, std::max<long>(t.nvls_overlap_ctas.load(), 1));
+  const int grid = grid_for_bytes(bytes, cap);
   ArenaView v = arena.next_view(grid, 0);
   allreduce_nvls_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)mc_in, (uint4*)mc_out, (int64_t)(bytes / 16),
                                                           scale);
@@ -56,12 +63,12 @@ bool allreduce_nvls_t(PeerArena& arena, const void* in, void* out, int64_t n, fl
 }  // namespace
 
 bool allreduce_nvls(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, bool overlapped) {
   if (!arena.nvls_enabled()) return false;
   switch (dt) {
-    case DType::F32: return allreduce_nvls_t<float>(arena, in, out, n, scale, stream);
-    case DType::F16: return allreduce_nvls_t<__half>(arena, in, out, n, scale, stream);
-    case DType::BF16: return allreduce_nvls_t<__nv_bfloat16>(arena, in, out, n, scale, stream);
+    case DType::F32: return allreduce_nvls_t<float>(arena, in, out, n, scale, stream, overlapped);
+    case DType::F16: return allreduce_nvls_t<__half>(arena, in, out, n, scale, stream, overlapped);
+    case DType::BF16: return allreduce_nvls_t<__nv_bfloat16>(arena, in, out, n, scale, stream, overlapped);
     default: return false;
   }
 }

@@ -25,7 +25,7 @@
 namespace bagua {
 namespace psync {
 
-constexpr int kSigPoison = kSigCounter + 1;  // rank-local: non-zero once any wait ran out
+using bagua::kSigPoison;  // rank-local: non-zero once any wait ran out, or the host aborted the communicator
 
 struct Launch {
   int block;  // index of this block inside its rank's grid

@@ -5,6 +5,7 @@
 
 #include "../comm/arena.h"
 #include "../kernels/fused.h"
+#include "../runtime/timeline.h"
 #include "comm_op.h"
 
 namespace bagua {
@@ -39,10 +40,19 @@ int shift_one_peer(int rank, int nranks, int64_t step) {
 
 namespace {
 
-// Arena of the communicator the hook runs on, or null when the fused path is off.
+// Arena of the communicator the hook runs on, or null when the fused path is off.  Before the
+// next fused kernel is launched on an arena, the status record its earlier kernels may have
+// left is read (host-mapped memory, a plain load): a wait that ran out makes this op fail, the
+// failure reaches the caller of `wait_pending_comm_ops`, and no further kernel is started
+// on a communicator that is aborted (its poison word would make each give up at once and
+// leave its bucket unreduced).
 PeerArena* fused_arena(SingleCommunicator& c, const RawTensor& t) {
   if (t.device_id() < 0 || c.nranks() < 2 || !c.fused_enabled()) return nullptr;
-  return c.arena();
+  PeerArena* a = c.arena();
+  if (!a) return nullptr;
+  c.check_device_status();
+  if (c.check_abort()) throw BaguaError(ErrorKind::Communicator, "communicator was aborted");
+  return a;
 }
 
 void note_fused() { EngineStats::global().fused_launches++; }
@@ -55,11 +65,22 @@ struct OpFrame {
     ct = bucket->get_communication_tensor(stream, force_copy, no_copy_back);
     if (ct.staged) EngineStats::global().staged_copies++;
     EngineStats::global().bytes_communicated += ct.raw->bytes_allocated();
+    gpu = ct.raw->device_id() >= 0;
+    // device time line: the span opens after the waits on the tensors' ready events
+    if (gpu) ticket = BucketTimeline::instance().begin(bucket->name(), ct.raw->bytes_allocated(), (cudaStream_t)stream);
   }
-  void finish() { ct.finish(EngineConfig::global().sync_per_bucket); }
+  void finish() {
+    if (ticket) BucketTimeline::instance().end(ticket, (cudaStream_t)stream);
+    const bool sync = EngineConfig::global().sync_per_bucket;
+    ct.finish(sync);
+    // after a stream synchronisation the status record is final for this bucket
+    if (gpu && sync) SingleCommunicator::check_all_device_status();
+  }
   std::unique_lock<std::mutex> lock;
   uint64_t stream;
   CommunicationTensor ct;
+  bool gpu = false;
+  uint64_t ticket = 0;
 };
 
 // ---------------------------------------------------------------------------------
@@ -77,7 +98,7 @@ class CentralizedFullPrecisionSynchronous : public CommOp {
       if (PeerArena* a = fused_arena(c, t)) {
         const float scale = average_ ? 1.0f / (float)c.nranks() : 1.0f;
         if (fused::allreduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,
-                             (cudaStream_t)c.stream())) {
+                             (cudaStream_t)c.stream(), /*overlapped=*/true)) {
           note_fused();
           return;
         }

@@ -178,6 +178,9 @@ size_t CommBackend::wait_pending_comm_ops() {
     watchdog_error_.clear();
   }
   if (!first_error.empty()) throw BaguaError(ErrorKind::Backend, "communication failed: " + first_error);
+  // Every bucket has been queued; kernels of earlier buckets (or steps) may have given up on a
+  // peer in the meantime.  Their status records are host-mapped, so looking costs a few loads.
+  if (device_id_ >= 0) SingleCommunicator::check_all_device_status();
   return n;
 }
 

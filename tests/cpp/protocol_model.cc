@@ -1,6 +1,7 @@
 // Host-thread model of the cross-GPU signalling protocol used by the fused kernels.
 //
-// compute-sanitizer cannot be run on the GPU pool, so the protocol (epoch-valued phase
+// A test program (tests/test_cpu_protocol_model.py builds it with g++): the kernels' memory
+// ordering cannot be checked by a device-side tool here, so the protocol (epoch-valued phase
 // words, the `done` chain that guards staging reuse, block-to-block pairing) is restated
 // here with std::thread + std::atomic and the same acquire/release structure and the same
 // index arithmetic as the kernels, and run under randomised and adversarial schedules:

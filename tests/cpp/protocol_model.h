@@ -1,7 +1,7 @@
 // Host-thread model of the fused kernels' signalling protocol (see protocol_model.cc).
 #pragma once
 
-#include "../common.h"
+#include "common.h"
 
 namespace bagua {
 

@@ -10,7 +10,7 @@
 #include "ops/comm_op.h"
 #include "pool/resource_pool.h"
 #include "runtime/backend.h"
-#include "runtime/protocol_model.h"
+#include "protocol_model.h"
 #include "tensor/tensor.h"
 
 using namespace bagua;

@@ -11,6 +11,8 @@
 
 namespace bagua {
 PeerArena* SingleCommunicator::arena() { UNREACHABLE(); }
+void SingleCommunicator::check_device_status() { UNREACHABLE(); }
+void SingleCommunicator::check_all_device_status() {}  // host-only backends never reach it; harmless if they do
 void SingleCommunicator::allreduce(const RawTensor&, RawTensor&, ReductionOp) { UNREACHABLE(); }
 void SingleCommunicator::allreduce_inplace(RawTensor&, ReductionOp) { UNREACHABLE(); }
 void SingleCommunicator::alltoall_inplace(RawTensor&) { UNREACHABLE(); }
@@ -23,7 +25,7 @@ void Communicator::execute_communication(RawTensor&, bool, bool, bool,
   UNREACHABLE();
 }
 namespace fused {
-bool allreduce(PeerArena&, const void*, void*, int64_t, DType, float, cudaStream_t) { UNREACHABLE(); }
+bool allreduce(PeerArena&, const void*, void*, int64_t, DType, float, cudaStream_t, bool) { UNREACHABLE(); }
 bool bytegrad(PeerArena&, void*, int64_t, DType, bool, cudaStream_t) { UNREACHABLE(); }
 bool pair_average(PeerArena&, const void*, void*, int64_t, DType, int, cudaStream_t) { UNREACHABLE(); }
 bool lp_ring(PeerArena&, void*, void*, void*, void*, int64_t, DType, cudaStream_t) { UNREACHABLE(); }

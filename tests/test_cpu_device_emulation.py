@@ -79,8 +79,8 @@ def test_alltoall_v_reports_sizes_that_sender_and_receiver_disagree_on(tmp_path)
     sender's rank, still receives exactly the bytes it asked for, and every rank returns."""
     exe = _build(tmp_path, None)
     for nranks in (2, 5):
-        run = subprocess.run([exe, str(nranks), "2", "1", "3", "-1", "5000", "1"], capture_output=True, text=True,
-                             timeout=120)
+        run = subprocess.run([exe, str(nranks), "2", "1", "3", "-1", "30000", "1"], capture_output=True, text=True,
+                             timeout=240)
         assert run.returncode == 1, run.stdout + run.stderr
         assert "0 wrong vectors, wait status 4, 1 failures" in run.stdout, run.stdout + run.stderr
 

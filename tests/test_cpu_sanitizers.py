@@ -1,8 +1,8 @@
 """Host runtime under ThreadSanitizer: a C++ stress program (tests/cpp/runtime_stress.cc) that
 drives the scheduler, channels, buckets and pools from several threads is compiled with
 -fsanitize=thread together with the engine's own sources and must finish with exit code 0
-and without a sanitizer report.  (Device-side checkers are not available on the GPU pool;
-this covers the host half of the engine.)"""
+and without a sanitizer report.  (This covers the host half of the engine; the device code runs under the
+same sanitizers in tests/test_cpu_device_emulation.py.)"""
 import os
 import shutil
 import subprocess
@@ -11,7 +11,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(ROOT, "bagua_core_b200", "csrc")
-SOURCES = ["runtime/backend.cc", "runtime/protocol_model.cc", "tensor/tensor.cc", "pool/resource_pool.cc", "ops/ops.cc", "telemetry/telemetry.cc",
+SOURCES = ["runtime/backend.cc", "runtime/timeline.cc", "tensor/tensor.cc", "pool/resource_pool.cc", "ops/ops.cc", "telemetry/telemetry.cc",
            "kernels/cpu_kernels.cc"]
 
 
@@ -31,7 +31,8 @@ def test_runtime_stress_is_clean_under_sanitizer(tmp_path, sanitizer):
         pytest.skip("needs g++ and the CUDA headers")
     exe = str(tmp_path / f"stress_{sanitizer}")
     cmd = [gxx, "-std=c++17", "-O1", "-g", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer", "-I", CSRC, "-I",
-           cuda_inc, "-I", _nccl_include(), os.path.join(ROOT, "tests", "cpp", "runtime_stress.cc"),
+           cuda_inc, "-I", _nccl_include(), "-I", os.path.join(ROOT, "tests", "cpp"),
+           os.path.join(ROOT, "tests", "cpp", "runtime_stress.cc"), os.path.join(ROOT, "tests", "cpp", "protocol_model.cc"),
            os.path.join(ROOT, "tests", "cpp", "stubs.cc")] + [os.path.join(CSRC, s) for s in SOURCES] + [
                "-o", exe, "-L/usr/local/cuda/lib64", "-lcudart", "-lpthread"]
     build = subprocess.run(cmd, capture_output=True, text=True)
