@@ -33,6 +33,7 @@ SOURCES = [
     "comm/nvls.cc",
     "comm/nccl_transport.cc",
     "comm/c10d_transport.cc",
+    "comm/solo_transport.cc",
     "ops/ops.cc",
     "telemetry/telemetry.cc",
     "capi/capi.cc",

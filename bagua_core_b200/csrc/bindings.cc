@@ -429,6 +429,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::call_guard<py::gil_scoped_release>())
       .def("set_watchdog_timeout", [](PyBackend& be, double s) { be.inner->set_watchdog_timeout(s); })
       .def("watchdog_timeout", [](PyBackend& be) { return be.inner->watchdog_timeout(); })
+      .def("pending", [](PyBackend& be) { return be.inner->pending(); },
+           "Scheduled buckets whose completion nobody has waited for yet.")
       .def("close", [](PyBackend& be) {
         py::gil_scoped_release rel;
         be.inner.reset();

@@ -17,8 +17,9 @@
  *    (num_elements % n_chunks == 0); output layout and numerics are exactly those of
  *    `BaguaTensorPy.compress("MinMaxUInt8", n_chunks, -1)`; `out_bytes` must be at least
  *    bagua_no_alloc_compressed_size(num_elements, n_chunks).
- *  - `in`, `out` are device pointers on the CURRENT device; `stream` is a stream of that
- *    device.  The work is enqueued; nothing is synchronised.
+ *  - `in`, `out` are device pointers on the CURRENT device (`in` aligned to 4 bytes, else
+ *    BAGUA_NO_ALLOC_ERR_INVALID); `stream` is a stream of that device.  The work is
+ *    enqueued; nothing is synchronised.
  *  - Limit: n_chunks * blocks_per_chunk partial results must fit the scratch, i.e. at
  *    most BAGUA_NO_ALLOC_MAX_PARTIALS (8192) — in practice n_chunks <= 8192.  Larger
  *    requests are refused with BAGUA_NO_ALLOC_ERR_TOO_LARGE and nothing is launched.

@@ -22,7 +22,10 @@ SingleCommunicator::SingleCommunicator(int rank, int nranks, int device_id, uint
                                        const std::string& unique_id)
     : rank_(rank), nranks_(nranks), device_id_(device_id), stream_(stream) {
   BAGUA_CHECK(nranks >= 1 && rank >= 0 && rank < nranks, Communicator, "invalid rank " << rank << " / " << nranks);
-  if (is_c10d_unique_id(unique_id)) {
+  if (is_solo_unique_id(unique_id)) {
+    BAGUA_CHECK(nranks == 1, Communicator, "the one-rank transport needs nranks = 1");
+    transport_ = make_solo_transport(device_id, stream);
+  } else if (is_c10d_unique_id(unique_id)) {
     BAGUA_CHECK(device_id < 0, Communicator, "the c10d transport works on host memory: pass device_id = -1");
     transport_ = make_c10d_transport(rank, nranks, unique_id.substr(5));
   } else {
@@ -139,12 +142,22 @@ void SingleCommunicator::allreduce(const RawTensor& send, RawTensor& recv, Reduc
   }
   transport_->allreduce(send.data_ptr(), recv.data_ptr(), send.num_elements_allocated(), send.dtype(), op);
 }
-void SingleCommunicator::allreduce_inplace(RawTensor& t, ReductionOp op) {
+void SingleCommunicator::allreduce_inplace(RawTensor& t, ReductionOp op, bool engine_op) {
   check_live();
-  if (PeerArena* a = p2p_arena()) {
+  PeerArena* a = nullptr;
+  if (engine_op && t.device_id() >= 0 && group_depth_ == 0) {
+    a = arena();
+    if (a) {
+      check_device_status();
+      check_live();
+    }
+  } else {
+    a = p2p_arena();
+  }
+  if (a) {
     const float scale = p2p_scale(op, nranks_);
     if (scale != 0.0f && fused::allreduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,
-                                          (cudaStream_t)stream_))
+                                          (cudaStream_t)stream_, engine_op))
       return;
   }
   transport_->allreduce(t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), op);
@@ -348,6 +361,27 @@ void SingleCommunicator::barrier() {
   transport_->barrier();
 }
 
+int64_t SingleCommunicator::agree_inter_nranks(int64_t mine) {
+  if (inter_nranks_ >= 0) return inter_nranks_;
+  check_live();
+  int64_t v = rank_ == 0 ? mine : 0;
+  if (nranks_ > 1) {
+    auto buf = PoolRawTensor::allocate(device_id_, DType::I64, 1, stream_);
+    if (device_id_ >= 0) {
+      BAGUA_CUDA_CHECK(cudaMemcpyAsync(buf->data_ptr(), &v, sizeof(v), cudaMemcpyHostToDevice, (cudaStream_t)stream_));
+      transport_->broadcast(buf->data_ptr(), 1, DType::I64, 0);
+      BAGUA_CUDA_CHECK(cudaMemcpyAsync(&v, buf->data_ptr(), sizeof(v), cudaMemcpyDeviceToHost, (cudaStream_t)stream_));
+      BAGUA_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_));
+    } else {
+      std::memcpy(buf->data_ptr(), &v, sizeof(v));
+      transport_->broadcast(buf->data_ptr(), 1, DType::I64, 0);
+      std::memcpy(&v, buf->data_ptr(), sizeof(v));
+    }
+  }
+  inter_nranks_ = v;
+  return v;
+}
+
 // ---- two-level ----------------------------------------------------------------------
 std::shared_ptr<Communicator> Communicator::create(SingleCommPtr internode, SingleCommPtr intranode,
                                                    bool hierarchical) {
@@ -359,9 +393,14 @@ std::shared_ptr<Communicator> Communicator::create(SingleCommPtr internode, Sing
     return c;
   }
   BAGUA_CHECK(intranode != nullptr, Communicator, "intra node communicator must be given in hierarchical mode");
-  if (intranode->rank() == 0) {
+  if (intranode->rank() == 0)
     BAGUA_CHECK(internode != nullptr, Communicator,
                 "inter node communicator must be given on the leader GPU in hierarchical mode");
+  // Collective over the node on first use: is the node the whole job?
+  static const bool flat_ok = env_long("BAGUA_B200_HIERARCHICAL_FLAT", 1) != 0;
+  if (flat_ok && intranode->agree_inter_nranks(internode ? internode->nranks() : 0) == 1)
+    c->solo_ = std::make_shared<SingleCommunicator>(0, 1, intranode->device_id(), intranode->stream(), "solo");
+  if (intranode->rank() == 0) {
     BAGUA_CHECK(intranode->stream() == internode->stream(), Communicator,
                 "intra node communicator should use the same stream as the inter node communicator");
     BAGUA_CHECK(intranode->device_id() == internode->device_id(), Communicator,
@@ -382,6 +421,14 @@ uint64_t Communicator::stream() const {
 
 void Communicator::execute_communication(RawTensor& t, bool intranode_average, bool pre, bool post,
                                          const std::function<void(SingleCommunicator&, RawTensor&)>& hook) {
+  if (solo_ && kind_ != Kind::Single && pre && post) {
+    // one node is the whole job: reduce to the leader + broadcast from it = one all-reduce (the
+    // fused kernel when this communicator's collectives run over peer memory), and the
+    // inter-node step over one rank is local, deterministic work that every rank does itself
+    intranode_->allreduce_inplace(t, intranode_average ? ReductionOp::AVG : ReductionOp::SUM, /*engine_op=*/true);
+    hook(*solo_, t);
+    return;
+  }
   switch (kind_) {
     case Kind::Single: hook(*internode_, t); return;
     case Kind::HierarchicalLeader:

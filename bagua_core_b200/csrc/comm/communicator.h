@@ -39,7 +39,10 @@ class SingleCommunicator {
 
   // Collectives; counts come from num_elements_allocated(), like the reference.
   void allreduce(const RawTensor& send, RawTensor& recv, ReductionOp op);
-  void allreduce_inplace(RawTensor& t, ReductionOp op);
+  // `engine_op`: the call is a bucket's communication (it runs as the fused kernel whenever fused
+  // kernels are enabled, whatever set_p2p_collectives says, takes the overlap CTA budget, and
+  // first looks at the status record earlier kernels may have left)
+  void allreduce_inplace(RawTensor& t, ReductionOp op, bool engine_op = false);
   void broadcast(RawTensor& t, int root);
   void reduce(const RawTensor& send, RawTensor& recv, int dst, ReductionOp op);
   void reduce_inplace(RawTensor& t, int dst, ReductionOp op);
@@ -88,6 +91,11 @@ class SingleCommunicator {
 
   Transport& transport() { return *transport_; }
 
+  // Collective over this (intra-node) communicator, once: rank 0 tells the others how many
+  // ranks the inter-node communicator it leads has (`mine` is ignored on the other ranks).
+  // Later calls return the cached answer without communicating.
+  int64_t agree_inter_nranks(int64_t mine);
+
  private:
   void check_live() const;
   void check_rank(int r, const char* what) const;
@@ -103,6 +111,7 @@ class SingleCommunicator {
   bool arena_tried_ = false;
   std::unique_ptr<PeerArena> arena_;
   std::mutex arena_mu_;
+  int64_t inter_nranks_ = -1;  // agree_inter_nranks(): not asked yet
 };
 
 using SingleCommPtr = std::shared_ptr<SingleCommunicator>;
@@ -125,6 +134,11 @@ class Communicator {
   static std::shared_ptr<Communicator> create(SingleCommPtr internode, SingleCommPtr intranode, bool hierarchical);
 
   Kind kind() const { return kind_; }
+  // Hierarchical, and the node is the whole job (the inter-node tier has one rank): the
+  // intra-node reduce + broadcast pair then runs as one all-reduce on every rank, and the
+  // inter-node step runs on every rank over a communicator of one rank (same bits as running
+  // it on the leader and broadcasting, one fused kernel instead of two library calls).
+  bool single_node() const { return solo_ != nullptr; }
   uint64_t stream() const;
   SingleCommPtr internode() const { return internode_; }
   SingleCommPtr intranode() const { return intranode_; }
@@ -135,7 +149,7 @@ class Communicator {
 
  private:
   Kind kind_ = Kind::Single;
-  SingleCommPtr internode_, intranode_;
+  SingleCommPtr internode_, intranode_, solo_;
 };
 
 }  // namespace bagua

@@ -51,6 +51,11 @@ int nccl_version();
 // in this process (see torch.distributed `ProcessGroup.group_name`).
 std::unique_ptr<Transport> make_c10d_transport(int rank, int nranks, const std::string& group_name);
 
+// Defined in solo_transport.cc: a communicator of one rank (unique id "solo"), on device memory
+// (stream-ordered copies) or, with device_id < 0, on host memory.
+std::unique_ptr<Transport> make_solo_transport(int device_id, uint64_t stream);
+inline bool is_solo_unique_id(const std::string& s) { return s == "solo"; }
+
 // Unique-id strings of the form "c10d:<group name>" select the c10d transport.
 inline bool is_c10d_unique_id(const std::string& s) { return s.rfind("c10d:", 0) == 0; }
 

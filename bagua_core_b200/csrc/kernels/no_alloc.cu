@@ -137,6 +137,8 @@ const char* bagua_no_alloc_last_error(void) { return g_error.c_str(); }
 int bagua_no_alloc_compress_minmax_u8_f32(const float* in, int64_t num_elements, int n_chunks, uint8_t* out,
                                           size_t out_bytes, void* stream) {
   if (!in || !out) return fail(BAGUA_NO_ALLOC_ERR_INVALID, "in and out must be device pointers, got NULL");
+  if ((uintptr_t)in % alignof(float) != 0)
+    return fail(BAGUA_NO_ALLOC_ERR_INVALID, "in must be aligned to 4 bytes (it is read as float)");
   if (num_elements <= 0 || n_chunks <= 0 || num_elements % n_chunks != 0)
     return fail(BAGUA_NO_ALLOC_ERR_INVALID, "num_elements must be positive and divisible by n_chunks");
   const size_t need = bagua_no_alloc_compressed_size(num_elements, n_chunks);

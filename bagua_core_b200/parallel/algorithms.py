@@ -76,10 +76,15 @@ class Algorithm:
 
     def init_post_backward_hook(self, bm):
         def hook():
+            self.flush_unready(bm)
             bm.pg.backend.wait_pending_comm_ops()
             bm.pg.wait_comm_stream()
 
         return hook
+
+    def flush_unready(self, bm):
+        """Gradients that did not arrive in this backward pass (parameters the loss did not use)."""
+        bm.flush_unready()
 
     def init_post_optimizer_step_hook(self, bm):
         return lambda: None
@@ -328,6 +333,21 @@ class QAdamAlgorithm(Algorithm):
             if t is not None:
                 hooks.append(p.register_post_accumulate_grad_hook(make(t)))
         return hooks
+
+    def flush_unready(self, bm):
+        if self._compressed:
+            # buckets with some gradients missing: update the momentum of those that did arrive
+            b1 = self.optimizer.param_groups[0]["betas"][0]
+            for b in bm.bagua_buckets:
+                arrived, b._qadam_arrived = getattr(b, "_qadam_arrived", []), []
+                if arrived:
+                    with torch.no_grad():
+                        ms = [a.tensor for a, _ in arrived]
+                        torch._foreach_mul_(ms, b1)
+                        torch._foreach_add_(ms, [g for _, g in arrived], alpha=1 - b1)
+                    for a, _ in arrived:
+                        bm.mark_ready(a)
+        bm.flush_unready()
 
     def state_dict(self, bm):
         return {"compressed": self._compressed}

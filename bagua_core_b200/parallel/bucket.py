@@ -38,7 +38,8 @@ class BaguaBucket:
         self.flattened: Optional[torch.Tensor] = None
         self.padding: Optional[BaguaTensor] = None
         self._alignment = max(1, alignment)
-        # allocator(numel, dtype, device) -> zero-filled 1-D tensor or None (e.g. symmetric memory)
+        # allocator(numel, dtype, device, tensors) -> 1-D tensor or None (e.g. symmetric memory); it may hand
+        # back the buffer these very tensors already live in, in this order (a re-bucketing with an unchanged layout)
         self._allocator = allocator
         if flatten:
             self._flatten()
@@ -52,7 +53,7 @@ class BaguaBucket:
         first = self.tensors[0].tensor
         total = sum(t.tensor.numel() for t in self.tensors)
         padded = (total + self._alignment - 1) // self._alignment * self._alignment
-        flat = self._allocator(padded, first.dtype, first.device) if self._allocator is not None else None
+        flat = self._allocator(padded, first.dtype, first.device, self.tensors) if self._allocator is not None else None
         if flat is None:
             flat = torch.zeros(padded, dtype=first.dtype, device=first.device)
         off = 0

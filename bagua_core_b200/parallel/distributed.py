@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from .._native import C as _C
 from .bucket import ALIGN_ELEMS_PER_RANK, BaguaBucket, BaguaTensor
 from .communication import BaguaProcessGroup, get_process_group
 
@@ -64,6 +65,10 @@ class BaguaModule(nn.Module):
             h.remove()
         self._hooks.clear()
         algo = self.bagua_algorithm
+        # flat buffers of the buckets being replaced: a bucket whose tensors already sit in one of them,
+        # in the same order, keeps it (symmetric memory is never given back to the arena, so a rebuild
+        # with an unchanged layout must not take a second set)
+        self._prev_flats = [b.flattened for b in self.bagua_buckets if b.flattened is not None]
         tensors = algo.init_tensors(self)
         groups = algo.tensors_to_buckets(self, tensors)
         align = ALIGN_ELEMS_PER_RANK * max(1, self.pg.world_size)
@@ -71,6 +76,7 @@ class BaguaModule(nn.Module):
             BaguaBucket(g, f"bucket_{i}", flatten=algo.flatten_buckets, alignment=align, allocator=self._alloc_flat)
             for i, g in enumerate(groups)
         ]
+        self._prev_flats = []
         for b in self.bagua_buckets:
             algo.init_operations(self, b)
         for opt in self.bagua_optimizers:
@@ -84,6 +90,7 @@ class BaguaModule(nn.Module):
             b._pending = len(b.tensors)
             for t in b.tensors:
                 t._bucket = b
+                t._step = -1
         self._mark_ready_native = self.pg.backend.mark_communication_ready
         self._on_cuda = bool(self.pg.is_cuda)
         self._hooks.extend(algo.init_backward_hooks(self))
@@ -93,19 +100,39 @@ class BaguaModule(nn.Module):
         self._wrap_optimizer_steps()
         self._arm()
 
-    def _alloc_flat(self, numel, dtype, device):
+    def _alloc_flat(self, numel, dtype, device, tensors=()):
         """Bucket storage: symmetric memory of the global communicator when there are peers
         (the engine then all-reduces the bucket in place over NVLink with no staging copy);
         None → the bucket falls back to an ordinary zero tensor.  Collective: every rank
         builds the same buckets in the same order."""
         import os
 
+        for old in getattr(self, "_prev_flats", ()):
+            if old.numel() == numel and old.dtype == dtype and old.device == device and tensors:
+                off, es, base = 0, old.element_size(), old.data_ptr()
+                for t in tensors:
+                    if t.tensor.dtype != dtype or t.tensor.data_ptr() != base + off * es:
+                        break
+                    off += t.tensor.numel()
+                else:
+                    return old
+
         if (not self.pg.is_cuda or self.pg.world_size < 2 or os.environ.get("BAGUA_B200_SYMMETRIC", "1") == "0"
                 or os.environ.get("BAGUA_B200_FUSED", "1") == "0"):
             return None
         if dtype not in (torch.float32, torch.float16, torch.bfloat16):
             return None
-        return self.pg.global_comm.alloc_symmetric(int(numel), dtype)
+        return self._bucket_comm().alloc_symmetric(int(numel), dtype)
+
+    def _bucket_comm(self):
+        """The communicator whose fused kernels will reduce the buckets: symmetric memory must come from
+        its arena.  A hierarchical algorithm on one node reduces over the intra-node communicator."""
+        if getattr(self.bagua_algorithm, "hierarchical", False):
+            self.pg.ensure_hierarchical()
+            intra = self.pg.intra_comm
+            if intra is not None and intra.nranks() == self.pg.world_size:
+                return intra
+        return self.pg.global_comm
 
     def _arm(self):
         for b in self.bagua_buckets:
@@ -131,6 +158,7 @@ class BaguaModule(nn.Module):
         """Tell the engine `t` holds its final value for this step (called from hooks)."""
         b = t._bucket
         b._pending -= 1
+        t._step = self.bagua_train_step_counter
         ev_ptr = 0
         if b._pending == 0 and self._on_cuda:
             ev = self._events.get(b.name)
@@ -140,7 +168,25 @@ class BaguaModule(nn.Module):
             ev_ptr = ev.cuda_event
         self._mark_ready_native(t.backend_tensor, ev_ptr)
 
+    def _timeline_mark(self, name):
+        """A named point on the compute stream in the engine's device time line (when it is recording)."""
+        if self._on_cuda and _C.bucket_timing():
+            _C.timeline_mark(name, torch.cuda.current_stream().cuda_stream)
+
+    def flush_unready(self):
+        """Marks every tensor that no hook has marked in this step, so that its bucket is still
+        communicated: a parameter that took no part in this step's loss gets no gradient hook, and
+        its bucket would otherwise wait for it forever (and hold back every bucket behind it).
+        Its gradient goes into the reduction as it is (zero after `zero_grad`)."""
+        step = self.bagua_train_step_counter
+        for b in self.bagua_buckets:
+            if b._pending > 0:
+                for t in b.tensors:
+                    if t._step != step:
+                        self.mark_ready(t)
+
     def forward(self, *args, **kwargs):
+        self._timeline_mark("step_begin")
         out = self.module(*args, **kwargs)
         if torch.is_grad_enabled() and not self._in_no_sync:
             self._pending_backward = True
@@ -161,13 +207,17 @@ class BaguaModule(nn.Module):
                 torch.autograd.Variable._execution_engine.queue_callback(outer._after_backward)
             return None
 
-        tensors[0].register_hook(on_grad)
+        # every output: the loss may depend on any of them (an auxiliary output listed first need not
+        # take part in it); the flag makes the callback run once per backward pass whichever fire
+        for t in tensors:
+            t.register_hook(on_grad)
 
     def _after_backward(self):
         self._callback_queued = False
         if not self._pending_backward:
             return
         self._pending_backward = False
+        self._timeline_mark("backward_end")
         self._post_backward()
         self._arm()
         self.bagua_train_step_counter += 1

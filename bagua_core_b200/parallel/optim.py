@@ -56,6 +56,27 @@ class FlatSGD(torch.optim.Optimizer):
         self.shadows_valid = False
         self._shadowed: List[torch.Tensor] = []
 
+    def _group_runs(self, bucket):
+        """[(start, end, group index)] over a bucket's flat elements: maximal runs of consecutive
+        parameters that belong to the same parameter group, so that each run is stepped with its own
+        group's learning rate, momentum and weight decay.  With one group (or a bucket whose parameters
+        all share a group) that is one run over the whole bucket, padding included."""
+        group_of = {id(p): gi for gi, g in enumerate(self.param_groups) for p in g["params"]}
+        runs, off = [], 0
+        for t in bucket.tensors:
+            n = t.owner.numel()
+            gi = group_of.get(id(t.owner))
+            if gi is None:
+                raise RuntimeError(f"parameter of bucket tensor `{t.name}` is not in this optimizer")
+            if runs and runs[-1][2] == gi:
+                runs[-1][1] = off + n
+            else:
+                runs.append([off, off + n, gi])
+            off += n
+        if runs:
+            runs[-1][1] = bucket.flattened.numel()  # the padding (zero gradient, zero weights) rides along
+        return [tuple(r) for r in runs]
+
     # called by BaguaModule after it has built gradient buckets
     def bagua_attach(self, bm):
         self._flat.clear()
@@ -76,7 +97,8 @@ class FlatSGD(torch.optim.Optimizer):
                     p.grad = flat_g[off:off + n].as_strided(tuple(p.shape), tuple(p.stride()))
                     self._attached_ids.add(id(p))
                     off += n
-                self._flat.append({"p": b.flattened, "g": flat_g, "m": torch.zeros_like(flat_g), "first": True})
+                self._flat.append({"p": b.flattened, "g": flat_g, "m": torch.zeros_like(flat_g), "first": True,
+                                   "runs": self._group_runs(b)})
                 continue
             if b.flattened is None or any(t.kind != "grad" for t in b.tensors):
                 continue
@@ -95,7 +117,8 @@ class FlatSGD(torch.optim.Optimizer):
                     p.set_(flat_p.untyped_storage(), off, shape, stride)
                     self._attached_ids.add(id(p))
                     off += n
-            entry = {"p": flat_p, "g": b.flattened, "m": torch.zeros_like(flat_p), "first": True}
+            entry = {"p": flat_p, "g": b.flattened, "m": torch.zeros_like(flat_p), "first": True,
+                     "runs": self._group_runs(b)}
             if self.bf16_shadow:
                 from ..ops.shadow import BF16Shadow
 
@@ -113,17 +136,23 @@ class FlatSGD(torch.optim.Optimizer):
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None
-        g0 = self.param_groups[0]
         stream = torch.cuda.current_stream().cuda_stream if (self._flat and self._flat[0]["p"].is_cuda) else 0
         for f in self._flat:
-            if "h" in f:
-                _C.k_sgd_momentum_flat_shadow(f["p"], f["g"], f["m"], f["h"], g0["lr"], g0["momentum"], g0["dampening"],
-                                              g0["weight_decay"], g0["nesterov"], f["first"], stream)
-            else:
-                _C.k_sgd_momentum_flat(f["p"], f["g"], f["m"], g0["lr"], g0["momentum"], g0["dampening"],
-                                       g0["weight_decay"], g0["nesterov"], f["first"], stream)
+            # one launch per run of parameters that share a parameter group (usually one per bucket),
+            # each with its own group's hyperparameters as they are now (schedulers change them in place)
+            whole = len(f["runs"]) == 1
+            for lo, hi, gi in f["runs"]:
+                g = self.param_groups[gi]
+                p_, g_, m_ = (f["p"], f["g"], f["m"]) if whole else (f["p"][lo:hi], f["g"][lo:hi], f["m"][lo:hi])
+                if "h" in f:
+                    h_ = f["h"] if whole else f["h"][lo:hi]
+                    _C.k_sgd_momentum_flat_shadow(p_, g_, m_, h_, g["lr"], g["momentum"], g["dampening"],
+                                                  g["weight_decay"], g["nesterov"], f["first"], stream)
+                else:
+                    _C.k_sgd_momentum_flat(p_, g_, m_, g["lr"], g["momentum"], g["dampening"], g["weight_decay"],
+                                           g["nesterov"], f["first"], stream)
+                self.kernel_launches += 1
             f["first"] = False
-            self.kernel_launches += 1
         if self._shadowed and not self.shadows_valid:
             self._validate_shadows()
         for group in self.param_groups:

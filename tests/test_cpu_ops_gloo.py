@@ -121,6 +121,46 @@ def test_hierarchical_equals_flat():
         assert torch.allclose(x, mean, atol=1e-6)
 
 
+def _hier_single_node(rank, world, compression):
+    """One node is the whole job: the intra-node communicator spans every rank, the inter-node one has
+    one rank (the leader)."""
+    import torch.distributed as dist
+
+    import bagua_core as bc
+
+    intra_group = dist.new_group(list(range(world)))
+    inter_group = dist.new_group([0])
+    intra = bc.BaguaSingleCommunicatorPy(rank, world, -1, 0, "c10d:" + intra_group.group_name)
+    inter = bc.BaguaSingleCommunicatorPy(0, 1, -1, 0, "c10d:" + inter_group.group_name) if rank == 0 else None
+    g = torch.Generator().manual_seed(rank)
+    x = torch.randn(16 * world * 64, generator=g)
+    orig = x.clone()
+    bt = bc.BaguaTensorPy(x, "x")
+    bucket = bc.BaguaBucketPy("b", [bt])
+    bucket.append_centralized_synchronous_op(inter, intra, hierarchical=True, average=True, scattergather=True,
+                                             compression=compression)
+    backend = bc.BaguaCommBackendPy(10, -1)
+    _run_bucket(backend, bucket, [bt])
+    backend.close()
+    return orig, x.clone()
+
+
+@pytest.mark.parametrize("compression", [None, "MinMaxUInt8"])
+def test_hierarchical_on_one_node_runs_flat_and_gives_the_two_level_result(monkeypatch, compression):
+    """With one node, reduce-to-leader + leader's step + broadcast is replaced by one all-reduce and the
+    leader's (one-rank, deterministic) step on every rank: bit-identical to the two-level path."""
+    out = {}
+    for flat in ("0", "1"):
+        monkeypatch.setenv("BAGUA_B200_HIERARCHICAL_FLAT", flat)
+        out[flat] = run_ranks(_hier_single_node, 3, args=(compression,))
+    mean = sum(o for o, _ in out["1"]) / 3
+    for r in range(3):
+        assert torch.equal(out["0"][r][1], out["1"][r][1]), r
+        assert torch.equal(out["1"][r][1], out["1"][0][1])
+        tol = 1e-6 if compression is None else 2 * float(mean.max() - mean.min()) / 255
+        assert (out["1"][r][1] - mean).abs().max().item() <= tol
+
+
 def _decentralized(rank, world, mode, steps):
     import bagua_core as bc
 

@@ -2,10 +2,8 @@
 reduce-scatter, broadcast, reduce, gather, scatter, barrier): on one GPU through the single-launch emulation, and
 on several GPUs against the library (NCCL) results.
 
-These kernels are newer than the rest of the GPU suite and are off by default in the
-communicator (`BAGUA_B200_P2P_COLLECTIVES`); their signalling and index arithmetic are
-covered on the CPU by tests/test_cpu_protocol_model.py.  The GPU cases here run when
-BAGUA_B200_TEST_P2P_COLLECTIVES=1."""
+Their signalling and index arithmetic are also covered on the CPU by
+tests/test_cpu_protocol_model.py and tests/test_cpu_device_emulation.py."""
 import os
 
 import pytest
@@ -13,11 +11,7 @@ import torch
 
 from mp_util import run_ranks
 
-pytestmark = [
-    pytest.mark.gpu,
-    pytest.mark.skipif(os.environ.get("BAGUA_B200_TEST_P2P_COLLECTIVES", "0") != "1",
-                       reason="set BAGUA_B200_TEST_P2P_COLLECTIVES=1 to run the peer-memory collective kernels"),
-]
+pytestmark = [pytest.mark.gpu]
 
 
 def _arena(n, staging_mb=64):

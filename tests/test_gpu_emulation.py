@@ -137,9 +137,6 @@ def test_emulated_arena_rejects_oversized_ops():
         arena.allreduce(xs, xs, True, "oneshot", 2)
 
 
-@pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_BYTEGRAD_PIPELINE") != "1",
-                    reason="ByteGrad with the reduced chunks travelling back one destination at a time: set "
-                           "BAGUA_B200_TEST_BYTEGRAD_PIPELINE=1 (first run on hardware pending)")
 @pytest.mark.parametrize("nranks", [2, 4, 8])
 @pytest.mark.parametrize("dt", [torch.float32, torch.float16])
 def test_emulated_bytegrad_pipelined_equals_the_default_variant(nranks, dt, monkeypatch):

@@ -209,8 +209,6 @@ def test_pool_reuses_blocks():
     assert bb._C.pool_stats(0)["device_allocs"] == a
 
 
-@pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_POOL_GUARD") != "1",
-                    reason="guard regions of device pool blocks: set BAGUA_B200_TEST_POOL_GUARD=1 (first run on hardware pending)")
 def test_pool_guard_regions_stay_intact_under_the_kernels_and_catch_a_stray_store():
     """Device pool blocks with guard regions: the compression kernels on ragged sizes leave every
     guard intact, and four bytes stored just past a block's capacity are found."""

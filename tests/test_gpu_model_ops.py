@@ -202,12 +202,8 @@ def test_conv_bias_relu_pool_module_matches_the_composition_under_autocast():
         assert (a - b).abs().max().item() <= 6e-2 * scale  # masks agree except where two conv algorithms round apart
 
 
-_SHADOW = pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_BF16_SHADOW") != "1",
-                             reason="bf16 weight copies written by the optimizer kernel: set BAGUA_B200_TEST_BF16_SHADOW=1 "
-                                    "(first run on hardware pending)")
 
 
-@_SHADOW
 @pytest.mark.parametrize("n", [1, 7, 4096, (1 << 20) + 3])
 def test_sgd_step_with_bf16_copy_equals_the_plain_step(n):
     import bagua_core_b200 as bb
@@ -234,7 +230,6 @@ def test_sgd_step_with_bf16_copy_equals_the_plain_step(n):
         assert torch.equal(q, q2) and torch.equal(hq, q2.to(torch.bfloat16))
 
 
-@_SHADOW
 def test_vgg_training_with_bf16_weight_copies_is_bit_identical_to_casting():
     """Same model, same data: lookups switched off (the blocks cast the fp32 weights in every forward pass) against
     lookups on (they read the optimizer's copies)."""
@@ -275,12 +270,8 @@ def test_vgg_training_with_bf16_weight_copies_is_bit_identical_to_casting():
     assert torch.equal(results[0][1], results[1][1])
 
 
-_WGRAD = pytest.mark.skipif(__import__("os").environ.get("BAGUA_B200_TEST_FUSED_WGRAD") != "1",
-                            reason="weight gradients accumulated by the GEMM (bagua_core_b200.ops.wgrad): set "
-                                   "BAGUA_B200_TEST_FUSED_WGRAD=1 (first run on hardware pending)")
 
 
-@_WGRAD
 @pytest.mark.parametrize("rows,n_in,n_out", [(32, 25088, 4096), (32, 4096, 1000), (5, 72, 24)])
 def test_linear_weight_gradient_accumulated_in_place_is_the_fp32_product(rows, n_in, n_out):
     """The library GEMM adds dyᵀ x (bf16 operands) into the fp32 gradient; compared with the same
@@ -314,7 +305,6 @@ def test_linear_weight_gradient_accumulated_in_place_is_the_fp32_product(rows, n
         W.enabled = saved
 
 
-@_WGRAD
 def test_vgg_training_with_in_place_weight_gradients_agrees_with_the_ordinary_path():
     import os
 

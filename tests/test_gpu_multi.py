@@ -262,6 +262,8 @@ def test_bucket_ops_fused_vs_library():
 
 
 def _train(rank, world, algo_name):
+    import time
+
     import bagua_core_b200 as bb
     import bagua_core_b200.parallel as P
     from bagua_core_b200.models import MLP
@@ -270,32 +272,53 @@ def _train(rank, world, algo_name):
     torch.manual_seed(3)
     model = MLP(64, 256, 10, depth=3).to(dev)
     pg = P.init_process_group(dev)
-    opt = P.FlatSGD(model.parameters(), lr=0.05, momentum=0.9)
-    algo = {"allreduce": P.GradientAllReduceAlgorithm, "bytegrad": P.ByteGradAlgorithm}[algo_name]()
+    steps = 6
+    if algo_name == "qadam":
+        opt = P.QAdamOptimizer(model.parameters(), lr=0.01, warmup_steps=2, eps=1e-2)
+        algo = P.QAdamAlgorithm(opt)
+    elif algo_name == "async":
+        opt = P.FlatSGD(model.parameters(), lr=0.01, momentum=0.9)
+        algo = P.AsyncModelAverageAlgorithm(sync_interval_ms=5)
+        steps = 40
+    else:
+        opt = P.FlatSGD(model.parameters(), lr=0.05, momentum=0.9)
+        algo = {"allreduce": P.GradientAllReduceAlgorithm, "bytegrad": P.ByteGradAlgorithm,
+                "allreduce_hier": lambda: P.GradientAllReduceAlgorithm(hierarchical=True),
+                "bytegrad_hier": lambda: P.ByteGradAlgorithm(hierarchical=True)}[algo_name]()
     bm = P.with_bagua(model, [opt], algo, bucket_bytes=64 * 1024)
     g = torch.Generator().manual_seed(11)
     xs = torch.randn(6, world * 16, 64, generator=g)
     ys = torch.randn(6, world * 16, 10, generator=g)
-    for s in range(6):
-        x = xs[s, rank * 16:(rank + 1) * 16].to(dev)
-        y = ys[s, rank * 16:(rank + 1) * 16].to(dev)
+    losses = []
+    for s in range(steps):
+        x = xs[s % 6, rank * 16:(rank + 1) * 16].to(dev)
+        y = ys[s % 6, rank * 16:(rank + 1) * 16].to(dev)
         opt.zero_grad()
-        torch.nn.functional.mse_loss(bm(x), y).backward()
+        loss = torch.nn.functional.mse_loss(bm(x), y)
+        loss.backward()
         opt.step()
+        losses.append(float(loss.item()))
+        if algo_name == "async":
+            time.sleep(0.005)  # let a few averaging rounds land between steps
+    extra = {}
+    if algo_name == "async":
+        algo.abort(bm)  # returns once no averaging round is in flight
+        extra["rounds"] = algo.rounds
+    if algo_name == "qadam":
+        extra["compressed"] = bool(bm.bagua_state_dict()["algorithm"]["compressed"])
+    if algo_name.endswith("_hier"):
+        extra["single_node"] = pg.intra_comm is not None and pg.intra_comm.nranks() == world
     torch.cuda.synchronize()
     pg.global_comm.check_device_status()
     flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()]).cpu()
     fused = bb._C.stats()["fused_launches"]
     P.destroy_process_group()
-    return flat, fused
+    return flat, fused, losses, extra
 
 
-@pytest.mark.parametrize("algo", ["allreduce", "bytegrad"])
-def test_with_bagua_training_multi_gpu(algo):
+def _reference_weights(world):
     from bagua_core_b200.models import MLP
 
-    world = _world()
-    res = run_ranks(_train, world, backend="nccl", args=(algo,), timeout=600)
     torch.manual_seed(3)
     model = MLP(64, 256, 10, depth=3)
     opt = torch.optim.SGD(model.parameters(), lr=0.05, momentum=0.9)
@@ -306,12 +329,54 @@ def test_with_bagua_training_multi_gpu(algo):
         opt.zero_grad()
         torch.nn.functional.mse_loss(model(xs[s]), ys[s]).backward()
         opt.step()
-    ref = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
-    for flat, fused in res:
+    return torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+
+
+@pytest.mark.parametrize("algo", ["allreduce", "bytegrad", "allreduce_hier", "bytegrad_hier"])
+def test_with_bagua_training_multi_gpu(algo):
+    world = _world()
+    res = run_ranks(_train, world, backend="nccl", args=(algo,), timeout=600)
+    ref = _reference_weights(world)
+    for flat, fused, _losses, extra in res:
         assert fused > 0, "training must run on the fused kernels"
         assert torch.equal(flat, res[0][0])
-        tol = 2e-4 if algo == "allreduce" else 5e-2
+        tol = 2e-4 if algo.startswith("allreduce") else 5e-2
         assert (flat - ref).abs().max().item() < tol
+        if algo.endswith("_hier"):
+            assert extra["single_node"], "one box: the hierarchical communicator must have gone flat"
+
+
+def test_hierarchical_allreduce_equals_flat_on_one_box():
+    """`hierarchical=True` on one NVSwitch box runs the same fused all-reduce as the flat algorithm:
+    the trained weights are bit-identical."""
+    world = _world()
+    flat = run_ranks(_train, world, backend="nccl", args=("allreduce",), timeout=600)
+    hier = run_ranks(_train, world, backend="nccl", args=("allreduce_hier",), timeout=600)
+    assert torch.equal(flat[0][0], hier[0][0])
+    assert hier[0][1] > 0
+
+
+def test_qadam_trains_on_gpus_and_switches_to_compressed_momentum():
+    world = _world()
+    res = run_ranks(_train, world, backend="nccl", args=("qadam",), timeout=600)
+    for flat, fused, losses, extra in res:
+        assert extra["compressed"], "after the warm-up the momentum buckets are exchanged compressed"
+        assert fused > 0
+        assert torch.isfinite(flat).all()
+        assert torch.equal(flat, res[0][0]), "every rank applies the same averaged momentum"
+    assert res[0][2][-1] < res[0][2][0]
+
+
+def test_async_model_average_on_gpus_keeps_replicas_together():
+    world = _world()
+    res = run_ranks(_train, world, backend="nccl", args=("async",), timeout=600)
+    ref = res[0][0]
+    for flat, fused, losses, extra in res:
+        assert extra["rounds"] > 0 and fused > 0
+        assert torch.isfinite(flat).all()
+        # replicas train on different data and are pulled together by the background averaging
+        assert (flat - ref).abs().max().item() < 0.2
+    assert res[0][2][-1] < res[0][2][0]
 
 
 def _sym_pair(rank, world):

@@ -59,3 +59,6 @@ def test_no_alloc_rejects_what_does_not_fit():
     assert rc == -2 and b"scratch" in lib.bagua_no_alloc_last_error()
     rc = lib.bagua_no_alloc_compress_minmax_u8_f32(x.data_ptr(), 16384, 8, out.data_ptr(), 64, None)
     assert rc == -1 and b"too small" in lib.bagua_no_alloc_last_error()
+    # an input pointer that cannot be read as float is refused before anything is launched
+    rc = lib.bagua_no_alloc_compress_minmax_u8_f32(x.data_ptr() + 2, 1024, 8, out.data_ptr(), 1 << 20, None)
+    assert rc == -1 and b"aligned" in lib.bagua_no_alloc_last_error()
