@@ -40,6 +40,7 @@ SOURCES = [
     "kernels/cpu_kernels.cc",
     "kernels/elementwise.cu",
     "kernels/minmax_uint8.cu",
+    "kernels/multi_copy.cu",
     "kernels/fused_allreduce.cu",
     "kernels/fused_bytegrad.cu",
     "kernels/fused_gossip.cu",

@@ -549,6 +549,35 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
 
   // raw kernels on torch tensors (tests, optimisers).  `stream` is a cudaStream_t value.
+  m.def(
+      "k_multi_copy",
+      [](std::vector<at::Tensor> tensors, at::Tensor flat, bool gather, uint64_t stream) {
+        // tensors packed back to back, in bytes, in list order
+        std::vector<kernels::MultiCopySeg> segs;
+        unsigned long long off = 0;
+        for (auto& t : tensors) {
+          BAGUA_CHECK(t.is_contiguous() && t.device() == flat.device(), Tensor,
+                      "multi_copy: tensors must be contiguous and on the flat buffer's device");
+          if (t.nbytes()) segs.push_back(kernels::MultiCopySeg{t.data_ptr(), off, (unsigned long long)t.nbytes()});
+          off += t.nbytes();
+        }
+        BAGUA_CHECK(flat.is_contiguous() && (unsigned long long)flat.nbytes() >= off, Tensor,
+                    "multi_copy: the flat buffer is too small");
+        kernels::Ctx c = ctx_of(flat, stream);
+        if (!c.is_cuda()) {
+          kernels::multi_copy(segs.data(), (int)segs.size(), flat.data_ptr(), (size_t)off, gather, c);
+          return;
+        }
+        at::Tensor table = at::empty({(int64_t)(segs.size() * sizeof(kernels::MultiCopySeg))},
+                                     at::TensorOptions().dtype(at::kByte).device(flat.device()));
+        BAGUA_CUDA_CHECK(cudaMemcpyAsync(table.data_ptr(), segs.data(), segs.size() * sizeof(kernels::MultiCopySeg),
+                                         cudaMemcpyHostToDevice, c.stream));
+        kernels::multi_copy((const kernels::MultiCopySeg*)table.data_ptr(), (int)segs.size(), flat.data_ptr(),
+                            (size_t)off, gather, c);
+        BAGUA_CUDA_CHECK(cudaStreamSynchronize(c.stream));  // `table` and `segs` die with this call
+      },
+      py::arg("tensors"), py::arg("flat"), py::arg("gather"), py::arg("stream"),
+      "Flatten (gather) or unflatten a list of tensors into / out of `flat` (packed back to back) with one kernel.");
   m.def("k_divide_inplace", [](at::Tensor x, float d, uint64_t stream) {
     kernels::divide_inplace(x.data_ptr(), dtype_from_torch(x.scalar_type()), x.numel(), d, ctx_of(x, stream));
   });

@@ -255,6 +255,20 @@ void copy_bytes(void* dst, const void* src, size_t bytes, const Ctx& c) {
   else
     std::memmove(dst, src, bytes);
 }
+void multi_copy(const MultiCopySeg* segs, int nseg, void* flat, size_t total_bytes, bool gather, const Ctx& c) {
+  if (nseg <= 0 || total_bytes == 0) return;
+  if (c.is_cuda()) {
+    cuda::multi_copy(segs, nseg, flat, total_bytes, gather, c.stream);
+    return;
+  }
+  for (int k = 0; k < nseg; ++k) {
+    char* f = (char*)flat + segs[k].offset;
+    if (gather)
+      std::memmove(f, segs[k].ptr, segs[k].bytes);
+    else
+      std::memmove(segs[k].ptr, f, segs[k].bytes);
+  }
+}
 void reduce_chunk_inplace(void* x, DType dt, int64_t chunk, int n_chunks, int target, bool average, const Ctx& c) {
   if (chunk <= 0) return;
   BAGUA_CHECK(target >= 0 && target < n_chunks, Tensor, "reduce_chunk_inplace: target chunk out of range");

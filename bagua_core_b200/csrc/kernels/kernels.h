@@ -38,6 +38,16 @@ void async_model_average(float* t, const float* reduced, const float* copy, floa
                          const Ctx& c);
 void copy_bytes(void* dst, const void* src, size_t bytes, const Ctx& c);
 
+// Flatten (gather = true: tensors -> flat) or unflatten (flat -> tensors) a list of tensors in
+// one launch.  Segments are sorted by `offset` and do not overlap; `segs` is a device array on
+// the CUDA path and a host array on the host path.
+struct MultiCopySeg {
+  void* ptr;                  // the tensor's data
+  unsigned long long offset;  // where it sits in the flat buffer, in bytes
+  unsigned long long bytes;
+};
+void multi_copy(const MultiCopySeg* segs, int nseg, void* flat, size_t total_bytes, bool gather, const Ctx& c);
+
 // x viewed as [num_chunks][chunk_size]: column sum (fp32, chunk order 0..n-1), optional
 // division by num_chunks, written into chunk `target_chunk`.
 void reduce_chunk_inplace(void* x, DType dt, int64_t chunk_size, int num_chunks, int target_chunk,

@@ -14,6 +14,7 @@ void addmul_inplace(void* x, const void* y, float f, DType dt, int64_t n, cudaSt
 void average_inplace(void* x, const void* y, DType dt, int64_t n, cudaStream_t s);
 void async_model_average(float* t, const float* r, const float* cp, float nranks, int64_t n, cudaStream_t s);
 void copy_bytes(void* dst, const void* src, size_t bytes, cudaStream_t s);
+void multi_copy(const MultiCopySeg* segs_dev, int nseg, void* flat, size_t total_bytes, bool gather, cudaStream_t s);
 void reduce_chunk_inplace(void* x, DType dt, int64_t chunk, int n_chunks, int target, bool average, cudaStream_t s);
 size_t compress_scratch_bytes(int n_chunks, int64_t chunk_size);
 void compress_minmax_u8(const void* in, DType dt, int64_t num_real, int64_t chunk, int n_chunks, uint8_t* out,

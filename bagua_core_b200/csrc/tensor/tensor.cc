@@ -233,15 +233,35 @@ CommunicationTensor BaguaBucket::get_communication_tensor(uint64_t stream, bool 
     ct.need_copy_back = false;
     return ct;
   }
+  // Staged: one launch gathers every tensor into a pool buffer (the reference issues one copy
+  // per tensor, datatypes/mod.rs:1012-1023).
   auto buf = PoolRawTensor::allocate(device_, dtype_, total, stream);
   const size_t es = dtype_bytes(dtype_);
-  size_t off = 0;
+  unsigned long long off = 0;
   kernels::Ctx c{device_, (cudaStream_t)stream};
+  ct.segments.reserve(tensors_.size());
   for (auto& t : tensors_) {
-    const size_t bytes = (size_t)t->num_elements_allocated() * es;
-    kernels::copy_bytes((char*)buf->data_ptr() + off, (void*)(uintptr_t)t->data_ptr(), bytes, c);
+    const unsigned long long bytes = (unsigned long long)t->num_elements_allocated() * es;
+    if (bytes) ct.segments.push_back(kernels::MultiCopySeg{(void*)(uintptr_t)t->data_ptr(), off, bytes});
     off += bytes;
   }
+  const kernels::MultiCopySeg* table = ct.segments.data();
+  if (device_ >= 0 && !ct.segments.empty()) {
+    const size_t tbytes = ct.segments.size() * sizeof(kernels::MultiCopySeg);
+    const bool same = seg_cache_dev_ && seg_cache_.size() == ct.segments.size() &&
+                      std::memcmp(seg_cache_.data(), ct.segments.data(), tbytes) == 0;
+    if (!same) {
+      // the stream orders the upload before the kernels that read it and after those that read the old
+      // table; the source is pageable memory, which the runtime stages before the call returns
+      seg_cache_dev_ = PoolRawTensor::allocate(device_, DType::U8, (int64_t)tbytes, stream);
+      seg_cache_ = ct.segments;
+      BAGUA_CUDA_CHECK(cudaMemcpyAsync(seg_cache_dev_->data_ptr(), seg_cache_.data(), tbytes, cudaMemcpyHostToDevice,
+                                       (cudaStream_t)stream));
+    }
+    ct.segments_dev = seg_cache_dev_;
+    table = (const kernels::MultiCopySeg*)seg_cache_dev_->data_ptr();
+  }
+  kernels::multi_copy(table, (int)ct.segments.size(), buf->data_ptr(), (size_t)off, /*gather=*/true, c);
   ct.raw = buf;
   ct.staged = true;
   ct.need_copy_back = !force_not_copy_back;
@@ -251,15 +271,12 @@ CommunicationTensor BaguaBucket::get_communication_tensor(uint64_t stream, bool 
 void CommunicationTensor::finish(bool sync_stream) {
   if (!raw) return;
   const int device = raw->device_id();
-  if (need_copy_back) {
-    const size_t es = dtype_bytes(raw->dtype());
-    size_t off = 0;
+  if (need_copy_back && !segments.empty()) {
+    // one launch scatters the result back (reference: one copy per tensor, datatypes/mod.rs:1048-1059)
     kernels::Ctx c{device, (cudaStream_t)stream};
-    for (auto& t : bucket_tensors) {
-      const size_t bytes = (size_t)t->num_elements_allocated() * es;
-      kernels::copy_bytes((void*)(uintptr_t)t->data_ptr(), (char*)raw->data_ptr() + off, bytes, c);
-      off += bytes;
-    }
+    const kernels::MultiCopySeg* table =
+        segments_dev ? (const kernels::MultiCopySeg*)segments_dev->data_ptr() : segments.data();
+    kernels::multi_copy(table, (int)segments.size(), raw->data_ptr(), raw->bytes_allocated(), /*gather=*/false, c);
   }
   // Pool leases are recycled per stream, so no host synchronisation is needed for
   // correctness; it happens only in reference-faithful mode.

@@ -127,6 +127,9 @@ class CommunicationTensor {
   bool staged = false;  // `raw` is a pool buffer holding a copy of the bucket
   uint64_t stream = 0;
   std::vector<TensorPtr> bucket_tensors;
+  // staged: where every tensor sits in `raw`; on a GPU the same table also lives on the device
+  std::vector<kernels::MultiCopySeg> segments;
+  std::shared_ptr<RawTensor> segments_dev;
   void finish(bool sync_stream);
 };
 
@@ -164,6 +167,9 @@ class BaguaBucket {
   mutable std::mutex mu_;       // guards ops_
   std::mutex exec_mu_;          // serialises op execution on this bucket
   std::vector<std::shared_ptr<CommOp>> ops_;
+  // Device copy of the flatten table, re-uploaded only when a tensor has moved (exec_mu_ held).
+  std::vector<kernels::MultiCopySeg> seg_cache_;
+  std::shared_ptr<RawTensor> seg_cache_dev_;
 };
 
 using BucketPtr = std::shared_ptr<BaguaBucket>;

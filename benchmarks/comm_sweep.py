@@ -68,6 +68,12 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--paths", default="fused,library")
+    ap.add_argument("--tunes", default="",
+                    help="engine tuning sets to run the whole sweep under, separated by ';', each a comma-separated "
+                         "list of key=value (bagua_core_b200._C.set_tuning), e.g. 'overlap_ctas=16;overlap_ctas=64'; "
+                         "rows carry the set in `tune`")
+    ap.add_argument("--comm-ctas", type=int, default=0, help="CTA budget of the all-reduce / pair kernels (0: default)")
+    ap.add_argument("--coop-ctas", type=int, default=0, help="CTA budget of ByteGrad / ring kernels (0: default)")
     args = ap.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -80,7 +86,10 @@ def main():
     dist.broadcast_object_list(uid, src=0)
     comm = bc.BaguaSingleCommunicatorPy(rank, world, local, stream.cuda_stream, uid[0])
     assert comm.fused_available()
+    if args.comm_ctas or args.coop_ctas:
+        comm.set_comm_ctas(args.comm_ctas, args.coop_ctas)
     backend = bc.BaguaCommBackendPy(100, local)
+    defaults = dict(bb._C.get_tuning())
 
     sizes = []
     s = args.min_bytes
@@ -117,7 +126,13 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) * 1e3  # µs
 
-    for op in args.ops.split(","):
+    tune_sets = [t for t in args.tunes.split(";") if t] or [""]
+    for tune, op in [(t, o) for t in tune_sets for o in args.ops.split(",")]:
+        for k, v in defaults.items():
+            bb._C.set_tuning(k, int(v))
+        for kv in [kv for kv in tune.split(",") if kv]:
+            k, v = kv.split("=")
+            bb._C.set_tuning(k, int(v))
         for S in sizes:
             n = max(align, (S // 4) // align * align)
             g = torch.Generator().manual_seed(rank)
@@ -136,8 +151,8 @@ def main():
                 else:
                     os.environ.pop("BAGUA_B200_BYTEGRAD_PIPELINE_MIN_CHUNK", None)
                 if path == "fused_sym":
-                    # bucket in symmetric memory: in-place two-shot without staging
-                    if op != "gradient_allreduce":
+                    # bucket in symmetric memory: peers load from and store into it directly, no staging
+                    if op not in ("gradient_allreduce", "shift_one"):
                         continue
                     comm.set_fused(True)
                     x = comm.alloc_symmetric(n, torch.float32)
@@ -189,7 +204,7 @@ def main():
                         bucket.append_python_op(lambda _name, b=bt: comm.broadcast(b, 0))
                 us = time_bucket(bucket, bt, iters, args.warmup)
                 wb = wire_bytes(op, n * 4, world)
-                row = {"op": op, "path": path, "bytes": n * 4, "n_gpus": world, "latency_us": us,
+                row = {"op": op, "path": path, "tune": tune, "bytes": n * 4, "n_gpus": world, "latency_us": us,
                        "busbw_gbs": wb / (us * 1e-6) / 1e9, "algbw_gbs": n * 4 / (us * 1e-6) / 1e9,
                        "frac_of_900": wb / (us * 1e-6) / 1e9 / 900.0, "frac_of_770_measured": wb / (us * 1e-6) / 1e9 / 770.0}
                 results.append(row)

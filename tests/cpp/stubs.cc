@@ -14,7 +14,7 @@ PeerArena* SingleCommunicator::arena() { UNREACHABLE(); }
 void SingleCommunicator::check_device_status() { UNREACHABLE(); }
 void SingleCommunicator::check_all_device_status() {}  // host-only backends never reach it; harmless if they do
 void SingleCommunicator::allreduce(const RawTensor&, RawTensor&, ReductionOp) { UNREACHABLE(); }
-void SingleCommunicator::allreduce_inplace(RawTensor&, ReductionOp) { UNREACHABLE(); }
+void SingleCommunicator::allreduce_inplace(RawTensor&, ReductionOp, bool) { UNREACHABLE(); }
 void SingleCommunicator::alltoall_inplace(RawTensor&) { UNREACHABLE(); }
 void SingleCommunicator::allgather_inplace(RawTensor&) { UNREACHABLE(); }
 void SingleCommunicator::send(const RawTensor&, int) { UNREACHABLE(); }
@@ -39,6 +39,7 @@ void addmul_inplace(void*, const void*, float, DType, int64_t, cudaStream_t) { U
 void average_inplace(void*, const void*, DType, int64_t, cudaStream_t) { UNREACHABLE(); }
 void async_model_average(float*, const float*, const float*, float, int64_t, cudaStream_t) { UNREACHABLE(); }
 void copy_bytes(void*, const void*, size_t, cudaStream_t) { UNREACHABLE(); }
+void multi_copy(const MultiCopySeg*, int, void*, size_t, bool, cudaStream_t) { UNREACHABLE(); }
 void reduce_chunk_inplace(void*, DType, int64_t, int, int, bool, cudaStream_t) { UNREACHABLE(); }
 size_t compress_scratch_bytes(int, int64_t) { return 0; }
 void compress_minmax_u8(const void*, DType, int64_t, int64_t, int, uint8_t*, size_t, int, void*, size_t, cudaStream_t) {

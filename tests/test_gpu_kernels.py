@@ -245,3 +245,66 @@ def test_pool_guard_regions_stay_intact_under_the_kernels_and_catch_a_stray_stor
         torch.cuda.synchronize()
         C.pool_release_cached(0)
         C.pool_set_guard(was)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.uint8])
+def test_multi_tensor_flatten_and_unflatten_in_one_launch(dt):
+    """The staged-bucket copy kernel: ragged tensor sizes (tiles that hold many small tensors, tensors that
+    span many tiles, odd byte counts and therefore odd offsets), gathered into a flat buffer and scattered
+    back, bit-equal to torch.cat; bytes outside the packed range stay untouched."""
+    import bagua_core_b200 as bb
+
+    sizes = [1, 7, 0, 33, 4096, 5, (1 << 18) + 3, 1023, 16, (3 << 16) + 1, 2, 70001]
+    g = torch.Generator().manual_seed(5)
+    ts = []
+    for i, n in enumerate(sizes):
+        base = torch.randint(0, 255, (n + 3,), generator=g).to(torch.float32)
+        t = base.to(dt).cuda()[i % 3:i % 3 + n]  # views at odd element offsets: every alignment class occurs
+        ts.append(t.contiguous() if i % 2 else t)
+    total = sum(t.numel() for t in ts)
+    flat = torch.full((total + 64,), 77, dtype=dt, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    bb._C.k_multi_copy(ts, flat, True, stream)
+    torch.cuda.synchronize()
+    assert torch.equal(flat[:total], torch.cat([t.reshape(-1) for t in ts]))
+    assert (flat[total:] == 77).all()
+    # scatter back what a communication op would have left in the flat buffer
+    flat[:total] = (flat[:total].float() * 0 + torch.arange(total, device="cuda") % 251).to(dt)
+    want = flat[:total].clone()
+    bb._C.k_multi_copy(ts, flat, False, stream)
+    torch.cuda.synchronize()
+    assert torch.equal(torch.cat([t.reshape(-1) for t in ts]), want)
+
+
+def test_a_bucket_of_scattered_tensors_is_staged_with_the_copy_kernel():
+    """Through the engine: a bucket whose tensors are not adjacent in memory is flattened into a pool
+    buffer, handed to the op and copied back (here the op divides by the rank count of one: the round trip
+    must leave every tensor's values in place and nothing else touched)."""
+    import bagua_core as bc
+    import bagua_core_b200 as bb
+
+    torch.cuda.set_device(0)
+    backing = torch.zeros(1 << 16, device="cuda")
+    views = [backing[10:1000], backing[2000:2007], backing[4096:4096 + 12345], backing[30000:30001]]
+    for i, v in enumerate(views):
+        v.copy_(torch.arange(v.numel(), device="cuda") + 1000 * i)
+    before = backing.clone()
+    seen = []
+    tensors = [bc.BaguaTensorPy(v, f"t{i}") for i, v in enumerate(views)]
+    bucket = bc.BaguaBucketPy("scattered", tensors)
+    stream = torch.cuda.Stream()
+    uid = bc.BaguaSingleCommunicatorPy.generate_nccl_unique_id_str()
+    comm = bc.BaguaSingleCommunicatorPy(0, 1, 0, stream.cuda_stream, uid)
+    bucket.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True)
+    backend = bc.BaguaCommBackendPy(4, 0)
+    backend.register_ordered_buckets([bucket])
+    staged0 = bb._C.stats()["staged_copies"]
+    torch.cuda.synchronize()
+    for _ in range(2):  # the second round reuses the cached table
+        for t in tensors:
+            backend.mark_communication_ready(t, 0)
+        assert backend.wait_pending_comm_ops() == 1
+    stream.synchronize()
+    assert bb._C.stats()["staged_copies"] == staged0 + 2
+    assert torch.equal(backing, before)
+    backend.close()
