@@ -457,7 +457,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("key"), py::arg("value"),
       "Size thresholds and CTA budgets of the fused kernels (keys: oneshot_bytes, oneshot_sym_bytes, overlap_ctas, "
-      "nvls_overlap_ctas, bytes_per_cta; defaults from BAGUA_B200_<KEY>).  Must be set identically on every rank.");
+      "nvls_overlap_ctas, coop_overlap_ctas, bytes_per_cta, sym_threads, tma_min_bytes, tma_ctas, "
+      "tma_overlap_ctas, tma_bytes_per_cta; defaults from BAGUA_B200_<KEY>).  Must be set identically on every rank.");
   m.def("get_tuning", []() {
     py::dict d;
     for (auto& kv : fused::Tuning::global().items()) d[py::str(kv.first)] = kv.second;
@@ -811,9 +812,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               pi.push_back(in[r].data_ptr());
               po.push_back(out[r].data_ptr());
             }
-            const auto md = mode == "oneshot"   ? fused::EmuAllreduceMode::OneShot
-                            : mode == "twoshot" ? fused::EmuAllreduceMode::TwoShot
-                                                : fused::EmuAllreduceMode::Symmetric;
+            const auto md = mode == "oneshot"         ? fused::EmuAllreduceMode::OneShot
+                            : mode == "twoshot"       ? fused::EmuAllreduceMode::TwoShot
+                            : mode == "symmetric_tma" ? fused::EmuAllreduceMode::SymmetricTma
+                                                      : fused::EmuAllreduceMode::Symmetric;
             py::gil_scoped_release rel;
             a.allreduce(pi, po, in[0].numel(), dtype_from_torch(in[0].scalar_type()),
                         average ? 1.0f / (float)a.nranks() : 1.0f, md, blocks);

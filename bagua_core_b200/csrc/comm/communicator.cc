@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include "../kernels/fused.h"
+#include "../runtime/stats.h"
 #include "arena.h"
 
 namespace bagua {
@@ -157,8 +158,11 @@ void SingleCommunicator::allreduce_inplace(RawTensor& t, ReductionOp op, bool en
   if (a) {
     const float scale = p2p_scale(op, nranks_);
     if (scale != 0.0f && fused::allreduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,
-                                          (cudaStream_t)stream_, engine_op))
+                                          (cudaStream_t)stream_, engine_op)) {
+      if (engine_op) EngineStats::global().fused_launches++;
       return;
+    }
+    if (engine_op) EngineStats::global().library_fallbacks++;
   }
   transport_->allreduce(t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), op);
 }

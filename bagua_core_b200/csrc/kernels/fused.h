@@ -38,6 +38,13 @@ struct Tuning {
   std::atomic<long> overlap_ctas{64};          // CTA budget of a bucket reduced under backward kernels
   std::atomic<long> bytes_per_cta{64 << 10};   // payload per CTA below the budget
   std::atomic<long> nvls_overlap_ctas{64};     // the overlap budget of the multimem all-reduce
+  std::atomic<long> coop_overlap_ctas{148};    // the overlap budget of the cooperative ByteGrad kernel
+  std::atomic<long> sym_threads{512};          // threads per block of the symmetric all-reduce (128, 256 or 512)
+  // symmetric buffers of at least this size take the bulk-copy (TMA) all-reduce; -1: never
+  std::atomic<long> tma_min_bytes{-1};
+  std::atomic<long> tma_ctas{32};              // its CTA budget when it has the GPU to itself
+  std::atomic<long> tma_overlap_ctas{16};      // ... and under backward kernels
+  std::atomic<long> tma_bytes_per_cta{256 << 10};  // bytes of the rank's own chunk per CTA below the budget
   static Tuning& global();
   bool set(const std::string& key, long value);  // false: unknown key
   std::vector<std::pair<std::string, long>> items() const;
@@ -56,7 +63,8 @@ bool allreduce_nvls(PeerArena& arena, const void* in, void* out, int64_t n, DTyp
                     cudaStream_t stream, bool overlapped = false);
 
 // In-place ByteGrad on `bucket` (n elements, n % (16*nranks) == 0).
-bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream);
+bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream,
+              bool overlapped = false);
 
 // out = (in + peer's in) / 2; `peer` pairs must be mutual.
 bool pair_average(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, int peer, cudaStream_t stream);
@@ -93,6 +101,10 @@ bool reduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, fl
             cudaStream_t stream);
 // Returns (on the stream) once every rank's stream has reached the call.
 bool barrier(PeerArena& arena, cudaStream_t stream);
+
+// Interference probe (benchmarks/interference_probe.py): a kernel of `grid` x `threads` that stays
+// resident for `micros` microseconds on `stream`; mode 1 also streams over [buf, buf + bytes).
+void debug_occupy(void* buf, size_t bytes, int grid, int threads, double micros, int mode, cudaStream_t stream);
 
 // Test hook: launches a one-CTA kernel that waits `wait_ms` for a signal nobody sends
 // and returns the status record the host read back (code != 0 expected).  Uses only

@@ -23,6 +23,7 @@
 #include "fused.h"
 #include "fused_emu.h"
 #include "fused_allreduce_bodies.cuh"
+#include "fused_allreduce_tma.cuh"
 #include "peer_sync.cuh"
 #include "vec_ops.cuh"
 
@@ -54,12 +55,49 @@ __global__ void __launch_bounds__(kThreads)
                              int64_t max_chunk_vecs, float scale) {  // in == out for the in-place call
   allreduce_twoshot_body<T>(v, psync::real_launch(), in, out, nvec, max_chunk_vecs, scale);
 }
-template <typename T>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, int TPB>
+__global__ void __launch_bounds__(TPB)
     allreduce_sym_kernel(const __grid_constant__ ArenaView v, const __grid_constant__ SymPtrs p, int64_t nvec,
                          float scale) {
-  allreduce_sym_body<T>(v, psync::real_launch(), p, nvec, scale);
+  allreduce_sym_body<T, TPB>(v, psync::real_launch(), p, nvec, scale);
 }
+template <typename T, int NR>
+__global__ void __launch_bounds__(kTmaThreads)
+    allreduce_sym_tma_kernel(const __grid_constant__ ArenaView v, const __grid_constant__ SymPtrs p, int64_t nvec,
+                             float scale) {
+  extern __shared__ __align__(128) unsigned char tma_smem[];
+  allreduce_sym_tma_body<T, NR>(v, psync::real_launch(), p, nvec, scale, tma_smem);
+}
+// emulation: the grids of all ranks in one cooperative launch (rank count known at run time)
+template <typename T>
+__global__ void __launch_bounds__(kTmaThreads)
+    allreduce_tma_emu_kernel(const EmuRank* __restrict__ ranks, int blocks, int64_t nvec, float scale) {
+  extern __shared__ __align__(128) unsigned char tma_smem[];
+  const EmuRank& e = ranks[blockIdx.x / blocks];
+  const Launch L{(int)(blockIdx.x % blocks), blocks};
+  SymPtrs p;
+  for (int r = 0; r < kArenaMaxRanks; ++r) {
+    p.in[r] = (const uint4*)e.sym_in[r];
+    p.out[r] = (uint4*)e.sym_out[r];
+  }
+  switch (e.view.nranks) {
+    case 2: allreduce_sym_tma_body<T, 2>(e.view, L, p, nvec, scale, tma_smem); break;
+    case 4: allreduce_sym_tma_body<T, 4>(e.view, L, p, nvec, scale, tma_smem); break;
+    case 8: allreduce_sym_tma_body<T, 8>(e.view, L, p, nvec, scale, tma_smem); break;
+    default: break;  // the host side only launches it for 2, 4 or 8 ranks
+  }
+}
+
+template <typename T, int NR>
+void launch_sym_tma(const ArenaView& v, const SymPtrs& p, int64_t nvec, float scale, int grid, cudaStream_t stream) {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    BAGUA_CUDA_CHECK(cudaFuncSetAttribute(allreduce_sym_tma_kernel<T, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          TmaCfg<NR>::kSmemBytes));
+  });
+  allreduce_sym_tma_kernel<T, NR><<<grid, kTmaThreads, TmaCfg<NR>::kSmemBytes, stream>>>(v, p, nvec, scale);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     pair_average_kernel(const __grid_constant__ ArenaView v, const uint4* __restrict__ in, uint4* __restrict__ out,
@@ -101,6 +139,29 @@ __global__ void __launch_bounds__(kThreads)
 __global__ void wait_probe_kernel(ArenaView v) {
   // waits for a phase signal from "rank 1" that nobody will ever send
   psync::cta_wait_phase(v, psync::real_launch(), 0, 1u << 1);
+}
+
+// Interference probe: occupies `grid` blocks of `threads` threads for `ns` nanoseconds of
+// %globaltimer.  mode 0 only spins; mode 1 also streams over `buf` (reads and writes it back
+// unchanged, 16 bytes per thread and iteration) for as long as it runs.  Bounded by the timer
+// and by an iteration cap; touches nothing outside `buf`.
+__global__ void occupy_kernel(uint4* buf, int64_t nvec, uint64_t ns, int mode) {
+  const uint64_t t0 = psync::globaltimer_ns();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (uint64_t it = 0; it < (1ull << 26); ++it) {
+    if (psync::globaltimer_ns() - t0 >= ns) break;
+    if (mode == 1 && nvec > 0) {
+      if (i >= nvec) i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+      if (i < nvec) {
+        uint4 x = buf[i];
+        buf[i] = x;
+      }
+      i += stride;
+    } else {
+      __nanosleep(100);
+    }
+  }
 }
 
 int pick_grid(const PeerArena& arena, size_t bytes, bool overlapped = false) {
@@ -150,8 +211,41 @@ bool allreduce_t(PeerArena& arena, const void* in, void* out, int64_t n, float s
       p.in[r] = (const uint4*)pin[r];
       p.out[r] = (uint4*)pout[r];
     }
-    ArenaView v = arena.next_view(grid, 0);
-    allreduce_sym_kernel<T><<<grid, kThreads, 0, stream>>>(v, p, nvec, scale);
+    // Large buckets: tiles travel through the bulk-copy engine (fused_allreduce_tma.cuh), which keeps
+    // an order of magnitude more bytes in flight per SM, so a handful of blocks carries the link.
+    const long tma_min = tune.tma_min_bytes.load();
+    if (tma_min >= 0 && bytes >= (size_t)tma_min && (N == 2 || N == 4 || N == 8)) {
+      const int64_t per = std::max<int64_t>(tune.tma_bytes_per_cta.load(), 64 << 10);
+      int64_t cap = std::max<long>(overlapped ? tune.tma_overlap_ctas.load() : tune.tma_ctas.load(), 1);
+      cap = std::min<int64_t>(cap, kArenaMaxBlocks);
+      const int g2 = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)((bytes / N + per - 1) / per), cap));
+      ArenaView v = arena.next_view(g2, 0);
+      if (N == 2)
+        launch_sym_tma<T, 2>(v, p, nvec, scale, g2, stream);
+      else if (N == 4)
+        launch_sym_tma<T, 4>(v, p, nvec, scale, g2, stream);
+      else
+        launch_sym_tma<T, 8>(v, p, nvec, scale, g2, stream);
+      BAGUA_CUDA_CHECK(cudaGetLastError());
+      arena.count_launch();
+      return true;
+    }
+    // Narrower blocks (sym_threads = 128 or 256) spread the same number of threads over more SMs
+    // and leave room on each for a compute kernel's blocks; the payload per block shrinks alike.
+    const long tpb = tune.sym_threads.load();
+    if (tpb == 128 || tpb == 256) {
+      const int64_t per = std::max<int64_t>(tune.bytes_per_cta.load(), 4096) * tpb / kThreads;
+      const int64_t cap = std::min<int64_t>(kArenaMaxBlocks, (int64_t)grid * (kThreads / tpb));
+      const int g2 = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)((bytes + per - 1) / per), cap));
+      ArenaView v = arena.next_view(g2, 0);
+      if (tpb == 128)
+        allreduce_sym_kernel<T, 128><<<g2, 128, 0, stream>>>(v, p, nvec, scale);
+      else
+        allreduce_sym_kernel<T, 256><<<g2, 256, 0, stream>>>(v, p, nvec, scale);
+    } else {
+      ArenaView v = arena.next_view(grid, 0);
+      allreduce_sym_kernel<T, kThreads><<<grid, kThreads, 0, stream>>>(v, p, nvec, scale);
+    }
   } else {
     const int64_t max_chunk = (nvec + N - 1) / N;
     arena.ensure_staging(((size_t)N * (size_t)max_chunk + (size_t)nvec) * 16);
@@ -211,6 +305,12 @@ Tuning& Tuning::global() {
     t.overlap_ctas = env_long("BAGUA_B200_OVERLAP_CTAS", 64);
     t.bytes_per_cta = env_long("BAGUA_B200_BYTES_PER_CTA", 64 << 10);
     t.nvls_overlap_ctas = env_long("BAGUA_B200_NVLS_OVERLAP_CTAS", 64);
+    t.coop_overlap_ctas = env_long("BAGUA_B200_COOP_OVERLAP_CTAS", 148);
+    t.sym_threads = env_long("BAGUA_B200_SYM_THREADS", 512);
+    t.tma_min_bytes = env_long("BAGUA_B200_TMA_MIN_BYTES", -1);
+    t.tma_ctas = env_long("BAGUA_B200_TMA_CTAS", 32);
+    t.tma_overlap_ctas = env_long("BAGUA_B200_TMA_OVERLAP_CTAS", 16);
+    t.tma_bytes_per_cta = env_long("BAGUA_B200_TMA_BYTES_PER_CTA", 256 << 10);
   });
   return t;
 }
@@ -221,6 +321,12 @@ bool Tuning::set(const std::string& key, long value) {
   else if (key == "overlap_ctas") overlap_ctas = value;
   else if (key == "bytes_per_cta") bytes_per_cta = value;
   else if (key == "nvls_overlap_ctas") nvls_overlap_ctas = value;
+  else if (key == "coop_overlap_ctas") coop_overlap_ctas = value;
+  else if (key == "sym_threads") sym_threads = value;
+  else if (key == "tma_min_bytes") tma_min_bytes = value;
+  else if (key == "tma_ctas") tma_ctas = value;
+  else if (key == "tma_overlap_ctas") tma_overlap_ctas = value;
+  else if (key == "tma_bytes_per_cta") tma_bytes_per_cta = value;
   else return false;
   return true;
 }
@@ -230,7 +336,13 @@ std::vector<std::pair<std::string, long>> Tuning::items() const {
           {"oneshot_sym_bytes", oneshot_sym_bytes.load()},
           {"overlap_ctas", overlap_ctas.load()},
           {"bytes_per_cta", bytes_per_cta.load()},
-          {"nvls_overlap_ctas", nvls_overlap_ctas.load()}};
+          {"nvls_overlap_ctas", nvls_overlap_ctas.load()},
+          {"coop_overlap_ctas", coop_overlap_ctas.load()},
+          {"sym_threads", sym_threads.load()},
+          {"tma_min_bytes", tma_min_bytes.load()},
+          {"tma_ctas", tma_ctas.load()},
+          {"tma_overlap_ctas", tma_overlap_ctas.load()},
+          {"tma_bytes_per_cta", tma_bytes_per_cta.load()}};
 }
 
 bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream,
@@ -268,6 +380,36 @@ void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n,
   }
 }
 
+namespace {
+template <typename T>
+void emu_tma_t(const EmuRank* dev, int nranks, int blocks, int64_t nvec, float scale) {
+  BAGUA_CHECK(nranks == 2 || nranks == 4 || nranks == 8, Communicator,
+              "the bulk-copy all-reduce is built for 2, 4 or 8 ranks");
+  const int smem = std::max(std::max((int)TmaCfg<2>::kSmemBytes, (int)TmaCfg<4>::kSmemBytes), (int)TmaCfg<8>::kSmemBytes);
+  BAGUA_CUDA_CHECK(
+      cudaFuncSetAttribute(allreduce_tma_emu_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int per_sm = 0, sms = 0, device = 0;
+  BAGUA_CUDA_CHECK(cudaGetDevice(&device));
+  BAGUA_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  BAGUA_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_tma_emu_kernel<T>, kTmaThreads, smem));
+  const int grid = nranks * blocks;
+  BAGUA_CHECK(grid <= per_sm * sms, Communicator,
+              "emulation needs " << grid << " co-resident blocks, the device holds " << per_sm * sms);
+  void* args[] = {(void*)&dev, (void*)&blocks, (void*)&nvec, (void*)&scale};
+  BAGUA_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)allreduce_tma_emu_kernel<T>, dim3(grid), dim3(kTmaThreads),
+                                               args, (size_t)smem, 0));
+}
+}  // namespace
+
+void emu_launch_allreduce_tma(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale) {
+  switch (dt) {
+    case DType::F32: emu_tma_t<float>(dev, nranks, blocks, n * 4 / 16, scale); break;
+    case DType::F16: emu_tma_t<__half>(dev, nranks, blocks, n * 2 / 16, scale); break;
+    case DType::BF16: emu_tma_t<__nv_bfloat16>(dev, nranks, blocks, n * 2 / 16, scale); break;
+    default: throw BaguaError(ErrorKind::Tensor, "emulated all-reduce: unsupported dtype");
+  }
+}
+
 void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, bool symmetric) {
   const int grid = nranks * blocks;
   const int sym = symmetric ? 1 : 0;
@@ -277,6 +419,12 @@ void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t
     case DType::BF16: coop_launch(pair_average_emu_kernel<__nv_bfloat16>, grid, dev, blocks, n * 2 / 16, sym); break;
     default: throw BaguaError(ErrorKind::Tensor, "emulated pair average: unsupported dtype");
   }
+}
+
+void debug_occupy(void* buf, size_t bytes, int grid, int threads, double micros, int mode, cudaStream_t stream) {
+  if (grid < 1 || threads < 32 || threads > 1024 || micros <= 0 || micros > 1e6) return;
+  occupy_kernel<<<grid, threads, 0, stream>>>((uint4*)buf, (int64_t)(bytes / 16), (uint64_t)(micros * 1e3), mode);
+  BAGUA_CUDA_CHECK(cudaGetLastError());
 }
 
 DeviceStatus debug_wait_timeout(int device, double wait_ms) {

@@ -137,10 +137,12 @@ struct SymPtrs {
 // NR is the rank count when it is 2, 4 or 8 (the loops over ranks then unroll with no
 // predicates and U = 16 / NR vectors per thread keep 16 loads in flight whatever the rank
 // count), 0 for any other count (bound checks against v.nranks, U = 2).
-template <typename T, int NR>
+// TPB = threads per block of the launch (kThreads in the emulation).
+template <typename T, int NR, int TPB = kThreads>
 __device__ __forceinline__ void allreduce_sym_body_n(const ArenaView& v, const Launch& L, const SymPtrs& p,
                                                      int64_t nvec, float scale) {
   using O = VecOps<T>;
+  constexpr int kThreads = TPB;  // shadows the file-wide constant inside this body
   constexpr int R = NR > 0 ? NR : kArenaMaxRanks;  // unrolled extent of the rank loops
   constexpr int U = NR > 0 ? 16 / NR : 2;          // vectors per thread per iteration
   const int me = v.rank, N = NR > 0 ? NR : v.nranks;
@@ -189,14 +191,14 @@ __device__ __forceinline__ void allreduce_sym_body_n(const ArenaView& v, const L
   psync::cta_finish_op(v, L);
 }
 
-template <typename T>
+template <typename T, int TPB = kThreads>
 __device__ __forceinline__ void allreduce_sym_body(const ArenaView& v, const Launch& L, const SymPtrs& p,
                                                    int64_t nvec, float scale) {
   switch (v.nranks) {
-    case 2: allreduce_sym_body_n<T, 2>(v, L, p, nvec, scale); break;
-    case 4: allreduce_sym_body_n<T, 4>(v, L, p, nvec, scale); break;
-    case 8: allreduce_sym_body_n<T, 8>(v, L, p, nvec, scale); break;
-    default: allreduce_sym_body_n<T, 0>(v, L, p, nvec, scale); break;
+    case 2: allreduce_sym_body_n<T, 2, TPB>(v, L, p, nvec, scale); break;
+    case 4: allreduce_sym_body_n<T, 4, TPB>(v, L, p, nvec, scale); break;
+    case 8: allreduce_sym_body_n<T, 8, TPB>(v, L, p, nvec, scale); break;
+    default: allreduce_sym_body_n<T, 0, TPB>(v, L, p, nvec, scale); break;
   }
 }
 

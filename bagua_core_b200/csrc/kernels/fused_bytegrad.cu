@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 template <typename T>
-bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStream_t stream) {
+bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStream_t stream, bool overlapped) {
   const int N = arena.nranks();
   if (n <= 0) return true;
   if (n % ((int64_t)16 * N) != 0 || (uintptr_t)bucket % 16 != 0) return false;
@@ -76,7 +76,13 @@ bool bytegrad_t(PeerArena& arena, void* bucket, int64_t n, bool average, cudaStr
   // one CTA per 32 Ki elements of the bucket, up to the arena's limit for cooperative
   // kernels (one per SM by default: several HBM passes plus quantiser math per element)
   int64_t g = (n + (32 << 10) - 1) / (32 << 10);
-  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, arena.max_coop_blocks()));
+  // A cooperative launch starts only when all of its CTAs fit on the GPU at once.  With one CTA
+  // per SM that means an idle GPU: the bucket then waits for the running backward kernels to
+  // drain and the kernels queued behind it wait for the bucket.  A bucket reduced during
+  // backward therefore takes the (smaller) overlap budget, which the GPU frees up quickly.
+  int64_t cap = arena.max_coop_blocks();
+  if (overlapped) cap = std::min<int64_t>(cap, std::max<long>(Tuning::global().coop_overlap_ctas.load(), 1));
+  int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g, cap));
   static int coop_limit = 0;
   if (coop_limit == 0) {
     int per_sm = 0, sms = 0, dev = 0;
@@ -131,11 +137,12 @@ void emu_launch_bytegrad(const EmuRank* dev, int nranks, int blocks, int64_t n, 
   }
 }
 
-bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream) {
+bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream,
+              bool overlapped) {
   switch (dt) {
-    case DType::F32: return bytegrad_t<float>(arena, bucket, n, average, stream);
-    case DType::F16: return bytegrad_t<__half>(arena, bucket, n, average, stream);
-    case DType::BF16: return bytegrad_t<__nv_bfloat16>(arena, bucket, n, average, stream);
+    case DType::F32: return bytegrad_t<float>(arena, bucket, n, average, stream, overlapped);
+    case DType::F16: return bytegrad_t<__half>(arena, bucket, n, average, stream, overlapped);
+    case DType::BF16: return bytegrad_t<__nv_bfloat16>(arena, bucket, n, average, stream, overlapped);
     default: return false;
   }
 }

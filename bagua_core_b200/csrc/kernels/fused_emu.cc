@@ -106,7 +106,10 @@ void EmulatedArena::allreduce(const std::vector<const void*>& in, const std::vec
     }
   }
   EmuRank* dev = prepare(host, blocks, 0, need);
-  emu_launch_allreduce(dev, nranks_, blocks, n, dt, scale, mode, aux);
+  if (mode == EmuAllreduceMode::SymmetricTma)
+    emu_launch_allreduce_tma(dev, nranks_, blocks, n, dt, scale);
+  else
+    emu_launch_allreduce(dev, nranks_, blocks, n, dt, scale, mode, aux);
   finish("all-reduce");
 }
 

@@ -33,7 +33,7 @@ struct EmuRank {
   int peer;         // pair-average partner
 };
 
-enum class EmuAllreduceMode { OneShot = 1, TwoShot = 2, Symmetric = 3 };
+enum class EmuAllreduceMode { OneShot = 1, TwoShot = 2, Symmetric = 3, SymmetricTma = 4 };
 enum class EmuCollective {
   AllGather = 1,
   AllToAll = 2,
@@ -100,6 +100,8 @@ class EmulatedArena {
 // Launchers defined next to the kernels they start (cooperative, nranks*blocks CTAs).
 void emu_launch_allreduce(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale,
                           EmuAllreduceMode mode, int64_t aux_vecs);
+// The bulk-copy (TMA) variant of the symmetric all-reduce; 2, 4 or 8 ranks.
+void emu_launch_allreduce_tma(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, float scale);
 void emu_launch_pair_average(const EmuRank* dev, int nranks, int blocks, int64_t n, DType dt, bool symmetric);
 // aux: bit 0 = symmetric variant, bit 1 = local chunk already in place (exchange);
 // the root rank for the broadcasts; root | in_place << 8 for scatter, gather and reduce.

@@ -14,6 +14,7 @@
 #pragma once
 
 #include "../comm/communicator.h"
+#include "../runtime/stats.h"
 #include "../tensor/tensor.h"
 
 namespace bagua {
@@ -22,16 +23,6 @@ struct EngineConfig {
   // Reference-faithful host behaviour: cudaStreamSynchronize after every bucket.
   bool sync_per_bucket = false;
   static EngineConfig& global();
-};
-
-struct EngineStats {
-  std::atomic<uint64_t> buckets_scheduled{0};
-  std::atomic<uint64_t> ops_executed{0};
-  std::atomic<uint64_t> fused_launches{0};
-  std::atomic<uint64_t> library_fallbacks{0};
-  std::atomic<uint64_t> staged_copies{0};
-  std::atomic<uint64_t> bytes_communicated{0};
-  static EngineStats& global();
 };
 
 class CommOp {

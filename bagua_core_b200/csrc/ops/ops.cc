@@ -3,6 +3,9 @@
 // body is also the CPU backend and the measured baseline.
 #include <cuda_runtime.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "../comm/arena.h"
 #include "../kernels/fused.h"
 #include "../runtime/timeline.h"
@@ -94,7 +97,26 @@ class CentralizedFullPrecisionSynchronous : public CommOp {
   void execute_background_communication(const BucketPtr& bucket) override {
     OpFrame f(bucket, *comm_, false, false);
     comm_->execute_communication(*f.ct.raw, average_, true, true, [&](SingleCommunicator& c, RawTensor& t) {
-      if (c.nranks() == 1) return;  // sum or mean over one rank: nothing to do
+      if (c.nranks() == 1) {
+        // Sum or mean over one rank: nothing to do.  With BAGUA_B200_PROBE_OCCUPY="ctas,threads,us_per_mb,mode"
+        // a stand-in kernel takes the place of the bucket's communication (same stream, same moment, a
+        // duration in proportion to the bucket's size), which shows on ONE GPU what a communication
+        // kernel of that shape costs the backward pass it overlaps (benchmarks/interference_probe.py).
+        static const std::string probe = [] {
+          const char* e = std::getenv("BAGUA_B200_PROBE_OCCUPY");
+          return std::string(e ? e : "");
+        }();
+        if (!probe.empty() && t.device_id() >= 0) {
+          int ctas = 0, threads = 0, mode = 0;
+          double us_per_mb = 0;
+          if (std::sscanf(probe.c_str(), "%d,%d,%lf,%d", &ctas, &threads, &us_per_mb, &mode) == 4) {
+            const double mb = (double)t.bytes_allocated() / (1 << 20);
+            fused::debug_occupy(t.data_ptr(), t.bytes_allocated(), ctas, threads, 15.0 + us_per_mb * mb, mode,
+                                (cudaStream_t)c.stream());
+          }
+        }
+        return;
+      }
       if (PeerArena* a = fused_arena(c, t)) {
         const float scale = average_ ? 1.0f / (float)c.nranks() : 1.0f;
         if (fused::allreduce(*a, t.data_ptr(), t.data_ptr(), t.num_elements_allocated(), t.dtype(), scale,
@@ -143,7 +165,7 @@ class CentralizedLowPrecisionSynchronous : public CommOp {
     comm_->execute_communication(*f.ct.raw, average_, true, true, [&](SingleCommunicator& c, RawTensor& t) {
       if (PeerArena* a = fused_arena(c, t)) {
         if (fused::bytegrad(*a, t.data_ptr(), t.num_elements_allocated(), t.dtype(), average_,
-                            (cudaStream_t)c.stream())) {
+                            (cudaStream_t)c.stream(), /*overlapped=*/true)) {
           note_fused();
           return;
         }

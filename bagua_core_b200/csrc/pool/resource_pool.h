@@ -6,8 +6,8 @@
 // memory for the CPU backend.  Events: created with cudaEventDisableTiming and recycled.
 // With guards on (BAGUA_B200_POOL_GUARD=1 or set_guard(true)) every new block gets 256 bytes
 // of a fixed pattern in front of it and behind its capacity; check_guards() reports blocks
-// whose pattern was overwritten (the memory checker of the GPU pool being closed to tools,
-// this is how an out-of-range store of a kernel into pool memory is found after a test).
+// whose pattern was overwritten: a check that needs no external memory-checking tool and finds
+// an out-of-range store of a kernel into pool memory after a test.
 // A lease owns its resource until destroyed — the reference copies the raw event out of
 // a pool guard that is dropped at once (bagua-core-internal/src/comm_ops/
 // decentralized_full_precision_asynchronous.rs:78,107), which this design rules out.

@@ -144,9 +144,11 @@ def init_process_group(device: Optional[torch.device] = None, schedule_channel_c
                 dist.init_process_group("gloo", rank=rank, world_size=world)
         keep: list = []
         if device.type == "cuda":
-            # highest priority so that communication kernels are scheduled ahead of backward kernels
+            # highest priority by default, so that communication kernels are scheduled ahead of the
+            # backward kernels queued before them (BAGUA_B200_COMM_PRIORITY=low|normal|high)
             lo, hi = torch.cuda.Stream.priority_range() if hasattr(torch.cuda.Stream, "priority_range") else (0, -1)
-            comm_stream = torch.cuda.Stream(device=device, priority=hi)
+            prio = {"low": lo, "normal": 0, "high": hi}.get(os.environ.get("BAGUA_B200_COMM_PRIORITY", "high"), hi)
+            comm_stream = torch.cuda.Stream(device=device, priority=prio)
             stream_ptr = comm_stream.cuda_stream
             dev_id = device.index
         else:

@@ -23,7 +23,7 @@ Bus bandwidth conventions (bytes that must cross each GPU's links, per direction
   shift_one:  S                        lp_ring:  2 · (S/4 + 32)
   allgather / alltoall / reduce_scatter: (N-1)/N · S      broadcast: S
 Roofline fraction = busbw / 900 GB/s (nominal NVLink 5 per direction) and / 770 GB/s
-(measured peer copy on this pool).
+(a measured peer-to-peer copy between two B200s through the NVSwitch).
 """
 from __future__ import annotations
 

@@ -54,6 +54,7 @@ def main():
         "allreduce_oneshot": (lambda: arena.allreduce(xs, xs, True, "oneshot", args.blocks), N * (N + 1 + N) * S),
         "allreduce_twoshot": (lambda: arena.allreduce(xs, xs, True, "twoshot", args.blocks), N * 6 * S),
         "allreduce_symmetric": (lambda: arena.allreduce(xs, xs, True, "symmetric", args.blocks), N * 2 * S),
+        "allreduce_symmetric_tma": (lambda: arena.allreduce(xs, xs, True, "symmetric_tma", args.blocks), N * 2 * S),
         "bytegrad": (lambda: arena.bytegrad(xs, True, args.blocks), int(N * 3.75 * S)),
         "lp_ring": (lambda: arena.lp_ring(xs, aux[0], aux[1], aux[2], args.blocks), int(N * 13.75 * S)),
     }

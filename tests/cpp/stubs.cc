@@ -26,8 +26,9 @@ void Communicator::execute_communication(RawTensor&, bool, bool, bool,
 }
 namespace fused {
 bool allreduce(PeerArena&, const void*, void*, int64_t, DType, float, cudaStream_t, bool) { UNREACHABLE(); }
-bool bytegrad(PeerArena&, void*, int64_t, DType, bool, cudaStream_t) { UNREACHABLE(); }
+bool bytegrad(PeerArena&, void*, int64_t, DType, bool, cudaStream_t, bool) { UNREACHABLE(); }
 bool pair_average(PeerArena&, const void*, void*, int64_t, DType, int, cudaStream_t) { UNREACHABLE(); }
+void debug_occupy(void*, size_t, int, int, double, int, cudaStream_t) { UNREACHABLE(); }
 bool lp_ring(PeerArena&, void*, void*, void*, void*, int64_t, DType, cudaStream_t) { UNREACHABLE(); }
 }  // namespace fused
 namespace kernels {

@@ -238,7 +238,10 @@ def _p2p_vs_library(rank, world):
             comm.set_p2p_collectives(p2p)
             before = comm.fused_launches()
             torch.cuda.synchronize()
-            res = fn()
+            # buffers are made and filled on the communicator's stream: allocation, fill, collective
+            # and any view taken of the result are then ordered with one another
+            with torch.cuda.stream(stream):
+                res = fn()
             stream.synchronize()
             comm.check_device_status()
             assert (comm.fused_launches() > before) == p2p
@@ -283,7 +286,7 @@ def _p2p_vs_library(rank, world):
             buf = big.clone()
             torch.cuda.synchronize()
             comm.reduce_scatter_inplace(T(buf, "b"), 0)
-            return buf[rank * chunk:(rank + 1) * chunk].clone()
+            return buf[rank * chunk:(rank + 1) * chunk]  # a view: read only after the caller has synchronised
 
         def broadcast():
             buf = big.clone()

@@ -41,6 +41,35 @@ def test_emulated_allreduce(nranks, mode, dt):
             assert torch.allclose(y.float(), ref * nranks, rtol=tol, atol=tol * nranks * max(1.0, ref.abs().max().item()))
 
 
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.bfloat16])
+def test_emulated_bulk_copy_allreduce_equals_the_load_store_kernel(nranks, dt):
+    """The symmetric all-reduce whose tiles travel through the bulk-copy engine (shared-memory ring,
+    mbarrier completion, bulk stores) gives the same bits as the kernel that uses ordinary loads and
+    stores: sizes below one tile, ragged tails, slices that are empty, many tiles per block (the ring
+    wraps several times), in place and out of place."""
+    arena = _arena(nranks)
+    ve = 4 if dt == torch.float32 else 8
+    for n, blocks in [(ve * nranks, 1), (ve * 37, 3), (ve * (1024 * nranks + 3), 2), (ve * 100003, 5), (1 << 22, 4),
+                      ((1 << 22) + ve * 13, 1)]:
+        xs = _inputs(nranks, n, dt, seed=n % 1000)
+        want = [torch.zeros_like(x) for x in xs]
+        arena.allreduce(xs, want, True, "symmetric", blocks)
+        outs = [torch.full_like(x, 7.0) for x in xs]
+        arena.allreduce(xs, outs, True, "symmetric_tma", blocks)
+        ref = torch.stack([x.float() for x in xs]).mean(0)
+        tol = 1e-6 if dt == torch.float32 else 1.6e-2
+        for o, w in zip(outs, want):
+            assert torch.equal(o, w), (n, blocks)
+            assert torch.allclose(o.float(), ref, rtol=tol, atol=tol * max(1.0, ref.abs().max().item()))
+        ys = [x.clone() for x in xs]
+        arena.allreduce(ys, ys, False, "symmetric_tma", blocks)  # in place, sum
+        zs = [x.clone() for x in xs]
+        arena.allreduce(zs, zs, False, "symmetric", blocks)
+        for y, z in zip(ys, zs):
+            assert torch.equal(y, z), (n, blocks)
+
+
 def test_emulated_mixed_ops_reuse_staging_safely():
     """Back-to-back ops with different layouts over the same staging (the `done` chain)."""
     nranks = 4
@@ -48,12 +77,12 @@ def test_emulated_mixed_ops_reuse_staging_safely():
     expect = sum(range(1, nranks + 1)) / nranks
     for rep in range(4):
         for n, mode, blocks in [(1 << 12, "oneshot", 2), (1 << 18, "twoshot", 6), (256, "oneshot", 1),
-                                (1 << 16, "symmetric", 4), (1 << 14, "twoshot", 3)]:
+                                (1 << 16, "symmetric", 4), (1 << 14, "twoshot", 3), (1 << 17, "symmetric_tma", 3)]:
             xs = [torch.full((n,), float(r + 1), device="cuda") for r in range(nranks)]
             arena.allreduce(xs, xs, True, mode, blocks)
             for x in xs:
                 assert torch.allclose(x, torch.full_like(x, expect))
-    assert arena.epoch() == 20
+    assert arena.epoch() == 24
 
 
 @pytest.mark.parametrize("symmetric", [False, True])

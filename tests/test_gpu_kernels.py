@@ -153,7 +153,7 @@ def test_device_wait_runs_out_and_reports():
 @pytest.mark.parametrize("dt", DTYPES)
 def test_kernels_stay_inside_their_buffers(n, dt):
     """Guard regions of a sentinel value on both sides of every operand must survive every
-    kernel (stand-in for a memory checker, which cannot be run on the GPU pool)."""
+    kernel (a memory check that needs no external tool)."""
     import bagua_core as bc
     import bagua_core_b200.ops as ops
 

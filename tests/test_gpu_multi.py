@@ -91,6 +91,23 @@ def _fused_allreduce(rank, world):
             assert torch.allclose(sym.float(), ref, rtol=tol, atol=tol * max(1.0, ref.abs().max().item())), (dt, rep)
             outs = _gather_all(sym.clone())
             assert all(torch.equal(outs[0], o) for o in outs)
+        # the same bucket through the bulk-copy (TMA) variant of the kernel: bit-identical result
+        if world in (2, 4, 8):
+            import bagua_core_b200 as bb
+
+            first = sym.clone()
+            sym.copy_(allx[rank])
+            torch.cuda.synchronize()
+            torch.distributed.barrier()
+            before = dict(bb._C.get_tuning())["tma_min_bytes"]
+            bb._C.set_tuning("tma_min_bytes", 1 << 20)
+            try:
+                assert comm.fused_allreduce(bt, bt, True)
+                stream.synchronize()
+                comm.check_device_status()
+            finally:
+                bb._C.set_tuning("tma_min_bytes", before)
+            assert torch.equal(sym, first), dt
     # back-to-back ops of different sizes without host sync in between (staging reuse protocol)
     xs = [torch.full((s,), float(rank + 1), device=dev) for s in (1 << 12, 1 << 22, 1 << 14, 1 << 21, 64)]
     torch.cuda.synchronize()
