@@ -42,6 +42,7 @@ SOURCES = [
     "kernels/minmax_uint8.cu",
     "kernels/multi_copy.cu",
     "kernels/fused_allreduce.cu",
+    "kernels/fused_allreduce_ce.cu",
     "kernels/fused_bytegrad.cu",
     "kernels/fused_gossip.cu",
     "kernels/fused_collectives.cu",

@@ -255,6 +255,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         auto* a = c.inner->arena();
         return a ? a->fused_launches() : (uint64_t)0;
       })
+      .def("fused_allreduce_ce",
+           [](PyComm& c, PyTensor& s, PyTensor& r, bool average) {
+             auto* a = c.inner->arena();
+             BAGUA_CHECK(a != nullptr, Communicator, "fused kernels are not available on this communicator");
+             auto sr = s.inner->raw();
+             auto rr = r.inner->raw();
+             BAGUA_CHECK(sr->dtype() == rr->dtype() && sr->num_elements_allocated() == rr->num_elements_allocated(),
+                         Tensor, "send and recv must agree in dtype and size");
+             return fused::allreduce_ce(*a, sr->data_ptr(), rr->data_ptr(), sr->num_elements_allocated(), sr->dtype(),
+                                        average ? 1.0f / (float)c.inner->nranks() : 1.0f,
+                                        (cudaStream_t)c.inner->stream());
+           },
+           py::arg("send_tensor"), py::arg("recv_tensor"), py::arg("average"),
+           py::call_guard<py::gil_scoped_release>(),
+           "All-reduce of symmetric buffers with the bytes moved by the copy engines (False: not symmetric).")
       .def("fused_allreduce",
            [](PyComm& c, PyTensor& s, PyTensor& r, bool average) {
              auto* a = c.inner->arena();
@@ -457,7 +472,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("key"), py::arg("value"),
       "Size thresholds and CTA budgets of the fused kernels (keys: oneshot_bytes, oneshot_sym_bytes, overlap_ctas, "
-      "nvls_overlap_ctas, coop_overlap_ctas, bytes_per_cta, sym_threads, tma_min_bytes, tma_ctas, "
+      "nvls_overlap_ctas, coop_overlap_ctas, bytes_per_cta, sym_threads, ce_min_bytes, tma_min_bytes, tma_isolated, tma_ctas, "
       "tma_overlap_ctas, tma_bytes_per_cta; defaults from BAGUA_B200_<KEY>).  Must be set identically on every rank.");
   m.def("get_tuning", []() {
     py::dict d;

@@ -34,14 +34,20 @@ namespace fused {
 // every rank must do alike (the thresholds select the algorithm, and ranks must agree on it).
 struct Tuning {
   std::atomic<long> oneshot_bytes{-1};         // staging path: one-shot up to this size (-1: by rank count)
-  std::atomic<long> oneshot_sym_bytes{128 << 10};  // symmetric buffers: one-shot up to this size
+  std::atomic<long> oneshot_sym_bytes{-1};     // symmetric buffers: one-shot up to this size (-1: by rank count)
   std::atomic<long> overlap_ctas{64};          // CTA budget of a bucket reduced under backward kernels
   std::atomic<long> bytes_per_cta{64 << 10};   // payload per CTA below the budget
   std::atomic<long> nvls_overlap_ctas{64};     // the overlap budget of the multimem all-reduce
   std::atomic<long> coop_overlap_ctas{148};    // the overlap budget of the cooperative ByteGrad kernel
   std::atomic<long> sym_threads{512};          // threads per block of the symmetric all-reduce (128, 256 or 512)
+  // symmetric buckets of at least this size, reduced under backward kernels, are moved by the copy
+  // engines (allreduce_ce); -1: never
+  std::atomic<long> ce_min_bytes{8 << 20};
   // symmetric buffers of at least this size take the bulk-copy (TMA) all-reduce; -1: never
-  std::atomic<long> tma_min_bytes{-1};
+  std::atomic<long> tma_min_bytes{1 << 20};
+  // 0: only buckets reduced under backward kernels take it (with the GPU to itself the load/store kernel
+  // is as fast and SM count does not matter); 1: every eligible call
+  std::atomic<long> tma_isolated{0};
   std::atomic<long> tma_ctas{32};              // its CTA budget when it has the GPU to itself
   std::atomic<long> tma_overlap_ctas{16};      // ... and under backward kernels
   std::atomic<long> tma_bytes_per_cta{256 << 10};  // bytes of the rank's own chunk per CTA below the budget
@@ -61,6 +67,12 @@ bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt,
 // `allreduce` tries this first.
 bool allreduce_nvls(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale,
                     cudaStream_t stream, bool overlapped = false);
+
+// The same for buffers in the symmetric heap with the bytes moved by the copy engines: rank r pulls
+// chunk r of every peer's input (DMA), reduces it with a short local kernel and pushes the result
+// into every peer's output (DMA); two one-block kernels do the signalling.  Returns false when the
+// buffers are not symmetric.
+bool allreduce_ce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream);
 
 // In-place ByteGrad on `bucket` (n elements, n % (16*nranks) == 0).
 bool bytegrad(PeerArena& arena, void* bucket, int64_t n, DType dt, bool average, cudaStream_t stream,

@@ -196,7 +196,10 @@ bool allreduce_t(PeerArena& arena, const void* in, void* out, int64_t n, float s
   // with two ranks the wire bytes are equal, so one-shot always wins; otherwise it wins while
   // the extra bytes cost less than the extra hop (about 16 MB of wire traffic per GPU).
   const long oneshot_env = tune.oneshot_bytes.load();
-  const size_t oneshot_max = sym                ? (size_t)std::max<long>(tune.oneshot_sym_bytes.load(), 0)
+  // (symmetric buffers: oneshot_sym_bytes; unset, 4 MB with two ranks, where the push sends no more
+  // bytes than the pull and saves one signalling round, 128 KB otherwise)
+  const long sym_env = tune.oneshot_sym_bytes.load();
+  const size_t oneshot_max = sym                ? (sym_env >= 0 ? (size_t)sym_env : N == 2 ? ((size_t)4 << 20) : ((size_t)128 << 10))
                              : oneshot_env >= 0 ? (size_t)oneshot_env
                              : N == 2           ? ((size_t)512 << 20)
                                                 : ((size_t)16 << 20) / (size_t)(N - 1);
@@ -214,7 +217,8 @@ bool allreduce_t(PeerArena& arena, const void* in, void* out, int64_t n, float s
     // Large buckets: tiles travel through the bulk-copy engine (fused_allreduce_tma.cuh), which keeps
     // an order of magnitude more bytes in flight per SM, so a handful of blocks carries the link.
     const long tma_min = tune.tma_min_bytes.load();
-    if (tma_min >= 0 && bytes >= (size_t)tma_min && (N == 2 || N == 4 || N == 8)) {
+    if (tma_min >= 0 && bytes >= (size_t)tma_min && (N == 2 || N == 4 || N == 8) &&
+        (overlapped || tune.tma_isolated.load() != 0)) {
       const int64_t per = std::max<int64_t>(tune.tma_bytes_per_cta.load(), 64 << 10);
       int64_t cap = std::max<long>(overlapped ? tune.tma_overlap_ctas.load() : tune.tma_ctas.load(), 1);
       cap = std::min<int64_t>(cap, kArenaMaxBlocks);
@@ -301,13 +305,15 @@ Tuning& Tuning::global() {
   static std::once_flag once;
   std::call_once(once, [] {
     t.oneshot_bytes = env_long("BAGUA_B200_ONESHOT_BYTES", -1);
-    t.oneshot_sym_bytes = env_long("BAGUA_B200_ONESHOT_SYM_BYTES", 128 << 10);
+    t.oneshot_sym_bytes = env_long("BAGUA_B200_ONESHOT_SYM_BYTES", -1);
     t.overlap_ctas = env_long("BAGUA_B200_OVERLAP_CTAS", 64);
     t.bytes_per_cta = env_long("BAGUA_B200_BYTES_PER_CTA", 64 << 10);
     t.nvls_overlap_ctas = env_long("BAGUA_B200_NVLS_OVERLAP_CTAS", 64);
     t.coop_overlap_ctas = env_long("BAGUA_B200_COOP_OVERLAP_CTAS", 148);
     t.sym_threads = env_long("BAGUA_B200_SYM_THREADS", 512);
-    t.tma_min_bytes = env_long("BAGUA_B200_TMA_MIN_BYTES", -1);
+    t.ce_min_bytes = env_long("BAGUA_B200_CE_MIN_BYTES", 8 << 20);
+    t.tma_min_bytes = env_long("BAGUA_B200_TMA_MIN_BYTES", 1 << 20);
+    t.tma_isolated = env_long("BAGUA_B200_TMA_ISOLATED", 0);
     t.tma_ctas = env_long("BAGUA_B200_TMA_CTAS", 32);
     t.tma_overlap_ctas = env_long("BAGUA_B200_TMA_OVERLAP_CTAS", 16);
     t.tma_bytes_per_cta = env_long("BAGUA_B200_TMA_BYTES_PER_CTA", 256 << 10);
@@ -323,7 +329,9 @@ bool Tuning::set(const std::string& key, long value) {
   else if (key == "nvls_overlap_ctas") nvls_overlap_ctas = value;
   else if (key == "coop_overlap_ctas") coop_overlap_ctas = value;
   else if (key == "sym_threads") sym_threads = value;
+  else if (key == "ce_min_bytes") ce_min_bytes = value;
   else if (key == "tma_min_bytes") tma_min_bytes = value;
+  else if (key == "tma_isolated") tma_isolated = value;
   else if (key == "tma_ctas") tma_ctas = value;
   else if (key == "tma_overlap_ctas") tma_overlap_ctas = value;
   else if (key == "tma_bytes_per_cta") tma_bytes_per_cta = value;
@@ -339,7 +347,9 @@ std::vector<std::pair<std::string, long>> Tuning::items() const {
           {"nvls_overlap_ctas", nvls_overlap_ctas.load()},
           {"coop_overlap_ctas", coop_overlap_ctas.load()},
           {"sym_threads", sym_threads.load()},
+          {"ce_min_bytes", ce_min_bytes.load()},
           {"tma_min_bytes", tma_min_bytes.load()},
+          {"tma_isolated", tma_isolated.load()},
           {"tma_ctas", tma_ctas.load()},
           {"tma_overlap_ctas", tma_overlap_ctas.load()},
           {"tma_bytes_per_cta", tma_bytes_per_cta.load()}};
@@ -348,6 +358,12 @@ std::vector<std::pair<std::string, long>> Tuning::items() const {
 bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt, float scale, cudaStream_t stream,
                bool overlapped) {
   if (arena.nvls_enabled() && allreduce_nvls(arena, in, out, n, dt, scale, stream, overlapped)) return true;
+  // Large symmetric buckets reduced under backward kernels: the copy engines carry the bytes
+  // (fused_allreduce_ce.cu), the SMs only run two one-block sync kernels and a short reduction.
+  const long ce_min = Tuning::global().ce_min_bytes.load();
+  if (overlapped && ce_min >= 0 && (size_t)n * dtype_bytes(dt) >= (size_t)ce_min &&
+      allreduce_ce(arena, in, out, n, dt, scale, stream))
+    return true;
   switch (dt) {
     case DType::F32: return allreduce_t<float>(arena, in, out, n, scale, stream, overlapped);
     case DType::F16: return allreduce_t<__half>(arena, in, out, n, scale, stream, overlapped);

@@ -358,10 +358,11 @@ def main():
         def e2e_loop_pipelined(n):
             """Same work per step (one host→device copy of the batch, one device→host read of a loss), but
             the copy of batch k+1 runs on a side stream under step k and the loss of step k is read while
-            step k+1 is already queued; all n losses are read before the function returns."""
+            the next three steps are already queued (a host that runs only one step ahead idles the GPU at
+            every hiccup); all n losses are read before the function returns."""
             from bagua_core_b200.utils.prefetch import DevicePrefetcher, LaggedScalarReader
 
-            pf, reader = DevicePrefetcher(device), LaggedScalarReader(device)
+            pf, reader = DevicePrefetcher(device), LaggedScalarReader(device, lag=3)
             pf.put(hx, hy)
             for i in range(n):
                 dx, dy = pf.get()

@@ -89,3 +89,15 @@ def test_prefetcher_and_lagged_reader_on_cpu():
     pf.get()
     with pytest.raises(RuntimeError):
         pf.get()
+
+
+def test_lagged_reader_with_a_deeper_lag_returns_every_value_once_and_in_order():
+    import torch
+
+    from bagua_core_b200.utils.prefetch import LaggedScalarReader
+
+    reader = LaggedScalarReader(torch.device("cpu"), lag=3)
+    got = [reader.push(torch.tensor(float(i))) for i in range(6)]
+    assert got == [None, None, None, 0.0, 1.0, 2.0]
+    assert reader.flush() == 5.0  # 3.0 and 4.0 were read on the way
+    assert reader.flush() is None

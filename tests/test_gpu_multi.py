@@ -99,15 +99,38 @@ def _fused_allreduce(rank, world):
             sym.copy_(allx[rank])
             torch.cuda.synchronize()
             torch.distributed.barrier()
-            before = dict(bb._C.get_tuning())["tma_min_bytes"]
+            before = dict(bb._C.get_tuning())
             bb._C.set_tuning("tma_min_bytes", 1 << 20)
+            bb._C.set_tuning("tma_isolated", 1)
             try:
                 assert comm.fused_allreduce(bt, bt, True)
                 stream.synchronize()
                 comm.check_device_status()
             finally:
-                bb._C.set_tuning("tma_min_bytes", before)
+                bb._C.set_tuning("tma_min_bytes", before["tma_min_bytes"])
+                bb._C.set_tuning("tma_isolated", before["tma_isolated"])
             assert torch.equal(sym, first), dt
+        # ... and with the bytes moved by the copy engines
+        sym.copy_(allx[rank])
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        assert comm.fused_allreduce_ce(bt, bt, True)
+        stream.synchronize()
+        comm.check_device_status()
+        if world in (2, 4, 8):
+            assert torch.equal(sym, first), dt
+        tol = 1e-6 if dt == torch.float32 else 1.6e-2
+        assert torch.allclose(sym.float(), ref, rtol=tol, atol=tol * max(1.0, ref.abs().max().item())), dt
+        # out of place into a second symmetric buffer, sum
+        out2 = comm.alloc_symmetric(n, dt)
+        sym.copy_(allx[rank])
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        assert comm.fused_allreduce_ce(bt, bc.BaguaTensorPy(out2, "o2"), False)
+        stream.synchronize()
+        comm.check_device_status()
+        assert torch.equal(sym, allx[rank])
+        assert torch.allclose(out2.float(), ref * world, rtol=tol, atol=tol * world * max(1.0, ref.abs().max().item())), dt
     # back-to-back ops of different sizes without host sync in between (staging reuse protocol)
     xs = [torch.full((s,), float(rank + 1), device=dev) for s in (1 << 12, 1 << 22, 1 << 14, 1 << 21, 64)]
     torch.cuda.synchronize()
