@@ -269,8 +269,11 @@ bool pair_average_t(PeerArena& arena, const void* in, void* out, int64_t n, int 
   if (bytes % 16 != 0 || (uintptr_t)in % 16 != 0 || (uintptr_t)out % 16 != 0) return false;
   const int grid = pick_grid(arena, bytes);
   void* pin[kArenaMaxRanks];
-  if (bytes > ((size_t)256 << 10) && arena.sym_translate(in, bytes, pin)) {
-    // weights live in the symmetric heap on every rank: read the partner's copy directly
+  const long sym_min = Tuning::global().pair_sym_min_bytes.load();
+  if (sym_min >= 0 && bytes >= (size_t)sym_min && arena.sym_translate(in, bytes, pin)) {
+    // weights live in the symmetric heap on every rank: read the partner's copy directly (one pass over
+    // the link instead of a push plus a local read; its second signalling round makes it the slower
+    // choice for small buckets: 63 vs 55 us at 16 MB, 158 vs 199 us at 64 MB on two GPUs)
     ArenaView v = arena.next_view(grid, 0);
     pair_average_sym_kernel<T><<<grid, kThreads, 0, stream>>>(v, (const uint4*)in, (const uint4*)pin[peer],
                                                                (uint4*)out, (int64_t)(bytes / 16), peer);
@@ -311,6 +314,7 @@ Tuning& Tuning::global() {
     t.nvls_overlap_ctas = env_long("BAGUA_B200_NVLS_OVERLAP_CTAS", 64);
     t.coop_overlap_ctas = env_long("BAGUA_B200_COOP_OVERLAP_CTAS", 148);
     t.sym_threads = env_long("BAGUA_B200_SYM_THREADS", 512);
+    t.pair_sym_min_bytes = env_long("BAGUA_B200_PAIR_SYM_MIN_BYTES", 32 << 20);
     t.ce_min_bytes = env_long("BAGUA_B200_CE_MIN_BYTES", 8 << 20);
     t.tma_min_bytes = env_long("BAGUA_B200_TMA_MIN_BYTES", 1 << 20);
     t.tma_isolated = env_long("BAGUA_B200_TMA_ISOLATED", 0);
@@ -329,6 +333,7 @@ bool Tuning::set(const std::string& key, long value) {
   else if (key == "nvls_overlap_ctas") nvls_overlap_ctas = value;
   else if (key == "coop_overlap_ctas") coop_overlap_ctas = value;
   else if (key == "sym_threads") sym_threads = value;
+  else if (key == "pair_sym_min_bytes") pair_sym_min_bytes = value;
   else if (key == "ce_min_bytes") ce_min_bytes = value;
   else if (key == "tma_min_bytes") tma_min_bytes = value;
   else if (key == "tma_isolated") tma_isolated = value;
@@ -347,6 +352,7 @@ std::vector<std::pair<std::string, long>> Tuning::items() const {
           {"nvls_overlap_ctas", nvls_overlap_ctas.load()},
           {"coop_overlap_ctas", coop_overlap_ctas.load()},
           {"sym_threads", sym_threads.load()},
+          {"pair_sym_min_bytes", pair_sym_min_bytes.load()},
           {"ce_min_bytes", ce_min_bytes.load()},
           {"tma_min_bytes", tma_min_bytes.load()},
           {"tma_isolated", tma_isolated.load()},

@@ -431,7 +431,8 @@ def _sym_pair(rank, world):
     assert comm.fused_available()
     comm.set_device_wait_ms(20000.0)
     backend = bc.BaguaCommBackendPy(10, rank)
-    n = 16 * world * 8209  # > 256 KiB so that the direct-load kernel is chosen
+    bb._C.set_tuning("pair_sym_min_bytes", 256 << 10)  # so that this bucket takes the direct-load kernel
+    n = 16 * world * 8209
     x = comm.alloc_symmetric(n, torch.float32)
     assert x is not None and comm.is_symmetric(x)
     g = torch.Generator().manual_seed(40 + rank)
