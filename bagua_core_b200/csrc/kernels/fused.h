@@ -38,7 +38,7 @@ struct Tuning {
   std::atomic<long> overlap_ctas{64};          // CTA budget of a bucket reduced under backward kernels
   std::atomic<long> bytes_per_cta{64 << 10};   // payload per CTA below the budget
   std::atomic<long> nvls_overlap_ctas{64};     // the overlap budget of the multimem all-reduce
-  std::atomic<long> coop_overlap_ctas{148};    // the overlap budget of the cooperative ByteGrad kernel
+  std::atomic<long> coop_overlap_ctas{32};     // the overlap budget of the cooperative ByteGrad kernel
   std::atomic<long> sym_threads{512};          // threads per block of the symmetric all-reduce (128, 256 or 512)
   std::atomic<long> pair_sym_min_bytes{32 << 20};  // pair average: direct peer loads from this size on (-1: never)
   // symmetric buckets of at least this size, reduced under backward kernels, are moved by the copy

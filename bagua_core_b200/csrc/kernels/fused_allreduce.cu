@@ -312,7 +312,7 @@ Tuning& Tuning::global() {
     t.overlap_ctas = env_long("BAGUA_B200_OVERLAP_CTAS", 64);
     t.bytes_per_cta = env_long("BAGUA_B200_BYTES_PER_CTA", 64 << 10);
     t.nvls_overlap_ctas = env_long("BAGUA_B200_NVLS_OVERLAP_CTAS", 64);
-    t.coop_overlap_ctas = env_long("BAGUA_B200_COOP_OVERLAP_CTAS", 148);
+    t.coop_overlap_ctas = env_long("BAGUA_B200_COOP_OVERLAP_CTAS", 32);
     t.sym_threads = env_long("BAGUA_B200_SYM_THREADS", 512);
     t.pair_sym_min_bytes = env_long("BAGUA_B200_PAIR_SYM_MIN_BYTES", 32 << 20);
     t.ce_min_bytes = env_long("BAGUA_B200_CE_MIN_BYTES", 8 << 20);

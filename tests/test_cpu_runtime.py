@@ -406,3 +406,29 @@ def test_show_version_runs(capfd):
     bc.show_version()
     err = capfd.readouterr().err
     assert "NCCL version" in err and "bagua-core-b200" in err
+
+
+def test_tuning_values_can_be_read_and_set_and_unknown_keys_are_refused():
+    import bagua_core_b200 as bb
+
+    before = dict(bb._C.get_tuning())
+    for key in ("oneshot_bytes", "oneshot_sym_bytes", "overlap_ctas", "ce_min_bytes", "tma_min_bytes",
+                "tma_overlap_ctas", "coop_overlap_ctas", "pair_sym_min_bytes"):
+        assert key in before
+    bb._C.set_tuning("overlap_ctas", 24)
+    assert dict(bb._C.get_tuning())["overlap_ctas"] == 24
+    bb._C.set_tuning("overlap_ctas", before["overlap_ctas"])
+    with pytest.raises(RuntimeError, match="unknown tuning key"):
+        bb._C.set_tuning("no_such_knob", 1)
+
+
+def test_bucket_time_line_is_empty_on_the_host_backend():
+    """Device time stamps exist only for GPU buckets; on host memory the switch is accepted and nothing is recorded."""
+    import bagua_core_b200 as bb
+
+    bb._C.set_bucket_timing(True)
+    try:
+        assert bb._C.bucket_timing()
+        assert bb._C.timeline_collect() == []
+    finally:
+        bb._C.set_bucket_timing(False)

@@ -308,3 +308,44 @@ def test_a_bucket_of_scattered_tensors_is_staged_with_the_copy_kernel():
     assert bb._C.stats()["staged_copies"] == staged0 + 2
     assert torch.equal(backing, before)
     backend.close()
+
+
+def test_bucket_time_line_records_one_span_per_bucket_and_the_marks():
+    """Two device events bracket each bucket's work on the communication stream; marks can be dropped on any
+    stream; times are relative to the first recorded event and ordered like the stream."""
+    import bagua_core as bc
+    import bagua_core_b200 as bb
+
+    torch.cuda.set_device(0)
+    x = torch.ones(1 << 20, device="cuda")
+    y = torch.ones(1 << 10, device="cuda")
+    tx, ty = bc.BaguaTensorPy(x, "x"), bc.BaguaTensorPy(y, "y")
+    stream = torch.cuda.Stream()
+    comm = bc.BaguaSingleCommunicatorPy(0, 1, 0, stream.cuda_stream, bc.BaguaSingleCommunicatorPy.generate_nccl_unique_id_str())
+    buckets = [bc.BaguaBucketPy("first", [tx]), bc.BaguaBucketPy("second", [ty])]
+    for b in buckets:
+        b.append_centralized_synchronous_op(comm, None, hierarchical=False, average=True)
+    backend = bc.BaguaCommBackendPy(4, 0)
+    backend.register_ordered_buckets(buckets)
+    bb._C.timeline_collect()
+    bb._C.set_bucket_timing(True)
+    try:
+        bb._C.timeline_mark("begin", torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        backend.mark_communication_ready(tx, 0)
+        backend.mark_communication_ready(ty, 0)
+        assert backend.wait_pending_comm_ops() == 2
+        stream.synchronize()
+        bb._C.timeline_mark("end", stream.cuda_stream)
+    finally:
+        bb._C.set_bucket_timing(False)
+    spans = bb._C.timeline_collect()
+    assert [(s["name"], s["kind"]) for s in spans] == [("begin", "mark"), ("first", "bucket"), ("second", "bucket"),
+                                                      ("end", "mark")]
+    assert spans[0]["start_ms"] == 0.0
+    assert spans[1]["bytes"] == 4 << 20 and spans[2]["bytes"] == 4 << 10
+    for s in spans:
+        assert s["end_ms"] >= s["start_ms"] >= 0.0
+    assert spans[1]["end_ms"] <= spans[2]["start_ms"] + 1e-3 and spans[2]["end_ms"] <= spans[3]["start_ms"] + 1e-3
+    assert bb._C.timeline_collect() == []
+    backend.close()
