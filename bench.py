@@ -331,6 +331,18 @@ def main():
     launches = block_launches[pick]
     value = world * batch * args.steps / (ms / 1e3)
 
+    # How long the launching thread needs to ISSUE one step (queue empty, nothing to wait for): when this
+    # approaches ms_per_step the loop is bound by the host, not by the GPU.
+    host_issue = []
+    for _ in range(5):
+        barrier()
+        t_h = time.perf_counter()
+        step(x, y)
+        host_issue.append((time.perf_counter() - t_h) * 1e3)
+    barrier()
+    host_issue.sort()
+    host_issue_ms = host_issue[len(host_issue) // 2]
+
     # ---- optional: device time line of the buckets' communication ------------------------
     timeline = None
     if args.timeline and on_gpu and args.impl != "ddp":
@@ -439,6 +451,7 @@ def main():
             "e2e": e2e,
             "gpu_launches": launches,
             "timed_blocks": {"n": len(block_ms), "reported": "median", "ms_per_step": [m / args.steps for m in block_ms]},
+            "host_issue_ms_per_step": host_issue_ms,
         }
         if timeline is not None:
             line["bucket_timeline"] = timeline
