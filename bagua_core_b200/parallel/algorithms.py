@@ -356,7 +356,14 @@ class QAdamAlgorithm(Algorithm):
 class AsyncModelAverageAlgorithm(_WeightAlgorithm):
     """Asynchronous model averaging: a background thread all-reduces the weights every
     `sync_interval_ms` while training continues; the delta is applied with atomics.
-    `abort(bm)` stops it (e.g. before evaluation), `resume(bm)` restarts it."""
+    `abort(bm)` stops it (e.g. before evaluation), `resume(bm)` restarts it.
+
+    Every rank's thread runs on its own timer, but an averaging round is a collective: before each
+    round the threads agree (one small host all-reduce on a control group of their own) whether any
+    rank has asked to stop.  If one has, no rank starts the round and every rank's thread ends, so a
+    rank that stops first never leaves its peers waiting inside a round for it.  `abort` is therefore
+    collective in effect (the first rank to call it stops averaging everywhere), and `resume` must be
+    called on every rank."""
 
     def __init__(self, peer_selection_mode: str = "all", sync_interval_ms: int = 500, warmup_steps: int = 0):
         assert peer_selection_mode == "all"
@@ -366,12 +373,18 @@ class AsyncModelAverageAlgorithm(_WeightAlgorithm):
         self._thread = None
         self._stop = threading.Event()
         self._lock = threading.Lock()
+        self._ctl_group = None  # host-side group on which the threads agree to go on or to stop
         self.rounds = 0
 
     def tensors_to_buckets(self, bm, tensors):
         return [list(tensors)]  # one bucket: the whole model is averaged at once
 
     def init_operations(self, bm, bucket):
+        import torch.distributed as dist
+
+        if self._ctl_group is None and bm.pg.world_size > 1:
+            # collective: every rank builds its buckets at the same point of `with_bagua`
+            self._ctl_group = dist.new_group(backend="gloo")
         bucket.clear_ops()
         if bm.bagua_train_step_counter < self.warmup_steps:
             bucket.append_centralized_synchronous_op(bm.pg, hierarchical=False, average=True)
@@ -400,9 +413,19 @@ class AsyncModelAverageAlgorithm(_WeightAlgorithm):
     def _loop(self, bm):
         if bm.pg.is_cuda:
             torch.cuda.set_device(bm.pg.device)
-        while not self._stop.wait(self.sync_interval_ms / 1000.0):
+        import torch.distributed as dist
+
+        while True:
+            self._stop.wait(self.sync_interval_ms / 1000.0)
             with self._lock:
-                if self._stop.is_set():
+                if self._ctl_group is not None:
+                    # does any rank want to stop?  All ranks get the same answer, so all go on or all leave.
+                    flag = torch.tensor([1 if self._stop.is_set() else 0], dtype=torch.int32)
+                    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self._ctl_group)
+                    if int(flag.item()):
+                        self._stop.set()
+                        break
+                elif self._stop.is_set():
                     break
                 for b in bm.bagua_buckets:
                     for t in b.tensors:
@@ -416,12 +439,17 @@ class AsyncModelAverageAlgorithm(_WeightAlgorithm):
         self._thread.start()
 
     def abort(self, bm):
-        """Stop averaging; returns once no averaging round is in flight."""
+        """Stop averaging; returns once no averaging round is in flight on this rank.  The other ranks'
+        threads learn of it at their next round and stop as well."""
         self._stop.set()
         if self._thread is not None:
             self._thread.join()
             self._thread = None
 
     def resume(self, bm):
+        """Restart averaging; call it on every rank."""
+        if self._thread is not None and not self._thread.is_alive():
+            self._thread.join()
+            self._thread = None
         if self._thread is None:
             self._start(bm)

@@ -263,6 +263,8 @@ def main():
             bb._C.set_tuning(k, int(v))
         if args.comm_ctas > 0 and on_gpu and world > 1:
             pg.global_comm.set_comm_ctas(args.comm_ctas, 0)
+        if on_gpu and world > 1 and args.impl == "ours":
+            _check_allreduce_paths(bb, pg, device, rank, world)
         if algo_name == "qadam":
             opt = P.QAdamOptimizer(model.parameters(), lr=1e-4, warmup_steps=2)
             algo = P.QAdamAlgorithm(opt)
@@ -463,6 +465,53 @@ def main():
     if dist.is_initialized():
         dist.destroy_process_group()
     return 0
+
+
+def _check_allreduce_paths(bb, pg, device, rank, world):
+    """Before anything is timed: one 16 MB all-reduce through the copy-engine path and one through the
+    bulk-copy kernel, checked against the known answer.  A path that gives a wrong result on this machine is
+    switched off on every rank (the load/store kernels then serve its sizes) and the fact is printed."""
+    import torch
+    import torch.distributed as dist
+
+    from bagua_core_b200 import BaguaTensorPy
+
+    comm = pg.global_comm
+    if not comm.fused_available():
+        return
+    n = 4 << 20
+    buf = comm.alloc_symmetric(n, torch.float32)
+    if buf is None:
+        return
+    want = (world + 1) / 2.0
+    bt = BaguaTensorPy(buf, "bench_path_check")
+    before = dict(bb._C.get_tuning())
+    bad = {"ce_min_bytes": 0, "tma_min_bytes": 0}
+    for key in bad:
+        buf.fill_(float(rank + 1))
+        torch.cuda.synchronize()
+        dist.barrier()
+        try:
+            if key == "ce_min_bytes":
+                ok = comm.fused_allreduce_ce(bt, bt, True)
+            else:
+                bb._C.set_tuning("tma_min_bytes", 1 << 20)
+                bb._C.set_tuning("tma_isolated", 1)
+                ok = comm.fused_allreduce(bt, bt, True) if world in (2, 4, 8) else True
+            pg.comm_stream.synchronize()
+            if ok and not bool(torch.all(buf == want).item()) and (key == "ce_min_bytes" or world in (2, 4, 8)):
+                bad[key] = 1
+        finally:
+            bb._C.set_tuning("tma_min_bytes", before["tma_min_bytes"])
+            bb._C.set_tuning("tma_isolated", before["tma_isolated"])
+    flags = torch.tensor([bad["ce_min_bytes"], bad["tma_min_bytes"]], device=device, dtype=torch.int32)
+    dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    for key, flag in zip(("ce_min_bytes", "tma_min_bytes"), flags.tolist()):
+        if flag:
+            bb._C.set_tuning(key, -1)
+            if rank == 0:
+                print(f"[bench] the all-reduce path behind `{key}` gave a wrong result in the start-up check; "
+                      "switched off", file=sys.stderr)
 
 
 def bucket_timeline(bb, step, x, y, barrier, steps=4):
