@@ -43,6 +43,44 @@ def test_async_model_average_converges_replicas():
     assert torch.allclose(a, b, atol=1e-5)
 
 
+def _async_uneven_stop(rank, world):
+    """Rank 0 stops averaging early and keeps training; the other ranks go on for a while.  Nobody may be
+    left waiting inside a round for the rank that stopped: the threads agree before every round."""
+    import bagua_core_b200.parallel as P
+    from bagua_core_b200.models import MLP
+
+    torch.manual_seed(7)
+    model = MLP(8, 16, 4, depth=2)
+    pg = P.init_process_group(torch.device("cpu"))
+    pg.backend.set_watchdog_timeout(20.0)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01)
+    algo = P.AsyncModelAverageAlgorithm(sync_interval_ms=10)
+    bm = P.with_bagua(model, [opt], algo)
+    x, y = torch.randn(4, 8), torch.randn(4, 4)
+    t0 = time.time()
+    for step in range(30 if rank == 0 else 120):
+        opt.zero_grad(set_to_none=False)
+        torch.nn.functional.mse_loss(bm(x), y).backward()
+        opt.step()
+        time.sleep(0.005)
+        if rank == 0 and step == 10:
+            algo.abort(bm)  # the other ranks' threads end at their next round
+    algo.abort(bm)
+    alive = algo._thread is not None
+    elapsed = time.time() - t0
+    rounds = algo.rounds
+    P.destroy_process_group()
+    return rounds, alive, elapsed
+
+
+def test_async_model_average_stops_everywhere_when_one_rank_stops():
+    res = run_ranks(_async_uneven_stop, 3, timeout=120)
+    rounds = [r[0] for r in res]
+    assert len(set(rounds)) == 1, rounds  # every rank ran exactly the rounds all of them agreed on
+    assert not any(r[1] for r in res)
+    assert all(r[2] < 60 for r in res)
+
+
 def _state_and_nosync(rank, world):
     import bagua_core_b200.parallel as P
     from bagua_core_b200.models import MLP
