@@ -65,7 +65,7 @@ void SingleCommunicator::abort() {
 
 void SingleCommunicator::check_all_device_status() {
   std::lock_guard<std::mutex> g(g_comms_mu);
-  for (SingleCommunicator* c : g_comms) c->check_device_status();
+  for (SingleCommunicator* c : g_comms) c->check_device_status(/*try_only=*/true);
 }
 
 void SingleCommunicator::check_live() const {
@@ -108,8 +108,15 @@ float p2p_scale(ReductionOp op, int nranks) {
 }
 }  // namespace
 
-void SingleCommunicator::check_device_status() {
-  std::lock_guard<std::mutex> g(arena_mu_);
+void SingleCommunicator::check_device_status(bool try_only) {
+  // try_only: a communicator whose arena is being set up right now (a collective that may take a
+  // while) is skipped instead of waited for; its record is looked at by the next check
+  std::unique_lock<std::mutex> g(arena_mu_, std::defer_lock);
+  if (try_only) {
+    if (!g.try_lock()) return;
+  } else {
+    g.lock();
+  }
   if (!arena_) return;
   DeviceStatus s = arena_->read_status();
   if (s.code == 0) return;

@@ -79,7 +79,7 @@ class SingleCommunicator {
   // Throws CommunicatorError if a fused kernel reported a device-side wait that ran out; the
   // communicator is marked aborted and the record is cleared, so the error is raised once and
   // every later use fails with "communicator was aborted".  A plain load of host-mapped memory.
-  void check_device_status();
+  void check_device_status(bool try_only = false);
   // The same for every live communicator of this process (what `wait_pending_comm_ops` calls).
   static void check_all_device_status();
   // Peer-memory kernels for the collectives above (all-reduce / reduce / reduce-scatter with SUM or

@@ -11,7 +11,7 @@
 
 namespace bagua {
 PeerArena* SingleCommunicator::arena() { UNREACHABLE(); }
-void SingleCommunicator::check_device_status() { UNREACHABLE(); }
+void SingleCommunicator::check_device_status(bool) { UNREACHABLE(); }
 void SingleCommunicator::check_all_device_status() {}  // host-only backends never reach it; harmless if they do
 void SingleCommunicator::allreduce(const RawTensor&, RawTensor&, ReductionOp) { UNREACHABLE(); }
 void SingleCommunicator::allreduce_inplace(RawTensor&, ReductionOp, bool) { UNREACHABLE(); }
