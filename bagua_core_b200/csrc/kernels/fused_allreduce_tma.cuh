@@ -24,6 +24,10 @@
 // when one gives up, the block stops issuing, waits (bounded again) for the loads it still has
 // in flight into its shared memory, waits for its stores, and leaves through cta_finish_op.
 //
+// The same body compiles for the host (BAGUA_HOST_EMULATION), with the copies and mbarriers
+// replaced by stand-ins that keep their counting rules, to run under the thread and address
+// sanitizers (tests/cpp/device_emulation.cc).
+//
 // The reference has no counterpart: its all-reduce is one NCCL call
 // (bagua-core-internal/src/comm_ops/centralized_full_precision_synchronous.rs:16-55).
 #pragma once
@@ -38,19 +42,35 @@ namespace bagua {
 namespace fused {
 namespace allreduce_bodies {
 
+#ifndef BAGUA_HOST_EMULATION
 constexpr int kTmaThreads = 256;
 constexpr int kTmaStageInBytes = 32 << 10;  // input of one stage: NR tiles of 32 KB / NR
+constexpr int kTmaRingBytes = 216 << 10;    // 2 ranks: 4 stages, 4 ranks: 5, 8 ranks: 6
+constexpr int kTmaMbarBytes = 8;
+#else
+// On the host the same body runs with one thread per CUDA thread of a one-warp block and a
+// ring small enough that the few hundred bytes of a test wrap it several times.
+constexpr int kTmaThreads = 32;
+constexpr int kTmaStageInBytes = 256;
+constexpr int kTmaRingBytes = 3 * (256 + 128);
+constexpr int kTmaMbarBytes = 16;  // the host's stand-in for an mbarrier, see tma::HostMbar
+#endif
 
 template <int NR>
 struct TmaCfg {
   static constexpr int kTileVecs = kTmaStageInBytes / 16 / NR;            // vectors per source tile
   static constexpr int kStageBytes = kTmaStageInBytes + kTileVecs * 16;   // N input tiles + one output tile
-  static constexpr int kStages = (216 << 10) / kStageBytes;               // 2 ranks: 4, 4 ranks: 5, 8 ranks: 6
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStages * 8;  // + one mbarrier per stage
+  static constexpr int kStages = kTmaRingBytes / kStageBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStages * kTmaMbarBytes;  // + one mbarrier per stage
 };
 
 #ifndef BAGUA_HOST_EMULATION
 namespace tma {
+
+using saddr_t = uint32_t;  // an address in this block's shared memory
+using bar_t = uint32_t;    // the shared-memory address of an mbarrier
+__device__ __forceinline__ bar_t bar_at(unsigned char* bars, int s) { return (uint32_t)__cvta_generic_to_shared(bars) + (uint32_t)(kTmaMbarBytes * s); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -92,8 +112,78 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+}  // namespace tma
+#else  // BAGUA_HOST_EMULATION
+// The host's bulk-copy engine: a copy is done by the thread that issues it, at once, and then
+// counted on the stage's barrier.  The barrier keeps the device's rules (one pending arrival per
+// phase, a transaction count in bytes that may go negative before the arrival arms it, a phase
+// that completes when both reach zero), so a body that arms too little, waits on the wrong
+// parity or reuses a stage too early stalls or trips the sanitizers here as well.
+namespace tma {
+
+struct HostMbar {
+  uint32_t lock;     // spin lock (acquire / release), so the sanitizers see the hand-over
+  uint32_t phase;    // completed phases
+  int32_t pending;   // arrivals the current phase still waits for
+  int32_t tx;        // bytes the current phase still waits for
+};
+static_assert(sizeof(HostMbar) == kTmaMbarBytes, "size of the emulated mbarrier");
+using saddr_t = unsigned char*;
+using bar_t = HostMbar*;
+
+inline bar_t bar_at(unsigned char* bars, int s) { return reinterpret_cast<HostMbar*>(bars) + s; }
+inline saddr_t smem_addr(const void* p) { return static_cast<unsigned char*>(const_cast<void*>(p)); }
+inline void mbar_lock(bar_t b) {
+  while (__atomic_exchange_n(&b->lock, 1u, __ATOMIC_ACQUIRE) != 0) sched_yield();
+}
+inline void mbar_unlock(bar_t b) { __atomic_store_n(&b->lock, 0u, __ATOMIC_RELEASE); }
+inline void mbar_settle(bar_t b, int32_t count) {  // under the lock
+  if (b->pending == 0 && b->tx == 0) {
+    b->phase += 1;
+    b->pending = count;
+  }
+}
+inline void mbar_init(bar_t b, uint32_t count) {
+  b->phase = 0;
+  b->pending = (int32_t)count;
+  b->tx = 0;
+  __atomic_store_n(&b->lock, 0u, __ATOMIC_RELEASE);
+}
+inline void fence_mbar_init() {}
+inline void mbar_expect_tx(bar_t b, uint32_t bytes) {
+  mbar_lock(b);
+  b->tx += (int32_t)bytes;
+  b->pending -= 1;
+  mbar_settle(b, 1);
+  mbar_unlock(b);
+}
+inline bool mbar_try_wait(bar_t b, uint32_t parity) {
+  mbar_lock(b);
+  const bool done = (b->phase & 1u) != parity;
+  mbar_unlock(b);
+  return done;
+}
+inline void bulk_load(saddr_t dst, const void* src, uint32_t bytes, bar_t b) {
+  std::memcpy(dst, src, bytes);
+  mbar_lock(b);
+  b->tx -= (int32_t)bytes;
+  mbar_settle(b, 1);
+  mbar_unlock(b);
+}
+inline void bulk_store(void* dst, saddr_t src, uint32_t bytes) { std::memcpy(dst, src, bytes); }
+inline void bulk_commit() {}
+template <int N>
+inline void bulk_wait_read() {}
+inline void bulk_wait_all() {}
+inline void fence_proxy_async() {}
+inline void fence_proxy_async_smem() {}
+
+}  // namespace tma
+#endif
+
+namespace tma {
 // One thread waits for phase `parity` of `bar`; bounded like every other wait.  Status code 5.
-__device__ __forceinline__ bool mbar_wait(const ArenaView& v, const Launch& L, uint32_t bar, uint32_t parity,
+__device__ __forceinline__ bool mbar_wait(const ArenaView& v, const Launch& L, bar_t bar, uint32_t parity,
                                           uint32_t stage) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint32_t* poison = v.signals[v.rank] + kSigPoison;
@@ -128,18 +218,21 @@ __device__ __forceinline__ void allreduce_sym_tma_body(const ArenaView& v, const
 
   uint4* in_s = reinterpret_cast<uint4*>(smem);                                     // [S][NR][TV]
   uint4* out_s = reinterpret_cast<uint4*>(smem + (size_t)S * kTmaStageInBytes);      // [S][TV]
-  const uint32_t bar0 = tma::smem_addr(smem + (size_t)S * C::kStageBytes);           // [S] mbarriers
-  const uint32_t in0 = tma::smem_addr(in_s), out0 = tma::smem_addr(out_s);
+  unsigned char* bars = smem + (size_t)S * C::kStageBytes;                          // [S] mbarriers
+  const tma::saddr_t in0 = tma::smem_addr(in_s), out0 = tma::smem_addr(out_s);
 
   if (tid == 0) {
-    for (int s = 0; s < S; ++s) tma::mbar_init(bar0 + 8 * s, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int s = 0; s < S; ++s) tma::mbar_init(tma::bar_at(bars, s), 1);
+    tma::fence_mbar_init();
   }
   // first signal: every peer's block b has started, i.e. that peer's input is final
   psync::cta_signal_phase(v, L, 0, all_peers_mask(v));
   bool ok = psync::cta_wait_phase(v, L, 0, all_peers_mask(v));
 
-  auto tile_vecs = [&](int64_t k) { return (int)min((int64_t)TV, hi - (lo + k * TV)); };
+  auto tile_vecs = [&](int64_t k) {
+    const int64_t left = hi - (lo + k * TV);
+    return (int)(left < TV ? left : TV);
+  };
   // Lanes 0 .. NR-1 of warp 0 are the issuers: lane r moves rank r's tiles (its loads and the
   // stores into rank r's output form that lane's own bulk async-groups), so the NR copies of a
   // tile are issued side by side instead of one after the other.  Lane 0 also arms the stage's
@@ -148,8 +241,8 @@ __device__ __forceinline__ void allreduce_sym_tma_body(const ArenaView& v, const
   auto issue_load = [&](int64_t k) {  // issuers
     const int s = (int)(k % S);
     const uint32_t bytes = (uint32_t)tile_vecs(k) * 16u;
-    if (tid == 0) tma::mbar_expect_tx(bar0 + 8 * s, bytes * NR);
-    tma::bulk_load(in0 + (uint32_t)((s * NR + tid) * TV) * 16u, p.in[tid] + lo + k * TV, bytes, bar0 + 8 * s);
+    if (tid == 0) tma::mbar_expect_tx(tma::bar_at(bars, s), bytes * NR);
+    tma::bulk_load(in0 + (uint32_t)((s * NR + tid) * TV) * 16u, p.in[tid] + lo + k * TV, bytes, tma::bar_at(bars, s));
   };
 
   int64_t issued = 0;  // tiles whose loads have been issued (the same in every issuer)
@@ -162,7 +255,7 @@ __device__ __forceinline__ void allreduce_sym_tma_body(const ArenaView& v, const
     for (; k < ntiles; ++k) {
       const int s = (int)(k % S);
       // everyone waits for the stage: the mbarrier's completion is what makes the copied bytes visible
-      bool got = tma::mbar_wait(v, L, bar0 + 8 * s, (uint32_t)((k / S) & 1), (uint32_t)s);
+      bool got = tma::mbar_wait(v, L, tma::bar_at(bars, s), (uint32_t)((k / S) & 1), (uint32_t)s);
       // the stores that last read out_s[s] (tile k - S) must have left shared memory
       if (issuer && k >= S) tma::bulk_wait_read<S - 1>();
       if (!__syncthreads_and(got)) {
@@ -194,7 +287,7 @@ __device__ __forceinline__ void allreduce_sym_tma_body(const ArenaView& v, const
   if (!ok) {
     if (tid == 0)  // lane 0 issued as many tiles as every other issuer
       for (int64_t q = k; q < issued; ++q)
-        tma::mbar_wait(v, L, bar0 + 8 * (int)(q % S), (uint32_t)((q / S) & 1), (uint32_t)(q % S));
+        tma::mbar_wait(v, L, tma::bar_at(bars, (int)(q % S)), (uint32_t)((q / S) & 1), (uint32_t)(q % S));
     __syncthreads();
   }
   if (issuer) {
@@ -208,7 +301,6 @@ __device__ __forceinline__ void allreduce_sym_tma_body(const ArenaView& v, const
   }
   psync::cta_finish_op(v, L);
 }
-#endif  // !BAGUA_HOST_EMULATION
 
 }  // namespace allreduce_bodies
 }  // namespace fused

@@ -26,6 +26,7 @@
 #include <cmath>
 
 #include "kernels/fused_allreduce_bodies.cuh"
+#include "kernels/fused_allreduce_tma.cuh"
 #include "kernels/fused_bytegrad_body.cuh"
 #include "kernels/fused_collectives_bodies.cuh"
 #include "kernels/fused_gossip_body.cuh"
@@ -60,6 +61,7 @@ enum class Kind {
   AllReduceTwoShot,
   AllReduceTwoShotInPlace,
   AllReduceSym,
+  AllReduceSymTma,
   PairAverage,
   PairAverageSym,
   ByteGrad,
@@ -221,6 +223,7 @@ void prepare(World& w, int me, uint32_t k) {
     case Kind::AllReduceOneShot:
     case Kind::AllReduceTwoShot:
     case Kind::AllReduceSym:
+    case Kind::AllReduceSymTma:
     case Kind::PairAverage:
     case Kind::PairAverageSym: fill(r.in, k, me, op.vecs); break;
     case Kind::AllReduceTwoShotInPlace:
@@ -290,6 +293,25 @@ void run_body(World& w, int me, int b, uint32_t k) {
         p.out[q] = outs.p[q];
       }
       allreduce_sym_body<float>(v, L, p, c, op.scale);
+      break;
+    }
+    case Kind::AllReduceSymTma: {
+      // the bulk-copy variant exists for 2, 4 and 8 ranks; other worlds take the load/store body,
+      // as the dispatch does
+      SymPtrs p;
+      for (int q = 0; q < kArenaMaxRanks; ++q) {
+        p.in[q] = ins.p[q];
+        p.out[q] = outs.p[q];
+      }
+      constexpr int kSlot = 12;  // the block's dynamic shared memory
+      if (w.N == 2)
+        allreduce_sym_tma_body<float, 2>(v, L, p, c, op.scale, hostemu::shared_array<unsigned char>(kSlot, TmaCfg<2>::kSmemBytes));
+      else if (w.N == 4)
+        allreduce_sym_tma_body<float, 4>(v, L, p, c, op.scale, hostemu::shared_array<unsigned char>(kSlot, TmaCfg<4>::kSmemBytes));
+      else if (w.N == 8)
+        allreduce_sym_tma_body<float, 8>(v, L, p, c, op.scale, hostemu::shared_array<unsigned char>(kSlot, TmaCfg<8>::kSmemBytes));
+      else
+        allreduce_sym_body<float>(v, L, p, c, op.scale);
       break;
     }
     case Kind::PairAverage: pair_average_body<float>(v, L, in, out, c, me ^ 1); break;
@@ -423,6 +445,7 @@ uint64_t verify(World& w, int me, uint32_t k) {
     case Kind::AllReduceTwoShot:
     case Kind::AllReduceTwoShotInPlace:
     case Kind::AllReduceSym:
+    case Kind::AllReduceSymTma:
     case Kind::AllReduceNvls:
       for (int64_t i = 0; i < c; ++i) {
         sum4(i, op.scale, e);
@@ -519,6 +542,7 @@ uint64_t verify(World& w, int me, uint32_t k) {
     case Kind::AllReduceOneShot:
     case Kind::AllReduceTwoShot:
     case Kind::AllReduceSym:
+    case Kind::AllReduceSymTma:
     case Kind::PairAverage:
     case Kind::PairAverageSym: out_extent = c, in_extent = c; break;
     case Kind::AllReduceTwoShotInPlace:
@@ -571,6 +595,7 @@ int main(int argc, char** argv) {
     if ((op.kind == Kind::PairAverage || op.kind == Kind::PairAverageSym) && w.N % 2) op.kind = Kind::Barrier;  // pairs need an even world
     op.vecs = 1 + (int64_t)(rng() % 40);
     if (op.kind == Kind::ByteGrad || op.kind == Kind::LpRing) op.vecs = 4 * (1 + (int64_t)(rng() % 10));  // 16-element groups
+    if (op.kind == Kind::AllReduceSymTma) op.vecs = 1 + (int64_t)(rng() % 400);  // many tiles: the stage ring wraps
     if (g_a2av_mismatch) op.kind = Kind::AllToAllV;
     if (op.kind == Kind::AllToAllV) op.vecs = kA2avMaxUnits;  // sizes the buffers; the op's own sizes come from a2av_bytes
     op.root = (int)(rng() % (uint32_t)w.N);
