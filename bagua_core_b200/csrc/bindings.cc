@@ -472,7 +472,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("key"), py::arg("value"),
       "Size thresholds and CTA budgets of the fused kernels (keys: oneshot_bytes, oneshot_sym_bytes, overlap_ctas, "
-      "nvls_overlap_ctas, coop_overlap_ctas, bytes_per_cta, sym_threads, pair_sym_min_bytes, ce_min_bytes, tma_min_bytes, tma_isolated, tma_ctas, "
+      "nvls_overlap_ctas, coop_overlap_ctas, bytes_per_cta, sym_threads, pair_sym_min_bytes, ce_min_bytes, ce_min_chunk_bytes, tma_min_bytes, tma_isolated, tma_ctas, "
       "tma_overlap_ctas, tma_bytes_per_cta; defaults from BAGUA_B200_<KEY>).  Must be set identically on every rank.");
   m.def("get_tuning", []() {
     py::dict d;

@@ -44,6 +44,10 @@ struct Tuning {
   // symmetric buckets of at least this size, reduced under backward kernels, are moved by the copy
   // engines (allreduce_ce); -1: never
   std::atomic<long> ce_min_bytes{8 << 20};
+  // ... and only when the chunk that travels between two ranks (size / ranks) is at least this large:
+  // the path queues 2 (ranks - 1) copies per bucket, and below this size their issue cost on the
+  // launching thread outweighs the SMs saved
+  std::atomic<long> ce_min_chunk_bytes{2 << 20};
   // symmetric buffers of at least this size take the bulk-copy (TMA) all-reduce; -1: never
   std::atomic<long> tma_min_bytes{1 << 20};
   // 0: only buckets reduced under backward kernels take it (with the GPU to itself the load/store kernel

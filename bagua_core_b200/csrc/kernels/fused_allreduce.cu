@@ -316,6 +316,7 @@ Tuning& Tuning::global() {
     t.sym_threads = env_long("BAGUA_B200_SYM_THREADS", 512);
     t.pair_sym_min_bytes = env_long("BAGUA_B200_PAIR_SYM_MIN_BYTES", 32 << 20);
     t.ce_min_bytes = env_long("BAGUA_B200_CE_MIN_BYTES", 8 << 20);
+    t.ce_min_chunk_bytes = env_long("BAGUA_B200_CE_MIN_CHUNK_BYTES", 2 << 20);
     t.tma_min_bytes = env_long("BAGUA_B200_TMA_MIN_BYTES", 1 << 20);
     t.tma_isolated = env_long("BAGUA_B200_TMA_ISOLATED", 0);
     t.tma_ctas = env_long("BAGUA_B200_TMA_CTAS", 32);
@@ -335,6 +336,7 @@ bool Tuning::set(const std::string& key, long value) {
   else if (key == "sym_threads") sym_threads = value;
   else if (key == "pair_sym_min_bytes") pair_sym_min_bytes = value;
   else if (key == "ce_min_bytes") ce_min_bytes = value;
+  else if (key == "ce_min_chunk_bytes") ce_min_chunk_bytes = value;
   else if (key == "tma_min_bytes") tma_min_bytes = value;
   else if (key == "tma_isolated") tma_isolated = value;
   else if (key == "tma_ctas") tma_ctas = value;
@@ -354,6 +356,7 @@ std::vector<std::pair<std::string, long>> Tuning::items() const {
           {"sym_threads", sym_threads.load()},
           {"pair_sym_min_bytes", pair_sym_min_bytes.load()},
           {"ce_min_bytes", ce_min_bytes.load()},
+          {"ce_min_chunk_bytes", ce_min_chunk_bytes.load()},
           {"tma_min_bytes", tma_min_bytes.load()},
           {"tma_isolated", tma_isolated.load()},
           {"tma_ctas", tma_ctas.load()},
@@ -367,7 +370,9 @@ bool allreduce(PeerArena& arena, const void* in, void* out, int64_t n, DType dt,
   // Large symmetric buckets reduced under backward kernels: the copy engines carry the bytes
   // (fused_allreduce_ce.cu), the SMs only run two one-block sync kernels and a short reduction.
   const long ce_min = Tuning::global().ce_min_bytes.load();
-  if (overlapped && ce_min >= 0 && (size_t)n * dtype_bytes(dt) >= (size_t)ce_min &&
+  const long ce_chunk = std::max(0l, Tuning::global().ce_min_chunk_bytes.load());
+  const size_t bytes = (size_t)n * dtype_bytes(dt);
+  if (overlapped && ce_min >= 0 && bytes >= (size_t)ce_min && bytes / (size_t)arena.nranks() >= (size_t)ce_chunk &&
       allreduce_ce(arena, in, out, n, dt, scale, stream))
     return true;
   switch (dt) {

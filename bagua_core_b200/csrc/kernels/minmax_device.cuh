@@ -238,18 +238,37 @@ __device__ __forceinline__ void store_qword(uint8_t* q, int64_t vec, uint32_t w)
   reinterpret_cast<uint32_t*>(q)[vec] = w;
 }
 __device__ __forceinline__ void store_qword(uint8_t* q, int64_t vec, uint2 w) { reinterpret_cast<uint2*>(q)[vec] = w; }
-__device__ __forceinline__ void lut_dqvec(const uint8_t* q, int64_t vec, float (&f)[4], const float* lut) {
-  const uint32_t w = reinterpret_cast<const uint32_t*>(q)[vec];
+// the quantised word of one vector: loaded first (so that several can be in flight), looked up later
+template <int VE>
+struct QWord;
+template <>
+struct QWord<4> {
+  using type = uint32_t;
+};
+template <>
+struct QWord<8> {
+  using type = uint2;
+};
+template <int VE>
+__device__ __forceinline__ typename QWord<VE>::type load_qword(const uint8_t* q, int64_t vec) {
+  return reinterpret_cast<const typename QWord<VE>::type*>(q)[vec];
+}
+__device__ __forceinline__ void lut_word(uint32_t w, float (&f)[4], const float* lut) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) f[k] = lut[(w >> (8 * k)) & 0xffu];
 }
-__device__ __forceinline__ void lut_dqvec(const uint8_t* q, int64_t vec, float (&f)[8], const float* lut) {
-  const uint2 w = reinterpret_cast<const uint2*>(q)[vec];
+__device__ __forceinline__ void lut_word(uint2 w, float (&f)[8], const float* lut) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     f[k] = lut[(w.x >> (8 * k)) & 0xffu];
     f[4 + k] = lut[(w.y >> (8 * k)) & 0xffu];
   }
+}
+__device__ __forceinline__ void lut_dqvec(const uint8_t* q, int64_t vec, float (&f)[4], const float* lut) {
+  lut_word(load_qword<4>(q, vec), f, lut);
+}
+__device__ __forceinline__ void lut_dqvec(const uint8_t* q, int64_t vec, float (&f)[8], const float* lut) {
+  lut_word(load_qword<8>(q, vec), f, lut);
 }
 
 // A chunk's dequantiser only has 256 possible outputs: tabulate them once per block (with

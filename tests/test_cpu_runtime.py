@@ -412,7 +412,7 @@ def test_tuning_values_can_be_read_and_set_and_unknown_keys_are_refused():
     import bagua_core_b200 as bb
 
     before = dict(bb._C.get_tuning())
-    for key in ("oneshot_bytes", "oneshot_sym_bytes", "overlap_ctas", "ce_min_bytes", "tma_min_bytes",
+    for key in ("oneshot_bytes", "oneshot_sym_bytes", "overlap_ctas", "ce_min_bytes", "ce_min_chunk_bytes", "tma_min_bytes",
                 "tma_overlap_ctas", "coop_overlap_ctas", "pair_sym_min_bytes"):
         assert key in before
     bb._C.set_tuning("overlap_ctas", 24)
