@@ -39,14 +39,6 @@ __device__ __forceinline__ void lp_ring_body(const ArenaView& v, const psync::La
   const uint32_t nb_mask = (1u << left) | (1u << right);
   const int64_t groups = n / 16;
   const int64_t lo = groups * b / G * 16, hi = groups * (b + 1) / G * 16;
-  // The loops walk the slice as 16-byte vectors of T (VE elements), consecutive lanes on
-  // consecutive vectors, so that a warp's instruction covers one contiguous span; U vectors of
-  // every stream are loaded before the first is used.
-  constexpr int VE = mmdev::Vec16<T>::VE;
-  constexpr int U = 2;
-  using QW = typename mmdev::QWord<VE>::type;
-  const int64_t vhi = hi / VE, vfirst = lo / VE + threadIdx.x;
-  constexpr int64_t kStep = (int64_t)U * kThreads;
   uint8_t* stage = v.staging[me];
   uint8_t* from_left = stage;                   // written by my left neighbour
   uint8_t* from_right = stage + slot_bytes;     // written by my right neighbour
@@ -60,30 +52,22 @@ __device__ __forceinline__ void lp_ring_body(const ArenaView& v, const psync::La
   // ---- P1: d = x + l/3 + r/3 - 5w/3 (stored in x), partial min/max ----
   float mn = FLT_MAX, mx = -FLT_MAX;
   if (ok) {
-    for (int64_t i0 = vfirst; i0 < vhi; i0 += kStep) {
-      float fx[U][VE], fl[U][VE], fr[U][VE], fw[U][VE];
+    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+      float fx[16], fl[16], fr[16], fw[16];
+      mmdev::load16(x + i, fx);
+      mmdev::load16(l + i, fl);
+      mmdev::load16(r + i, fr);
+      mmdev::load16(w + i, fw);
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (i0 + u * kThreads < vhi) {
-          mmdev::load_vec(x, i0 + u * kThreads, fx[u]);
-          mmdev::load_vec(l, i0 + u * kThreads, fl[u]);
-          mmdev::load_vec(r, i0 + u * kThreads, fr[u]);
-          mmdev::load_vec(w, i0 + u * kThreads, fw[u]);
-        }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (i0 + u * kThreads >= vhi) continue;
-#pragma unroll
-        for (int k = 0; k < VE; ++k) {
-          float d = rt<T>(fmaf(fl[u][k], third, fx[u][k]));
-          d = rt<T>(fmaf(fr[u][k], third, d));
-          d = rt<T>(fmaf(fw[u][k], m53, d));
-          fx[u][k] = d;
-          mn = fminf(mn, d);
-          mx = fmaxf(mx, d);
-        }
-        mmdev::store_vec(x, i0 + u * kThreads, fx[u]);
+      for (int k = 0; k < 16; ++k) {
+        float d = rt<T>(fmaf(fl[k], third, fx[k]));
+        d = rt<T>(fmaf(fr[k], third, d));
+        d = rt<T>(fmaf(fw[k], m53, d));
+        fx[k] = d;
+        mn = fminf(mn, d);
+        mx = fmaxf(mx, d);
       }
+      mmdev::store16(x + i, fx);
     }
   }
   mmdev::block_minmax<kThreads>(mn, mx);
@@ -110,19 +94,13 @@ __device__ __forceinline__ void lp_ring_body(const ArenaView& v, const psync::La
       mmdev::store_header<T>(to_right, mn, mx);
       mmdev::store_header<T>(own, mn, mx);
     }
-    for (int64_t i0 = vfirst; i0 < vhi; i0 += kStep) {
-      float f[U][VE];
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (i0 + u * kThreads < vhi) mmdev::load_vec(x, i0 + u * kThreads, f[u]);
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (i0 + u * kThreads >= vhi) continue;
-        const QW packed = mmdev::pack_qvec(f[u], g_own);
-        mmdev::store_qword(to_left + kHdr, i0 + u * kThreads, packed);
-        mmdev::store_qword(to_right + kHdr, i0 + u * kThreads, packed);
-        mmdev::store_qword(own + kHdr, i0 + u * kThreads, packed);
-      }
+    for (int64_t i = lo + (int64_t)threadIdx.x * 16; i < hi; i += (int64_t)kThreads * 16) {
+      float f[16];
+      mmdev::load16(x + i, f);
+      const uint4 packed = mmdev::pack_q16(f, g_own);
+      *reinterpret_cast<uint4*>(to_left + kHdr + i) = packed;
+      *reinterpret_cast<uint4*>(to_right + kHdr + i) = packed;
+      *reinterpret_cast<uint4*>(own + kHdr + i) = packed;
     }
     psync::cta_signal_phase(v, L, 0, nb_mask);
     ok = psync::cta_wait_phase(v, L, 0, nb_mask);
@@ -139,6 +117,15 @@ __device__ __forceinline__ void lp_ring_body(const ArenaView& v, const psync::La
     mmdev::build_dequant_lut<T>(s_lut + 256, g_r);
     mmdev::build_dequant_lut<T>(s_lut + 512, g_own);
     __syncthreads();
+    // This loop walks the slice as 16-byte vectors of T (VE elements), consecutive lanes on
+    // consecutive vectors, with U vectors of every stream loaded before the first is used: its four
+    // store streams then leave as contiguous 512-byte spans per warp instruction.  (The two loops
+    // above read 16 consecutive elements per thread; the vector walk measured slower for them.)
+    constexpr int VE = mmdev::Vec16<T>::VE;
+    constexpr int U = 2;
+    using QW = typename mmdev::QWord<VE>::type;
+    const int64_t vhi = hi / VE, vfirst = lo / VE + threadIdx.x;
+    constexpr int64_t kStep = (int64_t)U * kThreads;
     for (int64_t i0 = vfirst; i0 < vhi; i0 += kStep) {
       QW ql[U] = {}, qr[U] = {}, qo[U] = {};
       float cl[U][VE], cr[U][VE], cw[U][VE];
