@@ -58,6 +58,7 @@ class BaguaProcessGroup:
     inter_comm: Optional[BaguaSingleCommunicatorPy] = None
     _keep: list = field(default_factory=list)
     _hier_done: bool = False
+    cpu_affinity: dict = field(default_factory=dict)  # what utils.affinity.bind_to_gpu_cpus did for this rank
 
     @property
     def stream_ptr(self) -> int:
@@ -133,8 +134,13 @@ def init_process_group(device: Optional[torch.device] = None, schedule_channel_c
         rank, world = get_rank(), get_world_size()
         if device is None:
             device = torch.device("cuda", get_local_rank()) if torch.cuda.is_available() else torch.device("cpu")
+        affinity = {"applied": False, "cpus": 0, "reason": "host backend"}
         if device.type == "cuda":
             torch.cuda.set_device(device)
+            # before any of this package's threads exist: they inherit the mask
+            from ..utils.affinity import bind_for_cuda_device
+
+            affinity = bind_for_cuda_device(device)
         if not dist.is_initialized():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", "29500")
@@ -157,6 +163,7 @@ def init_process_group(device: Optional[torch.device] = None, schedule_channel_c
         all_ranks = list(range(world))
         global_comm = _new_comm(all_ranks, rank, device, stream_ptr, keep)
         _state = BaguaProcessGroup(rank, world, device, backend, comm_stream, global_comm, None, None, keep)
+        _state.cpu_affinity = affinity
         return _state
 
 

@@ -246,6 +246,7 @@ def main():
     n_params = sum(p.numel() for p in model.parameters())
     lr = 0.01 if args.model != "bert_large" else 1e-4
     my_kernels = lambda: 0  # noqa: E731
+    cpu_affinity = {}
 
     if args.impl == "ddp":
         if not dist.is_initialized():
@@ -258,6 +259,7 @@ def main():
         zero = lambda: opt.zero_grad(set_to_none=False)  # noqa: E731
     else:
         pg = P.init_process_group(device)
+        cpu_affinity = dict(getattr(pg, "cpu_affinity", {}) or {})
         for kv in args.tune:
             k, v = kv.split("=")
             bb._C.set_tuning(k, int(v))
@@ -454,6 +456,7 @@ def main():
             "gpu_launches": launches,
             "timed_blocks": {"n": len(block_ms), "reported": "median", "ms_per_step": [m / args.steps for m in block_ms]},
             "host_issue_ms_per_step": host_issue_ms,
+            "cpu_affinity": cpu_affinity,
         }
         if timeline is not None:
             line["bucket_timeline"] = timeline

@@ -101,3 +101,88 @@ def test_lagged_reader_with_a_deeper_lag_returns_every_value_once_and_in_order()
     assert got == [None, None, None, 0.0, 1.0, 2.0]
     assert reader.flush() == 5.0  # 3.0 and 4.0 were read on the way
     assert reader.flush() is None
+
+
+class _FakeNvml:
+    """Stands for the NVML binding: one GPU whose local CPUs are `cpus`."""
+
+    def __init__(self, cpus, fail=False):
+        self.cpus, self.fail, self.calls = set(cpus), fail, []
+
+    def nvmlInit(self):
+        if self.fail:
+            raise RuntimeError("no driver")
+        self.calls.append("init")
+
+    def nvmlShutdown(self):
+        self.calls.append("shutdown")
+
+    def nvmlDeviceGetHandleByUUID(self, uuid):
+        self.calls.append(("uuid", uuid))
+        if isinstance(uuid, bytes):
+            raise TypeError("str expected")
+        return "h"
+
+    def nvmlDeviceGetHandleByIndex(self, i):
+        self.calls.append(("index", i))
+        return "h"
+
+    def nvmlDeviceGetCpuAffinity(self, handle, n_words):
+        words = [0] * n_words
+        for c in self.cpus:
+            if c // 64 < n_words:
+                words[c // 64] |= 1 << (c % 64)
+        return words
+
+
+def test_cpu_affinity_follows_the_gpus_local_cpus_and_only_narrows(monkeypatch):
+    import os
+    import threading
+
+    from bagua_core_b200.utils import affinity
+
+    assert affinity._mask_words_to_cpus([0b101, 1]) == {0, 2, 64}
+    before = set(os.sched_getaffinity(0))
+    if len(before) < 4:
+        pytest.skip("needs four CPUs")
+    half = set(sorted(before)[: len(before) // 2])
+    stop = threading.Event()
+    seen = {}
+
+    def other_thread():
+        stop.wait()
+        seen["mask"] = set(os.sched_getaffinity(0))
+
+    th = threading.Thread(target=other_thread)
+    th.start()
+    try:
+        monkeypatch.delenv("BAGUA_B200_CPU_AFFINITY", raising=False)
+        # too few of the GPU's CPUs are ours: nothing changes
+        r = affinity.bind_to_gpu_cpus(0, min_cpus=2, nvml=_FakeNvml({max(before) + 1000, min(before)}))
+        assert r["applied"] is False and set(os.sched_getaffinity(0)) == before
+        # NVML not there: nothing changes
+        r = affinity.bind_to_gpu_cpus(0, nvml=_FakeNvml(half, fail=True))
+        assert r["applied"] is False and set(os.sched_getaffinity(0)) == before
+        # switched off
+        monkeypatch.setenv("BAGUA_B200_CPU_AFFINITY", "0")
+        assert affinity.bind_to_gpu_cpus(0, min_cpus=2, nvml=_FakeNvml(half))["reason"] == "switched off"
+        monkeypatch.delenv("BAGUA_B200_CPU_AFFINITY")
+        # the GPU's CPUs, cut to what the process may use; found by UUID; every thread moves
+        fake = _FakeNvml(half | {max(before) + 1000})
+        r = affinity.bind_to_gpu_cpus(0, min_cpus=2, nvml=fake, uuid="1234")
+        assert r == {"applied": True, "cpus": len(half), "reason": ""}
+        assert ("uuid", "GPU-1234") in fake.calls and fake.calls[-1] == "shutdown"
+        assert set(os.sched_getaffinity(0)) == half
+        stop.set()
+        th.join()
+        assert seen["mask"] == half
+        # a second call finds nothing to do
+        assert affinity.bind_to_gpu_cpus(0, min_cpus=2, nvml=_FakeNvml(half))["reason"] == "already there"
+    finally:
+        stop.set()
+        th.join()
+        for tid in affinity._all_thread_ids():
+            try:
+                os.sched_setaffinity(tid, before)
+            except OSError:
+                pass
