@@ -17,9 +17,10 @@ _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,
 class ClockSampler:
     """Context manager around `nvidia-smi -lms`.  Call `mark()` right before the timed region
     starts (it first waits for the sampler's first line, so short regions still get samples);
-    `summary()` then reports only samples taken after the mark."""
+    `summary()` then reports only samples taken after the mark.  Keep the period long and run one
+    sampler per job, not one per rank: every query takes driver locks that kernel launches wait for."""
 
-    def __init__(self, gpu_index: int = 0, period_ms: int = 50):
+    def __init__(self, gpu_index: int = 0, period_ms: int = 200):
         self.gpu_index = gpu_index
         self.period_ms = period_ms
         self._proc = None

@@ -312,7 +312,10 @@ def main():
         step(x, y)
     barrier()
     block_ms, block_launches = [], []
-    with (ClockSampler(local_rank) if on_gpu else _NoClocks()) as clocks:
+    # One sampler for the job (rank 0's GPU, every 100 ms): every NVML query takes driver locks that
+    # kernel launches of all ranks wait for, and one `nvidia-smi -lms 50` per rank (160 query rounds
+    # a second with eight ranks) showed up in the step time.
+    with (ClockSampler(local_rank, period_ms=100) if on_gpu and rank == 0 else _NoClocks()) as clocks:
         clocks.mark()
         for _ in range(max(1, args.repeats)):
             k0 = my_kernels()
