@@ -310,6 +310,13 @@ def main():
     x, y = make_batch(args.model, batch, seq, device)
     for _ in range(max(args.warmup, 3)):
         step(x, y)
+    # The model, the optimizer and the engine's objects are long-lived: take them out of the garbage
+    # collector's generations, so that a full collection on one rank does not land in a timed block
+    # (every rank waits for the slowest one at each bucket).  Collection itself stays on.
+    import gc
+
+    gc.collect()
+    gc.freeze()
     barrier()
     block_ms, block_launches = [], []
     # One sampler for the job (rank 0's GPU, every 100 ms): every NVML query takes driver locks that
