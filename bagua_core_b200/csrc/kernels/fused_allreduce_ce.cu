@@ -18,6 +18,8 @@
 // ever wait, and they are one block each.  In place is safe without a further round: chunk r
 // of a peer's buffer is read only by rank r's own pulls, which precede its pushes on its
 // stream.  Results are bit-identical to the load/store kernels (same order, same rounding).
+// tests/cpp/device_emulation.cc replays this sequence with the same signalling calls under the
+// thread sanitizer (in place and out of place).
 //
 // The reference has no counterpart (one NCCL call per bucket,
 // bagua-core-internal/src/comm_ops/centralized_full_precision_synchronous.rs:16-55).

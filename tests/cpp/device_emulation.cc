@@ -62,6 +62,8 @@ enum class Kind {
   AllReduceTwoShotInPlace,
   AllReduceSym,
   AllReduceSymTma,
+  AllReduceCe,
+  AllReduceCeInPlace,
   PairAverage,
   PairAverageSym,
   ByteGrad,
@@ -86,6 +88,7 @@ struct alignas(16) Vec {
 
 struct Rank {
   std::vector<Vec> staging, in, out, w, l, r;  // w / l / r: the replicas of the low-precision ring
+  std::vector<Vec> ce_stage;                   // rank-local staging of the copy-engine all-reduce (never shared)
   std::vector<uint32_t> signals;
   std::unique_ptr<std::barrier<>> bar;  // the rank's stream: all of its threads between ops
   uint64_t errors = 0;
@@ -224,8 +227,10 @@ void prepare(World& w, int me, uint32_t k) {
     case Kind::AllReduceTwoShot:
     case Kind::AllReduceSym:
     case Kind::AllReduceSymTma:
+    case Kind::AllReduceCe:
     case Kind::PairAverage:
     case Kind::PairAverageSym: fill(r.in, k, me, op.vecs); break;
+    case Kind::AllReduceCeInPlace:
     case Kind::AllReduceTwoShotInPlace:
     case Kind::AllReduceNvls: fill(r.out, k, me, op.vecs); break;
     case Kind::ByteGrad: fill(r.in, k, me, op.vecs * N); break;
@@ -312,6 +317,50 @@ void run_body(World& w, int me, int b, uint32_t k) {
         allreduce_sym_tma_body<float, 8>(v, L, p, c, op.scale, hostemu::shared_array<unsigned char>(kSlot, TmaCfg<8>::kSmemBytes));
       else
         allreduce_sym_body<float>(v, L, p, c, op.scale);
+      break;
+    }
+    case Kind::AllReduceCe:
+    case Kind::AllReduceCeInPlace: {
+      // The copy-engine all-reduce (kernels/fused_allreduce_ce.cu) is a stream of separate launches:
+      // one-block sync kernel, N-1 pulls, reduction, N-1 pushes, one-block sync kernel.  Here block 0
+      // of the rank plays that stream (a block barrier stands for each launch boundary, thread 0 for
+      // the copy engine), the other blocks have nothing to do.  What this checks is the ordering
+      // argument: phase 0 before any pull, every push before phase 1, and, in place, that nobody reads
+      // a chunk another rank is pushing into.
+      if (b != 0) break;
+      const Launch one{0, 1};
+      const bool in_place = op.kind == Kind::AllReduceCeInPlace;
+      const int N = w.N;
+      auto lo_of = [&](int q) { return c * q / N; };
+      const int64_t my_lo = lo_of(me), my_vecs = lo_of(me + 1) - my_lo, slot = (c + N - 1) / N;
+      uint4* stage = reinterpret_cast<uint4*>(r.ce_stage.data());
+      psync::cta_signal_phase(v, one, 0, all_peers_mask(v));
+      psync::cta_wait_phase(v, one, 0, all_peers_mask(v));
+      __syncthreads();
+      uint4* own = out + my_lo;
+      if (threadIdx.x == 0) {
+        for (int i = 1; i < N; ++i) {
+          const int q = (me + i) % N;
+          const uint4* src = in_place ? outs.p[q] : ins.p[q];
+          std::memcpy(stage + (int64_t)q * slot, src + my_lo, (size_t)my_vecs * sizeof(uint4));
+        }
+        if (!in_place) std::memcpy(own, in + my_lo, (size_t)my_vecs * sizeof(uint4));
+      }
+      __syncthreads();
+      for (int64_t i = threadIdx.x; i < my_vecs; i += kThreads) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int q = 0; q < N; ++q) VecOps<float>::acc(a, q == me ? own[i] : stage[(int64_t)q * slot + i]);
+        own[i] = VecOps<float>::pack(a, op.scale);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0)
+        for (int i = 1; i < N; ++i) {
+          const int q = (me + i) % N;
+          std::memcpy(outs.p[q] + my_lo, own, (size_t)my_vecs * sizeof(uint4));
+        }
+      psync::cta_signal_phase(v, one, 1, all_peers_mask(v));
+      psync::cta_wait_phase(v, one, 1, all_peers_mask(v));
+      psync::cta_finish_op(v, one);
       break;
     }
     case Kind::PairAverage: pair_average_body<float>(v, L, in, out, c, me ^ 1); break;
@@ -446,6 +495,8 @@ uint64_t verify(World& w, int me, uint32_t k) {
     case Kind::AllReduceTwoShotInPlace:
     case Kind::AllReduceSym:
     case Kind::AllReduceSymTma:
+    case Kind::AllReduceCe:
+    case Kind::AllReduceCeInPlace:
     case Kind::AllReduceNvls:
       for (int64_t i = 0; i < c; ++i) {
         sum4(i, op.scale, e);
@@ -543,8 +594,10 @@ uint64_t verify(World& w, int me, uint32_t k) {
     case Kind::AllReduceTwoShot:
     case Kind::AllReduceSym:
     case Kind::AllReduceSymTma:
+    case Kind::AllReduceCe:
     case Kind::PairAverage:
     case Kind::PairAverageSym: out_extent = c, in_extent = c; break;
+    case Kind::AllReduceCeInPlace:
     case Kind::AllReduceTwoShotInPlace:
     case Kind::AllReduceNvls: out_extent = c; break;
     case Kind::AllToAllV: out_extent = (int64_t)r.out.size(), in_extent = (int64_t)kA2avMaxUnits * N; break;  // bytes checked above
@@ -595,7 +648,7 @@ int main(int argc, char** argv) {
     if ((op.kind == Kind::PairAverage || op.kind == Kind::PairAverageSym) && w.N % 2) op.kind = Kind::Barrier;  // pairs need an even world
     op.vecs = 1 + (int64_t)(rng() % 40);
     if (op.kind == Kind::ByteGrad || op.kind == Kind::LpRing) op.vecs = 4 * (1 + (int64_t)(rng() % 10));  // 16-element groups
-    if (op.kind == Kind::AllReduceSymTma) op.vecs = 1 + (int64_t)(rng() % 400);  // many tiles: the stage ring wraps
+    if (op.kind == Kind::AllReduceSymTma || op.kind == Kind::AllReduceCe || op.kind == Kind::AllReduceCeInPlace) op.vecs = 1 + (int64_t)(rng() % 400);  // many tiles: the stage ring wraps
     if (g_a2av_mismatch) op.kind = Kind::AllToAllV;
     if (op.kind == Kind::AllToAllV) op.vecs = kA2avMaxUnits;  // sizes the buffers; the op's own sizes come from a2av_bytes
     op.root = (int)(rng() % (uint32_t)w.N);
@@ -617,6 +670,7 @@ int main(int argc, char** argv) {
     r.w.assign(buf_vecs, Vec{});
     r.l.assign(buf_vecs, Vec{});
     r.r.assign(buf_vecs, Vec{});
+    r.ce_stage.assign(buf_vecs + (size_t)w.N, Vec{});
     r.signals.assign((size_t)kSigWords, 0u);
     r.bar = std::make_unique<std::barrier<>>(w.G * kThreads);
   }
