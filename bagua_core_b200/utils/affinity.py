@@ -6,7 +6,8 @@ attached to (and to move it between steps): every launch then crosses the socket
 and the slowest rank's launching thread paces every collective.  `bind_to_gpu_cpus` asks NVML
 for the CPUs that are local to the GPU and restricts all threads of the process to the ones the
 process was already allowed to use.  It only ever narrows the existing mask, does nothing when
-fewer than `min_cpus` CPUs would be left, and changes nothing on the GPU (NVML is only read).
+fewer than `min_cpus` CPUs (or fewer than four per GPU that reports the same set) would be left,
+and changes nothing on the GPU (NVML is only read).
 
 The reference leaves placement to the launcher (it has no counterpart); NCCL does the same for
 its own threads.  Switch off with BAGUA_B200_CPU_AFFINITY=0.
@@ -52,25 +53,35 @@ def _nvml_handle(nvml, device_index: int, uuid: Optional[str], pci_bus_id: Optio
 
 
 def gpu_local_cpus(device_index: int, nvml=None, uuid: Optional[str] = None,
-                   pci_bus_id: Optional[str] = None) -> Optional[Set[int]]:
-    """CPUs that NVML reports as local to the GPU, or None when that cannot be found out."""
+                   pci_bus_id: Optional[str] = None):
+    """(CPUs that NVML reports as local to the GPU, number of GPUs of the machine that report the
+    same set), or (None, 0) when that cannot be found out."""
     own = nvml is None
     try:
         if own:
             import pynvml as nvml  # type: ignore
         nvml.nvmlInit()
     except Exception:
-        return None
+        return None, 0
     try:
         handle = _nvml_handle(nvml, device_index, uuid, pci_bus_id)
         if handle is None:
-            return None
-        n_cpus = os.cpu_count() or 64
-        words = nvml.nvmlDeviceGetCpuAffinity(handle, (n_cpus + 63) // 64)
-        cpus = _mask_words_to_cpus(words)
-        return cpus or None
+            return None, 0
+        n_words = ((os.cpu_count() or 64) + 63) // 64
+        cpus = _mask_words_to_cpus(nvml.nvmlDeviceGetCpuAffinity(handle, n_words))
+        if not cpus:
+            return None, 0
+        sharing = 0
+        try:
+            for i in range(int(nvml.nvmlDeviceGetCount())):
+                other = nvml.nvmlDeviceGetHandleByIndex(i)
+                if _mask_words_to_cpus(nvml.nvmlDeviceGetCpuAffinity(other, n_words)) == cpus:
+                    sharing += 1
+        except Exception:
+            sharing = 0
+        return cpus, max(sharing, 1)
     except Exception:
-        return None
+        return None, 0
     finally:
         try:
             nvml.nvmlShutdown()
@@ -86,7 +97,7 @@ def _all_thread_ids() -> list:
 
 
 def bind_to_gpu_cpus(device_index: int, min_cpus: int = 8, nvml=None, uuid: Optional[str] = None,
-                     pci_bus_id: Optional[str] = None) -> dict:
+                     pci_bus_id: Optional[str] = None, per_rank_cpus: int = 4) -> dict:
     """Restrict every thread of this process to the CPUs local to GPU `device_index`.
 
     Returns what was done: {"applied": bool, "cpus": count in force afterwards, "reason": why not}.
@@ -96,13 +107,17 @@ def bind_to_gpu_cpus(device_index: int, min_cpus: int = 8, nvml=None, uuid: Opti
     if not hasattr(os, "sched_setaffinity"):
         return {"applied": False, "cpus": 0, "reason": "no sched_setaffinity on this platform"}
     allowed = set(os.sched_getaffinity(0))
-    local = gpu_local_cpus(device_index, nvml=nvml, uuid=uuid, pci_bus_id=pci_bus_id)
+    local, sharing = gpu_local_cpus(device_index, nvml=nvml, uuid=uuid, pci_bus_id=pci_bus_id)
     if not local:
         return {"applied": False, "cpus": len(allowed), "reason": "NVML reports no CPU set for the GPU"}
     target = allowed & local
-    if len(target) < min_cpus:
+    # every GPU that reports the same set may have a rank of its own on it: leave each at least
+    # `per_rank_cpus`, or a mask that looked local would crowd the ranks onto a few cores
+    need = max(min_cpus, per_rank_cpus * sharing)
+    if len(target) < need:
         return {"applied": False, "cpus": len(allowed),
-                "reason": f"only {len(target)} of the GPU's CPUs are available to this process"}
+                "reason": f"only {len(target)} of the GPU's CPUs are available to this process "
+                          f"({sharing} GPU(s) share them, {need} wanted)"}
     if target == allowed:
         return {"applied": False, "cpus": len(allowed), "reason": "already there"}
     done = 0

@@ -106,8 +106,11 @@ def test_lagged_reader_with_a_deeper_lag_returns_every_value_once_and_in_order()
 class _FakeNvml:
     """Stands for the NVML binding: one GPU whose local CPUs are `cpus`."""
 
-    def __init__(self, cpus, fail=False):
-        self.cpus, self.fail, self.calls = set(cpus), fail, []
+    def __init__(self, cpus, fail=False, gpus=1):
+        self.cpus, self.fail, self.calls, self.gpus = set(cpus), fail, [], gpus
+
+    def nvmlDeviceGetCount(self):
+        return self.gpus
 
     def nvmlInit(self):
         if self.fail:
@@ -176,6 +179,15 @@ def test_cpu_affinity_follows_the_gpus_local_cpus_and_only_narrows(monkeypatch):
         stop.set()
         th.join()
         assert seen["mask"] == half
+        # eight GPUs report the same few CPUs: binding eight ranks there would crowd them, so it is refused
+        for tid in affinity._all_thread_ids():
+            try:
+                os.sched_setaffinity(tid, before)
+            except OSError:
+                pass  # a thread of an earlier test that has just exited
+        r = affinity.bind_to_gpu_cpus(0, min_cpus=2, nvml=_FakeNvml(half, gpus=8), per_rank_cpus=len(half))
+        assert r["applied"] is False and "8 GPU(s) share" in r["reason"] and set(os.sched_getaffinity(0)) == before
+        assert affinity.bind_to_gpu_cpus(0, min_cpus=2, nvml=_FakeNvml(half))["applied"] is True
         # a second call finds nothing to do
         assert affinity.bind_to_gpu_cpus(0, min_cpus=2, nvml=_FakeNvml(half))["reason"] == "already there"
     finally:
